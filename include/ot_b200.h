@@ -1,0 +1,157 @@
+/* ot_b200.h - C ABI of libot_b200.so, the sm_100a transducer-loss library.
+ *
+ * The library replaces the native half of the reference's loss path: the
+ * function bound at optimized_transducer/python/csrc/optimized_transducer.cc:12-19,
+ * i.e. ot::ComputeTransducerLoss (optimized_transducer/csrc/transducer-loss.h:60-63)
+ * and, below it, ot::ComputeTransducerLossCuda (optimized_transducer/csrc/cuda.cu:402-457)
+ * with its kernels (optimized_transducer/csrc/kernels.cu).
+ *
+ * Conventions
+ *  - Plain pointers and sizes only; every pointer named `d_*` is DEVICE memory
+ *    of the current CUDA device, `stream` is a cudaStream_t passed as void*.
+ *  - The library allocates no device memory.  The caller provides outputs and
+ *    one workspace whose size ot_b200_workspace_bytes() reports.
+ *  - Every function returns an ot_b200_status; nothing throws, traps or
+ *    asserts.  ot_b200_last_error() gives the message of the calling thread's
+ *    last failure.
+ *  - All work is enqueued on `stream`; functions return without synchronising
+ *    unless stated.  Re-entrant: no state is shared between calls except the
+ *    caller's workspace.
+ *  - Packed layout (README.md:131-204 of the reference): utterance b owns
+ *    T_b*(U_b+1) consecutive rows of `logits`, row(b,t,u) = split_b + t*(U_b+1) + u,
+ *    each row holding V values.  64-bit element offsets are used throughout
+ *    (the reference's kernels use 32-bit offsets, kernels.cu:49).
+ */
+#ifndef OT_B200_H_
+#define OT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OT_B200_ABI_VERSION 1
+
+typedef enum ot_b200_status {
+  OT_B200_OK = 0,
+  OT_B200_ERR_ARGUMENT = 1,   /* a host-visible argument is invalid            */
+  OT_B200_ERR_CUDA = 2,       /* a CUDA runtime call or a launch failed        */
+  OT_B200_ERR_WORKSPACE = 3,  /* workspace missing, misaligned or too small    */
+  OT_B200_ERR_INPUT = 4       /* the device-side input check found bad lengths
+                                 or targets (see ot_b200_input_error)          */
+} ot_b200_status;
+
+/* What the device-side input check (the counterpart of the data-dependent
+ * TORCH_CHECKs at transducer-loss.cc:49-66) can report. */
+typedef enum ot_b200_input_error {
+  OT_B200_INPUT_OK = 0,
+  OT_B200_INPUT_BAD_LOGIT_LENGTH = 1,   /* some T_b <= 0                               */
+  OT_B200_INPUT_BAD_TARGET_LENGTH = 2,  /* some U_b < 0 or U_b > max_u                 */
+  OT_B200_INPUT_ROWS_MISMATCH = 3,      /* sum T_b*(U_b+1) != rows  (:49-51)           */
+  OT_B200_INPUT_TARGET_RANGE = 4,       /* targets.max() >= V or a used target < 0 (:53-56) */
+  OT_B200_INPUT_MAX_U_MISMATCH = 5,     /* targets.size(1) != max_b U_b  (:62-66)      */
+  OT_B200_INPUT_ONE_SYM_INFEASIBLE = 6  /* one_sym_per_frame with U_b > T_b - 1: no
+                                           alignment exists; the reference returns
+                                           uninitialised memory here                  */
+} ot_b200_input_error;
+
+/* Bits of `flags`. */
+#define OT_B200_FROM_LOG_SOFTMAX 1u   /* input rows are log-softmax outputs         */
+#define OT_B200_ONE_SYM_PER_FRAME 2u  /* modified transducer                        */
+#define OT_B200_FP64 4u               /* logits/scores/grad are double, not float   */
+#define OT_B200_CHECK_INPUTS 8u       /* read the input-check status back (one wait
+                                         on an event recorded before the streaming
+                                         kernels; not allowed during stream capture) */
+#define OT_B200_FAST_MATH 16u         /* approximate exp/log in the recursions      */
+
+/* Byte offsets of the intermediate arrays inside the workspace, for callers
+ * (and tests) that want the stage outputs.  Element type is float, or double
+ * with OT_B200_FP64.  `den` is unused with OT_B200_FROM_LOG_SOFTMAX. */
+typedef struct ot_b200_workspace_layout {
+  uint64_t total_bytes;
+  uint64_t status_off;      /* int32[16]: [0] ot_b200_input_error, [1] utterance index */
+  uint64_t split_off;       /* int64[N+1]: first row of each utterance               */
+  uint64_t den_off;         /* real[rows]: row-wise logsumexp          (cuda.cu:427)  */
+  uint64_t lp_off;          /* real[rows][2]: blank / symbol log-prob  (kernels.cu:30-88) */
+  uint64_t alpha_off;       /* real[rows]                              (kernels.cu:200-313) */
+  uint64_t beta_off;        /* real[rows]                              (kernels.cu:415-519) */
+  uint64_t coef_off;        /* per-row gradient coefficients (library-private format) */
+  uint64_t scores_beta_off; /* real[N]: beta(0,0), the score seen from the beta side  */
+} ot_b200_workspace_layout;
+
+int ot_b200_abi_version(void);
+
+/* Message for the calling thread's most recent non-OK return ("" if none). */
+const char *ot_b200_last_error(void);
+
+/* Size and layout of the workspace for a batch of N utterances and `rows`
+ * packed rows.  Replaces the temporaries the reference allocates per call
+ * (row_splits/row_ids cuda.cu:411-415, denominator :427, log_probs :85,
+ * alpha/beta :173,249).  The workspace must be 256-byte aligned. */
+int ot_b200_workspace_layout_query(int32_t N, int64_t rows, uint32_t flags,
+                                   ot_b200_workspace_layout *out);
+int ot_b200_workspace_bytes(int32_t N, int64_t rows, uint32_t flags,
+                            uint64_t *bytes_out);
+
+/* Forward half: input check, row-wise logsumexp + blank/target gather, alpha
+ * and beta recursions, per-row gradient coefficients.
+ *   replaces: the checks of ot::ComputeTransducerLoss (transducer-loss.cc:49-66),
+ *   RowSplitsToRowIds (cuda.cu:40-59), ComputeLogProbs[ForLogSoftmax]
+ *   (cuda.cu:71-136), ComputeAlpha (cuda.cu:162-213), ComputeBeta (cuda.cu:237-287).
+ * d_logits        (rows, V) real, read only
+ * d_targets       (N, max_u) int32     d_logit_lengths, d_target_lengths  (N) int32
+ * d_scores        (N) real out: log P(y_b|x_b) = alpha(T-1,U) + lp_blank(T-1,U)
+ * With OT_B200_CHECK_INPUTS a failed input check returns OT_B200_ERR_INPUT
+ * (the streaming kernels then do not touch the inputs); without it the status
+ * stays in the workspace and ot_b200_read_input_status() can fetch it. */
+int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
+                    const int32_t *d_logit_lengths,
+                    const int32_t *d_target_lengths, int32_t N, int64_t rows,
+                    int32_t V, int32_t max_u, int32_t blank, uint32_t flags,
+                    void *d_workspace, uint64_t workspace_bytes, void *d_scores,
+                    void *stream);
+
+/* Backward half: one streaming pass that writes
+ *     grad = scale * d loss / d logits
+ * from the coefficients ot_b200_forward left in the workspace.
+ *   replaces: ComputeGradient[OneSymPerFrame] (cuda.cu:308-346) and
+ *   ComputeGradientForLogSoftmax[OneSymPerFrame] (cuda.cu:364-400), plus the two
+ *   elementwise passes of the Python layer (`grad /= N`, transducer_loss.py:150,
+ *   and `ctx.grad.mul_(loss_grad)`, :162), which are folded into `scale`.
+ * d_logits   the same rows ot_b200_forward saw
+ * d_grad     (rows, V) real out; MAY EQUAL d_logits (the reference's in-place
+ *            mode, cuda.cu:449).  With OT_B200_FROM_LOG_SOFTMAX d_logits is not
+ *            read and d_grad must be a separate buffer (cuda.cu:444).
+ * scale = scale_host * (d_scale ? *d_scale : 1); d_scale is a device scalar of
+ *            the real type (e.g. the upstream gradient of the loss). */
+int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows,
+                     int32_t V, int32_t blank, uint32_t flags,
+                     const void *d_workspace, uint64_t workspace_bytes,
+                     const void *d_scale, double scale_host, void *stream);
+
+/* One call with the reference's semantics, forward + (if d_grad != NULL)
+ * backward with scale 1:  the counterpart of
+ * _optimized_transducer.compute_transducer_loss
+ * (python/csrc/optimized_transducer.cc:15-19), which returns (scores, grad). */
+int ot_b200_compute_transducer_loss(const void *d_logits, void *d_grad,
+                                    const int32_t *d_targets,
+                                    const int32_t *d_logit_lengths,
+                                    const int32_t *d_target_lengths, int32_t N,
+                                    int64_t rows, int32_t V, int32_t max_u,
+                                    int32_t blank, uint32_t flags,
+                                    void *d_workspace, uint64_t workspace_bytes,
+                                    void *d_scores, void *stream);
+
+/* Copies the input-check status out of the workspace (synchronises `stream`).
+ * code_out receives an ot_b200_input_error, index_out the offending utterance. */
+int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes,
+                              int32_t N, int64_t rows, uint32_t flags,
+                              int32_t *code_out, int32_t *index_out,
+                              void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* OT_B200_H_ */

@@ -1,0 +1,14 @@
+"""B200-native (sm_100a) transducer loss, a drop-in for the loss path of
+csukuangfj/optimized_transducer:
+
+    import optimized_transducer_b200 as optimized_transducer
+    loss = optimized_transducer.transducer_loss(logits, targets, logit_lengths,
+                                                target_lengths, blank=0,
+                                                from_log_softmax=False)
+"""
+from .transducer_loss import (TransducerLoss, TransducerLossFunction,  # noqa: F401
+                              compute_transducer_loss, stage_outputs, transducer_loss)
+
+__version__ = "0.1.0"
+__all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
+           "compute_transducer_loss", "stage_outputs", "__version__"]

@@ -1,0 +1,206 @@
+// Stage 3: the gradient w.r.t. the packed logits, one streaming pass.
+//
+// Mode A (raw logits; may write in place over the logits) replaces
+// ComputeGradient / ComputeGradientOneSymPerFrame
+// (optimized_transducer/csrc/kernels.cu:522-651): per row, with the
+// coefficients (c, beta, sub_blank, sub_sym, tgt) of stage 2c,
+//     grad[v] = scale * ( exp((x[v]+c)+beta) - [v==blank] exp((x[v]+c)+sub_blank)
+//                                            - [v==tgt]   exp((x[v]+c)+sub_sym) )
+// The additions are made in the reference's order (cpu.cc:509-522) so that the
+// rounding of x[v]+c, which dominates the error for long utterances, is the
+// same as the reference's.
+//
+// Mode B (log-softmax input) replaces ComputeGradientForLogSoftmax /
+// ...OneSymPerFrame (kernels.cu:653-779): rows are zero except for the blank
+// and symbol entries, so the kernel only writes.
+//
+// `scale` folds the two elementwise passes of the reference's Python layer
+// (division by N for reduction="mean", multiplication by the upstream
+// gradient; transducer_loss.py:150,162) into this pass.
+//
+// One warp owns a row at a time; rows are visited from the END of the buffer
+// towards its start: the rows stage 1 read last are the ones still resident in
+// L2.  HBM traffic per row: V*sizeof(T) read + V*sizeof(T) written (mode A),
+// V*sizeof(T) written (mode B), plus one 32-byte (16-byte) coefficient record.
+#include "ot_common.cuh"
+
+namespace otb {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename T, int VEC> struct VecOf;
+template <> struct VecOf<float, 4> { using type = float4; };
+template <> struct VecOf<float, 1> { using type = float; };
+template <> struct VecOf<double, 2> { using type = double2; };
+template <> struct VecOf<double, 1> { using type = double; };
+
+template <typename T>
+__device__ __forceinline__ CoefA<T> load_coef(const CoefA<T> *p) {
+  // Every lane reads the same record: the loads are broadcasts.
+  CoefA<T> r;
+  if constexpr (sizeof(T) == 4) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(p));
+    r.c = a.x; r.beta = a.y; r.sub_blank = a.z; r.sub_sym = a.w;
+    r.tgt = __ldg(reinterpret_cast<const int32_t *>(p) + 4);
+  } else {
+    const double2 a = __ldg(reinterpret_cast<const double2 *>(p));
+    const double2 b = __ldg(reinterpret_cast<const double2 *>(p) + 1);
+    r.c = a.x; r.beta = a.y; r.sub_blank = b.x; r.sub_sym = b.y;
+    r.tgt = __ldg(reinterpret_cast<const int32_t *>(p) + 8);
+  }
+  return r;
+}
+
+template <typename T, int VEC, int CH>
+__global__ void __launch_bounds__(kThreads)
+gradient_kernel(const T *x, T *g, const CoefA<T> *__restrict__ coef,
+                const int32_t *__restrict__ status, int64_t rows, int V,
+                int blank, const T *__restrict__ d_scale, T scale_host) {
+  if (status[kStatusCode] != 0) return;
+  using VT = typename VecOf<T, VEC>::type;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
+  const int nvec = V / VEC;
+  const T scale = d_scale ? scale_host * __ldg(d_scale) : scale_host;
+  const int bvec = blank / VEC, bk = blank % VEC;
+
+  for (int64_t row = rows - 1 - warp0; row >= 0; row -= nwarps) {
+    const CoefA<T> rec = load_coef(coef + row);
+    const T *px = x + row * (int64_t)V;
+    T *pg = g + row * (int64_t)V;
+    if (rec.tgt == kTgtZeroRow) {
+      VT z;
+      T *ze = reinterpret_cast<T *>(&z);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) ze[k] = 0;
+      for (int vi = lane; vi < nvec; vi += kWarp)
+        *reinterpret_cast<VT *>(pg + (int64_t)vi * VEC) = z;
+      continue;
+    }
+    const int tvec = rec.tgt >= 0 ? rec.tgt / VEC : -1;
+    const int tk = rec.tgt >= 0 ? rec.tgt % VEC : 0;
+    for (int base = 0; base < nvec; base += kWarp * CH) {
+      VT v[CH];
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int vi = base + j * kWarp + lane;
+        if (vi < nvec) v[j] = *reinterpret_cast<const VT *>(px + (int64_t)vi * VEC);
+      }
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int vi = base + j * kWarp + lane;
+        if (vi < nvec) {
+          T *e = reinterpret_cast<T *>(&v[j]);
+          const int bsel = (vi == bvec) ? bk : -1;
+          const int tsel = (vi == tvec) ? tk : -1;
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) {
+            const T gv = e[k] + rec.c;
+            T val = r_exp(gv + rec.beta);
+            if (k == bsel) val -= r_exp(gv + rec.sub_blank);
+            else if (k == tsel) val -= r_exp(gv + rec.sub_sym);
+            e[k] = val * scale;
+          }
+          *reinterpret_cast<VT *>(pg + (int64_t)vi * VEC) = v[j];
+        }
+      }
+    }
+  }
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kThreads)
+gradient_logsoftmax_kernel(T *__restrict__ g, const CoefB<T> *__restrict__ coef,
+                           const int32_t *__restrict__ status, int64_t rows,
+                           int V, int blank, const T *__restrict__ d_scale,
+                           T scale_host) {
+  if (status[kStatusCode] != 0) return;
+  using VT = typename VecOf<T, VEC>::type;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
+  const int nvec = V / VEC;
+  const T scale = d_scale ? scale_host * __ldg(d_scale) : scale_host;
+  const int bvec = blank / VEC, bk = blank % VEC;
+  for (int64_t row = warp0; row < rows; row += nwarps) {
+    const CoefB<T> rec = coef[row];
+    T *pg = g + row * (int64_t)V;
+    const bool zero = rec.tgt == kTgtZeroRow;
+    const int tvec = (!zero && rec.tgt >= 0) ? rec.tgt / VEC : -1;
+    const int tk = rec.tgt >= 0 ? rec.tgt % VEC : 0;
+    for (int vi = lane; vi < nvec; vi += kWarp) {
+      VT z;
+      T *ze = reinterpret_cast<T *>(&z);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        T val = 0;
+        if (!zero && vi == bvec && k == bk) val = rec.val_blank * scale;
+        else if (vi == tvec && k == tk) val = rec.val_sym * scale;
+        ze[k] = val;
+      }
+      *reinterpret_cast<VT *>(pg + (int64_t)vi * VEC) = z;
+    }
+  }
+}
+
+unsigned stream_grid(int64_t rows) {
+  const int64_t want = (rows + (kThreads / kWarp) - 1) / (kThreads / kWarp);
+  const int64_t cap = (int64_t)sm_count() * 8;
+  return (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+template <typename T, int VEC, int CH>
+cudaError_t launch_grad_a(const Problem &p, void *grad, const void *d_scale,
+                          double scale_host, cudaStream_t s) {
+  gradient_kernel<T, VEC, CH><<<stream_grid(p.rows), kThreads, 0, s>>>(
+      static_cast<const T *>(p.logits), static_cast<T *>(grad),
+      reinterpret_cast<const CoefA<T> *>(p.ws + p.lay.coef),
+      reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V,
+      p.blank, static_cast<const T *>(d_scale), (T)scale_host);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_gradient_t(const Problem &p, void *grad, const void *d_scale,
+                              double scale_host, cudaStream_t s) {
+  constexpr int VEC = Vec16<T>::n;
+  const bool aligned = (p.V % VEC == 0) &&
+                       (reinterpret_cast<uintptr_t>(grad) % 16 == 0);
+  if (p.flags & OT_B200_FROM_LOG_SOFTMAX) {
+    const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
+    const CoefB<T> *coef = reinterpret_cast<const CoefB<T> *>(p.ws + p.lay.coef);
+    if (aligned)
+      gradient_logsoftmax_kernel<T, VEC><<<stream_grid(p.rows), kThreads, 0, s>>>(
+          static_cast<T *>(grad), coef, status, p.rows, p.V, p.blank,
+          static_cast<const T *>(d_scale), (T)scale_host);
+    else
+      gradient_logsoftmax_kernel<T, 1><<<stream_grid(p.rows), kThreads, 0, s>>>(
+          static_cast<T *>(grad), coef, status, p.rows, p.V, p.blank,
+          static_cast<const T *>(d_scale), (T)scale_host);
+    return cudaGetLastError();
+  }
+  const bool vec_ok = aligned && (reinterpret_cast<uintptr_t>(p.logits) % 16 == 0);
+  if (vec_ok) {
+    const int per_lane = (p.V / VEC + kWarp - 1) / kWarp;
+    if (per_lane <= 1) return launch_grad_a<T, VEC, 1>(p, grad, d_scale, scale_host, s);
+    if (per_lane <= 2) return launch_grad_a<T, VEC, 2>(p, grad, d_scale, scale_host, s);
+    return launch_grad_a<T, VEC, 4>(p, grad, d_scale, scale_host, s);
+  }
+  const int per_lane = (p.V + kWarp - 1) / kWarp;
+  if (per_lane <= 4) return launch_grad_a<T, 1, 4>(p, grad, d_scale, scale_host, s);
+  return launch_grad_a<T, 1, 8>(p, grad, d_scale, scale_host, s);
+}
+
+}  // namespace
+
+cudaError_t launch_gradient(const Problem &p, void *grad, const void *d_scale,
+                            double scale_host, cudaStream_t s) {
+  return (p.flags & OT_B200_FP64)
+             ? launch_gradient_t<double>(p, grad, d_scale, scale_host, s)
+             : launch_gradient_t<float>(p, grad, d_scale, scale_host, s);
+}
+
+}  // namespace otb

@@ -1,0 +1,155 @@
+// Shared declarations of the sm_100a transducer-loss kernels.
+//
+// Notation used in every file of this directory:
+//   N        utterances in the batch
+//   T_b, U_b frames and target symbols of utterance b; the lattice has
+//            T_b x (U_b+1) cells, U1 = U_b + 1
+//   row      index into the packed (rows, V) logits; row(b,t,u) = split[b] + t*U1 + u
+//   lp       per row (blank log-prob, next-symbol log-prob)
+//   den      per row logsumexp of the logits
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ot_b200.h"
+
+namespace otb {
+
+constexpr int kWarp = 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+// Workspace status words (int32 each).
+constexpr int kStatusCode = 0;   // ot_b200_input_error, 0 = inputs are valid
+constexpr int kStatusIndex = 1;  // utterance the code refers to
+constexpr int kStatusWords = 16;
+
+// Marker values of the `tgt` field of a gradient-coefficient record.
+constexpr int32_t kTgtNone = -1;     // no symbol column to patch in this row
+constexpr int32_t kTgtZeroRow = -2;  // the whole gradient row is zero
+
+// Per-row coefficients of the gradient w.r.t. raw logits (mode A), produced
+// once per row after alpha and beta are known, so that the streaming gradient
+// kernel needs a single broadcast load per row:
+//   grad[v] = exp((x[v] + c) + beta) - [v == blank] exp((x[v] + c) + sub_blank)
+//                                    - [v == tgt]   exp((x[v] + c) + sub_sym)
+// sub_* = -inf means "nothing to subtract".
+template <typename T>
+struct alignas(32) CoefA {
+  T c;          // alpha(t,u) - L - den(t,u), evaluated as (alpha + (-L)) - den
+  T beta;       // beta(t,u)
+  T sub_blank;  // beta of the blank successor (0 for the final cell)
+  T sub_sym;    // beta of the symbol successor
+  int32_t tgt;  // symbol column, or kTgtNone / kTgtZeroRow
+};
+
+// Mode B (input already log-softmax): the gradient row is zero except for at
+// most two entries, whose final values are stored directly.
+template <typename T>
+struct alignas(16) CoefB {
+  T val_blank;  // gradient at the blank column (0 if none)
+  T val_sym;    // gradient at the symbol column
+  int32_t tgt;  // symbol column, or kTgtNone / kTgtZeroRow
+};
+
+struct Layout {
+  uint64_t total, status, split, den, lp, alpha, beta, coef, scores_beta;
+};
+
+// Computes the workspace layout (all segments 256-byte aligned).
+Layout make_layout(int32_t N, int64_t rows, uint32_t flags);
+
+struct Problem {
+  const void *logits;
+  const int32_t *targets;
+  const int32_t *T;
+  const int32_t *U;
+  int32_t N;
+  int64_t rows;
+  int32_t V;
+  int32_t max_u;
+  int32_t blank;
+  uint32_t flags;
+  char *ws;
+  Layout lay;
+};
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// Host launchers, one per stage; each returns the cudaError_t of its launch.
+cudaError_t launch_prepare(const Problem &p, cudaStream_t s);
+cudaError_t launch_logprob(const Problem &p, cudaStream_t s);
+cudaError_t launch_lattice(const Problem &p, void *scores, cudaStream_t s);
+cudaError_t launch_coef(const Problem &p, cudaStream_t s);
+cudaError_t launch_gradient(const Problem &p, void *grad, const void *d_scale,
+                            double scale_host, cudaStream_t s);
+
+// ---------------------------------------------------------------------------
+// Device helpers
+// ---------------------------------------------------------------------------
+
+// 16-byte vector of the element type.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> { using type = float4; static constexpr int n = 4; };
+template <> struct Vec16<double> { using type = double2; static constexpr int n = 2; };
+
+template <typename T> __device__ __forceinline__ T neg_inf();
+template <> __device__ __forceinline__ float neg_inf<float>() { return -__int_as_float(0x7f800000); }
+template <> __device__ __forceinline__ double neg_inf<double>() { return -__longlong_as_double(0x7ff0000000000000LL); }
+
+__device__ __forceinline__ float r_exp(float x) { return expf(x); }
+__device__ __forceinline__ double r_exp(double x) { return exp(x); }
+__device__ __forceinline__ float r_log(float x) { return logf(x); }
+__device__ __forceinline__ double r_log(double x) { return log(x); }
+__device__ __forceinline__ float r_log1p(float x) { return log1pf(x); }
+__device__ __forceinline__ double r_log1p(double x) { return log1p(x); }
+__device__ __forceinline__ float r_max(float a, float b) { return fmaxf(a, b); }
+__device__ __forceinline__ double r_max(double a, double b) { return fmax(a, b); }
+
+template <typename T> __device__ __forceinline__ T min_log_diff();
+// log(machine epsilon): below this the smaller operand of a log-add is dropped
+// (optimized_transducer/csrc/cpu.cc:15-16,30).
+template <> __device__ __forceinline__ float min_log_diff<float>() { return -15.9423847198486328125f; }
+template <> __device__ __forceinline__ double min_log_diff<double>() { return -36.04365338911715; }
+
+// log(exp(a) + exp(b)) with the reference's cut-off (cpu.cc:18-35): a NaN or
+// too negative difference returns the larger operand.
+template <typename T, bool FAST>
+__device__ __forceinline__ T log_add(T a, T b) {
+  const T hi = (a < b) ? b : a;
+  const T d = (a < b) ? (a - b) : (b - a);
+  if (!(d >= min_log_diff<T>())) return hi;
+  if constexpr (FAST && sizeof(T) == 4) {
+    // ex2/lg2 approximations: absolute error of the correction < 3e-7.
+    return hi + __logf(1.0f + __expf(d));
+  } else {
+    return hi + r_log1p(r_exp(d));
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ T warp_max(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = r_max(v, __shfl_xor_sync(kFull, v, o));
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+  return v;
+}
+
+// Utterance that owns `row`: the b with split[b] <= row < split[b+1].
+__device__ __forceinline__ int find_utt(const int64_t *__restrict__ split, int N,
+                                        int64_t row) {
+  int lo = 0, hi = N;  // invariant: split[lo] <= row < split[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(split + mid) <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+}  // namespace otb

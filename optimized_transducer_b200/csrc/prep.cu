@@ -1,0 +1,188 @@
+// Stage 0 (input check + row splits) and stage 2c (per-row gradient
+// coefficients) of the transducer-loss path.
+//
+// Stage 0 replaces, without a host round trip, the data-dependent checks of
+// ot::ComputeTransducerLoss (optimized_transducer/csrc/transducer-loss.cc:49-66)
+// and the row_splits construction of ot::ComputeTransducerLossCuda
+// (optimized_transducer/csrc/cuda.cu:411-414).  The reference's row_ids array
+// (cuda.cu:40-59, moderngpu load_balance_search) has no counterpart: later
+// stages find the owning utterance with a binary search over `split`.
+#include "ot_common.cuh"
+
+namespace otb {
+
+namespace {
+
+constexpr int kPrepThreads = 512;
+
+__device__ __forceinline__ void raise(int32_t *status, int code, int index) {
+  if (atomicCAS(status + kStatusCode, 0, code) == 0) status[kStatusIndex] = index;
+}
+
+// One CTA.  Thread i owns the contiguous utterance range [i*per, (i+1)*per).
+__global__ void __launch_bounds__(kPrepThreads)
+prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
+               const int32_t *__restrict__ Ul, int N, int64_t rows, int V,
+               int max_u, int modified, int32_t *__restrict__ status,
+               int64_t *__restrict__ split) {
+  __shared__ long long warp_tot[kPrepThreads / kWarp];
+  __shared__ int warp_maxu[kPrepThreads / kWarp];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < kStatusWords) status[tid] = 0;
+  __syncthreads();
+
+  const int per = (N + kPrepThreads - 1) / kPrepThreads;
+  const int b0 = min(tid * per, N), b1 = min(b0 + per, N);
+  long long mine = 0;
+  int my_maxu = -1;
+  for (int b = b0; b < b1; ++b) {
+    const int t = Tl[b], u = Ul[b];
+    if (t <= 0) raise(status, OT_B200_INPUT_BAD_LOGIT_LENGTH, b);
+    if (u < 0 || u > max_u) raise(status, OT_B200_INPUT_BAD_TARGET_LENGTH, b);
+    if (modified && u > t - 1) raise(status, OT_B200_INPUT_ONE_SYM_INFEASIBLE, b);
+    mine += (long long)max(t, 0) * (long long)(max(u, 0) + 1);
+    my_maxu = max(my_maxu, u);
+  }
+  // Block-wide exclusive scan of `mine` (warp shuffles, then warp totals).
+  long long incl = mine;
+#pragma unroll
+  for (int o = 1; o < kWarp; o <<= 1) {
+    const long long v = __shfl_up_sync(kFull, incl, o);
+    if (lane >= o) incl += v;
+  }
+  int wmax = my_maxu;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wmax = max(wmax, __shfl_xor_sync(kFull, wmax, o));
+  if (lane == kWarp - 1) warp_tot[warp] = incl;
+  if (lane == 0) warp_maxu[warp] = wmax;
+  __syncthreads();
+  long long base = 0, total = 0;
+  int maxu_all = -1;
+  for (int w = 0; w < kPrepThreads / kWarp; ++w) {
+    if (w < warp) base += warp_tot[w];
+    total += warp_tot[w];
+    maxu_all = max(maxu_all, warp_maxu[w]);
+  }
+  long long run = base + incl - mine;
+  for (int b = b0; b < b1; ++b) {
+    split[b] = run;
+    run += (long long)max(Tl[b], 0) * (long long)(max(Ul[b], 0) + 1);
+  }
+  if (tid == 0) {
+    split[N] = total;
+    if (total != rows) raise(status, OT_B200_INPUT_ROWS_MISMATCH, 0);
+    if (maxu_all != max_u) raise(status, OT_B200_INPUT_MAX_U_MISMATCH, 0);
+  }
+  // targets.max() < V over the whole (N, max_u) array, as the reference
+  // checks it; in addition the entries that are used must not be negative.
+  const long long cells = (long long)N * max_u;
+  for (long long i = tid; i < cells; i += kPrepThreads) {
+    const int v = targets[i];
+    const int b = (int)(i / max_u), u = (int)(i % max_u);
+    if (v >= V || (u < Ul[b] && v < 0)) raise(status, OT_B200_INPUT_TARGET_RANGE, b);
+  }
+}
+
+// Thread per row.  Produces the record the streaming gradient kernels read.
+// Branch order and the order of the floating-point additions follow
+// ComputeGradient / ...OneSymPerFrame / ...ForLogSoftmax[OneSymPerFrame]
+// (optimized_transducer/csrc/cpu.cc:500-526, 582-604, 655-672, 722-745).
+// A non-finite log-likelihood zeroes the utterance's rows
+// (optimized_transducer/csrc/kernels.cu:556-563).
+template <typename T, bool MODE_B, bool MODIFIED>
+__global__ void __launch_bounds__(256)
+coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
+            const int32_t *__restrict__ Ul, const int64_t *__restrict__ split,
+            const int32_t *__restrict__ status, int N, int64_t rows, int max_u,
+            int blank, const T *__restrict__ den, const T *__restrict__ lp,
+            const T *__restrict__ alpha, const T *__restrict__ beta,
+            void *__restrict__ coef_out) {
+  if (status[kStatusCode] != 0) return;
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const int b = find_utt(split, N, row);
+  const int64_t off = __ldg(split + b);
+  const int Tn = __ldg(Tl + b), U = __ldg(Ul + b), U1 = U + 1;
+  const int idx = (int)(row - off);
+  const int t = idx / U1, u = idx - t * U1;
+  const int diff = Tn - 1 - U;
+  const T L = beta[off];
+
+  bool zero = !(L - L == (T)0);  // inf or nan
+  if (MODIFIED && (u > t || t - u > diff)) zero = true;
+
+  T c = 0, b_here = 0, sub_blank = neg_inf<T>(), sub_sym = neg_inf<T>();
+  int32_t tgt = kTgtNone;
+  bool blank_term = false, sym_term = false;
+  if (!zero) {
+    const T loss = -L;
+    c = alpha[row] + loss;
+    if (!MODE_B) c = c - den[row];
+    b_here = beta[row];
+    const bool last = (t == Tn - 1 && u == U);
+    const bool blank_ok = MODIFIED ? (t - u < diff) : (t < Tn - 1);
+    const int target_u = (u < U) ? __ldg(targets + (int64_t)b * max_u + u) : -1;
+    const T b_sym_next = (u < U) ? (MODIFIED ? beta[row + U1 + 1] : beta[row + 1]) : neg_inf<T>();
+    if (last) {
+      sub_blank = 0; blank_term = true;
+    } else if (blank_ok) {
+      sub_blank = beta[row + U1]; blank_term = true;
+    } else if (u < U && target_u == blank) {
+      sub_blank = b_sym_next; blank_term = true;
+    }
+    if (u < U && target_u != blank) {
+      sub_sym = b_sym_next; tgt = target_u; sym_term = true;
+    }
+  }
+  if (MODE_B) {
+    CoefB<T> r;
+    r.val_blank = blank_term ? -r_exp((lp[2 * row] + c) + sub_blank) : (T)0;
+    r.val_sym = sym_term ? -r_exp((lp[2 * row + 1] + c) + sub_sym) : (T)0;
+    r.tgt = zero ? kTgtZeroRow : tgt;
+    reinterpret_cast<CoefB<T> *>(coef_out)[row] = r;
+  } else {
+    CoefA<T> r;
+    r.c = c; r.beta = b_here; r.sub_blank = sub_blank; r.sub_sym = sub_sym;
+    r.tgt = zero ? kTgtZeroRow : tgt;
+    reinterpret_cast<CoefA<T> *>(coef_out)[row] = r;
+  }
+}
+
+template <typename T>
+cudaError_t launch_coef_t(const Problem &p, cudaStream_t s) {
+  const bool mode_b = p.flags & OT_B200_FROM_LOG_SOFTMAX;
+  const bool modified = p.flags & OT_B200_ONE_SYM_PER_FRAME;
+  const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
+  const int64_t *split = reinterpret_cast<const int64_t *>(p.ws + p.lay.split);
+  const T *den = reinterpret_cast<const T *>(p.ws + p.lay.den);
+  const T *lp = reinterpret_cast<const T *>(p.ws + p.lay.lp);
+  const T *alpha = reinterpret_cast<const T *>(p.ws + p.lay.alpha);
+  const T *beta = reinterpret_cast<const T *>(p.ws + p.lay.beta);
+  void *coef = p.ws + p.lay.coef;
+  const unsigned grid = (unsigned)((p.rows + 255) / 256);
+#define OTB_COEF(MB, MOD)                                                      \
+  coef_kernel<T, MB, MOD><<<grid, 256, 0, s>>>(p.targets, p.T, p.U, split,     \
+      status, p.N, p.rows, p.max_u, p.blank, den, lp, alpha, beta, coef)
+  if (mode_b) { if (modified) OTB_COEF(true, true); else OTB_COEF(true, false); }
+  else        { if (modified) OTB_COEF(false, true); else OTB_COEF(false, false); }
+#undef OTB_COEF
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_prepare(const Problem &p, cudaStream_t s) {
+  prepare_kernel<<<1, kPrepThreads, 0, s>>>(
+      p.targets, p.T, p.U, p.N, p.rows, p.V, p.max_u,
+      (p.flags & OT_B200_ONE_SYM_PER_FRAME) ? 1 : 0,
+      reinterpret_cast<int32_t *>(p.ws + p.lay.status),
+      reinterpret_cast<int64_t *>(p.ws + p.lay.split));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_coef(const Problem &p, cudaStream_t s) {
+  return (p.flags & OT_B200_FP64) ? launch_coef_t<double>(p, s)
+                                  : launch_coef_t<float>(p, s);
+}
+
+}  // namespace otb

@@ -1,0 +1,299 @@
+"""Python surface of the transducer loss, a mirror of the reference's
+``optimized_transducer/python/optimized_transducer/transducer_loss.py``.
+
+Same names, argument order, defaults and error behaviour as the reference:
+
+* :func:`transducer_loss` (reference ``transducer_loss.py:312-442``)
+* :class:`TransducerLoss` (``:173-309``; the reference's module does not call
+  ``super().__init__()`` and cannot be instantiated on current PyTorch, this
+  one can)
+* :class:`TransducerLossFunction` (``:7-170``)
+* :func:`compute_transducer_loss`, the counterpart of the reference's private
+  native entry ``_optimized_transducer.compute_transducer_loss``
+  (``python/csrc/optimized_transducer.cc:15-19``).
+
+All arithmetic runs in the sm_100a kernels of ``libot_b200.so``; PyTorch only
+provides device memory and the current stream.  There is no CPU path: tensors
+must live on a CUDA device.
+
+Gradient scheduling.  The reference computes the gradient inside ``forward``
+(overwriting ``logits`` there), divides it by N for ``reduction="mean"`` in a
+second pass and multiplies it by the upstream gradient in a third.  Here
+``forward`` stops after the alpha/beta recursions and ``backward`` runs one
+fused pass that applies both factors while it overwrites ``logits``; the
+observable results (loss, ``.grad`` of the leaves, ``logits`` overwritten by
+its gradient after ``backward``) are the same.  ``OT_EAGER_GRAD=1`` restores
+the reference's schedule, for callers that read ``logits`` between ``forward``
+and ``backward``.
+"""
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+
+__all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
+           "compute_transducer_loss", "stage_outputs"]
+
+
+def _checks_enabled():
+    return os.environ.get("OT_CHECKS", "1") != "0"
+
+
+def _eager_grad():
+    return os.environ.get("OT_EAGER_GRAD", "0") == "1"
+
+
+def _fast_math():
+    return os.environ.get("OT_FAST_MATH", "0") == "1"
+
+
+def _validate(logits, targets, logit_lengths, target_lengths, blank):
+    """The metadata checks of ot::ComputeTransducerLoss
+    (optimized_transducer/csrc/transducer-loss.cc:33-46, 58-60, 77-79); the
+    data-dependent ones (:49-56, :62-66) run on the device."""
+    who = "ComputeTransducerLoss"
+    if logits.dtype not in (torch.float32, torch.float64):
+        raise RuntimeError(f"{who}: expected logits to have scalar type Float "
+                           f"(Double is accepted as an extension), got {logits.dtype}")
+    for name, t in (("targets", targets), ("logit_lengths", logit_lengths),
+                    ("target_lengths", target_lengths)):
+        if t.dtype != torch.int32:
+            raise RuntimeError(f"{who}: expected {name} to have scalar type Int, got {t.dtype}")
+    for name, t in (("logits", logits), ("targets", targets),
+                    ("logit_lengths", logit_lengths), ("target_lengths", target_lengths)):
+        if not t.is_contiguous():
+            raise RuntimeError(f"{who}: expected {name} to be contiguous")
+    for name, t, d in (("logits", logits, 2), ("targets", targets, 2),
+                       ("logit_lengths", logit_lengths, 1), ("target_lengths", target_lengths, 1)):
+        if t.dim() != d:
+            raise RuntimeError(f"{who}: expected {name} to be {d}-dimensional, got {t.dim()}")
+    if logit_lengths.shape != target_lengths.shape:
+        raise RuntimeError(f"{who}: expected logit_lengths and target_lengths to have the same size")
+    if targets.size(0) != logit_lengths.size(0):
+        raise RuntimeError(f"{who}: targets.size(0) must equal the batch size")
+    if not logits.is_cuda:
+        raise RuntimeError(
+            "optimized_transducer_b200 runs on CUDA devices only (sm_100a kernels, no CPU path); "
+            f"logits is on {logits.device}")
+    for name, t in (("targets", targets), ("logit_lengths", logit_lengths),
+                    ("target_lengths", target_lengths)):
+        if t.device != logits.device:
+            raise RuntimeError(f"{who}: expected {name} to be on {logits.device}, got {t.device}")
+    if not (0 <= blank < logits.size(1)):
+        raise RuntimeError(f"blank vs logits.size(1) is {blank} vs {logits.size(1)}. "
+                           "Expect 0 <= blank < logits.size(1)")
+    if logits.size(0) == 0 or logit_lengths.size(0) == 0:
+        raise RuntimeError(f"{who}: empty batch")
+
+
+def _flags(logits, from_log_softmax, one_sym_per_frame, checks):
+    f = 0
+    if from_log_softmax:
+        f |= _lib.FROM_LOG_SOFTMAX
+    if one_sym_per_frame:
+        f |= _lib.ONE_SYM_PER_FRAME
+    if logits.dtype == torch.float64:
+        f |= _lib.FP64
+    if checks:
+        f |= _lib.CHECK_INPUTS
+    if _fast_math():
+        f |= _lib.FAST_MATH
+    return f
+
+
+class _Call:
+    """Pointers and sizes of one loss evaluation, plus its workspace."""
+
+    def __init__(self, logits, targets, logit_lengths, target_lengths, blank,
+                 from_log_softmax, one_sym_per_frame, checks=None):
+        _validate(logits, targets, logit_lengths, target_lengths, blank)
+        if checks is None:
+            checks = _checks_enabled()
+        self.lib = _lib.load()
+        self.logits = logits
+        self.n = int(logit_lengths.size(0))
+        self.rows = int(logits.size(0))
+        self.v = int(logits.size(1))
+        self.max_u = int(targets.size(1))
+        self.blank = int(blank)
+        self.from_log_softmax = bool(from_log_softmax)
+        self.flags = _flags(logits, from_log_softmax, one_sym_per_frame, checks)
+        self.layout = _lib.workspace_layout(self.n, self.rows, self.flags)
+        self.targets, self.t, self.u = targets, logit_lengths, target_lengths
+        with torch.cuda.device(logits.device):
+            self.workspace = torch.empty(int(self.layout.total_bytes), dtype=torch.uint8,
+                                         device=logits.device)
+            self.scores = torch.empty(self.n, dtype=logits.dtype, device=logits.device)
+
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.logits.device).cuda_stream)
+
+    def forward(self):
+        with torch.cuda.device(self.logits.device):
+            rc = self.lib.ot_b200_forward(
+                self.logits.data_ptr(), self.targets.data_ptr() if self.max_u else None,
+                self.t.data_ptr(), self.u.data_ptr(), self.n, self.rows, self.v, self.max_u,
+                self.blank, self.flags, self.workspace.data_ptr(), int(self.layout.total_bytes),
+                self.scores.data_ptr(), self._stream())
+        _lib.check(rc)
+        return self.scores
+
+    def backward(self, grad_out, scale_tensor=None, scale_host=1.0):
+        with torch.cuda.device(self.logits.device):
+            rc = self.lib.ot_b200_backward(
+                self.logits.data_ptr(), grad_out.data_ptr(), self.n, self.rows, self.v,
+                self.blank, self.flags & ~_lib.CHECK_INPUTS, self.workspace.data_ptr(),
+                int(self.layout.total_bytes),
+                scale_tensor.data_ptr() if scale_tensor is not None else None,
+                float(scale_host), self._stream())
+        _lib.check(rc)
+        return grad_out
+
+    def stage(self, name):
+        """A tensor view of one intermediate array inside the workspace."""
+        dt = self.logits.dtype
+        es = 8 if dt == torch.float64 else 4
+        if name == "split":
+            off, count, dtype, esz = self.layout.split_off, self.n + 1, torch.int64, 8
+        elif name == "status":
+            off, count, dtype, esz = self.layout.status_off, 16, torch.int32, 4
+        else:
+            off = getattr(self.layout, name + "_off")
+            count = {"den": self.rows, "lp": 2 * self.rows, "alpha": self.rows,
+                     "beta": self.rows, "scores_beta": self.n}[name]
+            dtype, esz = dt, es
+        return self.workspace[off:off + count * esz].view(dtype)
+
+
+def compute_transducer_loss(logits, targets, logit_lengths, target_lengths, blank,
+                            from_log_softmax, one_sym_per_frame):
+    """Counterpart of ``_optimized_transducer.compute_transducer_loss``.
+
+    Returns ``(scores, grad)``: ``scores[b] = log P(y_b | x_b)`` (the negated
+    loss, as the reference's native function returns it) and the gradient of
+    ``-scores.sum()``, or ``None`` if ``logits`` does not require grad.  With
+    ``from_log_softmax=False`` the gradient is written over ``logits`` and the
+    returned tensor shares its memory (reference ``cuda.cu:449``); otherwise it
+    is a new tensor (``cuda.cu:444``).
+    """
+    call = _Call(logits, targets, logit_lengths, target_lengths, blank,
+                 from_log_softmax, one_sym_per_frame)
+    scores = call.forward()
+    grad = None
+    if logits.requires_grad:
+        data = logits.detach()
+        grad = data if not from_log_softmax else torch.empty_like(data)
+        call.backward(grad)
+    return scores, grad
+
+
+def stage_outputs(logits, targets, logit_lengths, target_lengths, blank,
+                  from_log_softmax=False, one_sym_per_frame=False):
+    """Runs the forward half and returns its intermediate arrays (copies):
+    ``scores``, ``scores_beta``, ``den`` (None for log-softmax input), ``lp``
+    (rows, 2), ``alpha``, ``beta`` (rows) and ``split`` (N+1).  For tests and
+    debugging; cells outside the band of the modified recursion are undefined."""
+    call = _Call(logits, targets, logit_lengths, target_lengths, blank,
+                 from_log_softmax, one_sym_per_frame)
+    scores = call.forward()
+    out = {"scores": scores.clone(), "scores_beta": call.stage("scores_beta").clone(),
+           "den": None if from_log_softmax else call.stage("den").clone(),
+           "lp": call.stage("lp").clone().view(-1, 2), "alpha": call.stage("alpha").clone(),
+           "beta": call.stage("beta").clone(), "split": call.stage("split").clone()}
+    return out
+
+
+class TransducerLossFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, logit_lengths, target_lengths, blank,
+                from_log_softmax, one_sym_per_frame, reduction="mean"):
+        assert reduction in ("mean", "sum")
+        n = logit_lengths.size(0)
+        if _eager_grad():
+            # The reference's schedule (transducer_loss.py:135-154).
+            scores, grad = compute_transducer_loss(
+                logits, targets, logit_lengths, target_lengths, blank,
+                from_log_softmax, one_sym_per_frame)
+            loss = -1 * scores
+            if reduction == "mean":
+                loss = loss.mean()
+                if grad is not None:
+                    grad /= n
+            else:
+                loss = loss.sum()
+            ctx.grad = grad
+            ctx.call = None
+            return loss
+
+        call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
+                     from_log_softmax, one_sym_per_frame)
+        scores = call.forward()
+        loss = -scores.sum()
+        if reduction == "mean":
+            loss = loss / n
+        ctx.grad = None
+        ctx.call = call if logits.requires_grad else None
+        ctx.scale_host = (1.0 / n) if reduction == "mean" else 1.0
+        return loss
+
+    @staticmethod
+    def backward(ctx, loss_grad):
+        assert loss_grad.numel() == 1, loss_grad.numel()
+        if ctx.call is None:
+            if ctx.grad is None:
+                raise RuntimeError("the gradient of this transducer loss was already consumed, "
+                                   "or logits did not require grad")
+            grad = ctx.grad.mul_(loss_grad)  # reference transducer_loss.py:162
+            return (grad,) + (None,) * 7
+        call, ctx.call = ctx.call, None  # the workspace is released after this pass
+        data = call.logits
+        grad = torch.empty_like(data) if call.from_log_softmax else data
+        scale = loss_grad.detach().to(device=data.device, dtype=data.dtype).contiguous()
+        call.backward(grad, scale_tensor=scale, scale_host=ctx.scale_host)
+        return (grad,) + (None,) * 7
+
+
+class TransducerLoss(torch.nn.Module):
+    """Module form of :func:`transducer_loss` (reference ``transducer_loss.py:173-309``)."""
+
+    def __init__(self, blank: int, reduction: str = "mean"):
+        super().__init__()
+        assert reduction in ("mean", "sum")
+        self.blank = blank
+        self.reduction = reduction
+
+    def forward(self, logits, targets, logit_lengths, target_lengths,
+                from_log_softmax, one_sym_per_frame=False):
+        return TransducerLossFunction.apply(
+            logits, targets, logit_lengths, target_lengths, self.blank,
+            from_log_softmax, one_sym_per_frame, self.reduction)
+
+
+def transducer_loss(logits: torch.Tensor, targets: torch.Tensor,
+                    logit_lengths: torch.Tensor, target_lengths: torch.Tensor,
+                    blank: int, from_log_softmax: bool,
+                    one_sym_per_frame: bool = False,
+                    reduction: str = "mean") -> torch.Tensor:
+    """Transducer (RNN-T) loss over packed logits.
+
+    Args:
+      logits: (sum_b T_b*(U_b+1), V) float32 (float64 accepted), contiguous,
+        on a CUDA device: utterance b's (T_b, U_b+1, V) joiner output flattened
+        to rows and the utterances concatenated (reference README.md:131-204).
+        If it requires grad and ``from_log_softmax`` is False, ``backward``
+        overwrites it with its gradient.
+      targets: (N, max_b U_b) int32, not prepended with a blank.
+      logit_lengths: (N,) int32, T_b.   target_lengths: (N,) int32, U_b.
+      blank: id of the blank symbol.
+      from_log_softmax: True if ``logits`` already holds log-softmax outputs.
+      one_sym_per_frame: True for the modified transducer that emits at most
+        one symbol per frame (needs U_b <= T_b - 1).
+      reduction: "mean" (over utterances) or "sum"; "none" is not supported, as
+        in the reference (transducer_loss.py:126-128).
+    Returns: a 0-dim tensor with the reduced loss.
+    """
+    return TransducerLossFunction.apply(
+        logits, targets, logit_lengths, target_lengths, blank, from_log_softmax,
+        one_sym_per_frame, reduction)

@@ -1,0 +1,361 @@
+"""Parity of the CUDA path (through the C ABI) with the reference.
+
+Oracles, in order of authority:
+  1. ``tests/golden/reference_vectors.npz`` - outputs of the reference's own CPU
+     build on small batches (committed; made by tests/golden/make_golden.py);
+  2. ``oracle/`` - the C restatement of the reference's algorithm, pinned to (1)
+     by tests/test_oracle.py, in float32 and float64.
+
+Tolerances (float32 path), as the build's target states them:
+  per-utterance loss      1e-5 relative
+  alpha / beta, log-probs 1e-5, relative to max(1, |value|)
+  gradient                1e-5 max absolute error, where float32 can express it:
+                          the floor is helpers.fp32_grad_floor (two float32
+                          roundings at the magnitude of the log-likelihood).
+                          Beyond that magnitude the test that matters is
+                          test_float32_error_is_not_worse_than_the_references.
+float64 path: 1e-10 for all of the above.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import optimized_transducer_b200 as ot
+from optimized_transducer_b200 import _lib, synthetic
+from optimized_transducer_b200.transducer_loss import _Call
+from oracle import oracle as O
+from helpers import fp32_grad_floor, golden_case, golden_names, random_batch, splits
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def to_dev(x, targets, T, U):
+    return (torch.from_numpy(np.ascontiguousarray(x)).to(DEV),
+            torch.from_numpy(np.ascontiguousarray(targets)).to(DEV),
+            torch.from_numpy(np.ascontiguousarray(T)).to(DEV),
+            torch.from_numpy(np.ascontiguousarray(U)).to(DEV))
+
+
+def run_cuda(x, targets, T, U, blank=0, from_ls=False, modified=False, want_grad=True):
+    """scores, grad and the stage arrays of the CUDA path, as numpy."""
+    dx, dt, dT, dU = to_dev(x, targets, T, U)
+    st = ot.stage_outputs(dx, dt, dT, dU, blank, from_ls, modified)
+    out = {k: (None if v is None else v.cpu().numpy()) for k, v in st.items()}
+    if want_grad:
+        dx.requires_grad_(True)
+        scores, grad = ot.compute_transducer_loss(dx, dt, dT, dU, blank, from_ls, modified)
+        if not from_ls:
+            assert grad.data_ptr() == dx.data_ptr()  # in place, reference cuda.cu:449
+        else:
+            assert grad.data_ptr() != dx.data_ptr()  # reference cuda.cu:444
+        out["grad"] = grad.cpu().numpy()
+        np.testing.assert_array_equal(scores.cpu().numpy(), out["scores"])  # deterministic
+    return out
+
+
+def rel_to_one(a, b):
+    return np.abs(a - b) / np.maximum(1.0, np.abs(b))
+
+
+def check_against(out, ref, tol=1e-5, grad_tol=None, band=None):
+    assert np.max(np.abs(out["scores"] - ref["scores"]) / np.abs(ref["scores"])) <= tol
+    assert np.max(rel_to_one(out["scores_beta"], ref["scores_beta"])) <= tol
+    ok = ~np.isnan(ref["lp"])
+    if band is not None:
+        ok &= band[:, None]
+    assert np.max(rel_to_one(out["lp"][ok], ref["lp"][ok])) <= tol
+    for k in ("alpha", "beta"):
+        ok = ~np.isnan(ref[k])
+        assert np.max(rel_to_one(out[k][ok], ref[k][ok])) <= tol, k
+    if "grad" in out and ref.get("grad") is not None:
+        if grad_tol is None:
+            grad_tol = max(tol, fp32_grad_floor(ref["alpha"], ref["beta"]))
+        assert np.max(np.abs(out["grad"] - ref["grad"])) <= grad_tol
+
+
+# ---------------------------------------------------------------------------
+# 1. the reference's own outputs
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("name", golden_names())
+def test_reference_vectors(name):
+    c = golden_case(name)
+    out = run_cuda(c["x"], c["targets"], c["T"], c["U"], c["blank"], c["from_log_softmax"], c["modified"])
+    band = O.band_mask(c["T"], c["U"]) if c["modified"] else None
+    check_against(out, c, band=band)
+
+
+# ---------------------------------------------------------------------------
+# 2. seeded batches against the oracle, float32 and float64
+# ---------------------------------------------------------------------------
+CASES = [
+    # seed, N, T range, U range, V, scale
+    (21, 4, (50, 100), (10, 20), 500, 1.0),     # the CPU-runnable benchmark shape
+    (22, 3, (20, 40), (31, 33), 64, 1.0),       # lattice columns straddle one warp
+    (23, 2, (40, 70), (63, 66), 36, 2.0),       # two to three warps
+    (24, 2, (30, 50), (150, 200), 24, 1.0),     # seven warps
+    (25, 5, (1, 9), (0, 6), 10, 1.0),           # tiny and ragged, T = 1 and U = 0 present
+    (26, 2, (33, 47), (5, 9), 1030, 1.0),       # more than one chunk per row, V % 4 != 0
+    (27, 2, (25, 30), (5, 9), 2048, 1.0),       # several 16-byte chunks per lane
+]
+
+
+@pytest.mark.parametrize("modified", [False, True])
+@pytest.mark.parametrize("from_ls", [False, True])
+@pytest.mark.parametrize("case", CASES, ids=[str(c[0]) for c in CASES])
+def test_seeded_batches_float32(case, from_ls, modified):
+    seed, n, tr, ur, v, scale = case
+    x, tg, T, U = random_batch(seed, n, tr, ur, v, scale, modified=modified, log_softmax=from_ls)
+    if tg.shape[1] == 0:
+        pytest.skip("empty targets")
+    ref = O.oracle_loss(x, tg, T, U, 0, from_ls, modified)
+    out = run_cuda(x, tg, T, U, 0, from_ls, modified)
+    check_against(out, ref, band=O.band_mask(T, U) if modified else None)
+    if not from_ls:
+        assert np.max(rel_to_one(out["den"][O.band_mask(T, U)] if modified else out["den"],
+                                 ref["den"][O.band_mask(T, U)] if modified else ref["den"])) <= 1e-5
+
+
+@pytest.mark.parametrize("modified", [False, True])
+@pytest.mark.parametrize("from_ls", [False, True])
+@pytest.mark.parametrize("case", CASES[:5], ids=[str(c[0]) for c in CASES[:5]])
+def test_seeded_batches_float64(case, from_ls, modified):
+    seed, n, tr, ur, v, scale = case
+    x, tg, T, U = random_batch(seed, n, tr, ur, v, scale, modified=modified, log_softmax=from_ls,
+                               dtype=np.float64)
+    if tg.shape[1] == 0:
+        pytest.skip("empty targets")
+    ref = O.oracle_loss(x, tg, T, U, 0, from_ls, modified)
+    out = run_cuda(x, tg, T, U, 0, from_ls, modified)
+    check_against(out, ref, tol=1e-10, grad_tol=1e-10, band=O.band_mask(T, U) if modified else None)
+
+
+def test_float32_error_is_not_worse_than_the_references():
+    """On a long lattice float32 cannot hold 1e-5: the reference's own output is
+    ~1e-3 away from the float64 result.  The CUDA path must be as close to the
+    float64 result as the reference's algorithm in float32 is."""
+    x, tg, T, U = random_batch(31, 2, (200, 300), (40, 80), 500, 2.0)
+    truth = O.oracle_loss(x.astype(np.float64), tg, T, U, 0)
+    ref32 = O.oracle_loss(x, tg, T, U, 0)
+    out = run_cuda(x, tg, T, U, 0)
+    err_ref = np.max(np.abs(ref32["grad"] - truth["grad"]))
+    err_cuda = np.max(np.abs(out["grad"] - truth["grad"]))
+    assert err_cuda <= 1.5 * err_ref + 1e-6, (err_cuda, err_ref)
+    assert np.max(np.abs(out["scores"] - truth["scores"]) / np.abs(truth["scores"])) <= 1e-5
+    assert np.max(np.abs(out["grad"] - ref32["grad"])) <= fp32_grad_floor(ref32["alpha"], ref32["beta"])
+
+
+# ---------------------------------------------------------------------------
+# 3. the Python surface (the reference's tests, re-expressed)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+@pytest.mark.parametrize("from_ls", [False, True])
+@pytest.mark.parametrize("modified", [False, True])
+@pytest.mark.parametrize("eager", ["0", "1"])
+def test_autograd_surface(reduction, from_ls, modified, eager, monkeypatch):
+    """Leaves -> cat -> (log_softmax) -> loss -> (loss * 3).backward(), as in the
+    reference's python/tests/test_compute_transducer_loss.py:36-105."""
+    monkeypatch.setenv("OT_EAGER_GRAD", eager)
+    x, tg, T, U = random_batch(41, 2, (8, 12), (3, 6), 7, modified=modified)
+    sp = splits(T, U)
+    leaves = [torch.from_numpy(x[sp[i]:sp[i + 1]]).to(DEV).requires_grad_(True) for i in range(2)]
+    logits = torch.cat(leaves)
+    if from_ls:
+        logits = logits.log_softmax(dim=-1)
+    _, dt, dT, dU = to_dev(x, tg, T, U)
+    loss = ot.transducer_loss(logits=logits, targets=dt, logit_lengths=dT, target_lengths=dU,
+                              blank=0, reduction=reduction, from_log_softmax=from_ls,
+                              one_sym_per_frame=modified)
+    assert loss.dim() == 0
+    (loss * 3).backward()
+    ref = O.oracle_loss(x.astype(np.float64), tg, T, U, 0, False, modified)
+    scale = 3.0 / (2 if reduction == "mean" else 1)
+    want_loss = -ref["scores"].sum() / (2 if reduction == "mean" else 1)
+    assert abs(loss.item() - want_loss) <= 1e-5 * abs(want_loss)
+    for i in range(2):
+        np.testing.assert_allclose(leaves[i].grad.cpu().numpy(), scale * ref["grad"][sp[i]:sp[i + 1]],
+                                   rtol=0, atol=3e-5)
+
+
+def test_module_form_and_no_grad():
+    x, tg, T, U = random_batch(42, 3, (5, 9), (2, 4), 6)
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    before = dx.clone()
+    crit = ot.TransducerLoss(blank=0, reduction="sum")
+    loss = crit(dx, dt, dT, dU, from_log_softmax=False)
+    ref = O.oracle_loss(x, tg, T, U, 0)
+    assert abs(loss.item() + ref["scores"].sum()) <= 1e-5 * abs(ref["scores"].sum())
+    # no requires_grad: no gradient, logits untouched (reference cuda.cu:440-442)
+    scores, grad = ot.compute_transducer_loss(dx, dt, dT, dU, 0, False, False)
+    assert grad is None and torch.equal(dx, before)
+
+
+def test_backward_twice_is_refused():
+    x, tg, T, U = random_batch(43, 1, (4, 4), (2, 2), 5)
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    leaf = dx.clone().requires_grad_(True)
+    loss = ot.transducer_loss(leaf * 1.0, dt, dT, dU, 0, False)
+    loss.backward(retain_graph=True)
+    with pytest.raises(RuntimeError):
+        loss.backward()
+
+
+# ---------------------------------------------------------------------------
+# 4. in-place safety, determinism, flags
+# ---------------------------------------------------------------------------
+def test_in_place_equals_out_of_place_bitwise():
+    x, tg, T, U = random_batch(51, 3, (20, 30), (5, 12), 500, 2.0)
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    call = _Call(dx, dt, dT, dU, 0, False, False)
+    call.forward()
+    separate = torch.full_like(dx, float("nan"))
+    call.backward(separate)
+    assert torch.equal(dx.cpu(), torch.from_numpy(x))  # input intact so far
+    call.backward(dx)                                   # now over the logits
+    assert torch.equal(separate, dx)
+    ref = O.oracle_loss(x, tg, T, U, 0)
+    assert np.max(np.abs(dx.cpu().numpy() - ref["grad"])) <= max(1e-5, fp32_grad_floor(ref["alpha"], ref["beta"]))
+
+
+def test_scale_is_folded_into_the_gradient_pass():
+    x, tg, T, U = random_batch(52, 2, (6, 9), (2, 5), 12)
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    call = _Call(dx, dt, dT, dU, 0, False, False)
+    call.forward()
+    g1 = torch.empty_like(dx)
+    g2 = torch.empty_like(dx)
+    call.backward(g1)
+    call.backward(g2, scale_tensor=torch.tensor(3.0, device=DEV), scale_host=0.25)
+    torch.testing.assert_close(g2, g1 * 0.75, rtol=1e-6, atol=1e-7)
+
+
+def test_fast_math_flag_stays_within_tolerance(monkeypatch):
+    x, tg, T, U = random_batch(53, 3, (30, 60), (10, 40), 50)
+    ref = O.oracle_loss(x, tg, T, U, 0)
+    monkeypatch.setenv("OT_FAST_MATH", "1")
+    out = run_cuda(x, tg, T, U, 0)
+    check_against(out, ref)
+
+
+def test_wide_lattice_uses_generic_recursion():
+    """More than 1024 lattice columns (the reference's CUDA path cannot run
+    this: one thread per column, at most 1024, cuda.cu:197-205)."""
+    for modified in (False, True):
+        if modified:  # needs T >= U + 1
+            x, tg, T, U = random_batch(54, 1, (1101, 1105), (1030, 1100), 4, modified=True)
+        else:
+            x, tg, T, U = random_batch(54, 2, (3, 6), (1030, 1100), 8)
+        ref = O.oracle_loss(x, tg, T, U, 0, False, modified)
+        out = run_cuda(x, tg, T, U, 0, False, modified)
+        check_against(out, ref, band=O.band_mask(T, U) if modified else None)
+
+
+def test_infeasible_utterance_gives_zero_gradient_rows():
+    """-inf on every blank of one utterance: its likelihood is 0, log-likelihood
+    -inf; the gradient rows of that utterance are zero (reference CUDA
+    behaviour, kernels.cu:556-563), the other utterance is unaffected."""
+    x, tg, T, U = random_batch(55, 2, (5, 7), (2, 3), 6)
+    sp = splits(T, U)
+    x[sp[0]:sp[1], 0] = -np.inf
+    out = run_cuda(x, tg, T, U, 0)
+    assert np.isneginf(out["scores"][0]) and np.isfinite(out["scores"][1])
+    assert np.all(out["grad"][sp[0]:sp[1]] == 0)
+    ref = O.oracle_loss(x[sp[1]:], tg[1:, :U[1]], T[1:], U[1:], 0)
+    assert np.max(np.abs(out["grad"][sp[1]:] - ref["grad"])) <= 1e-5
+
+
+# ---------------------------------------------------------------------------
+# 5. device-side input check (transducer-loss.cc:49-66) and its error path
+# ---------------------------------------------------------------------------
+def _expect_input_error(x, tg, T, U, match, modified=False):
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    before = dx.clone()
+    with pytest.raises(RuntimeError, match=match):
+        ot.stage_outputs(dx, dt, dT, dU, 0, False, modified)
+    torch.cuda.synchronize()
+    assert torch.equal(dx, before)
+
+
+def test_input_errors_are_reported_not_faulted():
+    x, tg, T, U = random_batch(61, 3, (4, 6), (2, 3), 5)
+    _expect_input_error(x[:-1], tg, T, U, "logits.size\\(0\\)")
+    bad = tg.copy(); bad[0, 0] = 5
+    _expect_input_error(x, bad, T, U, "targets.max\\(\\)")
+    wide = np.concatenate([tg, np.ones((3, 1), np.int32)], axis=1)
+    _expect_input_error(x, wide, T, U, "target_lengths.max")
+    Tz = T.copy(); Tz[1] = 0
+    _expect_input_error(x, tg, Tz, U, "logit length")
+    # one symbol per frame with U > T - 1: the reference returns uninitialised memory
+    T2 = np.array([3, 5], np.int32); U2 = np.array([3, 2], np.int32)
+    x2 = np.zeros((int(splits(T2, U2)[-1]), 5), np.float32)
+    _expect_input_error(x2, np.ones((2, 3), np.int32), T2, U2, "one_sym_per_frame", modified=True)
+
+
+def test_status_word_without_the_blocking_check(monkeypatch):
+    monkeypatch.setenv("OT_CHECKS", "0")
+    x, tg, T, U = random_batch(62, 2, (4, 6), (2, 3), 5)
+    bad = tg.copy(); bad[1, 0] = 99
+    dx, dt, dT, dU = to_dev(x, bad, T, U)
+    call = _Call(dx, dt, dT, dU, 0, False, False)
+    call.forward()  # no exception: the status stays on the device
+    code, index = ctypes.c_int32(), ctypes.c_int32()
+    rc = call.lib.ot_b200_read_input_status(call.workspace.data_ptr(), int(call.layout.total_bytes),
+                                            call.n, call.rows, call.flags, ctypes.byref(code),
+                                            ctypes.byref(index), None)
+    assert rc == _lib.OK and code.value == 4 and index.value == 1
+
+
+# ---------------------------------------------------------------------------
+# 6. benchmark-sized inputs: properties that need no full-size oracle
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["cfg2", "cfg3", "cfg4"])
+def test_full_size_configs(name):
+    w = synthetic.CONFIGS[name]
+    T, U, tg = synthetic.make_lengths(w)
+    x = synthetic.make_logits(w, T, U, device=DEV)
+    dT, dU, dt = T.to(DEV), U.to(DEV), tg.to(DEV)
+    st = ot.stage_outputs(x, dt, dT, dU, 0, w.from_log_softmax, w.one_sym_per_frame)
+    sa, sb = st["scores"].double(), st["scores_beta"].double()
+    assert torch.isfinite(sa).all()
+    assert ((sa - sb).abs() / sa.abs()).max().item() <= 1e-5  # the check of cpu.cc:795-797
+    # two utterances against the oracle, on their own rows
+    sp = splits(T.numpy(), U.numpy())
+    leaf = x.clone().requires_grad_(True)
+    scores, grad = ot.compute_transducer_loss(leaf, dt, dT, dU, 0, w.from_log_softmax, w.one_sym_per_frame)
+    if not w.from_log_softmax:
+        # d loss / d logits sums to zero over the vocabulary, up to the rounding
+        # of beta at the magnitude of the log-likelihood (one ulp there is 2.4e-4)
+        assert grad.sum(dim=1).abs().max().item() <= 1e-3
+    for b in (0, w.n - 1):
+        xb = x[sp[b]:sp[b + 1]].cpu().numpy()
+        ref = O.oracle_loss(xb, tg[b:b + 1, :int(U[b])].numpy(), T[b:b + 1].numpy(), U[b:b + 1].numpy(), 0,
+                            w.from_log_softmax, w.one_sym_per_frame)
+        assert abs(scores[b].item() - ref["scores"][0]) <= 1e-5 * abs(ref["scores"][0])
+        gb = grad[sp[b]:sp[b + 1]].cpu().numpy()
+        assert np.max(np.abs(gb - ref["grad"])) <= max(1e-5, fp32_grad_floor(ref["alpha"], ref["beta"]))
+
+
+def test_offsets_beyond_2_to_the_31_elements():
+    """sum T*(U+1)*V > 2^31: the reference's kernels index with 32-bit offsets
+    (kernels.cu:49) and cannot address this batch.  The LAST utterance is
+    compared with the oracle run on its rows alone."""
+    n, t, u, v = 12, 1000, 199, 1024
+    T = np.full(n, t, np.int32); U = np.full(n, u, np.int32)
+    T[-1], U[-1] = 611, 143
+    rows = int(splits(T, U)[-1])
+    assert rows * v > 2 ** 31
+    g = torch.Generator(device=DEV).manual_seed(5)
+    x = torch.randn(rows, v, generator=g, device=DEV)
+    tg = torch.randint(1, v, (n, int(U.max())), dtype=torch.int32)
+    dT, dU, dt = torch.from_numpy(T).to(DEV), torch.from_numpy(U).to(DEV), tg.to(DEV)
+    sp = splits(T, U)
+    xb = x[sp[-2]:].cpu().numpy()
+    x.requires_grad_(True)
+    scores, grad = ot.compute_transducer_loss(x, dt, dT, dU, 0, False, False)
+    ref = O.oracle_loss(xb, tg[-1:, :U[-1]].numpy(), T[-1:], U[-1:], 0)
+    assert abs(scores[-1].item() - ref["scores"][0]) <= 1e-5 * abs(ref["scores"][0])
+    gb = grad[sp[-2]:].cpu().numpy()
+    assert np.max(np.abs(gb - ref["grad"])) <= max(1e-5, fp32_grad_floor(ref["alpha"], ref["beta"]))
