@@ -230,6 +230,10 @@ def run_ours(args, w):
     # ----- the batch (global), and this rank's shard of it
     n_global = w.n * world if args.scaling == "weak" else w.n
     T, U, tg = synthetic.make_lengths(w, n=n_global)
+    if args.utts:  # a smaller case of the same workload, for profiler captures
+        n_global = min(args.utts, n_global)
+        T, U = T[:n_global].contiguous(), U[:n_global].contiguous()
+        tg = tg[:n_global, :int(U.max())].contiguous()
     if world > 1:
         shard = sharding.shard_batch(T, U, tg, w.v, world, rank)
         T, U, tg = shard.T, shard.U, shard.targets
@@ -311,7 +315,7 @@ def run_ours(args, w):
     host.copy_(pristine)
     dev_buf = torch.empty_like(pristine)
     hT, hU, htg = T.pin_memory(), U.pin_memory(), tg.pin_memory()
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))
 
     def e2e_step():
         dev_buf.copy_(host, non_blocking=True)
@@ -328,15 +332,17 @@ def run_ours(args, w):
         loss.backward()
         return float(loss.item())  # device-to-host read of the result
 
-    e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
+    e2e_ms = float("nan")
+    if e2e_steps:
         e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
     # ----- max over ranks, whole-job totals
     stats = torch.tensor([elapsed_ms, e2e_ms, fwd_ms, bwd_ms], dtype=torch.float64, device=dev)
@@ -416,6 +422,9 @@ def main():
     ap.add_argument("--cpu-utts", type=int, default=8,
                     help="utterances of the CPU-baseline sample of our arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer measurement")
+    ap.add_argument("--utts", type=int, default=0,
+                    help="use only the first UTTS utterances (small case for profiler captures)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

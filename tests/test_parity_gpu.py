@@ -359,3 +359,23 @@ def test_offsets_beyond_2_to_the_31_elements():
     assert abs(scores[-1].item() - ref["scores"][0]) <= 1e-5 * abs(ref["scores"][0])
     gb = grad[sp[-2]:].cpu().numpy()
     assert np.max(np.abs(gb - ref["grad"])) <= max(1e-5, fp32_grad_floor(ref["alpha"], ref["beta"]))
+
+
+# ---------------------------------------------------------------------------
+# 7. the sharded entry point on one rank (multi-rank logic: tests/test_sharding.py)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+def test_sharded_loss_on_one_rank_equals_plain_loss(reduction):
+    from optimized_transducer_b200 import sharding
+    x, tg, T, U = random_batch(71, 3, (10, 20), (3, 8), 40)
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    a_leaf = dx.clone().requires_grad_(True)
+    b_leaf = dx.clone().requires_grad_(True)
+    a = ot.transducer_loss(a_leaf * 1.0, dt, dT, dU, 0, False, reduction=reduction)
+    b = sharding.sharded_transducer_loss(b_leaf * 1.0, dt, dT, dU, 0, False, reduction=reduction,
+                                         overlap=True)
+    (a * 2).backward()
+    (b * 2).backward()
+    sharding.wait_loss(b)
+    assert torch.allclose(a, b, rtol=1e-6)
+    assert torch.allclose(a_leaf.grad, b_leaf.grad, rtol=0, atol=1e-7)

@@ -1,0 +1,131 @@
+"""Batch sharding across ranks: partitioning, per-rank views of a batch, and the
+scalar all-reduce, the latter with two ``gloo`` ranks on the CPU.  The local
+loss of each rank comes from the CPU oracle here (the CUDA kernels need a GPU);
+what is tested is everything around them."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from optimized_transducer_b200 import sharding, synthetic
+from oracle import oracle as O
+
+
+def test_contiguous_partition_is_optimal_on_small_inputs():
+    import itertools
+    rng = np.random.default_rng(0)
+    for _ in range(30):
+        n, world = int(rng.integers(1, 9)), int(rng.integers(1, 5))
+        costs = [int(c) for c in rng.integers(1, 100, n)]
+        bounds = sharding.partition_contiguous(costs, world)
+        assert len(bounds) == world and bounds[0][0] == 0
+        assert all(bounds[i][1] == bounds[i + 1][0] for i in range(world - 1))
+        assert max(b for _, b in bounds) == n
+        got = max(sum(costs[a:b]) for a, b in bounds)
+        best = min(max(sum(costs[a:b]) for a, b in zip((0,) + cuts, cuts + (n,)))
+                   for k in range(min(world, n))
+                   for cuts in itertools.combinations(range(1, n), k)) if n > 1 else costs[0]
+        assert got == best
+        if n >= world:
+            assert all(b > a for a, b in bounds)
+
+
+def test_lpt_covers_every_utterance_once_and_balances():
+    w = synthetic.CONFIGS["cfg5"]
+    T, U, _ = synthetic.make_lengths(w)
+    costs = sharding.utterance_costs(T, U, w.v)
+    parts = sharding.partition_lpt(costs, 8)
+    assert sorted(b for p in parts for b in p) == list(range(w.n))
+    assert sharding.imbalance(costs, parts) < 1.05
+    cont = [list(range(a, b)) for a, b in sharding.partition_contiguous(costs, 8)]
+    assert sharding.imbalance(costs, cont) < 1.25
+
+
+@pytest.mark.parametrize("strategy", ["contiguous", "lpt", "auto"])
+def test_shards_tile_the_batch(strategy):
+    w = synthetic.CONFIGS["cfg2"]
+    T, U, tg = synthetic.make_lengths(w)
+    rows = synthetic.num_rows(T, U)
+    packed = torch.arange(rows, dtype=torch.float32).unsqueeze(1).repeat(1, 2)
+    seen = torch.zeros(rows, dtype=torch.int32)
+    owners = []
+    for rank in range(4):
+        s = sharding.shard_batch(T, U, tg, w.v, 4, rank, strategy)
+        owners += s.indices
+        assert s.targets.shape == (len(s.indices), int(s.U.max()))  # re-padded to the local max U
+        assert torch.equal(s.T, T[s.indices]) and torch.equal(s.U, U[s.indices])
+        for local, b in enumerate(s.indices):
+            assert torch.equal(s.targets[local, :int(U[b])], tg[b, :int(U[b])])
+        local_rows = sharding.slice_rows(packed, s)
+        assert local_rows.shape[0] == synthetic.num_rows(s.T, s.U)
+        seen[local_rows[:, 0].long()] += 1
+        if s.contiguous:
+            assert local_rows.data_ptr() == packed[s.row_ranges[0][0]:].data_ptr()  # a view
+    assert sorted(owners) == list(range(w.n)) and bool((seen == 1).all())
+
+
+def test_more_ranks_than_utterances():
+    T = torch.tensor([5, 7], dtype=torch.int32)
+    U = torch.tensor([2, 3], dtype=torch.int32)
+    tg = torch.ones(2, 3, dtype=torch.int32)
+    shards = [sharding.shard_batch(T, U, tg, 10, 4, r) for r in range(4)]
+    assert [len(s.indices) for s in shards] == [1, 1, 0, 0]
+    assert shards[3].targets.shape == (0, 0) and shards[3].cost == 0
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        w = synthetic.CONFIGS["cfg1"]
+        T, U, tg = synthetic.make_lengths(w)
+        x = synthetic.make_logits(w, T, U).double()
+        shard = sharding.shard_batch(T, U, tg, w.v, world, rank)
+        local_x = sharding.slice_rows(x, shard)
+        out = O.oracle_loss(local_x.numpy(), shard.targets.numpy(), shard.T.numpy(), shard.U.numpy(), 0)
+        local = torch.tensor(-out["scores"].sum(), dtype=torch.float64)
+        total, event = sharding.all_reduce_sum(local, overlap=True)  # CPU: no overlap, no event
+        assert event is None
+        q.put((rank, float(total), shard.indices))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_loss_equals_single_rank_loss():
+    """world_size 2 over gloo: the all-reduced sum of the shard losses is the
+    loss of the whole batch."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    w = synthetic.CONFIGS["cfg1"]
+    T, U, tg = synthetic.make_lengths(w)
+    x = synthetic.make_logits(w, T, U).double()
+    whole = -O.oracle_loss(x.numpy(), tg.numpy(), T.numpy(), U.numpy(), 0)["scores"].sum()
+    for rank, total, _ in got:
+        assert abs(total - whole) <= 1e-9 * abs(whole)
+    assert sorted(b for _, _, ix in got for b in ix) == list(range(w.n))
+
+
+def test_single_process_all_reduce_is_identity():
+    x = torch.tensor(3.5)
+    y, ev = sharding.all_reduce_sum(x)
+    assert ev is None and float(y) == 3.5 and y.data_ptr() != x.data_ptr()
