@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define OT_B200_ABI_VERSION 1
+#define OT_B200_ABI_VERSION 2
 
 typedef enum ot_b200_status {
   OT_B200_OK = 0,
@@ -68,17 +68,27 @@ typedef enum ot_b200_input_error {
 
 /* Byte offsets of the intermediate arrays inside the workspace, for callers
  * (and tests) that want the stage outputs.  Element type is float, or double
- * with OT_B200_FP64.  `den` is unused with OT_B200_FROM_LOG_SOFTMAX. */
+ * with OT_B200_FP64.  `den` is unused with OT_B200_FROM_LOG_SOFTMAX.
+ *
+ * den is indexed by packed row.  lp, alpha and beta are indexed by CELL:
+ *   cell(b,t,u) = cell_split[b] + (t+u)*(U_b+1) + u     standard transducer
+ *   cell(b,t,u) = cell_split[b] + t*(U_b+1) + u         OT_B200_ONE_SYM_PER_FRAME
+ * (the standard recursion advances along anti-diagonals t+u, and storing the
+ * cells in that order makes every access of the wavefront coalesced).  Entries
+ * that correspond to no lattice cell, and alpha/beta outside the band of the
+ * one-symbol-per-frame recursion, are undefined. */
 typedef struct ot_b200_workspace_layout {
   uint64_t total_bytes;
   uint64_t status_off;      /* int32[16]: [0] ot_b200_input_error, [1] utterance index */
-  uint64_t split_off;       /* int64[N+1]: first row of each utterance               */
+  uint64_t split_off;       /* int64[N+1]: first packed row of each utterance        */
+  uint64_t cell_split_off;  /* int64[N+1]: first cell of each utterance              */
   uint64_t den_off;         /* real[rows]: row-wise logsumexp          (cuda.cu:427)  */
-  uint64_t lp_off;          /* real[rows][2]: blank / symbol log-prob  (kernels.cu:30-88) */
-  uint64_t alpha_off;       /* real[rows]                              (kernels.cu:200-313) */
-  uint64_t beta_off;        /* real[rows]                              (kernels.cu:415-519) */
+  uint64_t lp_off;          /* real[cells][2]: blank / symbol log-prob (kernels.cu:30-88) */
+  uint64_t alpha_off;       /* real[cells]                             (kernels.cu:200-313) */
+  uint64_t beta_off;        /* real[cells]                             (kernels.cu:415-519) */
   uint64_t coef_off;        /* per-row gradient coefficients (library-private format) */
   uint64_t scores_beta_off; /* real[N]: beta(0,0), the score seen from the beta side  */
+  uint64_t max_cells;       /* capacity of the per-cell arrays                        */
 } ot_b200_workspace_layout;
 
 int ot_b200_abi_version(void);
@@ -86,23 +96,26 @@ int ot_b200_abi_version(void);
 /* Message for the calling thread's most recent non-OK return ("" if none). */
 const char *ot_b200_last_error(void);
 
-/* Size and layout of the workspace for a batch of N utterances and `rows`
- * packed rows.  Replaces the temporaries the reference allocates per call
- * (row_splits/row_ids cuda.cu:411-415, denominator :427, log_probs :85,
- * alpha/beta :173,249).  The workspace must be 256-byte aligned. */
-int ot_b200_workspace_layout_query(int32_t N, int64_t rows, uint32_t flags,
-                                   ot_b200_workspace_layout *out);
-int ot_b200_workspace_bytes(int32_t N, int64_t rows, uint32_t flags,
+/* Size and layout of the workspace for a batch of N utterances, `rows` packed
+ * rows and targets of width max_u.  Replaces the temporaries the reference
+ * allocates per call (row_splits/row_ids cuda.cu:411-415, denominator :427,
+ * log_probs :85, alpha/beta :173,249).  The workspace must be 256-byte aligned. */
+int ot_b200_workspace_layout_query(int32_t N, int64_t rows, int32_t max_u,
+                                   uint32_t flags, ot_b200_workspace_layout *out);
+int ot_b200_workspace_bytes(int32_t N, int64_t rows, int32_t max_u, uint32_t flags,
                             uint64_t *bytes_out);
 
 /* Forward half: input check, row-wise logsumexp + blank/target gather, alpha
- * and beta recursions, per-row gradient coefficients.
+ * and beta recursions, per-row gradient coefficients, reduced loss.
  *   replaces: the checks of ot::ComputeTransducerLoss (transducer-loss.cc:49-66),
  *   RowSplitsToRowIds (cuda.cu:40-59), ComputeLogProbs[ForLogSoftmax]
- *   (cuda.cu:71-136), ComputeAlpha (cuda.cu:162-213), ComputeBeta (cuda.cu:237-287).
+ *   (cuda.cu:71-136), ComputeAlpha (cuda.cu:162-213), ComputeBeta (cuda.cu:237-287)
+ *   and the reduction of the Python layer (transducer_loss.py:145-152).
  * d_logits        (rows, V) real, read only
  * d_targets       (N, max_u) int32     d_logit_lengths, d_target_lengths  (N) int32
  * d_scores        (N) real out: log P(y_b|x_b) = alpha(T-1,U) + lp_blank(T-1,U)
+ * d_loss          NULL, or one real out: loss_scale * -(sum_b scores[b])
+ *                 (loss_scale = 1 for reduction "sum", 1/N for "mean")
  * With OT_B200_CHECK_INPUTS a failed input check returns OT_B200_ERR_INPUT
  * (the streaming kernels then do not touch the inputs); without it the status
  * stays in the workspace and ot_b200_read_input_status() can fetch it. */
@@ -111,7 +124,7 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
                     const int32_t *d_target_lengths, int32_t N, int64_t rows,
                     int32_t V, int32_t max_u, int32_t blank, uint32_t flags,
                     void *d_workspace, uint64_t workspace_bytes, void *d_scores,
-                    void *stream);
+                    void *d_loss, double loss_scale, void *stream);
 
 /* Backward half: one streaming pass that writes
  *     grad = scale * d loss / d logits
@@ -124,10 +137,11 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
  * d_grad     (rows, V) real out; MAY EQUAL d_logits (the reference's in-place
  *            mode, cuda.cu:449).  With OT_B200_FROM_LOG_SOFTMAX d_logits is not
  *            read and d_grad must be a separate buffer (cuda.cu:444).
+ * N, rows, max_u, flags  as given to ot_b200_forward (they fix the layout)
  * scale = scale_host * (d_scale ? *d_scale : 1); d_scale is a device scalar of
  *            the real type (e.g. the upstream gradient of the loss). */
 int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows,
-                     int32_t V, int32_t blank, uint32_t flags,
+                     int32_t V, int32_t max_u, int32_t blank, uint32_t flags,
                      const void *d_workspace, uint64_t workspace_bytes,
                      const void *d_scale, double scale_host, void *stream);
 
@@ -147,9 +161,7 @@ int ot_b200_compute_transducer_loss(const void *d_logits, void *d_grad,
 /* Copies the input-check status out of the workspace (synchronises `stream`).
  * code_out receives an ot_b200_input_error, index_out the offending utterance. */
 int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes,
-                              int32_t N, int64_t rows, uint32_t flags,
-                              int32_t *code_out, int32_t *index_out,
-                              void *stream);
+                              int32_t *code_out, int32_t *index_out, void *stream);
 
 #ifdef __cplusplus
 }

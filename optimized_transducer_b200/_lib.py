@@ -9,7 +9,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libot_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # ot_b200_status
 OK, ERR_ARGUMENT, ERR_CUDA, ERR_WORKSPACE, ERR_INPUT = range(5)
@@ -36,8 +36,8 @@ EXPORTS = (
 
 class WorkspaceLayout(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint64) for n in (
-        "total_bytes", "status_off", "split_off", "den_off", "lp_off",
-        "alpha_off", "beta_off", "coef_off", "scores_beta_off")]
+        "total_bytes", "status_off", "split_off", "cell_split_off", "den_off", "lp_off",
+        "alpha_off", "beta_off", "coef_off", "scores_beta_off", "max_cells")]
 
 
 _lib = None
@@ -61,17 +61,18 @@ def load():
     lib.ot_b200_last_error.restype = ctypes.c_char_p
     lib.ot_b200_last_error.argtypes = []
     lib.ot_b200_workspace_layout_query.restype = ctypes.c_int
-    lib.ot_b200_workspace_layout_query.argtypes = [i32, i64, u32, ctypes.POINTER(WorkspaceLayout)]
+    lib.ot_b200_workspace_layout_query.argtypes = [i32, i64, i32, u32, ctypes.POINTER(WorkspaceLayout)]
     lib.ot_b200_workspace_bytes.restype = ctypes.c_int
-    lib.ot_b200_workspace_bytes.argtypes = [i32, i64, u32, ctypes.POINTER(u64)]
+    lib.ot_b200_workspace_bytes.argtypes = [i32, i64, i32, u32, ctypes.POINTER(u64)]
     lib.ot_b200_forward.restype = ctypes.c_int
-    lib.ot_b200_forward.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, vp]
+    lib.ot_b200_forward.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, vp,
+                                    ctypes.c_double, vp]
     lib.ot_b200_backward.restype = ctypes.c_int
-    lib.ot_b200_backward.argtypes = [vp, vp, i32, i64, i32, i32, u32, vp, u64, vp, ctypes.c_double, vp]
+    lib.ot_b200_backward.argtypes = [vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, ctypes.c_double, vp]
     lib.ot_b200_compute_transducer_loss.restype = ctypes.c_int
     lib.ot_b200_compute_transducer_loss.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, vp]
     lib.ot_b200_read_input_status.restype = ctypes.c_int
-    lib.ot_b200_read_input_status.argtypes = [vp, u64, i32, i64, u32, ctypes.POINTER(i32), ctypes.POINTER(i32), vp]
+    lib.ot_b200_read_input_status.argtypes = [vp, u64, ctypes.POINTER(i32), ctypes.POINTER(i32), vp]
     if lib.ot_b200_abi_version() != ABI_VERSION:
         raise ImportError("libot_b200.so was built from a different ABI version; rebuild it")
     _lib = lib
@@ -92,7 +93,8 @@ def check(rc):
     raise RuntimeError(f"libot_b200 returned status {rc}: {msg}")
 
 
-def workspace_layout(n, rows, flags):
+def workspace_layout(n, rows, max_u, flags):
     out = WorkspaceLayout()
-    check(load().ot_b200_workspace_layout_query(int(n), int(rows), int(flags), ctypes.byref(out)))
+    check(load().ot_b200_workspace_layout_query(int(n), int(rows), int(max_u), int(flags),
+                                                ctypes.byref(out)))
     return out

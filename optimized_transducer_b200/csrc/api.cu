@@ -69,17 +69,25 @@ int get_slot(StatusSlot **out) {
   return OT_B200_OK;
 }
 
-int check_common(int32_t N, int64_t rows, int32_t V, int32_t blank, uint32_t flags,
-                 const void *ws, uint64_t ws_bytes, Layout *lay) {
+constexpr uint32_t kKnownFlags = OT_B200_FROM_LOG_SOFTMAX | OT_B200_ONE_SYM_PER_FRAME |
+                                 OT_B200_FP64 | OT_B200_CHECK_INPUTS | OT_B200_FAST_MATH;
+
+int check_sizes(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   if (N <= 0) return fail(OT_B200_ERR_ARGUMENT, "N must be positive, got %d", N);
   if (rows <= 0) return fail(OT_B200_ERR_ARGUMENT, "rows must be positive, got %lld", (long long)rows);
+  if (max_u < 0) return fail(OT_B200_ERR_ARGUMENT, "max_u must not be negative, got %d", max_u);
+  if (flags & ~kKnownFlags) return fail(OT_B200_ERR_ARGUMENT, "unknown bits in flags: 0x%x", flags);
+  return OT_B200_OK;
+}
+
+int check_common(int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blank,
+                 uint32_t flags, const void *ws, uint64_t ws_bytes, Layout *lay) {
+  int rc = check_sizes(N, rows, max_u, flags);
+  if (rc) return rc;
   if (V <= 0) return fail(OT_B200_ERR_ARGUMENT, "V must be positive, got %d", V);
   if (blank < 0 || blank >= V)
     return fail(OT_B200_ERR_ARGUMENT, "blank vs logits.size(1) is %d vs %d. Expect 0 <= blank < logits.size(1)", blank, V);
-  if (flags & ~(OT_B200_FROM_LOG_SOFTMAX | OT_B200_ONE_SYM_PER_FRAME | OT_B200_FP64 |
-                OT_B200_CHECK_INPUTS | OT_B200_FAST_MATH))
-    return fail(OT_B200_ERR_ARGUMENT, "unknown bits in flags: 0x%x", flags);
-  *lay = make_layout(N, rows, flags);
+  *lay = make_layout(N, rows, max_u, flags);
   if (!ws) return fail(OT_B200_ERR_WORKSPACE, "workspace is NULL");
   if (reinterpret_cast<uintptr_t>(ws) % 256 != 0)
     return fail(OT_B200_ERR_WORKSPACE, "workspace must be 256-byte aligned");
@@ -104,19 +112,28 @@ int sm_count() {
   return cached[dev];
 }
 
-Layout make_layout(int32_t N, int64_t rows, uint32_t flags) {
+Layout make_layout(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   const uint64_t es = (flags & OT_B200_FP64) ? 8 : 4;
   const bool mode_b = flags & OT_B200_FROM_LOG_SOFTMAX;
+  const bool modified = flags & OT_B200_ONE_SYM_PER_FRAME;
   const uint64_t coef_rec = mode_b ? ((flags & OT_B200_FP64) ? sizeof(CoefB<double>) : sizeof(CoefB<float>))
                                    : ((flags & OT_B200_FP64) ? sizeof(CoefA<double>) : sizeof(CoefA<float>));
+  // Cells: the host knows rows, N and max_u but not the individual lengths.
+  // Standard (diagonal-major) blocks hold (T+U)*(U+1) entries, i.e. the rows of
+  // the utterance plus U*(U+1) <= max_u*(max_u+1); every block is rounded up by
+  // at most one entry.
   Layout l;
+  l.max_cells = rows + (int64_t)N +
+                (modified ? 0 : (int64_t)N * (int64_t)max_u * ((int64_t)max_u + 1));
+  const uint64_t cells = (uint64_t)l.max_cells;
   uint64_t off = 0;
   l.status = off;       off = align256(off + kStatusWords * sizeof(int32_t));
   l.split = off;        off = align256(off + (uint64_t)(N + 1) * sizeof(int64_t));
+  l.cell_split = off;   off = align256(off + (uint64_t)(N + 1) * sizeof(int64_t));
   l.den = off;          off = align256(off + (mode_b ? 0 : (uint64_t)rows * es));
-  l.lp = off;           off = align256(off + (uint64_t)rows * 2 * es);
-  l.alpha = off;        off = align256(off + (uint64_t)rows * es);
-  l.beta = off;         off = align256(off + (uint64_t)rows * es);
+  l.lp = off;           off = align256(off + cells * 2 * es);
+  l.alpha = off;        off = align256(off + cells * es);
+  l.beta = off;         off = align256(off + cells * es);
   l.coef = off;         off = align256(off + (uint64_t)rows * coef_rec);
   l.scores_beta = off;  off = align256(off + (uint64_t)N * es);
   l.total = off;
@@ -133,27 +150,32 @@ int ot_b200_abi_version(void) { return OT_B200_ABI_VERSION; }
 
 const char *ot_b200_last_error(void) { return g_err; }
 
-int ot_b200_workspace_layout_query(int32_t N, int64_t rows, uint32_t flags,
+int ot_b200_workspace_layout_query(int32_t N, int64_t rows, int32_t max_u, uint32_t flags,
                                    ot_b200_workspace_layout *out) {
   if (!out) return fail(OT_B200_ERR_ARGUMENT, "out is NULL");
-  if (N <= 0 || rows <= 0) return fail(OT_B200_ERR_ARGUMENT, "N and rows must be positive");
-  const Layout l = make_layout(N, rows, flags);
+  int rc = check_sizes(N, rows, max_u, flags);
+  if (rc) return rc;
+  const Layout l = make_layout(N, rows, max_u, flags);
   out->total_bytes = l.total;
   out->status_off = l.status;
   out->split_off = l.split;
+  out->cell_split_off = l.cell_split;
   out->den_off = l.den;
   out->lp_off = l.lp;
   out->alpha_off = l.alpha;
   out->beta_off = l.beta;
   out->coef_off = l.coef;
   out->scores_beta_off = l.scores_beta;
+  out->max_cells = (uint64_t)l.max_cells;
   return OT_B200_OK;
 }
 
-int ot_b200_workspace_bytes(int32_t N, int64_t rows, uint32_t flags, uint64_t *bytes_out) {
+int ot_b200_workspace_bytes(int32_t N, int64_t rows, int32_t max_u, uint32_t flags,
+                            uint64_t *bytes_out) {
   if (!bytes_out) return fail(OT_B200_ERR_ARGUMENT, "bytes_out is NULL");
-  if (N <= 0 || rows <= 0) return fail(OT_B200_ERR_ARGUMENT, "N and rows must be positive");
-  *bytes_out = make_layout(N, rows, flags).total;
+  int rc = check_sizes(N, rows, max_u, flags);
+  if (rc) return rc;
+  *bytes_out = make_layout(N, rows, max_u, flags).total;
   return OT_B200_OK;
 }
 
@@ -161,14 +183,13 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
                     const int32_t *d_logit_lengths, const int32_t *d_target_lengths,
                     int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blank,
                     uint32_t flags, void *d_workspace, uint64_t workspace_bytes,
-                    void *d_scores, void *stream) {
+                    void *d_scores, void *d_loss, double loss_scale, void *stream) {
   Problem p;
-  int rc = check_common(N, rows, V, blank, flags, d_workspace, workspace_bytes, &p.lay);
+  int rc = check_common(N, rows, V, max_u, blank, flags, d_workspace, workspace_bytes, &p.lay);
   if (rc) return rc;
   if (!d_logits || !d_logit_lengths || !d_target_lengths || !d_scores)
     return fail(OT_B200_ERR_ARGUMENT, "a required device pointer is NULL");
-  if (max_u < 0 || (max_u > 0 && !d_targets))
-    return fail(OT_B200_ERR_ARGUMENT, "targets missing or max_u negative");
+  if (max_u > 0 && !d_targets) return fail(OT_B200_ERR_ARGUMENT, "targets pointer is NULL");
   const uint64_t es = (flags & OT_B200_FP64) ? 8 : 4;
   if (reinterpret_cast<uintptr_t>(d_logits) % es != 0)
     return fail(OT_B200_ERR_ARGUMENT, "logits pointer is not aligned to its element size");
@@ -203,7 +224,7 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
   if (e != cudaSuccess) return fail_cuda(e, "launch logprob");
   e = launch_lattice(p, d_scores, s);
   if (e != cudaSuccess) return fail_cuda(e, "launch lattice");
-  e = launch_coef(p, s);
+  e = launch_coef(p, d_scores, d_loss, loss_scale, s);
   if (e != cudaSuccess) return fail_cuda(e, "launch coef");
   if (slot) {
     e = cudaEventSynchronize(slot->ev);
@@ -217,11 +238,11 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
 }
 
 int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows,
-                     int32_t V, int32_t blank, uint32_t flags, const void *d_workspace,
-                     uint64_t workspace_bytes, const void *d_scale, double scale_host,
-                     void *stream) {
+                     int32_t V, int32_t max_u, int32_t blank, uint32_t flags,
+                     const void *d_workspace, uint64_t workspace_bytes,
+                     const void *d_scale, double scale_host, void *stream) {
   Problem p;
-  int rc = check_common(N, rows, V, blank, flags, d_workspace, workspace_bytes, &p.lay);
+  int rc = check_common(N, rows, V, max_u, blank, flags, d_workspace, workspace_bytes, &p.lay);
   if (rc) return rc;
   if (!d_grad) return fail(OT_B200_ERR_ARGUMENT, "grad pointer is NULL");
   const bool mode_b = flags & OT_B200_FROM_LOG_SOFTMAX;
@@ -229,7 +250,7 @@ int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows
   if (mode_b && d_grad == d_logits)
     return fail(OT_B200_ERR_ARGUMENT, "with OT_B200_FROM_LOG_SOFTMAX the gradient needs its own buffer");
   p.logits = d_logits; p.targets = nullptr; p.T = nullptr; p.U = nullptr;
-  p.N = N; p.rows = rows; p.V = V; p.max_u = 0; p.blank = blank; p.flags = flags;
+  p.N = N; p.rows = rows; p.V = V; p.max_u = max_u; p.blank = blank; p.flags = flags;
   p.ws = static_cast<char *>(const_cast<void *>(d_workspace));
   cudaError_t e = launch_gradient(p, d_grad, d_scale, scale_host, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail_cuda(e, "launch gradient");
@@ -244,23 +265,22 @@ int ot_b200_compute_transducer_loss(const void *d_logits, void *d_grad,
                                     uint32_t flags, void *d_workspace,
                                     uint64_t workspace_bytes, void *d_scores, void *stream) {
   int rc = ot_b200_forward(d_logits, d_targets, d_logit_lengths, d_target_lengths, N, rows,
-                           V, max_u, blank, flags, d_workspace, workspace_bytes, d_scores, stream);
+                           V, max_u, blank, flags, d_workspace, workspace_bytes, d_scores,
+                           nullptr, 1.0, stream);
   if (rc || !d_grad) return rc;
-  return ot_b200_backward(d_logits, d_grad, N, rows, V, blank, flags, d_workspace,
+  return ot_b200_backward(d_logits, d_grad, N, rows, V, max_u, blank, flags, d_workspace,
                           workspace_bytes, nullptr, 1.0, stream);
 }
 
-int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes, int32_t N,
-                              int64_t rows, uint32_t flags, int32_t *code_out,
-                              int32_t *index_out, void *stream) {
+int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes,
+                              int32_t *code_out, int32_t *index_out, void *stream) {
   if (!d_workspace || !code_out) return fail(OT_B200_ERR_ARGUMENT, "NULL argument");
-  if (N <= 0 || rows <= 0) return fail(OT_B200_ERR_ARGUMENT, "N and rows must be positive");
-  const Layout l = make_layout(N, rows, flags);
-  if (workspace_bytes < l.total) return fail(OT_B200_ERR_WORKSPACE, "workspace too small");
+  if (workspace_bytes < kStatusWords * sizeof(int32_t))
+    return fail(OT_B200_ERR_WORKSPACE, "workspace too small");
   int32_t host[2] = {0, 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaError_t e = cudaMemcpyAsync(host, static_cast<const char *>(d_workspace) + l.status,
-                                  sizeof(host), cudaMemcpyDeviceToHost, s);
+  // the status words are the first segment of every workspace
+  cudaError_t e = cudaMemcpyAsync(host, d_workspace, sizeof(host), cudaMemcpyDeviceToHost, s);
   if (e != cudaSuccess) return fail_cuda(e, "copy status");
   e = cudaStreamSynchronize(s);
   if (e != cudaSuccess) return fail_cuda(e, "synchronize");

@@ -30,12 +30,6 @@ namespace {
 
 constexpr int kThreads = 256;
 
-template <typename T, int VEC> struct VecOf;
-template <> struct VecOf<float, 4> { using type = float4; };
-template <> struct VecOf<float, 1> { using type = float; };
-template <> struct VecOf<double, 2> { using type = double2; };
-template <> struct VecOf<double, 1> { using type = double; };
-
 template <typename T>
 __device__ __forceinline__ CoefA<T> load_coef(const CoefA<T> *p) {
   // Every lane reads the same record: the loads are broadcasts.
@@ -99,9 +93,9 @@ gradient_kernel(const T *x, T *g, const CoefA<T> *__restrict__ coef,
 #pragma unroll
           for (int k = 0; k < VEC; ++k) {
             const T gv = e[k] + rec.c;
-            T val = r_exp(gv + rec.beta);
-            if (k == bsel) val -= r_exp(gv + rec.sub_blank);
-            else if (k == tsel) val -= r_exp(gv + rec.sub_sym);
+            T val = s_exp(gv + rec.beta);
+            if (k == bsel) val -= s_exp(gv + rec.sub_blank);
+            else if (k == tsel) val -= s_exp(gv + rec.sub_sym);
             e[k] = val * scale;
           }
           *reinterpret_cast<VT *>(pg + (int64_t)vi * VEC) = v[j];
@@ -146,16 +140,21 @@ gradient_logsoftmax_kernel(T *__restrict__ g, const CoefB<T> *__restrict__ coef,
   }
 }
 
-unsigned stream_grid(int64_t rows) {
+// Exactly one resident wave of `kernel` (never more warps than rows): a larger
+// grid-stride grid would run a partial second wave at the end.
+template <typename K>
+unsigned stream_grid(K kernel, int *per_sm, int64_t rows) {
+  if (*per_sm == 0) *per_sm = blocks_per_sm(kernel, kThreads);
   const int64_t want = (rows + (kThreads / kWarp) - 1) / (kThreads / kWarp);
-  const int64_t cap = (int64_t)sm_count() * 8;
+  const int64_t cap = (int64_t)sm_count() * *per_sm;
   return (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
 }
 
 template <typename T, int VEC, int CH>
 cudaError_t launch_grad_a(const Problem &p, void *grad, const void *d_scale,
                           double scale_host, cudaStream_t s) {
-  gradient_kernel<T, VEC, CH><<<stream_grid(p.rows), kThreads, 0, s>>>(
+  static int per_sm = 0;
+  gradient_kernel<T, VEC, CH><<<stream_grid(gradient_kernel<T, VEC, CH>, &per_sm, p.rows), kThreads, 0, s>>>(
       static_cast<const T *>(p.logits), static_cast<T *>(grad),
       reinterpret_cast<const CoefA<T> *>(p.ws + p.lay.coef),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V,
@@ -172,12 +171,13 @@ cudaError_t launch_gradient_t(const Problem &p, void *grad, const void *d_scale,
   if (p.flags & OT_B200_FROM_LOG_SOFTMAX) {
     const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
     const CoefB<T> *coef = reinterpret_cast<const CoefB<T> *>(p.ws + p.lay.coef);
+    static int per_sm_v = 0, per_sm_1 = 0;
     if (aligned)
-      gradient_logsoftmax_kernel<T, VEC><<<stream_grid(p.rows), kThreads, 0, s>>>(
+      gradient_logsoftmax_kernel<T, VEC><<<stream_grid(gradient_logsoftmax_kernel<T, VEC>, &per_sm_v, p.rows), kThreads, 0, s>>>(
           static_cast<T *>(grad), coef, status, p.rows, p.V, p.blank,
           static_cast<const T *>(d_scale), (T)scale_host);
     else
-      gradient_logsoftmax_kernel<T, 1><<<stream_grid(p.rows), kThreads, 0, s>>>(
+      gradient_logsoftmax_kernel<T, 1><<<stream_grid(gradient_logsoftmax_kernel<T, 1>, &per_sm_1, p.rows), kThreads, 0, s>>>(
           static_cast<T *>(grad), coef, status, p.rows, p.V, p.blank,
           static_cast<const T *>(d_scale), (T)scale_host);
     return cudaGetLastError();

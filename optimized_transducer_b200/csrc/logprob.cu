@@ -5,11 +5,14 @@
 // ComputeLogProbs (optimized_transducer/csrc/kernels.cu:30-60), and, for
 // log-softmax input, ComputeLogProbsForLogSoftmax (kernels.cu:62-88).
 //
-// One warp owns a row at a time.  The row is read once with 16-byte coalesced
-// loads (all loads of a chunk are issued before the first use), reduced with an
-// online (max, sum) pair per lane and merged across the warp with shuffles;
-// the two gathered entries are re-read from the lines just fetched.  HBM
-// traffic: V*sizeof(T) bytes read and 3*sizeof(T) bytes written per row.
+// The grid is exactly one resident wave (SMs x blocks that fit per SM); a warp
+// takes runs of kRun consecutive rows and walks (b, t, u) incrementally inside
+// a run, so the owning utterance is searched once per run, not once per row.
+// A row is read once with 16-byte coalesced loads, all issued before the first
+// use; the reduction costs a subtract, a multiply, one ex2 and one add per
+// element (exp(x - m) = 2^((x - m)*log2e)).  The two gathered entries are re-read
+// from the lines just fetched.  HBM traffic per row: V*sizeof(T) bytes read,
+// 3*sizeof(T) bytes written.
 #include "ot_common.cuh"
 
 namespace otb {
@@ -17,12 +20,27 @@ namespace otb {
 namespace {
 
 constexpr int kThreads = 256;
+// Rows a warp takes at a time.  Runs are dealt to the warps round-robin, so
+// the grid sweeps the buffer front to back (the rows read last are contiguous
+// at the end, where stage 3 starts) while the search for the owning utterance
+// is paid once per run.
+constexpr int kRun = 8;
 
-template <typename T, int VEC> struct VecOf;
-template <> struct VecOf<float, 4> { using type = float4; };
-template <> struct VecOf<float, 1> { using type = float; };
-template <> struct VecOf<double, 2> { using type = double2; };
-template <> struct VecOf<double, 1> { using type = double; };
+// sum_k exp(x_k - m) accumulated into s, for one lane's part of a chunk.
+template <int N>
+__device__ __forceinline__ float add_exps(const float (&x)[N], float m, float s) {
+  // (x - m) first: its rounding error is random per element, whereas folding
+  // m*log2e into an FFMA would shift every term of the row the same way.
+#pragma unroll
+  for (int k = 0; k < N; ++k) s += ex2_approx((x[k] - m) * kLog2e);
+  return s;
+}
+template <int N>
+__device__ __forceinline__ double add_exps(const double (&x)[N], double m, double s) {
+#pragma unroll
+  for (int k = 0; k < N; ++k) s += exp(x[k] - m);
+  return s;
+}
 
 // T: element type.  VEC: elements per load (16 bytes, or 1 element when the
 // row stride or the base pointer is not 16-byte aligned).  CH: loads per lane
@@ -31,87 +49,99 @@ template <typename T, int VEC, int CH, bool MODIFIED>
 __global__ void __launch_bounds__(kThreads)
 logprob_kernel(const T *__restrict__ logits, const int32_t *__restrict__ targets,
                const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
-               const int64_t *__restrict__ split,
+               const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
                const int32_t *__restrict__ status, int N, int64_t rows, int V,
                int max_u, int blank, T *__restrict__ den, T *__restrict__ lp) {
   if (status[kStatusCode] != 0) return;
   using VT = typename VecOf<T, VEC>::type;
   const int lane = threadIdx.x & 31;
-  const int64_t warp0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const int nvec = V / VEC;
   const T ninf = neg_inf<T>();
+  const int64_t nruns = (rows + kRun - 1) / kRun;
 
-  for (int64_t row = warp0; row < rows; row += nwarps) {
+  for (int64_t run = warp; run < nruns; run += nwarps) {
+  const int64_t r0 = run * kRun;
+  const int64_t r1 = (r0 + kRun < rows) ? r0 + kRun : rows;
+  // Position of the run's first row; afterwards (b, t, u) advance with the rows.
+  int b = find_utt(split, N, r0);
+  int Tn = __ldg(Tl + b), U = __ldg(Ul + b), U1 = U + 1;
+  int64_t next_split = __ldg(split + b + 1);
+  int64_t coff = __ldg(cell_split + b);
+  int t, u;
+  {
+    const int idx = (int)(r0 - __ldg(split + b));
+    t = idx / U1; u = idx - t * U1;
+  }
+
+  for (int64_t row = r0; row < r1; ++row) {
     const T *p = logits + row * (int64_t)V;
-    const int b = find_utt(split, N, row);
-    const int U = __ldg(Ul + b), U1 = U + 1;
-    const int idx = (int)(row - __ldg(split + b));
-    const int t = idx / U1, u = idx - t * U1;
+    bool skip = false;
     if (MODIFIED) {
       // Cells outside the band u <= t <= u + (T-1-U) are never used
-      // (optimized_transducer/csrc/cpu.cc:295): skip their rows entirely.
-      const int diff = __ldg(Tl + b) - 1 - U;
-      if (u > t || t - u > diff) continue;
+      // (optimized_transducer/csrc/cpu.cc:295): their rows are not read.
+      skip = (u > t) || (t - u > Tn - 1 - U);
     }
-    T m = ninf, s = 0;
-    for (int base = 0; base < nvec; base += kWarp * CH) {
-      T x[CH][VEC];
+    if (!skip) {
+      T m = ninf, s = 0;
+      for (int base = 0; base < nvec; base += kWarp * CH) {
+        T x[CH * VEC];
 #pragma unroll
-      for (int j = 0; j < CH; ++j) {
-        const int vi = base + j * kWarp + lane;
-        if (vi < nvec) {
-          const VT v = *reinterpret_cast<const VT *>(p + (int64_t)vi * VEC);
-          const T *e = reinterpret_cast<const T *>(&v);
+        for (int j = 0; j < CH; ++j) {
+          const int vi = base + j * kWarp + lane;
+          if (vi < nvec) {
+            const VT v = *reinterpret_cast<const VT *>(p + (int64_t)vi * VEC);
+            const T *e = reinterpret_cast<const T *>(&v);
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) x[j][k] = e[k];
-        } else {
+            for (int k = 0; k < VEC; ++k) x[j * VEC + k] = e[k];
+          } else {
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) x[j][k] = ninf;
+            for (int k = 0; k < VEC; ++k) x[j * VEC + k] = ninf;
+          }
         }
+        T cm = x[0];
+#pragma unroll
+        for (int k = 1; k < CH * VEC; ++k) cm = r_max(cm, x[k]);
+        cm = warp_max(cm);  // the running maximum is uniform across the warp
+        if (cm > m) { s *= s_exp(m - cm); m = cm; }  // first chunk: s is 0
+        // An infinite maximum needs no sum (see below); skipping it avoids inf - inf.
+        if (m - m == (T)0) s = add_exps(x, m, s);
       }
-      T cm = ninf;
-#pragma unroll
-      for (int j = 0; j < CH; ++j)
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) cm = r_max(cm, x[j][k]);
-      if (cm > m) { s *= r_exp(m - cm); m = cm; }  // m == -inf: s is 0, stays 0
-      if (m > ninf) {
-#pragma unroll
-        for (int j = 0; j < CH; ++j)
-#pragma unroll
-          for (int k = 0; k < VEC; ++k) s += r_exp(x[j][k] - m);
+      // ATen's logsumexp replaces an infinite maximum by 0 before subtracting,
+      // which makes the result that same infinity.
+      const T d = (m - m == (T)0) ? r_log(warp_sum(s)) + m : m;
+      // Gather: lane 0 fetches the blank entry, lane 1 the symbol entry.
+      T g = 0;
+      if (lane == 0) g = p[blank] - d;
+      if (lane == 1 && u < U) g = p[__ldg(targets + (int64_t)b * max_u + u)] - d;
+      const T g1 = __shfl_sync(kFull, g, 1);
+      if (lane == 0) {
+        den[row] = d;
+        T *q = lp + 2 * (coff + cell_pos<MODIFIED>(t, u, U1));
+        if constexpr (sizeof(T) == 4) *reinterpret_cast<float2 *>(q) = make_float2(g, g1);
+        else *reinterpret_cast<double2 *>(q) = make_double2(g, g1);
       }
     }
-    const T M = warp_max(m);
-    // Follows ATen's logsumexp: an infinite maximum is replaced by 0 before
-    // the subtraction, which makes the result that same infinity.
-    T d;
-    if (M - M == (T)0) {
-      const T part = (m > ninf) ? s * r_exp(m - M) : (T)0;
-      d = r_log(warp_sum(part)) + M;
-    } else {
-      d = M;
-    }
-    // Gather: lane 0 fetches the blank entry, lane 1 the symbol entry.
-    T g = 0;
-    if (lane == 0) g = p[blank] - d;
-    if (lane == 1 && u < U) g = p[__ldg(targets + (int64_t)b * max_u + u)] - d;
-    const T g1 = __shfl_sync(kFull, g, 1);
-    if (lane == 0) {
-      den[row] = d;
-      T *q = lp + 2 * row;
-      q[0] = g;
-      q[1] = g1;
+    // advance to the next row
+    if (++u == U1) { u = 0; ++t; }
+    if (row + 1 == next_split && row + 1 < rows) {
+      ++b;
+      Tn = __ldg(Tl + b); U = __ldg(Ul + b); U1 = U + 1;
+      next_split = __ldg(split + b + 1);
+      coff = __ldg(cell_split + b);
+      t = 0; u = 0;
     }
   }
+  }  // runs
 }
 
 // Log-softmax input: nothing to reduce, only the gather (thread per row).
-template <typename T>
+template <typename T, bool MODIFIED>
 __global__ void __launch_bounds__(kThreads)
 gather_kernel(const T *__restrict__ logp, const int32_t *__restrict__ targets,
               const int32_t *__restrict__ Ul, const int64_t *__restrict__ split,
+              const int64_t *__restrict__ cell_split,
               const int32_t *__restrict__ status, int N, int64_t rows, int V,
               int max_u, int blank, T *__restrict__ lp) {
   if (status[kStatusCode] != 0) return;
@@ -119,41 +149,53 @@ gather_kernel(const T *__restrict__ logp, const int32_t *__restrict__ targets,
   if (row >= rows) return;
   const int b = find_utt(split, N, row);
   const int U = __ldg(Ul + b), U1 = U + 1;
-  const int u = (int)((row - __ldg(split + b)) % U1);
+  const int idx = (int)(row - __ldg(split + b));
+  const int t = idx / U1, u = idx - t * U1;
   const T *p = logp + row * (int64_t)V;
-  lp[2 * row] = p[blank];
-  lp[2 * row + 1] = (u < U) ? p[__ldg(targets + (int64_t)b * max_u + u)] : (T)0;
+  T *q = lp + 2 * (__ldg(cell_split + b) + cell_pos<MODIFIED>(t, u, U1));
+  q[0] = p[blank];
+  q[1] = (u < U) ? p[__ldg(targets + (int64_t)b * max_u + u)] : (T)0;
+}
+
+template <typename T, int VEC, int CH, bool MODIFIED>
+cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
+  auto kernel = logprob_kernel<T, VEC, CH, MODIFIED>;
+  static int per_sm = 0;  // occupancy of this instantiation (same on every B200)
+  if (per_sm == 0) per_sm = blocks_per_sm(kernel, kThreads);
+  const int64_t want = (p.rows + (kThreads / kWarp) - 1) / (kThreads / kWarp);
+  const int64_t cap = (int64_t)sm_count() * per_sm;
+  const unsigned grid = (unsigned)(want < cap ? want : cap);
+  kernel<<<grid, kThreads, 0, s>>>(
+      static_cast<const T *>(p.logits), p.targets, p.T, p.U,
+      reinterpret_cast<const int64_t *>(p.ws + p.lay.split),
+      reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
+      reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.N, p.rows, p.V,
+      p.max_u, p.blank, reinterpret_cast<T *>(p.ws + p.lay.den),
+      reinterpret_cast<T *>(p.ws + p.lay.lp));
+  return cudaGetLastError();
 }
 
 template <typename T, int VEC, int CH>
 cudaError_t launch_lse(const Problem &p, cudaStream_t s) {
-  const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
-  const int64_t *split = reinterpret_cast<const int64_t *>(p.ws + p.lay.split);
-  T *den = reinterpret_cast<T *>(p.ws + p.lay.den);
-  T *lp = reinterpret_cast<T *>(p.ws + p.lay.lp);
-  const T *x = static_cast<const T *>(p.logits);
-  // Persistent grid: a multiple of the SM count, never more warps than rows.
-  const int64_t want = (p.rows + (kThreads / kWarp) - 1) / (kThreads / kWarp);
-  const int64_t cap = (int64_t)sm_count() * 8;
-  const unsigned grid = (unsigned)(want < cap ? want : cap);
-  if (p.flags & OT_B200_ONE_SYM_PER_FRAME)
-    logprob_kernel<T, VEC, CH, true><<<grid, kThreads, 0, s>>>(
-        x, p.targets, p.T, p.U, split, status, p.N, p.rows, p.V, p.max_u, p.blank, den, lp);
-  else
-    logprob_kernel<T, VEC, CH, false><<<grid, kThreads, 0, s>>>(
-        x, p.targets, p.T, p.U, split, status, p.N, p.rows, p.V, p.max_u, p.blank, den, lp);
-  return cudaGetLastError();
+  return (p.flags & OT_B200_ONE_SYM_PER_FRAME) ? launch_lse_m<T, VEC, CH, true>(p, s)
+                                               : launch_lse_m<T, VEC, CH, false>(p, s);
 }
 
 template <typename T>
 cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
   if (p.flags & OT_B200_FROM_LOG_SOFTMAX) {
     const unsigned grid = (unsigned)((p.rows + kThreads - 1) / kThreads);
-    gather_kernel<T><<<grid, kThreads, 0, s>>>(
-        static_cast<const T *>(p.logits), p.targets, p.U,
-        reinterpret_cast<const int64_t *>(p.ws + p.lay.split),
-        reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.N, p.rows, p.V,
-        p.max_u, p.blank, reinterpret_cast<T *>(p.ws + p.lay.lp));
+    const T *x = static_cast<const T *>(p.logits);
+    const int64_t *split = reinterpret_cast<const int64_t *>(p.ws + p.lay.split);
+    const int64_t *csplit = reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split);
+    const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
+    T *lp = reinterpret_cast<T *>(p.ws + p.lay.lp);
+    if (p.flags & OT_B200_ONE_SYM_PER_FRAME)
+      gather_kernel<T, true><<<grid, kThreads, 0, s>>>(x, p.targets, p.U, split, csplit, status,
+                                                       p.N, p.rows, p.V, p.max_u, p.blank, lp);
+    else
+      gather_kernel<T, false><<<grid, kThreads, 0, s>>>(x, p.targets, p.U, split, csplit, status,
+                                                        p.N, p.rows, p.V, p.max_u, p.blank, lp);
     return cudaGetLastError();
   }
   constexpr int VEC = Vec16<T>::n;

@@ -5,7 +5,9 @@
 //   T_b, U_b frames and target symbols of utterance b; the lattice has
 //            T_b x (U_b+1) cells, U1 = U_b + 1
 //   row      index into the packed (rows, V) logits; row(b,t,u) = split[b] + t*U1 + u
-//   lp       per row (blank log-prob, next-symbol log-prob)
+//   cell     index into the per-cell workspace arrays (lp, alpha, beta);
+//            cell(b,t,u) = cell_split[b] + cell_pos(t,u), see below
+//   lp       per cell (blank log-prob, next-symbol log-prob)
 //   den      per row logsumexp of the logits
 #pragma once
 
@@ -27,6 +29,28 @@ constexpr int kStatusWords = 16;
 // Marker values of the `tgt` field of a gradient-coefficient record.
 constexpr int32_t kTgtNone = -1;     // no symbol column to patch in this row
 constexpr int32_t kTgtZeroRow = -2;  // the whole gradient row is zero
+
+// Layout of the per-cell arrays of one utterance.
+//
+// Standard transducer: the recursion advances along anti-diagonals d = t + u,
+// so cells are stored diagonal-major ("skewed"): cell_pos(t,u) = (t+u)*U1 + u.
+// At step d the threads u = 0..U touch consecutive addresses, i.e. every load
+// and store of the wavefront is coalesced.  The block has (T+U)*U1 entries; the
+// entries that correspond to no lattice cell are never read or written.
+//
+// One symbol per frame: both predecessors lie in frame t-1, the recursion is
+// frame-synchronous and the natural row-major order t*U1 + u is the coalesced
+// one.
+template <bool MODIFIED>
+__host__ __device__ __forceinline__ int64_t cell_pos(int t, int u, int U1) {
+  return MODIFIED ? (int64_t)t * U1 + u : (int64_t)(t + u) * U1 + u;
+}
+// Entries of one utterance's block, rounded up to an even count so that every
+// block starts 16-byte aligned in the (blank, symbol) array.
+__host__ __device__ __forceinline__ int64_t cell_block(int T, int U, bool modified) {
+  const int64_t n = modified ? (int64_t)T * (U + 1) : (int64_t)(T + U) * (U + 1);
+  return (n + 1) & ~int64_t(1);
+}
 
 // Per-row coefficients of the gradient w.r.t. raw logits (mode A), produced
 // once per row after alpha and beta are known, so that the streaming gradient
@@ -53,11 +77,12 @@ struct alignas(16) CoefB {
 };
 
 struct Layout {
-  uint64_t total, status, split, den, lp, alpha, beta, coef, scores_beta;
+  uint64_t total, status, split, cell_split, den, lp, alpha, beta, coef, scores_beta;
+  int64_t max_cells;  // capacity of the per-cell arrays
 };
 
 // Computes the workspace layout (all segments 256-byte aligned).
-Layout make_layout(int32_t N, int64_t rows, uint32_t flags);
+Layout make_layout(int32_t N, int64_t rows, int32_t max_u, uint32_t flags);
 
 struct Problem {
   const void *logits;
@@ -77,11 +102,20 @@ struct Problem {
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Blocks of `kernel` that fit on one SM at `threads` threads per block.
+template <typename K>
+int blocks_per_sm(K kernel, int threads) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) n = 1;
+  return n;
+}
+
 // Host launchers, one per stage; each returns the cudaError_t of its launch.
 cudaError_t launch_prepare(const Problem &p, cudaStream_t s);
 cudaError_t launch_logprob(const Problem &p, cudaStream_t s);
 cudaError_t launch_lattice(const Problem &p, void *scores, cudaStream_t s);
-cudaError_t launch_coef(const Problem &p, cudaStream_t s);
+cudaError_t launch_coef(const Problem &p, const void *scores, void *loss_out,
+                        double loss_scale, cudaStream_t s);
 cudaError_t launch_gradient(const Problem &p, void *grad, const void *d_scale,
                             double scale_host, cudaStream_t s);
 
@@ -93,6 +127,12 @@ cudaError_t launch_gradient(const Problem &p, void *grad, const void *d_scale,
 template <typename T> struct Vec16;
 template <> struct Vec16<float> { using type = float4; static constexpr int n = 4; };
 template <> struct Vec16<double> { using type = double2; static constexpr int n = 2; };
+
+template <typename T, int VEC> struct VecOf;
+template <> struct VecOf<float, 4> { using type = float4; };
+template <> struct VecOf<float, 1> { using type = float; };
+template <> struct VecOf<double, 2> { using type = double2; };
+template <> struct VecOf<double, 1> { using type = double; };
 
 template <typename T> __device__ __forceinline__ T neg_inf();
 template <> __device__ __forceinline__ float neg_inf<float>() { return -__int_as_float(0x7f800000); }
@@ -106,6 +146,21 @@ __device__ __forceinline__ float r_log1p(float x) { return log1pf(x); }
 __device__ __forceinline__ double r_log1p(double x) { return log1p(x); }
 __device__ __forceinline__ float r_max(float a, float b) { return fmaxf(a, b); }
 __device__ __forceinline__ double r_max(double a, double b) { return fmax(a, b); }
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// 2^x by the hardware approximation (relative error about 2^-22).
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// exp(x) for the streaming kernels: one multiply and one ex2.  For the
+// arguments that matter there (|x| < 30, results <= 1) the error is below
+// 2e-6 relative, far inside the 1e-5 absolute gradient tolerance.  Double
+// precision keeps the library routine.
+__device__ __forceinline__ float s_exp(float x) { return ex2_approx(x * kLog2e); }
+__device__ __forceinline__ double s_exp(double x) { return exp(x); }
 
 template <typename T> __device__ __forceinline__ T min_log_diff();
 // log(machine epsilon): below this the smaller operand of a log-add is dropped
@@ -122,7 +177,7 @@ __device__ __forceinline__ T log_add(T a, T b) {
   if (!(d >= min_log_diff<T>())) return hi;
   if constexpr (FAST && sizeof(T) == 4) {
     // ex2/lg2 approximations: absolute error of the correction < 3e-7.
-    return hi + __logf(1.0f + __expf(d));
+    return hi + __logf(1.0f + ex2_approx(d * kLog2e));
   } else {
     return hi + r_log1p(r_exp(d));
   }

@@ -1,12 +1,13 @@
-// Stage 0 (input check + row splits) and stage 2c (per-row gradient
-// coefficients) of the transducer-loss path.
+// Stage 0 (input check + row/cell splits) and stage 2c (per-row gradient
+// coefficients + the reduced loss) of the transducer-loss path.
 //
 // Stage 0 replaces, without a host round trip, the data-dependent checks of
 // ot::ComputeTransducerLoss (optimized_transducer/csrc/transducer-loss.cc:49-66)
 // and the row_splits construction of ot::ComputeTransducerLossCuda
 // (optimized_transducer/csrc/cuda.cu:411-414).  The reference's row_ids array
 // (cuda.cu:40-59, moderngpu load_balance_search) has no counterpart: later
-// stages find the owning utterance with a binary search over `split`.
+// stages find the owning utterance with a binary search over the splits, or
+// walk their rows in order.
 #include "ot_common.cuh"
 
 namespace otb {
@@ -19,13 +20,36 @@ __device__ __forceinline__ void raise(int32_t *status, int code, int index) {
   if (atomicCAS(status + kStatusCode, 0, code) == 0) status[kStatusIndex] = index;
 }
 
+// Block-wide exclusive prefix sum of one value per thread; `total` gets the sum.
+__device__ __forceinline__ long long block_exclusive_scan(long long mine, long long *smem,
+                                                          long long *total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  long long incl = mine;
+#pragma unroll
+  for (int o = 1; o < kWarp; o <<= 1) {
+    const long long v = __shfl_up_sync(kFull, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == kWarp - 1) smem[warp] = incl;
+  __syncthreads();
+  long long base = 0, tot = 0;
+  for (int w = 0; w < kPrepThreads / kWarp; ++w) {
+    if (w < warp) base += smem[w];
+    tot += smem[w];
+  }
+  __syncthreads();
+  *total = tot;
+  return base + incl - mine;
+}
+
 // One CTA.  Thread i owns the contiguous utterance range [i*per, (i+1)*per).
 __global__ void __launch_bounds__(kPrepThreads)
 prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
                const int32_t *__restrict__ Ul, int N, int64_t rows, int V,
-               int max_u, int modified, int32_t *__restrict__ status,
-               int64_t *__restrict__ split) {
-  __shared__ long long warp_tot[kPrepThreads / kWarp];
+               int max_u, int modified, int64_t max_cells,
+               int32_t *__restrict__ status, int64_t *__restrict__ split,
+               int64_t *__restrict__ cell_split) {
+  __shared__ long long scan_buf[kPrepThreads / kWarp];
   __shared__ int warp_maxu[kPrepThreads / kWarp];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid < kStatusWords) status[tid] = 0;
@@ -33,45 +57,43 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
 
   const int per = (N + kPrepThreads - 1) / kPrepThreads;
   const int b0 = min(tid * per, N), b1 = min(b0 + per, N);
-  long long mine = 0;
+  long long my_rows = 0, my_cells = 0;
   int my_maxu = -1;
   for (int b = b0; b < b1; ++b) {
     const int t = Tl[b], u = Ul[b];
     if (t <= 0) raise(status, OT_B200_INPUT_BAD_LOGIT_LENGTH, b);
     if (u < 0 || u > max_u) raise(status, OT_B200_INPUT_BAD_TARGET_LENGTH, b);
     if (modified && u > t - 1) raise(status, OT_B200_INPUT_ONE_SYM_INFEASIBLE, b);
-    mine += (long long)max(t, 0) * (long long)(max(u, 0) + 1);
+    const int tc = max(t, 0), uc = min(max(u, 0), max_u);
+    my_rows += (long long)tc * (uc + 1);
+    my_cells += cell_block(tc, uc, modified != 0);
     my_maxu = max(my_maxu, u);
   }
-  // Block-wide exclusive scan of `mine` (warp shuffles, then warp totals).
-  long long incl = mine;
-#pragma unroll
-  for (int o = 1; o < kWarp; o <<= 1) {
-    const long long v = __shfl_up_sync(kFull, incl, o);
-    if (lane >= o) incl += v;
-  }
+  long long total_rows, total_cells;
+  long long run_rows = block_exclusive_scan(my_rows, scan_buf, &total_rows);
+  long long run_cells = block_exclusive_scan(my_cells, scan_buf, &total_cells);
   int wmax = my_maxu;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) wmax = max(wmax, __shfl_xor_sync(kFull, wmax, o));
-  if (lane == kWarp - 1) warp_tot[warp] = incl;
   if (lane == 0) warp_maxu[warp] = wmax;
   __syncthreads();
-  long long base = 0, total = 0;
-  int maxu_all = -1;
-  for (int w = 0; w < kPrepThreads / kWarp; ++w) {
-    if (w < warp) base += warp_tot[w];
-    total += warp_tot[w];
-    maxu_all = max(maxu_all, warp_maxu[w]);
-  }
-  long long run = base + incl - mine;
   for (int b = b0; b < b1; ++b) {
-    split[b] = run;
-    run += (long long)max(Tl[b], 0) * (long long)(max(Ul[b], 0) + 1);
+    split[b] = run_rows;
+    cell_split[b] = run_cells;
+    const int tc = max(Tl[b], 0), uc = min(max(Ul[b], 0), max_u);
+    run_rows += (long long)tc * (uc + 1);
+    run_cells += cell_block(tc, uc, modified != 0);
   }
   if (tid == 0) {
-    split[N] = total;
-    if (total != rows) raise(status, OT_B200_INPUT_ROWS_MISMATCH, 0);
+    int maxu_all = -1;
+    for (int w = 0; w < kPrepThreads / kWarp; ++w) maxu_all = max(maxu_all, warp_maxu[w]);
+    split[N] = total_rows;
+    cell_split[N] = total_cells;
+    if (total_rows != rows) raise(status, OT_B200_INPUT_ROWS_MISMATCH, 0);
     if (maxu_all != max_u) raise(status, OT_B200_INPUT_MAX_U_MISMATCH, 0);
+    // Cannot happen for consistent inputs (the host sizes the workspace from
+    // rows, N and max_u); guards the per-cell arrays against inconsistent ones.
+    if (total_cells > max_cells) raise(status, OT_B200_INPUT_ROWS_MISMATCH, 0);
   }
   // targets.max() < V over the whole (N, max_u) array, as the reference
   // checks it; in addition the entries that are used must not be negative.
@@ -83,30 +105,53 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
   }
 }
 
-// Thread per row.  Produces the record the streaming gradient kernels read.
+// Thread per workspace cell, in the order alpha and beta are stored, so their
+// reads are coalesced; the 32-byte (16-byte) record of the cell's row is the
+// only scattered access.  Produces what the streaming gradient kernels read.
 // Branch order and the order of the floating-point additions follow
 // ComputeGradient / ...OneSymPerFrame / ...ForLogSoftmax[OneSymPerFrame]
 // (optimized_transducer/csrc/cpu.cc:500-526, 582-604, 655-672, 722-745).
 // A non-finite log-likelihood zeroes the utterance's rows
 // (optimized_transducer/csrc/kernels.cu:556-563).
+//
+// Block 0 also reduces the scores to the loss:
+//   *loss_out = loss_scale * -(sum_b scores[b])      (transducer_loss.py:145-152)
 template <typename T, bool MODE_B, bool MODIFIED>
 __global__ void __launch_bounds__(256)
 coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
             const int32_t *__restrict__ Ul, const int64_t *__restrict__ split,
-            const int32_t *__restrict__ status, int N, int64_t rows, int max_u,
-            int blank, const T *__restrict__ den, const T *__restrict__ lp,
+            const int64_t *__restrict__ cell_split,
+            const int32_t *__restrict__ status, int N, int max_u, int blank,
+            const T *__restrict__ den, const T *__restrict__ lp,
             const T *__restrict__ alpha, const T *__restrict__ beta,
-            void *__restrict__ coef_out) {
+            void *__restrict__ coef_out, const T *__restrict__ scores,
+            T *__restrict__ loss_out, double loss_scale) {
   if (status[kStatusCode] != 0) return;
-  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= rows) return;
-  const int b = find_utt(split, N, row);
-  const int64_t off = __ldg(split + b);
+  if (blockIdx.x == 0 && threadIdx.x < kWarp && loss_out != nullptr) {
+    double acc = 0;
+    for (int b = threadIdx.x; b < N; b += kWarp) acc += (double)scores[b];
+    acc = warp_sum(acc);
+    if (threadIdx.x == 0) *loss_out = (T)(-acc * loss_scale);
+  }
+  const int64_t cell = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (cell >= __ldg(cell_split + N)) return;
+  const int b = find_utt(cell_split, N, cell);
+  const int64_t coff = __ldg(cell_split + b);
   const int Tn = __ldg(Tl + b), U = __ldg(Ul + b), U1 = U + 1;
-  const int idx = (int)(row - off);
-  const int t = idx / U1, u = idx - t * U1;
+  const int64_t p = cell - coff;
+  int t, u;
+  if (MODIFIED) {
+    t = (int)(p / U1); u = (int)(p - (int64_t)t * U1);
+    if (t >= Tn) return;  // rounding pad of the block
+  } else {
+    const int d = (int)(p / U1);
+    u = (int)(p - (int64_t)d * U1);
+    t = d - u;
+    if (t < 0 || t >= Tn) return;  // no lattice cell is stored here
+  }
+  const int64_t row = __ldg(split + b) + (int64_t)t * U1 + u;
   const int diff = Tn - 1 - U;
-  const T L = beta[off];
+  const T L = beta[coff];  // beta(0,0) is the first entry in both layouts
 
   bool zero = !(L - L == (T)0);  // inf or nan
   if (MODIFIED && (u > t || t - u > diff)) zero = true;
@@ -116,17 +161,19 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
   bool blank_term = false, sym_term = false;
   if (!zero) {
     const T loss = -L;
-    c = alpha[row] + loss;
+    c = alpha[cell] + loss;
     if (!MODE_B) c = c - den[row];
-    b_here = beta[row];
+    b_here = beta[cell];
     const bool last = (t == Tn - 1 && u == U);
     const bool blank_ok = MODIFIED ? (t - u < diff) : (t < Tn - 1);
     const int target_u = (u < U) ? __ldg(targets + (int64_t)b * max_u + u) : -1;
-    const T b_sym_next = (u < U) ? (MODIFIED ? beta[row + U1 + 1] : beta[row + 1]) : neg_inf<T>();
+    // successors: blank -> (t+1,u), symbol -> (t,u+1) or (t+1,u+1) if modified;
+    // in both storage orders they sit U1 and U1+1 entries further.
+    const T b_sym_next = (u < U) ? beta[cell + U1 + 1] : neg_inf<T>();
     if (last) {
       sub_blank = 0; blank_term = true;
     } else if (blank_ok) {
-      sub_blank = beta[row + U1]; blank_term = true;
+      sub_blank = beta[cell + U1]; blank_term = true;
     } else if (u < U && target_u == blank) {
       sub_blank = b_sym_next; blank_term = true;
     }
@@ -136,8 +183,8 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
   }
   if (MODE_B) {
     CoefB<T> r;
-    r.val_blank = blank_term ? -r_exp((lp[2 * row] + c) + sub_blank) : (T)0;
-    r.val_sym = sym_term ? -r_exp((lp[2 * row + 1] + c) + sub_sym) : (T)0;
+    r.val_blank = blank_term ? -r_exp((lp[2 * cell] + c) + sub_blank) : (T)0;
+    r.val_sym = sym_term ? -r_exp((lp[2 * cell + 1] + c) + sub_sym) : (T)0;
     r.tgt = zero ? kTgtZeroRow : tgt;
     reinterpret_cast<CoefB<T> *>(coef_out)[row] = r;
   } else {
@@ -149,20 +196,23 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
 }
 
 template <typename T>
-cudaError_t launch_coef_t(const Problem &p, cudaStream_t s) {
+cudaError_t launch_coef_t(const Problem &p, const void *scores, void *loss_out,
+                          double loss_scale, cudaStream_t s) {
   const bool mode_b = p.flags & OT_B200_FROM_LOG_SOFTMAX;
   const bool modified = p.flags & OT_B200_ONE_SYM_PER_FRAME;
   const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
   const int64_t *split = reinterpret_cast<const int64_t *>(p.ws + p.lay.split);
+  const int64_t *csplit = reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split);
   const T *den = reinterpret_cast<const T *>(p.ws + p.lay.den);
   const T *lp = reinterpret_cast<const T *>(p.ws + p.lay.lp);
   const T *alpha = reinterpret_cast<const T *>(p.ws + p.lay.alpha);
   const T *beta = reinterpret_cast<const T *>(p.ws + p.lay.beta);
   void *coef = p.ws + p.lay.coef;
-  const unsigned grid = (unsigned)((p.rows + 255) / 256);
-#define OTB_COEF(MB, MOD)                                                      \
-  coef_kernel<T, MB, MOD><<<grid, 256, 0, s>>>(p.targets, p.T, p.U, split,     \
-      status, p.N, p.rows, p.max_u, p.blank, den, lp, alpha, beta, coef)
+  const unsigned grid = (unsigned)((p.lay.max_cells + 255) / 256);
+#define OTB_COEF(MB, MOD)                                                        \
+  coef_kernel<T, MB, MOD><<<grid, 256, 0, s>>>(p.targets, p.T, p.U, split,       \
+      csplit, status, p.N, p.max_u, p.blank, den, lp, alpha, beta, coef,         \
+      static_cast<const T *>(scores), static_cast<T *>(loss_out), loss_scale)
   if (mode_b) { if (modified) OTB_COEF(true, true); else OTB_COEF(true, false); }
   else        { if (modified) OTB_COEF(false, true); else OTB_COEF(false, false); }
 #undef OTB_COEF
@@ -174,15 +224,17 @@ cudaError_t launch_coef_t(const Problem &p, cudaStream_t s) {
 cudaError_t launch_prepare(const Problem &p, cudaStream_t s) {
   prepare_kernel<<<1, kPrepThreads, 0, s>>>(
       p.targets, p.T, p.U, p.N, p.rows, p.V, p.max_u,
-      (p.flags & OT_B200_ONE_SYM_PER_FRAME) ? 1 : 0,
+      (p.flags & OT_B200_ONE_SYM_PER_FRAME) ? 1 : 0, p.lay.max_cells,
       reinterpret_cast<int32_t *>(p.ws + p.lay.status),
-      reinterpret_cast<int64_t *>(p.ws + p.lay.split));
+      reinterpret_cast<int64_t *>(p.ws + p.lay.split),
+      reinterpret_cast<int64_t *>(p.ws + p.lay.cell_split));
   return cudaGetLastError();
 }
 
-cudaError_t launch_coef(const Problem &p, cudaStream_t s) {
-  return (p.flags & OT_B200_FP64) ? launch_coef_t<double>(p, s)
-                                  : launch_coef_t<float>(p, s);
+cudaError_t launch_coef(const Problem &p, const void *scores, void *loss_out,
+                        double loss_scale, cudaStream_t s) {
+  return (p.flags & OT_B200_FP64) ? launch_coef_t<double>(p, scores, loss_out, loss_scale, s)
+                                  : launch_coef_t<float>(p, scores, loss_out, loss_scale, s);
 }
 
 }  // namespace otb

@@ -186,7 +186,8 @@ class _ShardedLoss(torch.autograd.Function):
         if logit_lengths.numel() > 0:
             call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
                          from_log_softmax, one_sym_per_frame)
-            local = -call.forward().sum()
+            local = torch.empty((), dtype=logits.dtype, device=logits.device)
+            call.forward(loss_out=local, loss_scale=1.0)
         else:  # a rank without utterances still joins the collective
             call = None
             local = torch.zeros((), dtype=logits.dtype, device=logits.device)

@@ -119,8 +119,9 @@ class _Call:
         self.max_u = int(targets.size(1))
         self.blank = int(blank)
         self.from_log_softmax = bool(from_log_softmax)
+        self.modified = bool(one_sym_per_frame)
         self.flags = _flags(logits, from_log_softmax, one_sym_per_frame, checks)
-        self.layout = _lib.workspace_layout(self.n, self.rows, self.flags)
+        self.layout = _lib.workspace_layout(self.n, self.rows, self.max_u, self.flags)
         self.targets, self.t, self.u = targets, logit_lengths, target_lengths
         with torch.cuda.device(logits.device):
             self.workspace = torch.empty(int(self.layout.total_bytes), dtype=torch.uint8,
@@ -130,13 +131,16 @@ class _Call:
     def _stream(self):
         return ctypes.c_void_p(torch.cuda.current_stream(self.logits.device).cuda_stream)
 
-    def forward(self):
+    def forward(self, loss_out=None, loss_scale=1.0):
+        """Enqueues the forward half.  ``loss_out``: optional 0-dim tensor that
+        receives ``loss_scale * -(sum of scores)``."""
         with torch.cuda.device(self.logits.device):
             rc = self.lib.ot_b200_forward(
                 self.logits.data_ptr(), self.targets.data_ptr() if self.max_u else None,
                 self.t.data_ptr(), self.u.data_ptr(), self.n, self.rows, self.v, self.max_u,
                 self.blank, self.flags, self.workspace.data_ptr(), int(self.layout.total_bytes),
-                self.scores.data_ptr(), self._stream())
+                self.scores.data_ptr(), loss_out.data_ptr() if loss_out is not None else None,
+                float(loss_scale), self._stream())
         _lib.check(rc)
         return self.scores
 
@@ -144,27 +148,46 @@ class _Call:
         with torch.cuda.device(self.logits.device):
             rc = self.lib.ot_b200_backward(
                 self.logits.data_ptr(), grad_out.data_ptr(), self.n, self.rows, self.v,
-                self.blank, self.flags & ~_lib.CHECK_INPUTS, self.workspace.data_ptr(),
-                int(self.layout.total_bytes),
+                self.max_u, self.blank, self.flags & ~_lib.CHECK_INPUTS,
+                self.workspace.data_ptr(), int(self.layout.total_bytes),
                 scale_tensor.data_ptr() if scale_tensor is not None else None,
                 float(scale_host), self._stream())
         _lib.check(rc)
         return grad_out
 
     def stage(self, name):
-        """A tensor view of one intermediate array inside the workspace."""
+        """A tensor view of one intermediate array inside the workspace, in the
+        library's own order (per-cell arrays are NOT in packed-row order, see
+        :meth:`cell_index`)."""
         dt = self.logits.dtype
         es = 8 if dt == torch.float64 else 4
-        if name == "split":
-            off, count, dtype, esz = self.layout.split_off, self.n + 1, torch.int64, 8
+        cells = int(self.layout.max_cells)
+        if name in ("split", "cell_split"):
+            off, count, dtype, esz = getattr(self.layout, name + "_off"), self.n + 1, torch.int64, 8
         elif name == "status":
             off, count, dtype, esz = self.layout.status_off, 16, torch.int32, 4
         else:
             off = getattr(self.layout, name + "_off")
-            count = {"den": self.rows, "lp": 2 * self.rows, "alpha": self.rows,
-                     "beta": self.rows, "scores_beta": self.n}[name]
+            count = {"den": self.rows, "lp": 2 * cells, "alpha": cells,
+                     "beta": cells, "scores_beta": self.n}[name]
             dtype, esz = dt, es
         return self.workspace[off:off + count * esz].view(dtype)
+
+    def cell_index(self):
+        """(rows,) int64 tensor: the cell of every packed row, i.e. the gather
+        index that brings a per-cell array into packed-row order
+        (``cell(b,t,u)`` as documented in ``include/ot_b200.h``)."""
+        dev = self.logits.device
+        T = self.t.to(torch.int64)
+        U1 = self.u.to(torch.int64) + 1
+        split = self.stage("split")[:-1]
+        cell_split = self.stage("cell_split")[:-1]
+        b = torch.repeat_interleave(torch.arange(self.n, device=dev), T * U1)
+        idx = torch.arange(self.rows, device=dev) - split[b]
+        t = idx // U1[b]
+        u = idx - t * U1[b]
+        pos = t * U1[b] + u if self.modified else (t + u) * U1[b] + u
+        return cell_split[b] + pos
 
 
 def compute_transducer_loss(logits, targets, logit_lengths, target_lengths, blank,
@@ -198,10 +221,11 @@ def stage_outputs(logits, targets, logit_lengths, target_lengths, blank,
     call = _Call(logits, targets, logit_lengths, target_lengths, blank,
                  from_log_softmax, one_sym_per_frame)
     scores = call.forward()
+    cell = call.cell_index()
     out = {"scores": scores.clone(), "scores_beta": call.stage("scores_beta").clone(),
            "den": None if from_log_softmax else call.stage("den").clone(),
-           "lp": call.stage("lp").clone().view(-1, 2), "alpha": call.stage("alpha").clone(),
-           "beta": call.stage("beta").clone(), "split": call.stage("split").clone()}
+           "lp": call.stage("lp").view(-1, 2)[cell], "alpha": call.stage("alpha")[cell],
+           "beta": call.stage("beta")[cell], "split": call.stage("split").clone()}
     return out
 
 
@@ -229,13 +253,12 @@ class TransducerLossFunction(torch.autograd.Function):
 
         call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
                      from_log_softmax, one_sym_per_frame)
-        scores = call.forward()
-        loss = -scores.sum()
-        if reduction == "mean":
-            loss = loss / n
+        scale = (1.0 / n) if reduction == "mean" else 1.0
+        loss = torch.empty((), dtype=logits.dtype, device=logits.device)
+        call.forward(loss_out=loss, loss_scale=scale)  # the reduction runs on the device too
         ctx.grad = None
-        ctx.call = call if logits.requires_grad else None
-        ctx.scale_host = (1.0 / n) if reduction == "mean" else 1.0
+        ctx.call = call if ctx.needs_input_grad[0] else None
+        ctx.scale_host = scale
         return loss
 
     @staticmethod

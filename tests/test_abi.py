@@ -34,19 +34,23 @@ def test_abi_version():
 
 @pytest.mark.parametrize("flags", [0, _lib.FROM_LOG_SOFTMAX, _lib.FP64, _lib.FP64 | _lib.FROM_LOG_SOFTMAX])
 def test_workspace_layout_is_aligned_and_ordered(flags):
-    n, rows = 7, 12345
-    lay = _lib.workspace_layout(n, rows, flags)
+    n, rows, max_u = 7, 12345, 20
+    lay = _lib.workspace_layout(n, rows, max_u, flags)
     es = 8 if flags & _lib.FP64 else 4
-    offs = [lay.status_off, lay.split_off, lay.den_off, lay.lp_off, lay.alpha_off,
-            lay.beta_off, lay.coef_off, lay.scores_beta_off, lay.total_bytes]
+    offs = [lay.status_off, lay.split_off, lay.cell_split_off, lay.den_off, lay.lp_off,
+            lay.alpha_off, lay.beta_off, lay.coef_off, lay.scores_beta_off, lay.total_bytes]
     assert all(o % 256 == 0 for o in offs)
-    assert offs == sorted(offs)
+    assert offs == sorted(offs) and lay.status_off == 0
+    # room for every diagonal-major block: rows + sum U*(U+1) + one pad entry each
+    assert lay.max_cells >= rows + n * max_u * (max_u + 1) + n
     assert lay.lp_off - lay.den_off >= (0 if flags & _lib.FROM_LOG_SOFTMAX else rows * es)
-    assert lay.alpha_off - lay.lp_off >= 2 * rows * es
-    assert lay.beta_off - lay.alpha_off >= rows * es
+    assert lay.alpha_off - lay.lp_off >= 2 * lay.max_cells * es
+    assert lay.beta_off - lay.alpha_off >= lay.max_cells * es
     total = ctypes.c_uint64()
-    assert _lib.load().ot_b200_workspace_bytes(n, rows, flags, ctypes.byref(total)) == _lib.OK
+    assert _lib.load().ot_b200_workspace_bytes(n, rows, max_u, flags, ctypes.byref(total)) == _lib.OK
     assert total.value == lay.total_bytes
+    mod = _lib.workspace_layout(n, rows, max_u, flags | _lib.ONE_SYM_PER_FRAME)
+    assert mod.max_cells == rows + n  # row-major blocks, one pad entry each
 
 
 def test_argument_errors_without_touching_a_gpu():
@@ -55,26 +59,26 @@ def test_argument_errors_without_touching_a_gpu():
     ws = (ctypes.addressof(buf) + 255) & ~255
     one = ctypes.c_void_p(ws)
     # N <= 0
-    rc = lib.ot_b200_forward(one, one, one, one, 0, 10, 5, 1, 0, 0, one, 1 << 15, one, None)
+    rc = lib.ot_b200_forward(one, one, one, one, 0, 10, 5, 1, 0, 0, one, 1 << 15, one, None, 1.0, None)
     assert rc == _lib.ERR_ARGUMENT and "N must be positive" in _lib.last_error()
     # blank out of range: the reference's wording (transducer-loss.cc:58-60)
-    rc = lib.ot_b200_forward(one, one, one, one, 1, 10, 5, 1, 5, 0, one, 1 << 15, one, None)
+    rc = lib.ot_b200_forward(one, one, one, one, 1, 10, 5, 1, 5, 0, one, 1 << 15, one, None, 1.0, None)
     assert rc == _lib.ERR_ARGUMENT and "Expect 0 <= blank < logits.size(1)" in _lib.last_error()
     # workspace too small / missing / misaligned
-    rc = lib.ot_b200_forward(one, one, one, one, 1, 10, 5, 1, 0, 0, one, 16, one, None)
+    rc = lib.ot_b200_forward(one, one, one, one, 1, 10, 5, 1, 0, 0, one, 16, one, None, 1.0, None)
     assert rc == _lib.ERR_WORKSPACE
-    rc = lib.ot_b200_forward(one, one, one, one, 1, 10, 5, 1, 0, 0, None, 1 << 15, one, None)
+    rc = lib.ot_b200_forward(one, one, one, one, 1, 10, 5, 1, 0, 0, None, 1 << 15, one, None, 1.0, None)
     assert rc == _lib.ERR_WORKSPACE
-    rc = lib.ot_b200_forward(one, one, one, one, 1, 10, 5, 1, 0, 0, ctypes.c_void_p(ws + 8), 1 << 15, one, None)
+    rc = lib.ot_b200_forward(one, one, one, one, 1, 10, 5, 1, 0, 0, ctypes.c_void_p(ws + 8), 1 << 15, one, None, 1.0, None)
     assert rc == _lib.ERR_WORKSPACE
     # unknown flag bits
-    rc = lib.ot_b200_forward(one, one, one, one, 1, 10, 5, 1, 0, 1 << 20, one, 1 << 15, one, None)
+    rc = lib.ot_b200_forward(one, one, one, one, 1, 10, 5, 1, 0, 1 << 20, one, 1 << 15, one, None, 1.0, None)
     assert rc == _lib.ERR_ARGUMENT
     # NULL logits
-    rc = lib.ot_b200_forward(None, one, one, one, 1, 10, 5, 1, 0, 0, one, 1 << 15, one, None)
+    rc = lib.ot_b200_forward(None, one, one, one, 1, 10, 5, 1, 0, 0, one, 1 << 15, one, None, 1.0, None)
     assert rc == _lib.ERR_ARGUMENT
     # log-softmax gradient must not alias its input (cuda.cu:444 allocates a new tensor)
-    rc = lib.ot_b200_backward(one, one, 1, 10, 5, 0, _lib.FROM_LOG_SOFTMAX, one, 1 << 15, None, 1.0, None)
+    rc = lib.ot_b200_backward(one, one, 1, 10, 5, 1, 0, _lib.FROM_LOG_SOFTMAX, one, 1 << 15, None, 1.0, None)
     assert rc == _lib.ERR_ARGUMENT
     with pytest.raises(RuntimeError):
         _lib.check(rc)
