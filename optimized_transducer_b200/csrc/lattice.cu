@@ -16,12 +16,14 @@
 //   one symbol per frame: both predecessors lie in the previous frame, so the
 //                         sweep is frame-synchronous, T-1 steps
 //
-// The per-cell arrays (lp in, alpha/beta out) are stored in wavefront order
-// (see cell_pos in ot_common.cuh): at every step the threads of a warp read and
-// write consecutive addresses, and the address of a thread advances by U+1
-// entries per step.  The log-probs do not depend on the recursion, so they are
-// loaded kPrefetch steps ahead into a register ring.  Alpha and beta are
-// written as a side effect (the gradient stage needs them), never read back.
+// The kernel is latency-bound (a chain of T+U dependent log-add-exps), so
+// nothing on the chain may wait for global memory.  The per-cell arrays are
+// stored in wavefront order (cell_pos in ot_common.cuh): the log-probs the
+// steps consume are one contiguous stream, which TMA bulk copies
+// (cp.async.bulk + mbarrier, kStages chunks in flight) bring into shared memory
+// ahead of the recursion; a step reads its two log-probs from shared memory,
+// one step early.  Alpha and beta are written to global memory as a side effect
+// (coalesced, never read back here).
 //
 // Lattices wider than 1024 columns use the generic kernel at the end of the
 // file (several columns per thread, wavefront kept in global memory).
@@ -31,8 +33,35 @@ namespace otb {
 
 namespace {
 
-constexpr int kPrefetch = 8;
 constexpr int kMaxWarps = 32;
+constexpr int kStages = 3;
+constexpr int kStatusLatticeTimeout = 2;  // status word: a bulk copy never arrived
+constexpr int kChunkBytes = 16384;         // target size of one staged chunk
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// One-dimensional TMA copy global -> this CTA's shared memory, completion
+// signalled on `bar`.  dst, src and bytes are multiples of 16.
+__device__ __forceinline__ void tma_load_1d(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
 
 // Barrier over the first `nthreads` threads of the CTA (the warps that own a
 // lattice column); warps beyond them have already returned.
@@ -63,67 +92,110 @@ template <typename T> struct Pair;
 template <> struct Pair<float> { using type = float2; };
 template <> struct Pair<double> { using type = double2; };
 
+// `rows_per_chunk` (even) wavefront rows are staged per bulk copy; the dynamic
+// shared memory holds kStages chunks of rows_per_chunk * (max_u+1) pairs.
 template <typename T, bool FAST, bool MODIFIED>
 __global__ void __launch_bounds__(1024)
 lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
                const int32_t *__restrict__ Ul, const int64_t *__restrict__ cell_split,
-               const int32_t *__restrict__ status, T *__restrict__ alpha,
+               int32_t *__restrict__ status, T *__restrict__ alpha,
                T *__restrict__ beta, T *__restrict__ scores,
-               T *__restrict__ scores_beta) {
+               T *__restrict__ scores_beta, int rows_per_chunk, int stage_pairs) {
+  using P = typename Pair<T>::type;
+  extern __shared__ __align__(128) unsigned char stage_mem[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ T xchg[2][kMaxWarps];
   if (status[kStatusCode] != 0) return;
-  using P = typename Pair<T>::type;
   const int b = blockIdx.x >> 1;
   const bool backward = blockIdx.x & 1;
   const int Tn = Tl[b], U = Ul[b], U1 = U + 1;
   const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
   const int nwarps = (U1 + kWarp - 1) / kWarp;
   if (warp >= nwarps) return;
+  const int nact = nwarps * kWarp;
   const int64_t off = cell_split[b];
   const P *lp2 = reinterpret_cast<const P *>(lp) + off;
+  P *stage = reinterpret_cast<P *>(stage_mem);
   const bool col = u < U1;  // this thread owns a lattice column
   const int diff = Tn - 1 - U;
-  // Steps (first..last) during which this thread computes a cell, and the
-  // lattice row t of its first step.  Standard: step s is diagonal s, t = s - u.
-  // Modified: step s is frame s, the band is u <= t <= u + diff.
+  // Steps (s_lo..s_hi) during which this thread computes a cell.  Standard:
+  // step s is diagonal s, t = s - u.  Modified: step s is frame s, and the band
+  // is u <= t <= u + diff.  In both layouts cell (step s, column u) is entry
+  // s*U1 + u of the utterance's block.
   int s_lo, s_hi;
   if (MODIFIED) { s_lo = u; s_hi = u + diff; }
   else { s_lo = u; s_hi = u + Tn - 1; }
   if (!col) { s_lo = 1 << 30; s_hi = -1; }
+  const int top = MODIFIED ? Tn - 1 : Tn - 1 + U;  // step of the final cell (T-1, U)
+
+  // Wavefront rows 0 .. top-1 are streamed: alpha's step s reads row s-1
+  // (ascending), beta's step s reads row s (descending).
+  const int nrows = top;
+  const int R = rows_per_chunk;
+  const int nchunks = (nrows + R - 1) / R;
+  if (u == 0) {
+    for (int i = 0; i < kStages; ++i) mbar_init(&full_bar[i], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (nwarps > 1) bar_active(nact); else __syncwarp();
+  // Chunk j in processing order covers memory rows [row0, row0 + n).
+  auto chunk_rows = [&](int j, int &row0, int &n) {
+    const int m = backward ? nchunks - 1 - j : j;
+    row0 = m * R;
+    n = min(R, nrows - row0);
+  };
+  auto issue = [&](int j) {  // thread 0 only
+    int row0, n;
+    chunk_rows(j, row0, n);
+    // whole pairs, rounded up to 16 bytes (the block is padded to an even count)
+    const uint32_t bytes = (uint32_t)((((int64_t)n * U1 * sizeof(P)) + 15) & ~int64_t(15));
+    uint64_t *bar = &full_bar[j % kStages];
+    mbar_expect_tx(bar, bytes);
+    tma_load_1d(stage + (int64_t)(j % kStages) * stage_pairs, lp2 + (int64_t)row0 * U1, bytes, bar);
+  };
+  if (u == 0) for (int j = 0; j < kStages && j < nchunks; ++j) issue(j);
+  auto wait_chunk = [&](int j) {
+    uint64_t *bar = &full_bar[j % kStages];
+    const uint32_t parity = (uint32_t)((j / kStages) & 1);
+    // Bounded: a copy that never lands is reported through the status word and
+    // the recursion goes on with whatever the stage holds (no thread leaves the
+    // barriers of the steps early, so nothing can hang).
+    for (int spin = 0; spin < (1 << 22); ++spin)
+      if (mbar_try_wait(bar, parity)) return;
+    atomicCAS(status + kStatusLatticeTimeout, 0, 1 + b);
+  };
   int xs = 0;
 
   if (!backward) {
     // ------------------------------ alpha ------------------------------
-    // cell (step s, column u) lives at entry s*U1 + u in both layouts.
     T *al = alpha + off;
     T own = 0;
     if (u == 0) al[0] = 0;
     T left = neighbour<T, false>(own, xchg, xs++, lane, warp, nwarps);
-    const int last = MODIFIED ? Tn - 1 : Tn - 1 + U;
-    // What step s needs sits in the previous wavefront row: the blank log-prob
-    // of this column, (s-1)*U1 + u, and the symbol log-prob of column u-1.
-    // Standard: blank(t-1,u), sym(t,u-1).  Modified: blank(t-1,u), sym(t-1,u-1).
-    auto fetch = [&](int s, T &vb, T &vs) {
-      vb = 0; vs = 0;
-      if (s <= s_lo || s > s_hi) {          // not active, or the first cell of the column
-        if (s != s_lo || u == 0) return;    // ... which still needs the symbol term
-      }
-      const T *q = reinterpret_cast<const T *>(lp2 + ((int64_t)(s - 1) * U1 + u));
-      if (s > s_lo) vb = q[0];
-      if (u >= 1) vs = q[-1];
-    };
-    T pb[kPrefetch], ps[kPrefetch];
-#pragma unroll
-    for (int k = 0; k < kPrefetch; ++k) fetch(1 + k, pb[k], ps[k]);
     T *st = al + (int64_t)U1 + u;  // entry of step 1
-    for (int s0 = 1; s0 <= last; s0 += kPrefetch) {
-#pragma unroll
-      for (int k = 0; k < kPrefetch; ++k) {
-        const int s = s0 + k;
-        if (s > last) break;
-        const T lb = pb[k], ls = ps[k];
-        fetch(s + kPrefetch, pb[k], ps[k]);
-        if (s >= s_lo && s <= s_hi && s > 0) {
+    for (int j = 0; j < nchunks; ++j) {
+      int row0, n;
+      chunk_rows(j, row0, n);
+      wait_chunk(j);
+      const P *rowp = stage + (int64_t)(j % kStages) * stage_pairs + u;
+      // Step s = row + 1 needs, from wavefront row `row`: the blank log-prob of
+      // this column (standard blank(t-1,u); modified the same) and the symbol
+      // log-prob of column u-1 (standard sym(t,u-1); modified sym(t-1,u-1)).
+      auto fetch = [&](int s, const P *q, T &vb, T &vs) {
+        vb = 0; vs = 0;
+        if (s < s_lo || s > s_hi) return;
+        if (s > s_lo) vb = q[0].x;
+        if (u >= 1) vs = q[-1].y;
+      };
+      T nb, ns;
+      fetch(row0 + 1, rowp, nb, ns);
+      for (int i = 0; i < n; ++i) {
+        const int s = row0 + 1 + i;
+        const T lb = nb, ls = ns;
+        rowp += U1;
+        if (i + 1 < n) fetch(s + 1, rowp, nb, ns);
+        if (s >= s_lo && s <= s_hi) {
           T nv;
           if (u == 0) nv = own + lb;                 // only the blank predecessor
           else if (s == s_lo) nv = left + ls;        // only the symbol predecessor
@@ -134,42 +206,46 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         st += U1;
         left = neighbour<T, false>(own, xchg, xs++, lane, warp, nwarps);
       }
+      // Every thread is past its last read of this stage (it took part in the
+      // exchange of the chunk's last step): refill it.
+      if (nwarps == 1) __syncwarp();
+      if (u == 0 && j + kStages < nchunks) issue(j + kStages);
     }
     if (u == U) {
       const int64_t fin = cell_pos<MODIFIED>(Tn - 1, U, U1);
-      scores[b] = own + reinterpret_cast<const T *>(lp2 + fin)[0];
+      scores[b] = own + lp2[fin].x;
     }
   } else {
     // ------------------------------- beta ------------------------------
     // Runs the steps backwards; step s needs (blank, symbol) of its own cell.
     T *be = beta + off;
     T own = 0;
-    const int top = MODIFIED ? Tn - 1 : Tn - 1 + U;  // step of the final cell (T-1, U)
     if (u == U) {
-      own = reinterpret_cast<const T *>(lp2 + ((int64_t)top * U1 + U))[0];
+      own = lp2[(int64_t)top * U1 + U].x;
       be[(int64_t)top * U1 + U] = own;
     }
     T right = neighbour<T, true>(own, xchg, xs++, lane, warp, nwarps);
     // The final cell is done; column U therefore stops one step earlier.
     const int hi = (u == U) ? s_hi - 1 : s_hi;
-    auto fetch = [&](int s, T &vb, T &vs) {
-      vb = 0; vs = 0;
-      if (s < s_lo || s > hi) return;
-      const P v = lp2[(int64_t)s * U1 + u];
-      vb = v.x; vs = v.y;
-    };
-    const int first = top - 1;
-    T pb[kPrefetch], ps[kPrefetch];
-#pragma unroll
-    for (int k = 0; k < kPrefetch; ++k) fetch(first - k, pb[k], ps[k]);
-    T *st = be + ((int64_t)first * U1 + u);
-    for (int s0 = first; s0 >= 0; s0 -= kPrefetch) {
-#pragma unroll
-      for (int k = 0; k < kPrefetch; ++k) {
-        const int s = s0 - k;
-        if (s < 0) break;
-        const T lb = pb[k], ls = ps[k];
-        fetch(s - kPrefetch, pb[k], ps[k]);
+    T *st = be + ((int64_t)(top - 1) * U1 + u);  // entry of the first step
+    for (int j = 0; j < nchunks; ++j) {
+      int row0, n;
+      chunk_rows(j, row0, n);
+      wait_chunk(j);
+      const P *rowp = stage + (int64_t)(j % kStages) * stage_pairs + (int64_t)(n - 1) * U1 + u;
+      auto fetch = [&](int s, const P *q, T &vb, T &vs) {
+        vb = 0; vs = 0;
+        if (s < s_lo || s > hi) return;
+        const P v = q[0];
+        vb = v.x; vs = v.y;
+      };
+      T nb, ns;
+      fetch(row0 + n - 1, rowp, nb, ns);
+      for (int i = n - 1; i >= 0; --i) {
+        const int s = row0 + i;
+        const T lb = nb, ls = ns;
+        rowp -= U1;
+        if (i > 0) fetch(s - 1, rowp, nb, ns);
         if (s >= s_lo && s <= hi) {
           T nv;
           if (u == U) nv = own + lb;               // only the blank successor
@@ -181,6 +257,8 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         st -= U1;
         right = neighbour<T, true>(own, xchg, xs++, lane, warp, nwarps);
       }
+      if (nwarps == 1) __syncwarp();
+      if (u == 0 && j + kStages < nchunks) issue(j + kStages);
     }
     if (u == 0) scores_beta[b] = own;
   }
@@ -263,30 +341,54 @@ lattice_generic_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   }
 }
 
+template <typename T, bool FAST, bool MODIFIED>
+cudaError_t launch_staged(const Problem &p, void *scores, cudaStream_t s) {
+  using P = typename Pair<T>::type;
+  auto kernel = lattice_kernel<T, FAST, MODIFIED>;
+  const int cols = p.max_u + 1;
+  // rows per chunk: even, at least 2, about kChunkBytes per chunk
+  int R = (int)(kChunkBytes / ((int64_t)cols * sizeof(P)));
+  R = (R < 2) ? 2 : (R > 256 ? 256 : (R & ~1));
+  const int stage_pairs = ((R * cols + 1) & ~1) + 2;  // + slack for the 16-byte round-up
+  const size_t smem = (size_t)kStages * stage_pairs * sizeof(P);
+  static size_t granted[64] = {0};  // per device: dynamic shared memory opted in so far
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (smem > 48 * 1024 && smem > granted[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    granted[dev] = smem;
+  }
+  const unsigned block = (unsigned)((cols + kWarp - 1) / kWarp * kWarp);
+  kernel<<<2u * (unsigned)p.N, block, smem, s>>>(
+      reinterpret_cast<const T *>(p.ws + p.lay.lp), p.T, p.U,
+      reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
+      reinterpret_cast<int32_t *>(p.ws + p.lay.status),
+      reinterpret_cast<T *>(p.ws + p.lay.alpha), reinterpret_cast<T *>(p.ws + p.lay.beta),
+      static_cast<T *>(scores), reinterpret_cast<T *>(p.ws + p.lay.scores_beta), R, stage_pairs);
+  return cudaGetLastError();
+}
+
 template <typename T>
 cudaError_t launch_lattice_t(const Problem &p, void *scores, cudaStream_t s) {
-  const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
-  const int64_t *csplit = reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split);
-  const T *lp = reinterpret_cast<const T *>(p.ws + p.lay.lp);
-  T *alpha = reinterpret_cast<T *>(p.ws + p.lay.alpha);
-  T *beta = reinterpret_cast<T *>(p.ws + p.lay.beta);
-  T *sb = reinterpret_cast<T *>(p.ws + p.lay.scores_beta);
-  T *sa = static_cast<T *>(scores);
   const bool modified = p.flags & OT_B200_ONE_SYM_PER_FRAME;
   const bool fast = p.flags & OT_B200_FAST_MATH;
-  const unsigned grid = 2u * (unsigned)p.N;
-  const int cols = p.max_u + 1;
-  if (cols > 1024) {
+  if (p.max_u + 1 > 1024) {
+    const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
+    const int64_t *csplit = reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split);
+    const T *lp = reinterpret_cast<const T *>(p.ws + p.lay.lp);
+    T *alpha = reinterpret_cast<T *>(p.ws + p.lay.alpha);
+    T *beta = reinterpret_cast<T *>(p.ws + p.lay.beta);
+    T *sb = reinterpret_cast<T *>(p.ws + p.lay.scores_beta);
+    T *sa = static_cast<T *>(scores);
+    const unsigned grid = 2u * (unsigned)p.N;
     if (modified) lattice_generic_kernel<T, true><<<grid, 1024, 0, s>>>(lp, p.T, p.U, csplit, status, alpha, beta, sa, sb);
     else lattice_generic_kernel<T, false><<<grid, 1024, 0, s>>>(lp, p.T, p.U, csplit, status, alpha, beta, sa, sb);
     return cudaGetLastError();
   }
-  const unsigned block = (unsigned)((cols + kWarp - 1) / kWarp * kWarp);
-#define OTB_LAT(F, M) lattice_kernel<T, F, M><<<grid, block, 0, s>>>(lp, p.T, p.U, csplit, status, alpha, beta, sa, sb)
-  if (fast) { if (modified) OTB_LAT(true, true); else OTB_LAT(true, false); }
-  else      { if (modified) OTB_LAT(false, true); else OTB_LAT(false, false); }
-#undef OTB_LAT
-  return cudaGetLastError();
+  if (fast) return modified ? launch_staged<T, true, true>(p, scores, s) : launch_staged<T, true, false>(p, scores, s);
+  return modified ? launch_staged<T, false, true>(p, scores, s) : launch_staged<T, false, false>(p, scores, s);
 }
 
 }  // namespace

@@ -303,8 +303,7 @@ def test_status_word_without_the_blocking_check(monkeypatch):
     call.forward()  # no exception: the status stays on the device
     code, index = ctypes.c_int32(), ctypes.c_int32()
     rc = call.lib.ot_b200_read_input_status(call.workspace.data_ptr(), int(call.layout.total_bytes),
-                                            call.n, call.rows, call.flags, ctypes.byref(code),
-                                            ctypes.byref(index), None)
+                                            ctypes.byref(code), ctypes.byref(index), None)
     assert rc == _lib.OK and code.value == 4 and index.value == 1
 
 
