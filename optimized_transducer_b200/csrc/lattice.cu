@@ -115,7 +115,8 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   const int nact = nwarps * kWarp;
   const int64_t off = cell_split[b];
   const P *lp2 = reinterpret_cast<const P *>(lp) + off;
-  P *stage = reinterpret_cast<P *>(stage_mem);
+  // two pairs of slack in front: column 0 reads (and discards) the pair before its row
+  P *stage = reinterpret_cast<P *>(stage_mem) + 2;
   const bool col = u < U1;  // this thread owns a lattice column
   const int diff = Tn - 1 - U;
   // Steps (s_lo..s_hi) during which this thread computes a cell.  Standard:
@@ -166,43 +167,48 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     atomicCAS(status + kStatusLatticeTimeout, 0, 1 + b);
   };
   int xs = 0;
+  const T ninf = neg_inf<T>();
+  const int uc = col ? u : U;  // column used for addressing (keeps idle lanes in bounds)
+  // A step is branch-free: both predecessors always enter the log-add, and a
+  // predecessor that does not exist contributes -inf (a column that has not
+  // started holds -inf, a log-prob outside the column's step range is read as
+  // -inf), for which log_add returns the other operand exactly.
 
   if (!backward) {
     // ------------------------------ alpha ------------------------------
     T *al = alpha + off;
-    T own = 0;
+    T own = (u == 0) ? (T)0 : ninf;
     if (u == 0) al[0] = 0;
     T left = neighbour<T, false>(own, xchg, xs++, lane, warp, nwarps);
-    T *st = al + (int64_t)U1 + u;  // entry of step 1
+    T *st = al + (int64_t)U1 + uc;  // entry of step 1
+    const unsigned span = (unsigned)(s_hi - s_lo);
     for (int j = 0; j < nchunks; ++j) {
       int row0, n;
       chunk_rows(j, row0, n);
       wait_chunk(j);
-      const P *rowp = stage + (int64_t)(j % kStages) * stage_pairs + u;
+      const P *rowp = stage + (int64_t)(j % kStages) * stage_pairs + uc;
       // Step s = row + 1 needs, from wavefront row `row`: the blank log-prob of
-      // this column (standard blank(t-1,u); modified the same) and the symbol
-      // log-prob of column u-1 (standard sym(t,u-1); modified sym(t-1,u-1)).
+      // this column (blank(t-1,u)) if s_lo < s <= s_hi, and the symbol log-prob
+      // of column u-1 (standard sym(t,u-1); modified sym(t-1,u-1)) if u >= 1
+      // and s_lo <= s <= s_hi.
       auto fetch = [&](int s, const P *q, T &vb, T &vs) {
-        vb = 0; vs = 0;
-        if (s < s_lo || s > s_hi) return;
-        if (s > s_lo) vb = q[0].x;
-        if (u >= 1) vs = q[-1].y;
+        const T x = q[0].x, y = q[-1].y;
+        const unsigned rel = (unsigned)(s - s_lo);
+        vb = (rel - 1u < span) ? x : ninf;
+        vs = (rel <= span && u >= 1) ? y : ninf;
       };
       T nb, ns;
       fetch(row0 + 1, rowp, nb, ns);
+#pragma unroll 2
       for (int i = 0; i < n; ++i) {
         const int s = row0 + 1 + i;
         const T lb = nb, ls = ns;
         rowp += U1;
         if (i + 1 < n) fetch(s + 1, rowp, nb, ns);
-        if (s >= s_lo && s <= s_hi) {
-          T nv;
-          if (u == 0) nv = own + lb;                 // only the blank predecessor
-          else if (s == s_lo) nv = left + ls;        // only the symbol predecessor
-          else nv = log_add<T, FAST>(own + lb, left + ls);
-          *st = nv;
-          own = nv;
-        }
+        const T nv = log_add<T, FAST>(own + lb, left + ls);
+        const bool act = (unsigned)(s - s_lo) <= span;
+        if (act) *st = nv;
+        own = act ? nv : own;  // a column changes only during its own steps
         st += U1;
         left = neighbour<T, false>(own, xchg, xs++, lane, warp, nwarps);
       }
@@ -219,7 +225,7 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     // ------------------------------- beta ------------------------------
     // Runs the steps backwards; step s needs (blank, symbol) of its own cell.
     T *be = beta + off;
-    T own = 0;
+    T own = ninf;
     if (u == U) {
       own = lp2[(int64_t)top * U1 + U].x;
       be[(int64_t)top * U1 + U] = own;
@@ -227,33 +233,33 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     T right = neighbour<T, true>(own, xchg, xs++, lane, warp, nwarps);
     // The final cell is done; column U therefore stops one step earlier.
     const int hi = (u == U) ? s_hi - 1 : s_hi;
-    T *st = be + ((int64_t)(top - 1) * U1 + u);  // entry of the first step
+    const unsigned span = (hi >= s_lo) ? (unsigned)(hi - s_lo) : 0u;
+    const bool any = hi >= s_lo;
+    T *st = be + ((int64_t)(top - 1) * U1 + uc);  // entry of the first step
     for (int j = 0; j < nchunks; ++j) {
       int row0, n;
       chunk_rows(j, row0, n);
       wait_chunk(j);
-      const P *rowp = stage + (int64_t)(j % kStages) * stage_pairs + (int64_t)(n - 1) * U1 + u;
+      const P *rowp = stage + (int64_t)(j % kStages) * stage_pairs + (int64_t)(n - 1) * U1 + uc;
+      // (blank(t,u), sym(t,u)) of the step's own cell; column U has no symbol.
       auto fetch = [&](int s, const P *q, T &vb, T &vs) {
-        vb = 0; vs = 0;
-        if (s < s_lo || s > hi) return;
         const P v = q[0];
-        vb = v.x; vs = v.y;
+        const bool in = any && (unsigned)(s - s_lo) <= span;
+        vb = in ? v.x : ninf;
+        vs = (in && u < U) ? v.y : ninf;
       };
       T nb, ns;
       fetch(row0 + n - 1, rowp, nb, ns);
+#pragma unroll 2
       for (int i = n - 1; i >= 0; --i) {
         const int s = row0 + i;
         const T lb = nb, ls = ns;
         rowp -= U1;
         if (i > 0) fetch(s - 1, rowp, nb, ns);
-        if (s >= s_lo && s <= hi) {
-          T nv;
-          if (u == U) nv = own + lb;               // only the blank successor
-          else if (s == s_hi) nv = right + ls;     // last row / band edge: only the symbol successor
-          else nv = log_add<T, FAST>(own + lb, right + ls);
-          *st = nv;
-          own = nv;
-        }
+        const T nv = log_add<T, FAST>(own + lb, right + ls);
+        const bool act = any && (unsigned)(s - s_lo) <= span;
+        if (act) *st = nv;
+        own = act ? nv : own;   // column U keeps the final cell until its steps begin
         st -= U1;
         right = neighbour<T, true>(own, xchg, xs++, lane, warp, nwarps);
       }
@@ -350,12 +356,13 @@ cudaError_t launch_staged(const Problem &p, void *scores, cudaStream_t s) {
   int R = (int)(kChunkBytes / ((int64_t)cols * sizeof(P)));
   R = (R < 2) ? 2 : (R > 256 ? 256 : (R & ~1));
   const int stage_pairs = ((R * cols + 1) & ~1) + 2;  // + slack for the 16-byte round-up
-  const size_t smem = (size_t)kStages * stage_pairs * sizeof(P);
+  const size_t smem = ((size_t)kStages * stage_pairs + 2) * sizeof(P);
   static size_t granted[64] = {0};  // per device: dynamic shared memory opted in so far
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
-  if (smem > 48 * 1024 && smem > granted[dev]) {
+  // static shared memory counts against the 48 KB default as well
+  if (smem + 2048 > 48 * 1024 && smem > granted[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     granted[dev] = smem;

@@ -172,15 +172,18 @@ template <> __device__ __forceinline__ double min_log_diff<double>() { return -3
 // too negative difference returns the larger operand.
 template <typename T, bool FAST>
 __device__ __forceinline__ T log_add(T a, T b) {
+  // Written without branches: the correction is always evaluated and then
+  // selected, so a warp never diverges inside the recursion.
   const T hi = (a < b) ? b : a;
   const T d = (a < b) ? (a - b) : (b - a);
-  if (!(d >= min_log_diff<T>())) return hi;
+  T corr;
   if constexpr (FAST && sizeof(T) == 4) {
     // ex2/lg2 approximations: absolute error of the correction < 3e-7.
-    return hi + __logf(1.0f + ex2_approx(d * kLog2e));
+    corr = __logf(1.0f + ex2_approx(d * kLog2e));
   } else {
-    return hi + r_log1p(r_exp(d));
+    corr = r_log1p(r_exp(d));
   }
+  return (d >= min_log_diff<T>()) ? hi + corr : hi;
 }
 
 template <typename T>
