@@ -9,21 +9,30 @@
 // One CTA per (utterance, direction): 2N CTAs, alpha and beta of an utterance
 // run concurrently.  Thread u owns lattice column u and keeps the wavefront in
 // registers: its own previous value is the t-neighbour, the u-neighbour comes
-// from the adjacent lane by a warp shuffle and across warps through two
-// shared-memory words per warp and one named barrier per step.
+// from the adjacent lane by a warp shuffle.
 //
 //   standard transducer : anti-diagonal wavefront, T+U-1 steps
 //   one symbol per frame: both predecessors lie in the previous frame, so the
 //                         sweep is frame-synchronous, T-1 steps
 //
-// The kernel is latency-bound (a chain of T+U dependent log-add-exps), so
-// nothing on the chain may wait for global memory.  The per-cell arrays are
-// stored in wavefront order (cell_pos in ot_common.cuh): the log-probs the
-// steps consume are one contiguous stream, which TMA bulk copies
-// (cp.async.bulk + mbarrier, kStages chunks in flight) bring into shared memory
-// ahead of the recursion; a step reads its two log-probs from shared memory,
-// one step early.  Alpha and beta are written to global memory as a side effect
-// (coalesced, never read back here).
+// The kernel is latency-bound: a chain of T+U dependent log-add-exps.  Three
+// things keep everything else off that chain:
+//  * The per-cell arrays are stored in wavefront order (cell_pos in
+//    ot_common.cuh), so the log-probs the steps consume are one contiguous
+//    stream.  TMA bulk copies (cp.async.bulk + mbarrier, kStages chunks in
+//    flight) bring it into shared memory ahead of the recursion; a step reads
+//    its two log-probs from shared memory one step early.
+//  * A step is branch-free: a predecessor that does not exist enters the
+//    log-add as -inf.
+//  * Warps are not synchronised with each other.  The value that crosses a warp
+//    boundary goes through a small ring in shared memory whose slots double as
+//    flags (a reserved NaN bit pattern means "empty"): the producing lane waits
+//    for an empty slot, the consuming lane for a full one and empties it again.
+//    The consumer settles a few dozen cycles behind the producer, after which
+//    neither waits.  Every wait is bounded; a wait that runs out sets a status
+//    word and the kernel carries on (with wrong numbers, never with a hang).
+// Alpha and beta are written to global memory as a side effect (coalesced,
+// never read back here).
 //
 // Lattices wider than 1024 columns use the generic kernel at the end of the
 // file (several columns per thread, wavefront kept in global memory).
@@ -34,9 +43,12 @@ namespace otb {
 namespace {
 
 constexpr int kMaxWarps = 32;
-constexpr int kStages = 3;
-constexpr int kStatusLatticeTimeout = 2;  // status word: a bulk copy never arrived
+constexpr int kStages = 4;
+constexpr int kRing = 64;                  // slots per warp boundary (power of two)
+constexpr int kStatusLatticeTimeout = 2;   // status word: a bounded wait ran out
 constexpr int kChunkBytes = 16384;         // target size of one staged chunk
+constexpr int kSpinCopy = 1 << 22;         // polls granted to a bulk copy
+constexpr int kSpinRing = 1 << 20;         // polls granted to a ring slot
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -69,24 +81,14 @@ __device__ __forceinline__ void bar_active(int nthreads) {
   asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
 }
 
-// Hands `own` of column u to column u+1 (DOWN == false) or to column u-1
-// (DOWN == true) and returns what this thread receives.  `xs` counts the
-// exchanges and selects one of two shared-memory buffers, so a warp that runs
-// ahead cannot overwrite a word a slower warp has not read yet.
-template <typename T, bool DOWN>
-__device__ __forceinline__ T neighbour(T own, T (*xchg)[kMaxWarps], int xs,
-                                       int lane, int warp, int nwarps) {
-  T got = DOWN ? __shfl_down_sync(kFull, own, 1) : __shfl_up_sync(kFull, own, 1);
-  if (nwarps > 1) {
-    const int edge_out = DOWN ? 0 : kWarp - 1;
-    const int edge_in = DOWN ? kWarp - 1 : 0;
-    if (lane == edge_out) xchg[xs & 1][warp] = own;
-    bar_active(nwarps * kWarp);
-    const int src = DOWN ? warp + 1 : warp - 1;
-    if (lane == edge_in && src >= 0 && src < nwarps) got = xchg[xs & 1][src];
-  }
-  return got;
-}
+// Ring slots: a reserved quiet-NaN payload marks an empty slot.  Arithmetic
+// never produces it (the hardware's own NaN is the canonical pattern).
+__device__ __forceinline__ float empty_slot(float) { return __uint_as_float(0x7fc0dead); }
+__device__ __forceinline__ double empty_slot(double) { return __longlong_as_double(0x7ff8dead0000beefLL); }
+__device__ __forceinline__ bool is_empty(float v) { return __float_as_uint(v) == 0x7fc0deadu; }
+__device__ __forceinline__ bool is_empty(double v) { return __double_as_longlong(v) == 0x7ff8dead0000beefLL; }
+template <typename T> __device__ __forceinline__ T ld_vol(const T *p) { return *reinterpret_cast<const volatile T *>(p); }
+template <typename T> __device__ __forceinline__ void st_vol(T *p, T v) { *reinterpret_cast<volatile T *>(p) = v; }
 
 template <typename T> struct Pair;
 template <> struct Pair<float> { using type = float2; };
@@ -104,7 +106,8 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   using P = typename Pair<T>::type;
   extern __shared__ __align__(128) unsigned char stage_mem[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
-  __shared__ T xchg[2][kMaxWarps];
+  __shared__ T ring[kMaxWarps][kRing];   // ring[w]: values produced by warp w's boundary lane
+  __shared__ int done_chunk[kMaxWarps];  // chunks warp w has finished reading
   if (status[kStatusCode] != 0) return;
   const int b = blockIdx.x >> 1;
   const bool backward = blockIdx.x & 1;
@@ -128,6 +131,8 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   else { s_lo = u; s_hi = u + Tn - 1; }
   if (!col) { s_lo = 1 << 30; s_hi = -1; }
   const int top = MODIFIED ? Tn - 1 : Tn - 1 + U;  // step of the final cell (T-1, U)
+  const T ninf = neg_inf<T>();
+  const T kEmpty = empty_slot(T(0));
 
   // Wavefront rows 0 .. top-1 are streamed: alpha's step s reads row s-1
   // (ascending), beta's step s reads row s (descending).
@@ -139,7 +144,9 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (nwarps > 1) bar_active(nact); else __syncwarp();
+  for (int i = lane; i < kRing; i += kWarp) ring[warp][i] = kEmpty;
+  if (lane == 0) done_chunk[warp] = 0;
+  if (nwarps > 1) bar_active(nact); else __syncwarp();  // the only CTA-wide barrier
   // Chunk j in processing order covers memory rows [row0, row0 + n).
   auto chunk_rows = [&](int j, int &row0, int &n) {
     const int m = backward ? nchunks - 1 - j : j;
@@ -156,19 +163,31 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     tma_load_1d(stage + (int64_t)(j % kStages) * stage_pairs, lp2 + (int64_t)row0 * U1, bytes, bar);
   };
   if (u == 0) for (int j = 0; j < kStages && j < nchunks; ++j) issue(j);
+  auto timeout = [&]() { atomicCAS(status + kStatusLatticeTimeout, 0, 1 + b); };
   auto wait_chunk = [&](int j) {
     uint64_t *bar = &full_bar[j % kStages];
     const uint32_t parity = (uint32_t)((j / kStages) & 1);
-    // Bounded: a copy that never lands is reported through the status word and
-    // the recursion goes on with whatever the stage holds (no thread leaves the
-    // barriers of the steps early, so nothing can hang).
-    for (int spin = 0; spin < (1 << 22); ++spin)
+    for (int spin = 0; spin < kSpinCopy; ++spin)
       if (mbar_try_wait(bar, parity)) return;
-    atomicCAS(status + kStatusLatticeTimeout, 0, 1 + b);
+    timeout();
   };
-  int xs = 0;
-  const T ninf = neg_inf<T>();
-  const int uc = col ? u : U;  // column used for addressing (keeps idle lanes in bounds)
+  // After chunk j: publish it, and let thread 0 refill the stage of chunk j-1
+  // once every warp has finished reading that chunk.
+  auto chunk_done = [&](int j) {
+    __syncwarp();
+    if (lane == 0) st_vol(&done_chunk[warp], j + 1);
+    if (u == 0 && j >= 1 && j - 1 + kStages < nchunks) {
+      for (int w = 1; w < nwarps; ++w) {
+        int spin = 0;
+        while (ld_vol(&done_chunk[w]) < j && ++spin < kSpinCopy) {}
+        if (spin >= kSpinCopy) timeout();
+      }
+      issue(j - 1 + kStages);
+    }
+  };
+  constexpr int kMask = kRing - 1;
+  // Column used for addressing (keeps the idle lanes of the last warp in bounds).
+  const int uc = col ? u : U;
   // A step is branch-free: both predecessors always enter the log-add, and a
   // predecessor that does not exist contributes -inf (a column that has not
   // started holds -inf, a log-prob outside the column's step range is read as
@@ -176,10 +195,17 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
 
   if (!backward) {
     // ------------------------------ alpha ------------------------------
+    // Boundary values flow upwards: lane 31 of warp w -> lane 0 of warp w+1.
+    const bool produce = (lane == kWarp - 1) && (warp + 1 < nwarps);
+    const bool consume = (lane == 0) && (warp > 0);
+    T *out_ring = ring[warp];
+    const T *in_ring = ring[consume ? warp - 1 : 0];
     T *al = alpha + off;
     T own = (u == 0) ? (T)0 : ninf;
     if (u == 0) al[0] = 0;
-    T left = neighbour<T, false>(own, xchg, xs++, lane, warp, nwarps);
+    // value the consumer lane needs at step 1: column u-1 before any step
+    T edge = ninf;
+    T slot_state = kEmpty;  // producer: the slot of the coming step, as last seen
     T *st = al + (int64_t)U1 + uc;  // entry of step 1
     const unsigned span = (unsigned)(s_hi - s_lo);
     for (int j = 0; j < nchunks; ++j) {
@@ -199,23 +225,38 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       };
       T nb, ns;
       fetch(row0 + 1, rowp, nb, ns);
-#pragma unroll 2
       for (int i = 0; i < n; ++i) {
         const int s = row0 + 1 + i;
         const T lb = nb, ls = ns;
         rowp += U1;
         if (i + 1 < n) fetch(s + 1, rowp, nb, ns);
+        T left = __shfl_up_sync(kFull, own, 1);
+        if (consume) {
+          if (s > 1) {
+            const T *slot = in_ring + ((s - 1) & kMask);
+            int spin = 0;
+            while (is_empty(edge) && ++spin < kSpinRing) edge = ld_vol(slot);
+            if (spin >= kSpinRing) timeout();
+            st_vol(const_cast<T *>(slot), kEmpty);  // hand the slot back
+          }
+          left = edge;
+        }
         const T nv = log_add<T, FAST>(own + lb, left + ls);
         const bool act = (unsigned)(s - s_lo) <= span;
         if (act) *st = nv;
         own = act ? nv : own;  // a column changes only during its own steps
         st += U1;
-        left = neighbour<T, false>(own, xchg, xs++, lane, warp, nwarps);
+        if (produce) {
+          T *slot = out_ring + (s & kMask);
+          int spin = 0;
+          while (!is_empty(slot_state) && ++spin < kSpinRing) slot_state = ld_vol(slot);
+          if (spin >= kSpinRing) timeout();
+          st_vol(slot, own);
+          slot_state = ld_vol(out_ring + ((s + 1) & kMask));  // for the next step
+        }
+        if (consume) edge = ld_vol(in_ring + (s & kMask));     // for the next step
       }
-      // Every thread is past its last read of this stage (it took part in the
-      // exchange of the chunk's last step): refill it.
-      if (nwarps == 1) __syncwarp();
-      if (u == 0 && j + kStages < nchunks) issue(j + kStages);
+      chunk_done(j);
     }
     if (u == U) {
       const int64_t fin = cell_pos<MODIFIED>(Tn - 1, U, U1);
@@ -224,13 +265,21 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   } else {
     // ------------------------------- beta ------------------------------
     // Runs the steps backwards; step s needs (blank, symbol) of its own cell.
+    // Boundary values flow downwards: lane 0 of warp w -> lane 31 of warp w-1.
+    const bool produce = (lane == 0) && (warp > 0);
+    const bool consume = (lane == kWarp - 1) && (warp + 1 < nwarps);
+    T *out_ring = ring[warp];
+    const T *in_ring = ring[consume ? warp + 1 : 0];
     T *be = beta + off;
+    const T fin = lp2[(int64_t)top * U1 + U].x;  // beta(T-1,U) = blank log-prob of the final cell
     T own = ninf;
     if (u == U) {
-      own = lp2[(int64_t)top * U1 + U].x;
+      own = fin;
       be[(int64_t)top * U1 + U] = own;
     }
-    T right = neighbour<T, true>(own, xchg, xs++, lane, warp, nwarps);
+    // value the consumer lane needs at the first step: column u+1 before any step
+    T edge = (u + 1 == U) ? fin : ninf;
+    T slot_state = kEmpty;
     // The final cell is done; column U therefore stops one step earlier.
     const int hi = (u == U) ? s_hi - 1 : s_hi;
     const unsigned span = (hi >= s_lo) ? (unsigned)(hi - s_lo) : 0u;
@@ -250,21 +299,38 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       };
       T nb, ns;
       fetch(row0 + n - 1, rowp, nb, ns);
-#pragma unroll 2
       for (int i = n - 1; i >= 0; --i) {
         const int s = row0 + i;
         const T lb = nb, ls = ns;
         rowp -= U1;
         if (i > 0) fetch(s - 1, rowp, nb, ns);
+        T right = __shfl_down_sync(kFull, own, 1);
+        if (consume) {
+          if (s < top - 1) {
+            const T *slot = in_ring + ((s + 1) & kMask);
+            int spin = 0;
+            while (is_empty(edge) && ++spin < kSpinRing) edge = ld_vol(slot);
+            if (spin >= kSpinRing) timeout();
+            st_vol(const_cast<T *>(slot), kEmpty);
+          }
+          right = edge;
+        }
         const T nv = log_add<T, FAST>(own + lb, right + ls);
         const bool act = any && (unsigned)(s - s_lo) <= span;
         if (act) *st = nv;
         own = act ? nv : own;   // column U keeps the final cell until its steps begin
         st -= U1;
-        right = neighbour<T, true>(own, xchg, xs++, lane, warp, nwarps);
+        if (produce) {
+          T *slot = out_ring + (s & kMask);
+          int spin = 0;
+          while (!is_empty(slot_state) && ++spin < kSpinRing) slot_state = ld_vol(slot);
+          if (spin >= kSpinRing) timeout();
+          st_vol(slot, own);
+          slot_state = ld_vol(out_ring + ((s - 1) & kMask));
+        }
+        if (consume) edge = ld_vol(in_ring + (s & kMask));
       }
-      if (nwarps == 1) __syncwarp();
-      if (u == 0 && j + kStages < nchunks) issue(j + kStages);
+      chunk_done(j);
     }
     if (u == 0) scores_beta[b] = own;
   }
