@@ -196,65 +196,67 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   if (!backward) {
     // ------------------------------ alpha ------------------------------
     // Boundary values flow upwards: lane 31 of warp w -> lane 0 of warp w+1.
+    // Slot (s & kMask) of ring[w] carries column 32w+31 after step s.
     const bool produce = (lane == kWarp - 1) && (warp + 1 < nwarps);
     const bool consume = (lane == 0) && (warp > 0);
     T *out_ring = ring[warp];
-    const T *in_ring = ring[consume ? warp - 1 : 0];
+    T *in_ring = ring[consume ? warp - 1 : 0];
     T *al = alpha + off;
     T own = (u == 0) ? (T)0 : ninf;
     if (u == 0) al[0] = 0;
-    // value the consumer lane needs at step 1: column u-1 before any step
-    T edge = ninf;
-    T slot_state = kEmpty;  // producer: the slot of the coming step, as last seen
+    T edge = ninf;          // consumer: column u-1 as step 1 needs it (before any step)
+    T slot_state = kEmpty;  // producer: the slot of the current step, as last seen
     T *st = al + (int64_t)U1 + uc;  // entry of step 1
     const unsigned span = (unsigned)(s_hi - s_lo);
+    // Step s = row + 1 needs, from wavefront row `row`: the blank log-prob of
+    // this column (blank(t-1,u)) if s_lo < s <= s_hi, and the symbol log-prob of
+    // column u-1 (standard sym(t,u-1); modified sym(t-1,u-1)) if u >= 1 and
+    // s_lo <= s <= s_hi.
+    auto mask = [&](int s, T x, T y, T &vb, T &vs) {
+      const unsigned rel = (unsigned)(s - s_lo);
+      vb = (rel - 1u < span) ? x : ninf;
+      vs = (rel <= span && u >= 1) ? y : ninf;
+    };
     for (int j = 0; j < nchunks; ++j) {
       int row0, n;
       chunk_rows(j, row0, n);
       wait_chunk(j);
       const P *rowp = stage + (int64_t)(j % kStages) * stage_pairs + uc;
-      // Step s = row + 1 needs, from wavefront row `row`: the blank log-prob of
-      // this column (blank(t-1,u)) if s_lo < s <= s_hi, and the symbol log-prob
-      // of column u-1 (standard sym(t,u-1); modified sym(t-1,u-1)) if u >= 1
-      // and s_lo <= s <= s_hi.
-      auto fetch = [&](int s, const P *q, T &vb, T &vs) {
-        const T x = q[0].x, y = q[-1].y;
-        const unsigned rel = (unsigned)(s - s_lo);
-        vb = (rel - 1u < span) ? x : ninf;
-        vs = (rel <= span && u >= 1) ? y : ninf;
-      };
-      T nb, ns;
-      fetch(row0 + 1, rowp, nb, ns);
+      T lb, ls;
+      mask(row0 + 1, rowp[0].x, rowp[-1].y, lb, ls);
       for (int i = 0; i < n; ++i) {
         const int s = row0 + 1 + i;
-        const T lb = nb, ls = ns;
+        // (1) loads for the NEXT step, issued before the dependent chain
         rowp += U1;
-        if (i + 1 < n) fetch(s + 1, rowp, nb, ns);
+        const bool more = i + 1 < n;
+        const T x_next = more ? rowp[0].x : ninf;
+        const T y_next = more ? rowp[-1].y : ninf;
+        const T edge_next = consume ? ld_vol(in_ring + (s & kMask)) : ninf;
+        const T state_next = produce ? ld_vol(out_ring + ((s + 1) & kMask)) : kEmpty;
+        // (2) the chain
         T left = __shfl_up_sync(kFull, own, 1);
-        if (consume) {
-          if (s > 1) {
-            const T *slot = in_ring + ((s - 1) & kMask);
-            int spin = 0;
-            while (is_empty(edge) && ++spin < kSpinRing) edge = ld_vol(slot);
-            if (spin >= kSpinRing) timeout();
-            st_vol(const_cast<T *>(slot), kEmpty);  // hand the slot back
-          }
-          left = edge;
-        }
+        left = consume ? edge : left;
         const T nv = log_add<T, FAST>(own + lb, left + ls);
         const bool act = (unsigned)(s - s_lo) <= span;
-        if (act) *st = nv;
         own = act ? nv : own;  // a column changes only during its own steps
+        // (3) stores
+        if (act) *st = nv;
         st += U1;
-        if (produce) {
-          T *slot = out_ring + (s & kMask);
+        if (produce) st_vol(out_ring + (s & kMask), own);
+        if (consume && s > 1) st_vol(in_ring + ((s - 1) & kMask), kEmpty);  // hand the slot back
+        // (4) next step's operands
+        mask(s + 1, x_next, y_next, lb, ls);
+        edge = edge_next;
+        slot_state = state_next;
+        // (5) rare: the neighbour warp is not far enough ahead (or behind)
+        if ((consume && is_empty(edge)) || (produce && !is_empty(slot_state))) {
           int spin = 0;
-          while (!is_empty(slot_state) && ++spin < kSpinRing) slot_state = ld_vol(slot);
+          if (consume)
+            while (is_empty(edge) && ++spin < kSpinRing) edge = ld_vol(in_ring + (s & kMask));
+          if (produce)
+            while (!is_empty(slot_state) && ++spin < kSpinRing) slot_state = ld_vol(out_ring + ((s + 1) & kMask));
           if (spin >= kSpinRing) timeout();
-          st_vol(slot, own);
-          slot_state = ld_vol(out_ring + ((s + 1) & kMask));  // for the next step
         }
-        if (consume) edge = ld_vol(in_ring + (s & kMask));     // for the next step
       }
       chunk_done(j);
     }
@@ -266,10 +268,11 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     // ------------------------------- beta ------------------------------
     // Runs the steps backwards; step s needs (blank, symbol) of its own cell.
     // Boundary values flow downwards: lane 0 of warp w -> lane 31 of warp w-1.
+    // Slot (s & kMask) of ring[w] carries column 32w after step s.
     const bool produce = (lane == 0) && (warp > 0);
     const bool consume = (lane == kWarp - 1) && (warp + 1 < nwarps);
     T *out_ring = ring[warp];
-    const T *in_ring = ring[consume ? warp + 1 : 0];
+    T *in_ring = ring[consume ? warp + 1 : 0];
     T *be = beta + off;
     const T fin = lp2[(int64_t)top * U1 + U].x;  // beta(T-1,U) = blank log-prob of the final cell
     T own = ninf;
@@ -277,58 +280,62 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       own = fin;
       be[(int64_t)top * U1 + U] = own;
     }
-    // value the consumer lane needs at the first step: column u+1 before any step
-    T edge = (u + 1 == U) ? fin : ninf;
+    T edge = (u + 1 == U) ? fin : ninf;  // consumer: column u+1 before any step
     T slot_state = kEmpty;
     // The final cell is done; column U therefore stops one step earlier.
     const int hi = (u == U) ? s_hi - 1 : s_hi;
     const unsigned span = (hi >= s_lo) ? (unsigned)(hi - s_lo) : 0u;
     const bool any = hi >= s_lo;
     T *st = be + ((int64_t)(top - 1) * U1 + uc);  // entry of the first step
+    // (blank(t,u), sym(t,u)) of the step's own cell; column U has no symbol.
+    auto mask = [&](int s, T x, T y, T &vb, T &vs) {
+      const bool in = any && (unsigned)(s - s_lo) <= span;
+      vb = in ? x : ninf;
+      vs = (in && u < U) ? y : ninf;
+    };
     for (int j = 0; j < nchunks; ++j) {
       int row0, n;
       chunk_rows(j, row0, n);
       wait_chunk(j);
       const P *rowp = stage + (int64_t)(j % kStages) * stage_pairs + (int64_t)(n - 1) * U1 + uc;
-      // (blank(t,u), sym(t,u)) of the step's own cell; column U has no symbol.
-      auto fetch = [&](int s, const P *q, T &vb, T &vs) {
-        const P v = q[0];
-        const bool in = any && (unsigned)(s - s_lo) <= span;
-        vb = in ? v.x : ninf;
-        vs = (in && u < U) ? v.y : ninf;
-      };
-      T nb, ns;
-      fetch(row0 + n - 1, rowp, nb, ns);
+      T lb, ls;
+      {
+        const P v = rowp[0];
+        mask(row0 + n - 1, v.x, v.y, lb, ls);
+      }
       for (int i = n - 1; i >= 0; --i) {
         const int s = row0 + i;
-        const T lb = nb, ls = ns;
+        // (1) loads for the NEXT step (s - 1)
         rowp -= U1;
-        if (i > 0) fetch(s - 1, rowp, nb, ns);
+        P v_next;
+        v_next.x = ninf; v_next.y = ninf;
+        if (i > 0) v_next = rowp[0];
+        const T edge_next = consume ? ld_vol(in_ring + (s & kMask)) : ninf;
+        const T state_next = produce ? ld_vol(out_ring + ((s - 1) & kMask)) : kEmpty;
+        // (2) the chain
         T right = __shfl_down_sync(kFull, own, 1);
-        if (consume) {
-          if (s < top - 1) {
-            const T *slot = in_ring + ((s + 1) & kMask);
-            int spin = 0;
-            while (is_empty(edge) && ++spin < kSpinRing) edge = ld_vol(slot);
-            if (spin >= kSpinRing) timeout();
-            st_vol(const_cast<T *>(slot), kEmpty);
-          }
-          right = edge;
-        }
+        right = consume ? edge : right;
         const T nv = log_add<T, FAST>(own + lb, right + ls);
         const bool act = any && (unsigned)(s - s_lo) <= span;
-        if (act) *st = nv;
         own = act ? nv : own;   // column U keeps the final cell until its steps begin
+        // (3) stores
+        if (act) *st = nv;
         st -= U1;
-        if (produce) {
-          T *slot = out_ring + (s & kMask);
+        if (produce) st_vol(out_ring + (s & kMask), own);
+        if (consume && s < top - 1) st_vol(in_ring + ((s + 1) & kMask), kEmpty);
+        // (4) next step's operands
+        mask(s - 1, v_next.x, v_next.y, lb, ls);
+        edge = edge_next;
+        slot_state = state_next;
+        // (5) rare: the neighbour warp is not far enough ahead (or behind)
+        if ((consume && is_empty(edge)) || (produce && !is_empty(slot_state))) {
           int spin = 0;
-          while (!is_empty(slot_state) && ++spin < kSpinRing) slot_state = ld_vol(slot);
+          if (consume)
+            while (is_empty(edge) && ++spin < kSpinRing) edge = ld_vol(in_ring + (s & kMask));
+          if (produce)
+            while (!is_empty(slot_state) && ++spin < kSpinRing) slot_state = ld_vol(out_ring + ((s - 1) & kMask));
           if (spin >= kSpinRing) timeout();
-          st_vol(slot, own);
-          slot_state = ld_vol(out_ring + ((s - 1) & kMask));
         }
-        if (consume) edge = ld_vol(in_ring + (s & kMask));
       }
       chunk_done(j);
     }
@@ -427,8 +434,8 @@ cudaError_t launch_staged(const Problem &p, void *scores, cudaStream_t s) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
-  // static shared memory counts against the 48 KB default as well
-  if (smem + 2048 > 48 * 1024 && smem > granted[dev]) {
+  // always opt in: static shared memory (rings) counts against the 48 KB default too
+  if (smem > granted[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     granted[dev] = smem;
