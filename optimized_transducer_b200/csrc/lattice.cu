@@ -251,8 +251,13 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         // (5) rare: the neighbour warp is not far enough ahead (or behind)
         if ((consume && is_empty(edge)) || (produce && !is_empty(slot_state))) {
           int spin = 0;
-          if (consume)
+          if (consume) {
             while (is_empty(edge) && ++spin < kSpinRing) edge = ld_vol(in_ring + (s & kMask));
+            // Drop a whole step behind the producer: from then on the early
+            // load of (1) finds its slot filled and this path is not taken.
+            if (s + 1 <= top)
+              while (is_empty(ld_vol(in_ring + ((s + 1) & kMask))) && ++spin < kSpinRing) {}
+          }
           if (produce)
             while (!is_empty(slot_state) && ++spin < kSpinRing) slot_state = ld_vol(out_ring + ((s + 1) & kMask));
           if (spin >= kSpinRing) timeout();
@@ -330,8 +335,11 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         // (5) rare: the neighbour warp is not far enough ahead (or behind)
         if ((consume && is_empty(edge)) || (produce && !is_empty(slot_state))) {
           int spin = 0;
-          if (consume)
+          if (consume) {
             while (is_empty(edge) && ++spin < kSpinRing) edge = ld_vol(in_ring + (s & kMask));
+            if (s - 1 >= 0)  // drop a whole step behind the producer (see alpha)
+              while (is_empty(ld_vol(in_ring + ((s - 1) & kMask))) && ++spin < kSpinRing) {}
+          }
           if (produce)
             while (!is_empty(slot_state) && ++spin < kSpinRing) slot_state = ld_vol(out_ring + ((s - 1) & kMask));
           if (spin >= kSpinRing) timeout();
