@@ -9,30 +9,21 @@
 // One CTA per (utterance, direction): 2N CTAs, alpha and beta of an utterance
 // run concurrently.  Thread u owns lattice column u and keeps the wavefront in
 // registers: its own previous value is the t-neighbour, the u-neighbour comes
-// from the adjacent lane by a warp shuffle.
+// from the adjacent lane by a warp shuffle and across warps through two
+// shared-memory words per warp and one named barrier per step.
 //
 //   standard transducer : anti-diagonal wavefront, T+U-1 steps
 //   one symbol per frame: both predecessors lie in the previous frame, so the
 //                         sweep is frame-synchronous, T-1 steps
 //
-// The kernel is latency-bound: a chain of T+U dependent log-add-exps.  Three
-// things keep everything else off that chain:
-//  * The per-cell arrays are stored in wavefront order (cell_pos in
-//    ot_common.cuh), so the log-probs the steps consume are one contiguous
-//    stream.  TMA bulk copies (cp.async.bulk + mbarrier, kStages chunks in
-//    flight) bring it into shared memory ahead of the recursion; a step reads
-//    its two log-probs from shared memory one step early.
-//  * A step is branch-free: a predecessor that does not exist enters the
-//    log-add as -inf.
-//  * Warps are not synchronised with each other.  The value that crosses a warp
-//    boundary goes through a small ring in shared memory whose slots double as
-//    flags (a reserved NaN bit pattern means "empty"): the producing lane waits
-//    for an empty slot, the consuming lane for a full one and empties it again.
-//    The consumer settles a few dozen cycles behind the producer, after which
-//    neither waits.  Every wait is bounded; a wait that runs out sets a status
-//    word and the kernel carries on (with wrong numbers, never with a hang).
-// Alpha and beta are written to global memory as a side effect (coalesced,
-// never read back here).
+// The kernel is latency-bound (a chain of T+U dependent log-add-exps), so
+// nothing on the chain may wait for global memory.  The per-cell arrays are
+// stored in wavefront order (cell_pos in ot_common.cuh): the log-probs the
+// steps consume are one contiguous stream, which TMA bulk copies
+// (cp.async.bulk + mbarrier, kStages chunks in flight) bring into shared memory
+// ahead of the recursion; a step reads its two log-probs from shared memory,
+// one step early.  Alpha and beta are written to global memory as a side effect
+// (coalesced, never read back here).
 //
 // Lattices wider than 1024 columns use the generic kernel at the end of the
 // file (several columns per thread, wavefront kept in global memory).
@@ -43,12 +34,9 @@ namespace otb {
 namespace {
 
 constexpr int kMaxWarps = 32;
-constexpr int kStages = 4;
-constexpr int kRing = 64;                  // slots per warp boundary (power of two)
-constexpr int kStatusLatticeTimeout = 2;   // status word: a bounded wait ran out
+constexpr int kStages = 3;
+constexpr int kStatusLatticeTimeout = 2;  // status word: a bulk copy never arrived
 constexpr int kChunkBytes = 16384;         // target size of one staged chunk
-constexpr int kSpinCopy = 1 << 22;         // polls granted to a bulk copy
-constexpr int kSpinRing = 1 << 20;         // polls granted to a ring slot
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -81,14 +69,24 @@ __device__ __forceinline__ void bar_active(int nthreads) {
   asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
 }
 
-// Ring slots: a reserved quiet-NaN payload marks an empty slot.  Arithmetic
-// never produces it (the hardware's own NaN is the canonical pattern).
-__device__ __forceinline__ float empty_slot(float) { return __uint_as_float(0x7fc0dead); }
-__device__ __forceinline__ double empty_slot(double) { return __longlong_as_double(0x7ff8dead0000beefLL); }
-__device__ __forceinline__ bool is_empty(float v) { return __float_as_uint(v) == 0x7fc0deadu; }
-__device__ __forceinline__ bool is_empty(double v) { return __double_as_longlong(v) == 0x7ff8dead0000beefLL; }
-template <typename T> __device__ __forceinline__ T ld_vol(const T *p) { return *reinterpret_cast<const volatile T *>(p); }
-template <typename T> __device__ __forceinline__ void st_vol(T *p, T v) { *reinterpret_cast<volatile T *>(p) = v; }
+// Hands `own` of column u to column u+1 (DOWN == false) or to column u-1
+// (DOWN == true) and returns what this thread receives.  `xs` counts the
+// exchanges and selects one of two shared-memory buffers, so a warp that runs
+// ahead cannot overwrite a word a slower warp has not read yet.
+template <typename T, bool DOWN>
+__device__ __forceinline__ T neighbour(T own, T (*xchg)[kMaxWarps], int xs,
+                                       int lane, int warp, int nwarps) {
+  T got = DOWN ? __shfl_down_sync(kFull, own, 1) : __shfl_up_sync(kFull, own, 1);
+  if (nwarps > 1) {
+    const int edge_out = DOWN ? 0 : kWarp - 1;
+    const int edge_in = DOWN ? kWarp - 1 : 0;
+    if (lane == edge_out) xchg[xs & 1][warp] = own;
+    bar_active(nwarps * kWarp);
+    const int src = DOWN ? warp + 1 : warp - 1;
+    if (lane == edge_in && src >= 0 && src < nwarps) got = xchg[xs & 1][src];
+  }
+  return got;
+}
 
 template <typename T> struct Pair;
 template <> struct Pair<float> { using type = float2; };
@@ -106,8 +104,7 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   using P = typename Pair<T>::type;
   extern __shared__ __align__(128) unsigned char stage_mem[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
-  __shared__ T ring[kMaxWarps][kRing];   // ring[w]: values produced by warp w's boundary lane
-  __shared__ int done_chunk[kMaxWarps];  // chunks warp w has finished reading
+  __shared__ T xchg[2][kMaxWarps];
   if (status[kStatusCode] != 0) return;
   const int b = blockIdx.x >> 1;
   const bool backward = blockIdx.x & 1;
@@ -131,8 +128,6 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   else { s_lo = u; s_hi = u + Tn - 1; }
   if (!col) { s_lo = 1 << 30; s_hi = -1; }
   const int top = MODIFIED ? Tn - 1 : Tn - 1 + U;  // step of the final cell (T-1, U)
-  const T ninf = neg_inf<T>();
-  const T kEmpty = empty_slot(T(0));
 
   // Wavefront rows 0 .. top-1 are streamed: alpha's step s reads row s-1
   // (ascending), beta's step s reads row s (descending).
@@ -144,9 +139,7 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  for (int i = lane; i < kRing; i += kWarp) ring[warp][i] = kEmpty;
-  if (lane == 0) done_chunk[warp] = 0;
-  if (nwarps > 1) bar_active(nact); else __syncwarp();  // the only CTA-wide barrier
+  if (nwarps > 1) bar_active(nact); else __syncwarp();
   // Chunk j in processing order covers memory rows [row0, row0 + n).
   auto chunk_rows = [&](int j, int &row0, int &n) {
     const int m = backward ? nchunks - 1 - j : j;
@@ -163,31 +156,19 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     tma_load_1d(stage + (int64_t)(j % kStages) * stage_pairs, lp2 + (int64_t)row0 * U1, bytes, bar);
   };
   if (u == 0) for (int j = 0; j < kStages && j < nchunks; ++j) issue(j);
-  auto timeout = [&]() { atomicCAS(status + kStatusLatticeTimeout, 0, 1 + b); };
   auto wait_chunk = [&](int j) {
     uint64_t *bar = &full_bar[j % kStages];
     const uint32_t parity = (uint32_t)((j / kStages) & 1);
-    for (int spin = 0; spin < kSpinCopy; ++spin)
+    // Bounded: a copy that never lands is reported through the status word and
+    // the recursion goes on with whatever the stage holds (no thread leaves the
+    // barriers of the steps early, so nothing can hang).
+    for (int spin = 0; spin < (1 << 22); ++spin)
       if (mbar_try_wait(bar, parity)) return;
-    timeout();
+    atomicCAS(status + kStatusLatticeTimeout, 0, 1 + b);
   };
-  // After chunk j: publish it, and let thread 0 refill the stage of chunk j-1
-  // once every warp has finished reading that chunk.
-  auto chunk_done = [&](int j) {
-    __syncwarp();
-    if (lane == 0) st_vol(&done_chunk[warp], j + 1);
-    if (u == 0 && j >= 1 && j - 1 + kStages < nchunks) {
-      for (int w = 1; w < nwarps; ++w) {
-        int spin = 0;
-        while (ld_vol(&done_chunk[w]) < j && ++spin < kSpinCopy) {}
-        if (spin >= kSpinCopy) timeout();
-      }
-      issue(j - 1 + kStages);
-    }
-  };
-  constexpr int kMask = kRing - 1;
-  // Column used for addressing (keeps the idle lanes of the last warp in bounds).
-  const int uc = col ? u : U;
+  int xs = 0;
+  const T ninf = neg_inf<T>();
+  const int uc = col ? u : U;  // column used for addressing (keeps idle lanes in bounds)
   // A step is branch-free: both predecessors always enter the log-add, and a
   // predecessor that does not exist contributes -inf (a column that has not
   // started holds -inf, a log-prob outside the column's step range is read as
@@ -195,75 +176,46 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
 
   if (!backward) {
     // ------------------------------ alpha ------------------------------
-    // Boundary values flow upwards: lane 31 of warp w -> lane 0 of warp w+1.
-    // Slot (s & kMask) of ring[w] carries column 32w+31 after step s.
-    const bool produce = (lane == kWarp - 1) && (warp + 1 < nwarps);
-    const bool consume = (lane == 0) && (warp > 0);
-    T *out_ring = ring[warp];
-    T *in_ring = ring[consume ? warp - 1 : 0];
     T *al = alpha + off;
     T own = (u == 0) ? (T)0 : ninf;
     if (u == 0) al[0] = 0;
-    T edge = ninf;          // consumer: column u-1 as step 1 needs it (before any step)
-    T slot_state = kEmpty;  // producer: the slot of the current step, as last seen
+    T left = neighbour<T, false>(own, xchg, xs++, lane, warp, nwarps);
     T *st = al + (int64_t)U1 + uc;  // entry of step 1
     const unsigned span = (unsigned)(s_hi - s_lo);
-    // Step s = row + 1 needs, from wavefront row `row`: the blank log-prob of
-    // this column (blank(t-1,u)) if s_lo < s <= s_hi, and the symbol log-prob of
-    // column u-1 (standard sym(t,u-1); modified sym(t-1,u-1)) if u >= 1 and
-    // s_lo <= s <= s_hi.
-    auto mask = [&](int s, T x, T y, T &vb, T &vs) {
-      const unsigned rel = (unsigned)(s - s_lo);
-      vb = (rel - 1u < span) ? x : ninf;
-      vs = (rel <= span && u >= 1) ? y : ninf;
-    };
     for (int j = 0; j < nchunks; ++j) {
       int row0, n;
       chunk_rows(j, row0, n);
       wait_chunk(j);
       const P *rowp = stage + (int64_t)(j % kStages) * stage_pairs + uc;
-      T lb, ls;
-      mask(row0 + 1, rowp[0].x, rowp[-1].y, lb, ls);
+      // Step s = row + 1 needs, from wavefront row `row`: the blank log-prob of
+      // this column (blank(t-1,u)) if s_lo < s <= s_hi, and the symbol log-prob
+      // of column u-1 (standard sym(t,u-1); modified sym(t-1,u-1)) if u >= 1
+      // and s_lo <= s <= s_hi.
+      auto fetch = [&](int s, const P *q, T &vb, T &vs) {
+        const T x = q[0].x, y = q[-1].y;
+        const unsigned rel = (unsigned)(s - s_lo);
+        vb = (rel - 1u < span) ? x : ninf;
+        vs = (rel <= span && u >= 1) ? y : ninf;
+      };
+      T nb, ns;
+      fetch(row0 + 1, rowp, nb, ns);
+#pragma unroll 2
       for (int i = 0; i < n; ++i) {
         const int s = row0 + 1 + i;
-        // (1) loads for the NEXT step, issued before the dependent chain
+        const T lb = nb, ls = ns;
         rowp += U1;
-        const bool more = i + 1 < n;
-        const T x_next = more ? rowp[0].x : ninf;
-        const T y_next = more ? rowp[-1].y : ninf;
-        const T edge_next = consume ? ld_vol(in_ring + (s & kMask)) : ninf;
-        const T state_next = produce ? ld_vol(out_ring + ((s + 1) & kMask)) : kEmpty;
-        // (2) the chain
-        T left = __shfl_up_sync(kFull, own, 1);
-        left = consume ? edge : left;
+        if (i + 1 < n) fetch(s + 1, rowp, nb, ns);
         const T nv = log_add<T, FAST>(own + lb, left + ls);
         const bool act = (unsigned)(s - s_lo) <= span;
-        own = act ? nv : own;  // a column changes only during its own steps
-        // (3) stores
         if (act) *st = nv;
+        own = act ? nv : own;  // a column changes only during its own steps
         st += U1;
-        if (produce) st_vol(out_ring + (s & kMask), own);
-        if (consume && s > 1) st_vol(in_ring + ((s - 1) & kMask), kEmpty);  // hand the slot back
-        // (4) next step's operands
-        mask(s + 1, x_next, y_next, lb, ls);
-        edge = edge_next;
-        slot_state = state_next;
-        // (5) rare: the neighbour warp is not far enough ahead (or behind)
-        if ((consume && is_empty(edge)) || (produce && !is_empty(slot_state))) {
-          int spin = 0;
-          if (consume) {
-            while (is_empty(edge) && ++spin < kSpinRing) edge = ld_vol(in_ring + (s & kMask));
-            // Drop a whole step behind the producer: from then on the early
-            // load of (1) finds its slot filled and this path is not taken.
-            if (s + 1 <= top)
-              while (is_empty(ld_vol(in_ring + ((s + 1) & kMask))) && ++spin < kSpinRing) {}
-          }
-          if (produce)
-            while (!is_empty(slot_state) && ++spin < kSpinRing) slot_state = ld_vol(out_ring + ((s + 1) & kMask));
-          if (spin >= kSpinRing) timeout();
-        }
+        left = neighbour<T, false>(own, xchg, xs++, lane, warp, nwarps);
       }
-      chunk_done(j);
+      // Every thread is past its last read of this stage (it took part in the
+      // exchange of the chunk's last step): refill it.
+      if (nwarps == 1) __syncwarp();
+      if (u == 0 && j + kStages < nchunks) issue(j + kStages);
     }
     if (u == U) {
       const int64_t fin = cell_pos<MODIFIED>(Tn - 1, U, U1);
@@ -272,80 +224,47 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   } else {
     // ------------------------------- beta ------------------------------
     // Runs the steps backwards; step s needs (blank, symbol) of its own cell.
-    // Boundary values flow downwards: lane 0 of warp w -> lane 31 of warp w-1.
-    // Slot (s & kMask) of ring[w] carries column 32w after step s.
-    const bool produce = (lane == 0) && (warp > 0);
-    const bool consume = (lane == kWarp - 1) && (warp + 1 < nwarps);
-    T *out_ring = ring[warp];
-    T *in_ring = ring[consume ? warp + 1 : 0];
     T *be = beta + off;
-    const T fin = lp2[(int64_t)top * U1 + U].x;  // beta(T-1,U) = blank log-prob of the final cell
     T own = ninf;
     if (u == U) {
-      own = fin;
+      own = lp2[(int64_t)top * U1 + U].x;
       be[(int64_t)top * U1 + U] = own;
     }
-    T edge = (u + 1 == U) ? fin : ninf;  // consumer: column u+1 before any step
-    T slot_state = kEmpty;
+    T right = neighbour<T, true>(own, xchg, xs++, lane, warp, nwarps);
     // The final cell is done; column U therefore stops one step earlier.
     const int hi = (u == U) ? s_hi - 1 : s_hi;
     const unsigned span = (hi >= s_lo) ? (unsigned)(hi - s_lo) : 0u;
     const bool any = hi >= s_lo;
     T *st = be + ((int64_t)(top - 1) * U1 + uc);  // entry of the first step
-    // (blank(t,u), sym(t,u)) of the step's own cell; column U has no symbol.
-    auto mask = [&](int s, T x, T y, T &vb, T &vs) {
-      const bool in = any && (unsigned)(s - s_lo) <= span;
-      vb = in ? x : ninf;
-      vs = (in && u < U) ? y : ninf;
-    };
     for (int j = 0; j < nchunks; ++j) {
       int row0, n;
       chunk_rows(j, row0, n);
       wait_chunk(j);
       const P *rowp = stage + (int64_t)(j % kStages) * stage_pairs + (int64_t)(n - 1) * U1 + uc;
-      T lb, ls;
-      {
-        const P v = rowp[0];
-        mask(row0 + n - 1, v.x, v.y, lb, ls);
-      }
+      // (blank(t,u), sym(t,u)) of the step's own cell; column U has no symbol.
+      auto fetch = [&](int s, const P *q, T &vb, T &vs) {
+        const P v = q[0];
+        const bool in = any && (unsigned)(s - s_lo) <= span;
+        vb = in ? v.x : ninf;
+        vs = (in && u < U) ? v.y : ninf;
+      };
+      T nb, ns;
+      fetch(row0 + n - 1, rowp, nb, ns);
+#pragma unroll 2
       for (int i = n - 1; i >= 0; --i) {
         const int s = row0 + i;
-        // (1) loads for the NEXT step (s - 1)
+        const T lb = nb, ls = ns;
         rowp -= U1;
-        P v_next;
-        v_next.x = ninf; v_next.y = ninf;
-        if (i > 0) v_next = rowp[0];
-        const T edge_next = consume ? ld_vol(in_ring + (s & kMask)) : ninf;
-        const T state_next = produce ? ld_vol(out_ring + ((s - 1) & kMask)) : kEmpty;
-        // (2) the chain
-        T right = __shfl_down_sync(kFull, own, 1);
-        right = consume ? edge : right;
+        if (i > 0) fetch(s - 1, rowp, nb, ns);
         const T nv = log_add<T, FAST>(own + lb, right + ls);
         const bool act = any && (unsigned)(s - s_lo) <= span;
-        own = act ? nv : own;   // column U keeps the final cell until its steps begin
-        // (3) stores
         if (act) *st = nv;
+        own = act ? nv : own;   // column U keeps the final cell until its steps begin
         st -= U1;
-        if (produce) st_vol(out_ring + (s & kMask), own);
-        if (consume && s < top - 1) st_vol(in_ring + ((s + 1) & kMask), kEmpty);
-        // (4) next step's operands
-        mask(s - 1, v_next.x, v_next.y, lb, ls);
-        edge = edge_next;
-        slot_state = state_next;
-        // (5) rare: the neighbour warp is not far enough ahead (or behind)
-        if ((consume && is_empty(edge)) || (produce && !is_empty(slot_state))) {
-          int spin = 0;
-          if (consume) {
-            while (is_empty(edge) && ++spin < kSpinRing) edge = ld_vol(in_ring + (s & kMask));
-            if (s - 1 >= 0)  // drop a whole step behind the producer (see alpha)
-              while (is_empty(ld_vol(in_ring + ((s - 1) & kMask))) && ++spin < kSpinRing) {}
-          }
-          if (produce)
-            while (!is_empty(slot_state) && ++spin < kSpinRing) slot_state = ld_vol(out_ring + ((s - 1) & kMask));
-          if (spin >= kSpinRing) timeout();
-        }
+        right = neighbour<T, true>(own, xchg, xs++, lane, warp, nwarps);
       }
-      chunk_done(j);
+      if (nwarps == 1) __syncwarp();
+      if (u == 0 && j + kStages < nchunks) issue(j + kStages);
     }
     if (u == 0) scores_beta[b] = own;
   }
@@ -442,7 +361,7 @@ cudaError_t launch_staged(const Problem &p, void *scores, cudaStream_t s) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
-  // always opt in: static shared memory (rings) counts against the 48 KB default too
+  // always opt in: static shared memory counts against the 48 KB default as well
   if (smem > granted[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
