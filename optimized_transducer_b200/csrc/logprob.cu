@@ -5,14 +5,23 @@
 // ComputeLogProbs (optimized_transducer/csrc/kernels.cu:30-60), and, for
 // log-softmax input, ComputeLogProbsForLogSoftmax (kernels.cu:62-88).
 //
-// The grid is exactly one resident wave (SMs x blocks that fit per SM); a warp
-// takes runs of kRun consecutive rows and walks (b, t, u) incrementally inside
-// a run, so the owning utterance is searched once per run, not once per row.
-// A row is read once with 16-byte coalesced loads, all issued before the first
-// use; the reduction costs a subtract, a multiply, one ex2 and one add per
-// element (exp(x - m) = 2^((x - m)*log2e)).  The two gathered entries are re-read
-// from the lines just fetched.  HBM traffic per row: V*sizeof(T) bytes read,
-// 3*sizeof(T) bytes written.
+// The kernel is HBM-bound only if it is lean: at the roofline an SM has about
+// 150 issue slots per 2000-byte row.  So
+//  * a row is owned by a GROUP of LPR lanes (32, 16 or 8), i.e. a warp works on
+//    32/LPR rows at once: the per-row bookkeeping (position in the lattice,
+//    reductions, gather, stores) is paid once per warp instruction for all of
+//    them, and the shuffle reductions are log2(LPR) deep;
+//  * the reduction costs one FFMA, one ex2 and one add per element
+//    (exp(x - m) = 2^(x*log2e - m*log2e));
+//  * a group takes runs of kRun consecutive rows and walks (b, t, u)
+//    incrementally inside a run, so the owning utterance is searched once per
+//    run, not once per row.
+// The grid is exactly one resident wave (SMs x blocks that fit per SM).  Runs
+// are dealt round-robin, so the grid sweeps the buffer front to back and the
+// rows read last are contiguous at the end, where stage 3 starts.  A row is
+// read once with 16-byte coalesced loads, all issued before the first use; the
+// two gathered entries are re-read from the lines just fetched.  HBM traffic
+// per row: V*sizeof(T) bytes read, 3*sizeof(T) bytes written.
 #include "ot_common.cuh"
 
 namespace otb {
@@ -20,19 +29,14 @@ namespace otb {
 namespace {
 
 constexpr int kThreads = 256;
-// Rows a warp takes at a time.  Runs are dealt to the warps round-robin, so
-// the grid sweeps the buffer front to back (the rows read last are contiguous
-// at the end, where stage 3 starts) while the search for the owning utterance
-// is paid once per run.
-constexpr int kRun = 8;
+constexpr int kRun = 8;  // rows a group takes at a time
 
 // sum_k exp(x_k - m) accumulated into s, for one lane's part of a chunk.
 template <int N>
 __device__ __forceinline__ float add_exps(const float (&x)[N], float m, float s) {
-  // (x - m) first: its rounding error is random per element, whereas folding
-  // m*log2e into an FFMA would shift every term of the row the same way.
+  const float mneg = -m * kLog2e;
 #pragma unroll
-  for (int k = 0; k < N; ++k) s += ex2_approx((x[k] - m) * kLog2e);
+  for (int k = 0; k < N; ++k) s += ex2_approx(fmaf(x[k], kLog2e, mneg));
   return s;
 }
 template <int N>
@@ -42,10 +46,23 @@ __device__ __forceinline__ double add_exps(const double (&x)[N], double m, doubl
   return s;
 }
 
+template <typename T, int LPR>
+__device__ __forceinline__ T group_max(T v, unsigned mask) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v = r_max(v, __shfl_xor_sync(mask, v, o));
+  return v;
+}
+template <typename T, int LPR>
+__device__ __forceinline__ T group_sum(T v, unsigned mask) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(mask, v, o);
+  return v;
+}
+
 // T: element type.  VEC: elements per load (16 bytes, or 1 element when the
-// row stride or the base pointer is not 16-byte aligned).  CH: loads per lane
-// per chunk, i.e. a chunk covers 32*VEC*CH elements of the row.
-template <typename T, int VEC, int CH, bool MODIFIED>
+// row stride or the base pointer is not 16-byte aligned).  LPR: lanes per row.
+// CH: loads per lane per chunk, i.e. a chunk covers LPR*VEC*CH elements.
+template <typename T, int VEC, int CH, int LPR, bool MODIFIED>
 __global__ void __launch_bounds__(kThreads)
 logprob_kernel(const T *__restrict__ logits, const int32_t *__restrict__ targets,
                const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
@@ -54,86 +71,88 @@ logprob_kernel(const T *__restrict__ logits, const int32_t *__restrict__ targets
                int max_u, int blank, T *__restrict__ den, T *__restrict__ lp) {
   if (status[kStatusCode] != 0) return;
   using VT = typename VecOf<T, VEC>::type;
+  constexpr int kGroups = kWarp / LPR;  // rows a warp works on at once
   const int lane = threadIdx.x & 31;
-  const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
-  const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
+  const int gl = lane % LPR;            // lane within the group
+  const unsigned gmask = (LPR == 32) ? kFull : (((1u << LPR) - 1u) << (lane - gl));
+  const int64_t group = ((((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5) * kGroups) + lane / LPR;
+  const int64_t ngroups = (((int64_t)gridDim.x * kThreads) >> 5) * kGroups;
   const int nvec = V / VEC;
   const T ninf = neg_inf<T>();
   const int64_t nruns = (rows + kRun - 1) / kRun;
 
-  for (int64_t run = warp; run < nruns; run += nwarps) {
-  const int64_t r0 = run * kRun;
-  const int64_t r1 = (r0 + kRun < rows) ? r0 + kRun : rows;
-  // Position of the run's first row; afterwards (b, t, u) advance with the rows.
-  int b = find_utt(split, N, r0);
-  int Tn = __ldg(Tl + b), U = __ldg(Ul + b), U1 = U + 1;
-  int64_t next_split = __ldg(split + b + 1);
-  int64_t coff = __ldg(cell_split + b);
-  int t, u;
-  {
-    const int idx = (int)(r0 - __ldg(split + b));
-    t = idx / U1; u = idx - t * U1;
-  }
-
-  for (int64_t row = r0; row < r1; ++row) {
-    const T *p = logits + row * (int64_t)V;
-    bool skip = false;
-    if (MODIFIED) {
-      // Cells outside the band u <= t <= u + (T-1-U) are never used
-      // (optimized_transducer/csrc/cpu.cc:295): their rows are not read.
-      skip = (u > t) || (t - u > Tn - 1 - U);
+  for (int64_t run = group; run < nruns; run += ngroups) {
+    const int64_t r0 = run * kRun;
+    const int64_t r1 = (r0 + kRun < rows) ? r0 + kRun : rows;
+    // Position of the run's first row; afterwards (b, t, u) advance with the rows.
+    int b = find_utt(split, N, r0);
+    int Tn = __ldg(Tl + b), U = __ldg(Ul + b), U1 = U + 1;
+    int64_t next_split = __ldg(split + b + 1);
+    int64_t coff = __ldg(cell_split + b);
+    int t, u;
+    {
+      const int idx = (int)(r0 - __ldg(split + b));
+      t = idx / U1; u = idx - t * U1;
     }
-    if (!skip) {
-      T m = ninf, s = 0;
-      for (int base = 0; base < nvec; base += kWarp * CH) {
-        T x[CH * VEC];
+    for (int64_t row = r0; row < r1; ++row) {
+      const T *p = logits + row * (int64_t)V;
+      bool skip = false;
+      if (MODIFIED) {
+        // Cells outside the band u <= t <= u + (T-1-U) are never used
+        // (optimized_transducer/csrc/cpu.cc:295): their rows are not read.
+        skip = (u > t) || (t - u > Tn - 1 - U);
+      }
+      if (!skip) {
+        T m = ninf, s = 0;
+        for (int base = 0; base < nvec; base += LPR * CH) {
+          T x[CH * VEC];
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          const int vi = base + j * kWarp + lane;
-          if (vi < nvec) {
-            const VT v = *reinterpret_cast<const VT *>(p + (int64_t)vi * VEC);
-            const T *e = reinterpret_cast<const T *>(&v);
+          for (int j = 0; j < CH; ++j) {
+            const int vi = base + j * LPR + gl;
+            if (vi < nvec) {
+              const VT v = *reinterpret_cast<const VT *>(p + (int64_t)vi * VEC);
+              const T *e = reinterpret_cast<const T *>(&v);
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) x[j * VEC + k] = e[k];
-          } else {
+              for (int k = 0; k < VEC; ++k) x[j * VEC + k] = e[k];
+            } else {
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) x[j * VEC + k] = ninf;
+              for (int k = 0; k < VEC; ++k) x[j * VEC + k] = ninf;
+            }
           }
-        }
-        T cm = x[0];
+          T cm = x[0];
 #pragma unroll
-        for (int k = 1; k < CH * VEC; ++k) cm = r_max(cm, x[k]);
-        cm = warp_max(cm);  // the running maximum is uniform across the warp
-        if (cm > m) { s *= s_exp(m - cm); m = cm; }  // first chunk: s is 0
-        // An infinite maximum needs no sum (see below); skipping it avoids inf - inf.
-        if (m - m == (T)0) s = add_exps(x, m, s);
+          for (int k = 1; k < CH * VEC; ++k) cm = r_max(cm, x[k]);
+          cm = group_max<T, LPR>(cm, gmask);  // the running maximum is uniform across the group
+          if (cm > m) { s *= s_exp(m - cm); m = cm; }  // first chunk: s is 0
+          // An infinite maximum needs no sum (see below); skipping it avoids inf - inf.
+          if (m - m == (T)0) s = add_exps(x, m, s);
+        }
+        // ATen's logsumexp replaces an infinite maximum by 0 before subtracting,
+        // which makes the result that same infinity.
+        const T d = (m - m == (T)0) ? r_log(group_sum<T, LPR>(s, gmask)) + m : m;
+        // Gather: the group's lane 0 fetches the blank entry, lane 1 the symbol entry.
+        T g = 0;
+        if (gl == 0) g = p[blank] - d;
+        if (gl == 1 && u < U) g = p[__ldg(targets + (int64_t)b * max_u + u)] - d;
+        const T g1 = __shfl_sync(gmask, g, (lane - gl) + 1);
+        if (gl == 0) {
+          den[row] = d;
+          T *q = lp + 2 * (coff + cell_pos<MODIFIED>(t, u, U1));
+          if constexpr (sizeof(T) == 4) *reinterpret_cast<float2 *>(q) = make_float2(g, g1);
+          else *reinterpret_cast<double2 *>(q) = make_double2(g, g1);
+        }
       }
-      // ATen's logsumexp replaces an infinite maximum by 0 before subtracting,
-      // which makes the result that same infinity.
-      const T d = (m - m == (T)0) ? r_log(warp_sum(s)) + m : m;
-      // Gather: lane 0 fetches the blank entry, lane 1 the symbol entry.
-      T g = 0;
-      if (lane == 0) g = p[blank] - d;
-      if (lane == 1 && u < U) g = p[__ldg(targets + (int64_t)b * max_u + u)] - d;
-      const T g1 = __shfl_sync(kFull, g, 1);
-      if (lane == 0) {
-        den[row] = d;
-        T *q = lp + 2 * (coff + cell_pos<MODIFIED>(t, u, U1));
-        if constexpr (sizeof(T) == 4) *reinterpret_cast<float2 *>(q) = make_float2(g, g1);
-        else *reinterpret_cast<double2 *>(q) = make_double2(g, g1);
+      // advance to the next row
+      if (++u == U1) { u = 0; ++t; }
+      if (row + 1 == next_split && row + 1 < rows) {
+        ++b;
+        Tn = __ldg(Tl + b); U = __ldg(Ul + b); U1 = U + 1;
+        next_split = __ldg(split + b + 1);
+        coff = __ldg(cell_split + b);
+        t = 0; u = 0;
       }
-    }
-    // advance to the next row
-    if (++u == U1) { u = 0; ++t; }
-    if (row + 1 == next_split && row + 1 < rows) {
-      ++b;
-      Tn = __ldg(Tl + b); U = __ldg(Ul + b); U1 = U + 1;
-      next_split = __ldg(split + b + 1);
-      coff = __ldg(cell_split + b);
-      t = 0; u = 0;
     }
   }
-  }  // runs
 }
 
 // Log-softmax input: nothing to reduce, only the gather (thread per row).
@@ -157,12 +176,13 @@ gather_kernel(const T *__restrict__ logp, const int32_t *__restrict__ targets,
   q[1] = (u < U) ? p[__ldg(targets + (int64_t)b * max_u + u)] : (T)0;
 }
 
-template <typename T, int VEC, int CH, bool MODIFIED>
+template <typename T, int VEC, int CH, int LPR, bool MODIFIED>
 cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
-  auto kernel = logprob_kernel<T, VEC, CH, MODIFIED>;
+  auto kernel = logprob_kernel<T, VEC, CH, LPR, MODIFIED>;
   static int per_sm = 0;  // occupancy of this instantiation (same on every B200)
   if (per_sm == 0) per_sm = blocks_per_sm(kernel, kThreads);
-  const int64_t want = (p.rows + (kThreads / kWarp) - 1) / (kThreads / kWarp);
+  constexpr int rows_per_block = (kThreads / kWarp) * (kWarp / LPR);
+  const int64_t want = (p.rows + rows_per_block - 1) / rows_per_block;
   const int64_t cap = (int64_t)sm_count() * per_sm;
   const unsigned grid = (unsigned)(want < cap ? want : cap);
   kernel<<<grid, kThreads, 0, s>>>(
@@ -175,10 +195,10 @@ cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
   return cudaGetLastError();
 }
 
-template <typename T, int VEC, int CH>
+template <typename T, int VEC, int CH, int LPR>
 cudaError_t launch_lse(const Problem &p, cudaStream_t s) {
-  return (p.flags & OT_B200_ONE_SYM_PER_FRAME) ? launch_lse_m<T, VEC, CH, true>(p, s)
-                                               : launch_lse_m<T, VEC, CH, false>(p, s);
+  return (p.flags & OT_B200_ONE_SYM_PER_FRAME) ? launch_lse_m<T, VEC, CH, LPR, true>(p, s)
+                                               : launch_lse_m<T, VEC, CH, LPR, false>(p, s);
 }
 
 template <typename T>
@@ -202,15 +222,17 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
   const bool vec_ok = (p.V % VEC == 0) &&
                       (reinterpret_cast<uintptr_t>(p.logits) % 16 == 0);
   if (vec_ok) {
-    const int per_lane = (p.V / VEC + kWarp - 1) / kWarp;  // 16-byte loads per lane
-    if (per_lane <= 1) return launch_lse<T, VEC, 1>(p, s);
-    if (per_lane <= 2) return launch_lse<T, VEC, 2>(p, s);
-    if (per_lane <= 4) return launch_lse<T, VEC, 4>(p, s);
-    return launch_lse<T, VEC, 8>(p, s);
+    const int nvec = p.V / VEC;  // 16-byte loads per row
+    // Up to 8 loads per lane: pick the narrowest group that covers the row in
+    // one chunk; rows longer than 32*8 loads loop over chunks.
+    if (nvec <= 8 * 4) return launch_lse<T, VEC, 4, 8>(p, s);
+    if (nvec <= 8 * 8) return launch_lse<T, VEC, 8, 8>(p, s);
+    if (nvec <= 16 * 8) return launch_lse<T, VEC, 8, 16>(p, s);
+    return launch_lse<T, VEC, 8, 32>(p, s);
   }
   const int per_lane = (p.V + kWarp - 1) / kWarp;
-  if (per_lane <= 4) return launch_lse<T, 1, 4>(p, s);
-  return launch_lse<T, 1, 16>(p, s);
+  if (per_lane <= 4) return launch_lse<T, 1, 4, 32>(p, s);
+  return launch_lse<T, 1, 16, 32>(p, s);
 }
 
 }  // namespace
