@@ -163,6 +163,28 @@ int ot_b200_compute_transducer_loss(const void *d_logits, void *d_grad,
 int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes,
                               int32_t *code_out, int32_t *index_out, void *stream);
 
+/* Scores without any allocation.  This entry point has no counterpart in the
+ * reference (every path of the reference allocates its temporaries through
+ * torch).  It exists for callers that cannot provide a workspace because they
+ * cannot allocate device memory where the loss is evaluated: a server that has
+ * given the whole GPU to its own arena, a plug-in hook that must not allocate.
+ * The scratch (the alpha lattice) is a fixed array inside the library image,
+ * reserved on every GPU that loads the library: 16 MiB, enough for
+ * 4 Mi lattice cells (rows = sum_b T_b*(U_b+1) <= 4194304); larger batches
+ * return OT_B200_ERR_ARGUMENT.  float32, standard transducer, log-softmax
+ * input; computes only the per-utterance scores
+ *     d_scores[b] = log P(y_b | x_b)
+ * (an utterance whose lengths or targets are invalid gets NaN).  Calls no
+ * cudaMalloc/cudaFree and no allocating library routine.  All calls share the
+ * one array, so calls that overlap on the GPU race: serialise them.  The first
+ * call on a device looks the array's address up (cudaGetSymbolAddress); make
+ * that call before any stream capture. */
+int ot_b200_scores_noalloc(const float *d_log_probs, const int32_t *d_targets,
+                           const int32_t *d_logit_lengths,
+                           const int32_t *d_target_lengths, int32_t N, int64_t rows,
+                           int32_t V, int32_t max_u, int32_t blank, float *d_scores,
+                           void *stream);
+
 #ifdef __cplusplus
 }
 #endif

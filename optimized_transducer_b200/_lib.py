@@ -31,6 +31,7 @@ EXPORTS = (
     "ot_b200_backward",
     "ot_b200_compute_transducer_loss",
     "ot_b200_read_input_status",
+    "ot_b200_scores_noalloc",
 )
 
 
@@ -73,6 +74,8 @@ def load():
     lib.ot_b200_compute_transducer_loss.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, vp]
     lib.ot_b200_read_input_status.restype = ctypes.c_int
     lib.ot_b200_read_input_status.argtypes = [vp, u64, ctypes.POINTER(i32), ctypes.POINTER(i32), vp]
+    lib.ot_b200_scores_noalloc.restype = ctypes.c_int
+    lib.ot_b200_scores_noalloc.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i32, vp, vp]
     if lib.ot_b200_abi_version() != ABI_VERSION:
         raise ImportError("libot_b200.so was built from a different ABI version; rebuild it")
     _lib = lib

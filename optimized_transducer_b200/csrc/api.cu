@@ -99,6 +99,8 @@ int check_common(int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blan
 
 }  // namespace
 
+void set_last_error(const char *msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;

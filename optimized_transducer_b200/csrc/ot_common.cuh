@@ -102,6 +102,9 @@ struct Problem {
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Stores the message ot_b200_last_error() returns for the calling thread.
+void set_last_error(const char *msg);
+
 // Blocks of `kernel` that fit on one SM at `threads` threads per block.
 template <typename K>
 int blocks_per_sm(K kernel, int threads) {
