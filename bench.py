@@ -224,7 +224,11 @@ def run_ours(args, w):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # The scalar all-reduce shares the GPU with the (persistent, full-occupancy)
+        # gradient kernel: give NCCL's stream priority so its one CTA is placed first.
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.is_high_priority_stream = True
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
         from optimized_transducer_b200 import sharding
 
     # ----- the batch (global), and this rank's shard of it

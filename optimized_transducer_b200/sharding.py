@@ -164,7 +164,10 @@ _SIDE = {}
 def _side_stream(device):
     key = (device.type, device.index)
     if key not in _SIDE:
-        _SIDE[key] = torch.cuda.Stream(device=device)
+        # high priority: the collective's single CTA must not queue behind the
+        # full-occupancy gradient kernel (also create the NCCL process group with
+        # ProcessGroupNCCL.Options().is_high_priority_stream = True)
+        _SIDE[key] = torch.cuda.Stream(device=device, priority=-1)
     return _SIDE[key]
 
 
