@@ -232,10 +232,16 @@ def test_scale_is_folded_into_the_gradient_pass():
     torch.testing.assert_close(g2, g1 * 0.75, rtol=1e-6, atol=1e-7)
 
 
-def test_fast_math_flag_stays_within_tolerance(monkeypatch):
+@pytest.mark.parametrize("fast", ["0", "1"])
+def test_both_log_add_variants_stay_within_tolerance(fast, monkeypatch):
+    """OT_FAST_MATH=1 (default): ex2/lg2.approx in the recursions; =0: expf/log1pf."""
     x, tg, T, U = random_batch(53, 3, (30, 60), (10, 40), 50)
     ref = O.oracle_loss(x, tg, T, U, 0)
-    monkeypatch.setenv("OT_FAST_MATH", "1")
+    monkeypatch.setenv("OT_FAST_MATH", fast)
+    out = run_cuda(x, tg, T, U, 0)
+    check_against(out, ref)
+    x, tg, T, U = random_batch(31, 2, (200, 300), (40, 80), 500, 2.0)
+    ref = O.oracle_loss(x, tg, T, U, 0)
     out = run_cuda(x, tg, T, U, 0)
     check_against(out, ref)
 
