@@ -127,7 +127,7 @@ __device__ __forceinline__ RowTerms<T> row_terms(const Cursor &c, int64_t row, T
 }
 
 template <typename T, int VEC, int CH, int LPR, bool MODIFIED>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, sizeof(T) == 4 ? 5 : 2)
 gradient_kernel(const T *x, T *g, const int32_t *__restrict__ targets,
                 const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
                 const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
@@ -154,9 +154,20 @@ gradient_kernel(const T *x, T *g, const int32_t *__restrict__ targets,
     cursor_seek(cur, r0, split, cell_split, Tl, Ul, N);
     T L = beta[cur.coff];  // beta(0,0) is the first entry in both storage orders
     for (int64_t row = r0; row < r1; ++row) {
-      const RowTerms<T> rt = row_terms<T, false, MODIFIED>(cur, row, L, targets, max_u, blank, den, alpha, beta);
       const T *px = x + row * (int64_t)V;
       T *pg = g + row * (int64_t)V;
+      // The row's first chunk is requested before its scalars: nothing in the
+      // loads depends on them, and the scalars' own latency hides behind them.
+      const bool offband = MODIFIED && (cur.u > cur.t || cur.t - cur.u > cur.Tn - 1 - cur.U);
+      VT v[CH];
+      if (!offband) {
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int vi = j * LPR + gl;
+          if (vi < nvec) v[j] = *reinterpret_cast<const VT *>(px + (int64_t)vi * VEC);
+        }
+      }
+      const RowTerms<T> rt = row_terms<T, false, MODIFIED>(cur, row, L, targets, max_u, blank, den, alpha, beta);
       if (rt.zero) {
         VT z;
         T *ze = reinterpret_cast<T *>(&z);
@@ -168,11 +179,12 @@ gradient_kernel(const T *x, T *g, const int32_t *__restrict__ targets,
         const int tvec = rt.tgt >= 0 ? rt.tgt / VEC : -1;
         const int tk = rt.tgt >= 0 ? rt.tgt % VEC : 0;
         for (int base = 0; base < nvec; base += LPR * CH) {
-          VT v[CH];
+          if (base > 0) {
 #pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            const int vi = base + j * LPR + gl;
-            if (vi < nvec) v[j] = *reinterpret_cast<const VT *>(px + (int64_t)vi * VEC);
+            for (int j = 0; j < CH; ++j) {
+              const int vi = base + j * LPR + gl;
+              if (vi < nvec) v[j] = *reinterpret_cast<const VT *>(px + (int64_t)vi * VEC);
+            }
           }
 #pragma unroll
           for (int j = 0; j < CH; ++j) {
