@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define OT_B200_ABI_VERSION 3
+#define OT_B200_ABI_VERSION 2
 
 typedef enum ot_b200_status {
   OT_B200_OK = 0,
@@ -86,6 +86,7 @@ typedef struct ot_b200_workspace_layout {
   uint64_t lp_off;          /* real[cells][2]: blank / symbol log-prob (kernels.cu:30-88) */
   uint64_t alpha_off;       /* real[cells]                             (kernels.cu:200-313) */
   uint64_t beta_off;        /* real[cells]                             (kernels.cu:415-519) */
+  uint64_t coef_off;        /* per-row gradient coefficients (library-private format) */
   uint64_t scores_beta_off; /* real[N]: beta(0,0), the score seen from the beta side  */
   uint64_t max_cells;       /* capacity of the per-cell arrays                        */
 } ot_b200_workspace_layout;
@@ -105,7 +106,7 @@ int ot_b200_workspace_bytes(int32_t N, int64_t rows, int32_t max_u, uint32_t fla
                             uint64_t *bytes_out);
 
 /* Forward half: input check, row-wise logsumexp + blank/target gather, alpha
- * and beta recursions, reduced loss.
+ * and beta recursions, per-row gradient coefficients, reduced loss.
  *   replaces: the checks of ot::ComputeTransducerLoss (transducer-loss.cc:49-66),
  *   RowSplitsToRowIds (cuda.cu:40-59), ComputeLogProbs[ForLogSoftmax]
  *   (cuda.cu:71-136), ComputeAlpha (cuda.cu:162-213), ComputeBeta (cuda.cu:237-287)
@@ -127,8 +128,7 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
 
 /* Backward half: one streaming pass that writes
  *     grad = scale * d loss / d logits
- * from the alpha, beta and logsumexp arrays ot_b200_forward left in the
- * workspace.
+ * from the coefficients ot_b200_forward left in the workspace.
  *   replaces: ComputeGradient[OneSymPerFrame] (cuda.cu:308-346) and
  *   ComputeGradientForLogSoftmax[OneSymPerFrame] (cuda.cu:364-400), plus the two
  *   elementwise passes of the Python layer (`grad /= N`, transducer_loss.py:150,
@@ -137,13 +137,10 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
  * d_grad     (rows, V) real out; MAY EQUAL d_logits (the reference's in-place
  *            mode, cuda.cu:449).  With OT_B200_FROM_LOG_SOFTMAX d_logits is not
  *            read and d_grad must be a separate buffer (cuda.cu:444).
- * d_targets, d_logit_lengths, d_target_lengths, N, rows, max_u, flags
- *            as given to ot_b200_forward (the sizes fix the workspace layout)
+ * N, rows, max_u, flags  as given to ot_b200_forward (they fix the layout)
  * scale = scale_host * (d_scale ? *d_scale : 1); d_scale is a device scalar of
  *            the real type (e.g. the upstream gradient of the loss). */
-int ot_b200_backward(const void *d_logits, void *d_grad, const int32_t *d_targets,
-                     const int32_t *d_logit_lengths,
-                     const int32_t *d_target_lengths, int32_t N, int64_t rows,
+int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows,
                      int32_t V, int32_t max_u, int32_t blank, uint32_t flags,
                      const void *d_workspace, uint64_t workspace_bytes,
                      const void *d_scale, double scale_host, void *stream);

@@ -9,7 +9,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libot_b200.so")
 
-ABI_VERSION = 3
+ABI_VERSION = 2
 
 # ot_b200_status
 OK, ERR_ARGUMENT, ERR_CUDA, ERR_WORKSPACE, ERR_INPUT = range(5)
@@ -38,7 +38,7 @@ EXPORTS = (
 class WorkspaceLayout(ctypes.Structure):
     _fields_ = [(n, ctypes.c_uint64) for n in (
         "total_bytes", "status_off", "split_off", "cell_split_off", "den_off", "lp_off",
-        "alpha_off", "beta_off", "scores_beta_off", "max_cells")]
+        "alpha_off", "beta_off", "coef_off", "scores_beta_off", "max_cells")]
 
 
 _lib = None
@@ -69,8 +69,7 @@ def load():
     lib.ot_b200_forward.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, vp,
                                     ctypes.c_double, vp]
     lib.ot_b200_backward.restype = ctypes.c_int
-    lib.ot_b200_backward.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp,
-                                     ctypes.c_double, vp]
+    lib.ot_b200_backward.argtypes = [vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, ctypes.c_double, vp]
     lib.ot_b200_compute_transducer_loss.restype = ctypes.c_int
     lib.ot_b200_compute_transducer_loss.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, vp]
     lib.ot_b200_read_input_status.restype = ctypes.c_int

@@ -118,6 +118,8 @@ Layout make_layout(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   const uint64_t es = (flags & OT_B200_FP64) ? 8 : 4;
   const bool mode_b = flags & OT_B200_FROM_LOG_SOFTMAX;
   const bool modified = flags & OT_B200_ONE_SYM_PER_FRAME;
+  const uint64_t coef_rec = mode_b ? ((flags & OT_B200_FP64) ? sizeof(CoefB<double>) : sizeof(CoefB<float>))
+                                   : ((flags & OT_B200_FP64) ? sizeof(CoefA<double>) : sizeof(CoefA<float>));
   // Cells: the host knows rows, N and max_u but not the individual lengths.
   // Standard (diagonal-major) blocks hold (T+U)*(U+1) entries, i.e. the rows of
   // the utterance plus U*(U+1) <= max_u*(max_u+1); every block is rounded up by
@@ -134,6 +136,7 @@ Layout make_layout(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   l.lp = off;           off = align256(off + cells * 2 * es);
   l.alpha = off;        off = align256(off + cells * es);
   l.beta = off;         off = align256(off + cells * es);
+  l.coef = off;         off = align256(off + (uint64_t)rows * coef_rec);
   l.scores_beta = off;  off = align256(off + (uint64_t)N * es);
   l.total = off;
   return l;
@@ -163,6 +166,7 @@ int ot_b200_workspace_layout_query(int32_t N, int64_t rows, int32_t max_u, uint3
   out->lp_off = l.lp;
   out->alpha_off = l.alpha;
   out->beta_off = l.beta;
+  out->coef_off = l.coef;
   out->scores_beta_off = l.scores_beta;
   out->max_cells = (uint64_t)l.max_cells;
   return OT_B200_OK;
@@ -222,10 +226,8 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
   if (e != cudaSuccess) return fail_cuda(e, "launch logprob");
   e = launch_lattice(p, d_scores, s);
   if (e != cudaSuccess) return fail_cuda(e, "launch lattice");
-  if (d_loss) {
-    e = launch_loss(p, d_scores, d_loss, loss_scale, s);
-    if (e != cudaSuccess) return fail_cuda(e, "launch loss");
-  }
+  e = launch_coef(p, d_scores, d_loss, loss_scale, s);
+  if (e != cudaSuccess) return fail_cuda(e, "launch coef");
   if (slot) {
     e = cudaEventSynchronize(slot->ev);
     if (e != cudaSuccess) return fail_cuda(e, "wait for status");
@@ -237,10 +239,9 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
   return OT_B200_OK;
 }
 
-int ot_b200_backward(const void *d_logits, void *d_grad, const int32_t *d_targets,
-                     const int32_t *d_logit_lengths, const int32_t *d_target_lengths,
-                     int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blank,
-                     uint32_t flags, const void *d_workspace, uint64_t workspace_bytes,
+int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows,
+                     int32_t V, int32_t max_u, int32_t blank, uint32_t flags,
+                     const void *d_workspace, uint64_t workspace_bytes,
                      const void *d_scale, double scale_host, void *stream) {
   Problem p;
   int rc = check_common(N, rows, V, max_u, blank, flags, d_workspace, workspace_bytes, &p.lay);
@@ -250,9 +251,7 @@ int ot_b200_backward(const void *d_logits, void *d_grad, const int32_t *d_target
   if (!mode_b && !d_logits) return fail(OT_B200_ERR_ARGUMENT, "logits pointer is NULL");
   if (mode_b && d_grad == d_logits)
     return fail(OT_B200_ERR_ARGUMENT, "with OT_B200_FROM_LOG_SOFTMAX the gradient needs its own buffer");
-  if (!d_logit_lengths || !d_target_lengths || (max_u > 0 && !d_targets))
-    return fail(OT_B200_ERR_ARGUMENT, "lengths or targets pointer is NULL");
-  p.logits = d_logits; p.targets = d_targets; p.T = d_logit_lengths; p.U = d_target_lengths;
+  p.logits = d_logits; p.targets = nullptr; p.T = nullptr; p.U = nullptr;
   p.N = N; p.rows = rows; p.V = V; p.max_u = max_u; p.blank = blank; p.flags = flags;
   p.ws = static_cast<char *>(const_cast<void *>(d_workspace));
   cudaError_t e = launch_gradient(p, d_grad, d_scale, scale_host, static_cast<cudaStream_t>(stream));
@@ -271,9 +270,8 @@ int ot_b200_compute_transducer_loss(const void *d_logits, void *d_grad,
                            V, max_u, blank, flags, d_workspace, workspace_bytes, d_scores,
                            nullptr, 1.0, stream);
   if (rc || !d_grad) return rc;
-  return ot_b200_backward(d_logits, d_grad, d_targets, d_logit_lengths, d_target_lengths, N,
-                          rows, V, max_u, blank, flags, d_workspace, workspace_bytes, nullptr,
-                          1.0, stream);
+  return ot_b200_backward(d_logits, d_grad, N, rows, V, max_u, blank, flags, d_workspace,
+                          workspace_bytes, nullptr, 1.0, stream);
 }
 
 int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes,

@@ -26,6 +26,10 @@ constexpr int kStatusCode = 0;   // ot_b200_input_error, 0 = inputs are valid
 constexpr int kStatusIndex = 1;  // utterance the code refers to
 constexpr int kStatusWords = 16;
 
+// Marker values of the `tgt` field of a gradient-coefficient record.
+constexpr int32_t kTgtNone = -1;     // no symbol column to patch in this row
+constexpr int32_t kTgtZeroRow = -2;  // the whole gradient row is zero
+
 // Layout of the per-cell arrays of one utterance.
 //
 // Standard transducer: the recursion advances along anti-diagonals d = t + u,
@@ -48,8 +52,32 @@ __host__ __device__ __forceinline__ int64_t cell_block(int T, int U, bool modifi
   return (n + 1) & ~int64_t(1);
 }
 
+// Per-row coefficients of the gradient w.r.t. raw logits (mode A), produced
+// once per row after alpha and beta are known, so that the streaming gradient
+// kernel needs a single broadcast load per row:
+//   grad[v] = exp((x[v] + c) + beta) - [v == blank] exp((x[v] + c) + sub_blank)
+//                                    - [v == tgt]   exp((x[v] + c) + sub_sym)
+// sub_* = -inf means "nothing to subtract".
+template <typename T>
+struct alignas(32) CoefA {
+  T c;          // alpha(t,u) - L - den(t,u), evaluated as (alpha + (-L)) - den
+  T beta;       // beta(t,u)
+  T sub_blank;  // beta of the blank successor (0 for the final cell)
+  T sub_sym;    // beta of the symbol successor
+  int32_t tgt;  // symbol column, or kTgtNone / kTgtZeroRow
+};
+
+// Mode B (input already log-softmax): the gradient row is zero except for at
+// most two entries, whose final values are stored directly.
+template <typename T>
+struct alignas(16) CoefB {
+  T val_blank;  // gradient at the blank column (0 if none)
+  T val_sym;    // gradient at the symbol column
+  int32_t tgt;  // symbol column, or kTgtNone / kTgtZeroRow
+};
+
 struct Layout {
-  uint64_t total, status, split, cell_split, den, lp, alpha, beta, scores_beta;
+  uint64_t total, status, split, cell_split, den, lp, alpha, beta, coef, scores_beta;
   int64_t max_cells;  // capacity of the per-cell arrays
 };
 
@@ -89,7 +117,7 @@ int blocks_per_sm(K kernel, int threads) {
 cudaError_t launch_prepare(const Problem &p, cudaStream_t s);
 cudaError_t launch_logprob(const Problem &p, cudaStream_t s);
 cudaError_t launch_lattice(const Problem &p, void *scores, cudaStream_t s);
-cudaError_t launch_loss(const Problem &p, const void *scores, void *loss_out,
+cudaError_t launch_coef(const Problem &p, const void *scores, void *loss_out,
                         double loss_scale, cudaStream_t s);
 cudaError_t launch_gradient(const Problem &p, void *grad, const void *d_scale,
                             double scale_host, cudaStream_t s);

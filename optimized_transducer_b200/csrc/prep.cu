@@ -1,5 +1,5 @@
-// Stage 0 (input check + row/cell splits) and the reduction of the scores to
-// the loss.
+// Stage 0 (input check + row/cell splits) and stage 2c (per-row gradient
+// coefficients + the reduced loss) of the transducer-loss path.
 //
 // Stage 0 replaces, without a host round trip, the data-dependent checks of
 // ot::ComputeTransducerLoss (optimized_transducer/csrc/transducer-loss.cc:49-66)
@@ -105,18 +105,129 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
   }
 }
 
-// One warp: *loss_out = loss_scale * -(sum_b scores[b])   (the reduction of the
-// reference's Python layer, transducer_loss.py:145-152).  Lane-strided partial
-// sums in double and a fixed shuffle tree: the result does not depend on timing.
-template <typename T>
-__global__ void __launch_bounds__(kWarp)
-loss_kernel(const T *__restrict__ scores, const int32_t *__restrict__ status, int N,
+// Thread per workspace cell, in the order alpha and beta are stored, so their
+// reads are coalesced; the 32-byte (16-byte) record of the cell's row is the
+// only scattered access.  Produces what the streaming gradient kernels read.
+// Branch order and the order of the floating-point additions follow
+// ComputeGradient / ...OneSymPerFrame / ...ForLogSoftmax[OneSymPerFrame]
+// (optimized_transducer/csrc/cpu.cc:500-526, 582-604, 655-672, 722-745).
+// A non-finite log-likelihood zeroes the utterance's rows
+// (optimized_transducer/csrc/kernels.cu:556-563).
+//
+// Block 0 also reduces the scores to the loss:
+//   *loss_out = loss_scale * -(sum_b scores[b])      (transducer_loss.py:145-152)
+template <typename T, bool MODE_B, bool MODIFIED>
+__global__ void __launch_bounds__(256)
+coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
+            const int32_t *__restrict__ Ul, const int64_t *__restrict__ split,
+            const int64_t *__restrict__ cell_split,
+            const int32_t *__restrict__ status, int N, int max_u, int blank,
+            const T *__restrict__ den, const T *__restrict__ lp,
+            const T *__restrict__ alpha, const T *__restrict__ beta,
+            void *__restrict__ coef_out, const T *__restrict__ scores,
             T *__restrict__ loss_out, double loss_scale) {
   if (status[kStatusCode] != 0) return;
-  double acc = 0;
-  for (int b = threadIdx.x; b < N; b += kWarp) acc += (double)scores[b];
-  acc = warp_sum(acc);
-  if (threadIdx.x == 0) *loss_out = (T)(-acc * loss_scale);
+  if (blockIdx.x == 0 && threadIdx.x < kWarp && loss_out != nullptr) {
+    double acc = 0;
+    for (int b = threadIdx.x; b < N; b += kWarp) acc += (double)scores[b];
+    acc = warp_sum(acc);
+    if (threadIdx.x == 0) *loss_out = (T)(-acc * loss_scale);
+  }
+  const int64_t cell = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // A block's 256 cells nearly always belong to one utterance: two threads
+  // search for the block's first and last cell, the others only search between.
+  __shared__ int b_range[2];
+  const int64_t total_cells = __ldg(cell_split + N);
+  if (threadIdx.x == 0 || threadIdx.x == kWarp) {
+    int64_t probe = (int64_t)blockIdx.x * blockDim.x + (threadIdx.x ? blockDim.x - 1 : 0);
+    if (probe >= total_cells) probe = total_cells - 1;
+    b_range[threadIdx.x ? 1 : 0] = (probe >= 0) ? find_utt(cell_split, N, probe) : 0;
+  }
+  __syncthreads();
+  if (cell >= total_cells) return;
+  int b = b_range[0];
+  while (b < b_range[1] && __ldg(cell_split + b + 1) <= cell) ++b;
+  const int64_t coff = __ldg(cell_split + b);
+  const int Tn = __ldg(Tl + b), U = __ldg(Ul + b), U1 = U + 1;
+  const int64_t p = cell - coff;
+  int t, u;
+  if (MODIFIED) {
+    t = (int)(p / U1); u = (int)(p - (int64_t)t * U1);
+    if (t >= Tn) return;  // rounding pad of the block
+  } else {
+    const int d = (int)(p / U1);
+    u = (int)(p - (int64_t)d * U1);
+    t = d - u;
+    if (t < 0 || t >= Tn) return;  // no lattice cell is stored here
+  }
+  const int64_t row = __ldg(split + b) + (int64_t)t * U1 + u;
+  const int diff = Tn - 1 - U;
+  const T L = beta[coff];  // beta(0,0) is the first entry in both layouts
+
+  bool zero = !(L - L == (T)0);  // inf or nan
+  if (MODIFIED && (u > t || t - u > diff)) zero = true;
+
+  T c = 0, b_here = 0, sub_blank = neg_inf<T>(), sub_sym = neg_inf<T>();
+  int32_t tgt = kTgtNone;
+  bool blank_term = false, sym_term = false;
+  if (!zero) {
+    const T loss = -L;
+    c = alpha[cell] + loss;
+    if (!MODE_B) c = c - den[row];
+    b_here = beta[cell];
+    const bool last = (t == Tn - 1 && u == U);
+    const bool blank_ok = MODIFIED ? (t - u < diff) : (t < Tn - 1);
+    const int target_u = (u < U) ? __ldg(targets + (int64_t)b * max_u + u) : -1;
+    // successors: blank -> (t+1,u), symbol -> (t,u+1) or (t+1,u+1) if modified;
+    // in both storage orders they sit U1 and U1+1 entries further.
+    const T b_sym_next = (u < U) ? beta[cell + U1 + 1] : neg_inf<T>();
+    if (last) {
+      sub_blank = 0; blank_term = true;
+    } else if (blank_ok) {
+      sub_blank = beta[cell + U1]; blank_term = true;
+    } else if (u < U && target_u == blank) {
+      sub_blank = b_sym_next; blank_term = true;
+    }
+    if (u < U && target_u != blank) {
+      sub_sym = b_sym_next; tgt = target_u; sym_term = true;
+    }
+  }
+  if (MODE_B) {
+    CoefB<T> r;
+    r.val_blank = blank_term ? -r_exp((lp[2 * cell] + c) + sub_blank) : (T)0;
+    r.val_sym = sym_term ? -r_exp((lp[2 * cell + 1] + c) + sub_sym) : (T)0;
+    r.tgt = zero ? kTgtZeroRow : tgt;
+    reinterpret_cast<CoefB<T> *>(coef_out)[row] = r;
+  } else {
+    CoefA<T> r;
+    r.c = c; r.beta = b_here; r.sub_blank = sub_blank; r.sub_sym = sub_sym;
+    r.tgt = zero ? kTgtZeroRow : tgt;
+    reinterpret_cast<CoefA<T> *>(coef_out)[row] = r;
+  }
+}
+
+template <typename T>
+cudaError_t launch_coef_t(const Problem &p, const void *scores, void *loss_out,
+                          double loss_scale, cudaStream_t s) {
+  const bool mode_b = p.flags & OT_B200_FROM_LOG_SOFTMAX;
+  const bool modified = p.flags & OT_B200_ONE_SYM_PER_FRAME;
+  const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
+  const int64_t *split = reinterpret_cast<const int64_t *>(p.ws + p.lay.split);
+  const int64_t *csplit = reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split);
+  const T *den = reinterpret_cast<const T *>(p.ws + p.lay.den);
+  const T *lp = reinterpret_cast<const T *>(p.ws + p.lay.lp);
+  const T *alpha = reinterpret_cast<const T *>(p.ws + p.lay.alpha);
+  const T *beta = reinterpret_cast<const T *>(p.ws + p.lay.beta);
+  void *coef = p.ws + p.lay.coef;
+  const unsigned grid = (unsigned)((p.lay.max_cells + 255) / 256);
+#define OTB_COEF(MB, MOD)                                                        \
+  coef_kernel<T, MB, MOD><<<grid, 256, 0, s>>>(p.targets, p.T, p.U, split,       \
+      csplit, status, p.N, p.max_u, p.blank, den, lp, alpha, beta, coef,         \
+      static_cast<const T *>(scores), static_cast<T *>(loss_out), loss_scale)
+  if (mode_b) { if (modified) OTB_COEF(true, true); else OTB_COEF(true, false); }
+  else        { if (modified) OTB_COEF(false, true); else OTB_COEF(false, false); }
+#undef OTB_COEF
+  return cudaGetLastError();
 }
 
 }  // namespace
@@ -131,16 +242,10 @@ cudaError_t launch_prepare(const Problem &p, cudaStream_t s) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_loss(const Problem &p, const void *scores, void *loss_out,
+cudaError_t launch_coef(const Problem &p, const void *scores, void *loss_out,
                         double loss_scale, cudaStream_t s) {
-  const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
-  if (p.flags & OT_B200_FP64)
-    loss_kernel<double><<<1, kWarp, 0, s>>>(static_cast<const double *>(scores), status, p.N,
-                                            static_cast<double *>(loss_out), loss_scale);
-  else
-    loss_kernel<float><<<1, kWarp, 0, s>>>(static_cast<const float *>(scores), status, p.N,
-                                           static_cast<float *>(loss_out), loss_scale);
-  return cudaGetLastError();
+  return (p.flags & OT_B200_FP64) ? launch_coef_t<double>(p, scores, loss_out, loss_scale, s)
+                                  : launch_coef_t<float>(p, scores, loss_out, loss_scale, s);
 }
 
 }  // namespace otb

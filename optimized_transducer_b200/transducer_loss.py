@@ -150,9 +150,7 @@ class _Call:
     def backward(self, grad_out, scale_tensor=None, scale_host=1.0):
         with torch.cuda.device(self.logits.device):
             rc = self.lib.ot_b200_backward(
-                self.logits.data_ptr(), grad_out.data_ptr(),
-                self.targets.data_ptr() if self.max_u else None, self.t.data_ptr(),
-                self.u.data_ptr(), self.n, self.rows, self.v,
+                self.logits.data_ptr(), grad_out.data_ptr(), self.n, self.rows, self.v,
                 self.max_u, self.blank, self.flags & ~_lib.CHECK_INPUTS,
                 self.workspace.data_ptr(), int(self.layout.total_bytes),
                 scale_tensor.data_ptr() if scale_tensor is not None else None,

@@ -38,7 +38,7 @@ def test_workspace_layout_is_aligned_and_ordered(flags):
     lay = _lib.workspace_layout(n, rows, max_u, flags)
     es = 8 if flags & _lib.FP64 else 4
     offs = [lay.status_off, lay.split_off, lay.cell_split_off, lay.den_off, lay.lp_off,
-            lay.alpha_off, lay.beta_off, lay.scores_beta_off, lay.total_bytes]
+            lay.alpha_off, lay.beta_off, lay.coef_off, lay.scores_beta_off, lay.total_bytes]
     assert all(o % 256 == 0 for o in offs)
     assert offs == sorted(offs) and lay.status_off == 0
     # room for every diagonal-major block: rows + sum U*(U+1) + one pad entry each
@@ -78,7 +78,7 @@ def test_argument_errors_without_touching_a_gpu():
     rc = lib.ot_b200_forward(None, one, one, one, 1, 10, 5, 1, 0, 0, one, 1 << 15, one, None, 1.0, None)
     assert rc == _lib.ERR_ARGUMENT
     # log-softmax gradient must not alias its input (cuda.cu:444 allocates a new tensor)
-    rc = lib.ot_b200_backward(one, one, one, one, one, 1, 10, 5, 1, 0, _lib.FROM_LOG_SOFTMAX, one, 1 << 15, None, 1.0, None)
+    rc = lib.ot_b200_backward(one, one, 1, 10, 5, 1, 0, _lib.FROM_LOG_SOFTMAX, one, 1 << 15, None, 1.0, None)
     assert rc == _lib.ERR_ARGUMENT
     with pytest.raises(RuntimeError):
         _lib.check(rc)
