@@ -27,6 +27,9 @@
 //
 // Lattices wider than 1024 columns use the generic kernel at the end of the
 // file (several columns per thread, wavefront kept in global memory).
+#include <stdlib.h>
+#include <string.h>
+
 #include "ot_common.cuh"
 
 namespace otb {
@@ -270,6 +273,215 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Skewed variant: one CTA barrier per K steps instead of one per step.
+//
+// The recursion is cut into blocks of K consecutive steps (K = the rows of one
+// staged chunk).  In phase p, warp w works on block p - delay(w), where the
+// delay grows by one per warp in the direction the boundary values flow (alpha:
+// delay = w; beta: delay = nwarps-1-w).  The value a warp needs from its
+// neighbour at step s was therefore produced one phase earlier: it is read
+// from a small shared-memory ring (indexed by step) with a plain load, one step
+// ahead, and nothing is exchanged inside a phase.  Cost: nwarps-1 extra phases
+// while the pipeline of warps fills; gain: the barrier and the shared-memory
+// round trip leave the per-step dependency chain, which is then only
+// shuffle -> add -> log-add.
+//
+// Chunk c of the log-probs (rows [cK, cK+K) of the wavefront-ordered array) is
+// used in phases c .. c+nwarps-1 and is requested two phases before its first
+// use, so the stage ring needs nwarps + 3 stages.
+constexpr int kSkewRing = 64;   // ring entries per warp boundary; >= 4*K
+constexpr int kSkewMaxK = 16;
+constexpr int kSkewMaxStages = kMaxWarps + 3;
+
+template <typename T, bool FAST, bool MODIFIED>
+__global__ void __launch_bounds__(1024)
+lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
+                    const int32_t *__restrict__ Ul, const int64_t *__restrict__ cell_split,
+                    int32_t *__restrict__ status, T *__restrict__ alpha,
+                    T *__restrict__ beta, T *__restrict__ scores,
+                    T *__restrict__ scores_beta, int K, int stage_pairs, int nstages) {
+  using P = typename Pair<T>::type;
+  extern __shared__ __align__(128) unsigned char stage_mem[];
+  __shared__ __align__(8) uint64_t full_bar[kSkewMaxStages];
+  __shared__ T edge[kMaxWarps][kSkewRing];  // edge[w][s & 63]: boundary column of warp w after step s
+  if (status[kStatusCode] != 0) return;
+  const int b = blockIdx.x >> 1;
+  const bool backward = blockIdx.x & 1;
+  const int Tn = Tl[b], U = Ul[b], U1 = U + 1;
+  const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
+  const int nwarps = (U1 + kWarp - 1) / kWarp;
+  if (warp >= nwarps) return;
+  const int nact = nwarps * kWarp;
+  const int64_t off = cell_split[b];
+  const P *lp2 = reinterpret_cast<const P *>(lp) + off;
+  P *stage = reinterpret_cast<P *>(stage_mem) + 2;  // slack: column 0 reads the pair before its row
+  const bool col = u < U1;
+  const int diff = Tn - 1 - U;
+  int s_lo, s_hi;
+  if (MODIFIED) { s_lo = u; s_hi = u + diff; }
+  else { s_lo = u; s_hi = u + Tn - 1; }
+  if (!col) { s_lo = 1 << 30; s_hi = -1; }
+  const int top = MODIFIED ? Tn - 1 : Tn - 1 + U;
+  const T ninf = neg_inf<T>();
+  const int uc = col ? u : U;
+  constexpr int kMask = kSkewRing - 1;
+
+  const int nrows = top;  // wavefront rows 0 .. top-1 are streamed
+  const int nchunks = (nrows + K - 1) / K;
+  const int nphases = nchunks > 0 ? nchunks + nwarps - 1 : 0;
+  const int delay = backward ? nwarps - 1 - warp : warp;
+  if (u == 0) {
+    for (int i = 0; i < nstages; ++i) mbar_init(&full_bar[i], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  // Chunk j (processing order) covers memory rows [row0, row0 + n).
+  auto chunk_rows = [&](int j, int &row0, int &n) {
+    const int m = backward ? nchunks - 1 - j : j;
+    row0 = m * K;
+    n = min(K, nrows - row0);
+  };
+  auto issue = [&](int j) {  // thread 0 only
+    int row0, n;
+    chunk_rows(j, row0, n);
+    const uint32_t bytes = (uint32_t)((((int64_t)n * U1 * sizeof(P)) + 15) & ~int64_t(15));
+    uint64_t *bar = &full_bar[j % nstages];
+    mbar_expect_tx(bar, bytes);
+    tma_load_1d(stage + (int64_t)(j % nstages) * stage_pairs, lp2 + (int64_t)row0 * U1, bytes, bar);
+  };
+  auto wait_chunk = [&](int j) {
+    uint64_t *bar = &full_bar[j % nstages];
+    const uint32_t parity = (uint32_t)((j / nstages) & 1);
+    for (int spin = 0; spin < (1 << 22); ++spin)
+      if (mbar_try_wait(bar, parity)) return;
+    atomicCAS(status + kStatusLatticeTimeout, 0, 1 + b);  // bounded: report and carry on
+  };
+
+  if (!backward) {
+    // ------------------------------ alpha ------------------------------
+    const bool produce = (lane == kWarp - 1) && (warp + 1 < nwarps);
+    const bool consume = (lane == 0) && (warp > 0);
+    T *out_edge = edge[warp];
+    const T *in_edge = edge[consume ? warp - 1 : 0];
+    // "after step 0": columns 31, 63, ... have not started
+    if (lane == 0) out_edge[0] = ninf;
+    T *al = alpha + off;
+    T own = (u == 0) ? (T)0 : ninf;
+    if (u == 0) al[0] = 0;
+    if (nwarps > 1) bar_active(nact); else __syncwarp();
+    if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);
+    const unsigned span = (unsigned)(s_hi - s_lo);
+    auto mask = [&](int s, T x, T y, T &vb, T &vs) {
+      const unsigned rel = (unsigned)(s - s_lo);
+      vb = (rel - 1u < span) ? x : ninf;
+      vs = (rel <= span && u >= 1) ? y : ninf;
+    };
+    for (int p = 0; p < nphases; ++p) {
+      if (u == 0 && p + 2 < nchunks) issue(p + 2);
+      const int q = p - delay;
+      if (q >= 0 && q < nchunks) {
+        int row0, n;
+        chunk_rows(q, row0, n);
+        wait_chunk(q);
+        const P *rowp = stage + (int64_t)(q % nstages) * stage_pairs + uc;
+        T *st = al + (int64_t)(row0 + 1) * U1 + uc;  // entry of the block's first step
+        T lb, ls;
+        mask(row0 + 1, rowp[0].x, rowp[-1].y, lb, ls);
+        T e_cur = consume ? in_edge[row0 & kMask] : ninf;  // column u-1 after step row0
+        for (int i = 0; i < n; ++i) {
+          const int s = row0 + 1 + i;
+          // loads for the next step first
+          rowp += U1;
+          const bool more = i + 1 < n;
+          const T x_next = more ? rowp[0].x : ninf;
+          const T y_next = more ? rowp[-1].y : ninf;
+          const T e_next = (consume && more) ? in_edge[s & kMask] : ninf;
+          // the chain
+          T left = __shfl_up_sync(kFull, own, 1);
+          left = consume ? e_cur : left;
+          const T nv = log_add<T, FAST>(own + lb, left + ls);
+          const bool act = (unsigned)(s - s_lo) <= span;
+          own = act ? nv : own;
+          // stores
+          if (act) *st = nv;
+          st += U1;
+          if (produce) out_edge[s & kMask] = own;
+          mask(s + 1, x_next, y_next, lb, ls);
+          e_cur = e_next;
+        }
+      }
+      if (nwarps > 1) bar_active(nact); else __syncwarp();
+    }
+    if (u == U) {
+      const int64_t fin = cell_pos<MODIFIED>(Tn - 1, U, U1);
+      scores[b] = own + lp2[fin].x;
+    }
+  } else {
+    // ------------------------------- beta ------------------------------
+    const bool produce = (lane == 0) && (warp > 0);
+    const bool consume = (lane == kWarp - 1) && (warp + 1 < nwarps);
+    T *out_edge = edge[warp];
+    const T *in_edge = edge[consume ? warp + 1 : 0];
+    T *be = beta + off;
+    const T fin = lp2[(int64_t)top * U1 + U].x;  // beta(T-1,U)
+    T own = ninf;
+    if (u == U) {
+      own = fin;
+      be[(int64_t)top * U1 + U] = own;
+    }
+    // "after step top": the boundary column of this warp before any step
+    if (lane == 0) out_edge[top & kMask] = (u == U) ? fin : ninf;
+    if (nwarps > 1) bar_active(nact); else __syncwarp();
+    if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);
+    const int hi = (u == U) ? s_hi - 1 : s_hi;  // the final cell is done
+    const unsigned span = (hi >= s_lo) ? (unsigned)(hi - s_lo) : 0u;
+    const bool any = hi >= s_lo;
+    auto mask = [&](int s, T x, T y, T &vb, T &vs) {
+      const bool in = any && (unsigned)(s - s_lo) <= span;
+      vb = in ? x : ninf;
+      vs = (in && u < U) ? y : ninf;
+    };
+    for (int p = 0; p < nphases; ++p) {
+      if (u == 0 && p + 2 < nchunks) issue(p + 2);
+      const int q = p - delay;
+      if (q >= 0 && q < nchunks) {
+        int row0, n;
+        chunk_rows(q, row0, n);
+        wait_chunk(q);
+        const P *rowp = stage + (int64_t)(q % nstages) * stage_pairs + (int64_t)(n - 1) * U1 + uc;
+        T *st = be + (int64_t)(row0 + n - 1) * U1 + uc;  // entry of the block's first step
+        T lb, ls;
+        {
+          const P v = rowp[0];
+          mask(row0 + n - 1, v.x, v.y, lb, ls);
+        }
+        T e_cur = consume ? in_edge[(row0 + n) & kMask] : ninf;  // column u+1 after step row0+n
+        for (int i = n - 1; i >= 0; --i) {
+          const int s = row0 + i;
+          rowp -= U1;
+          P v_next;
+          v_next.x = ninf; v_next.y = ninf;
+          if (i > 0) v_next = rowp[0];
+          const T e_next = (consume && i > 0) ? in_edge[s & kMask] : ninf;
+          T right = __shfl_down_sync(kFull, own, 1);
+          right = consume ? e_cur : right;
+          const T nv = log_add<T, FAST>(own + lb, right + ls);
+          const bool act = any && (unsigned)(s - s_lo) <= span;
+          own = act ? nv : own;
+          if (act) *st = nv;
+          st -= U1;
+          if (produce) out_edge[s & kMask] = own;
+          mask(s - 1, v_next.x, v_next.y, lb, ls);
+          e_cur = e_next;
+        }
+      }
+      if (nwarps > 1) bar_active(nact); else __syncwarp();
+    }
+    if (u == 0) scores_beta[b] = own;
+  }
+}
+
 // Generic fallback for lattices with more than 1024 columns: thread i owns the
 // columns i, i+blockDim, ...; the wavefront lives in the alpha/beta arrays in
 // global memory and one CTA barrier separates consecutive steps.
@@ -347,9 +559,63 @@ lattice_generic_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   }
 }
 
+// The skewed kernel needs (warps + 3) stages of K rows; it is used when that
+// fits into kSkewSmemBudget with K >= 2.  OT_B200_LATTICE=lockstep forces the
+// per-step-barrier kernel (for comparison).
+constexpr size_t kSkewSmemBudget = 160 * 1024;
+
+bool lockstep_forced() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char *e = getenv("OT_B200_LATTICE");
+    cached = (e && strcmp(e, "lockstep") == 0) ? 1 : 0;
+  }
+  return cached == 1;
+}
+
+// Returns cudaErrorNotSupported when the lattice is too wide for the skewed kernel.
+template <typename T, bool FAST, bool MODIFIED>
+cudaError_t launch_skewed(const Problem &p, void *scores, cudaStream_t s) {
+  using P = typename Pair<T>::type;
+  auto kernel = lattice_skew_kernel<T, FAST, MODIFIED>;
+  const int cols = p.max_u + 1;
+  const int nwarps = (cols + kWarp - 1) / kWarp;
+  const int nstages = nwarps + 3;
+  int K = kSkewMaxK;
+  size_t smem = 0;
+  int stage_pairs = 0;
+  for (; K >= 2; K -= 2) {
+    stage_pairs = ((K * cols + 1) & ~1) + 2;
+    smem = ((size_t)nstages * stage_pairs + 2) * sizeof(P);
+    if (smem <= kSkewSmemBudget) break;
+  }
+  if (K < 2 || lockstep_forced()) return cudaErrorNotSupported;
+  static size_t granted[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (smem > granted[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    granted[dev] = smem;
+  }
+  kernel<<<2u * (unsigned)p.N, (unsigned)(nwarps * kWarp), smem, s>>>(
+      reinterpret_cast<const T *>(p.ws + p.lay.lp), p.T, p.U,
+      reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
+      reinterpret_cast<int32_t *>(p.ws + p.lay.status),
+      reinterpret_cast<T *>(p.ws + p.lay.alpha), reinterpret_cast<T *>(p.ws + p.lay.beta),
+      static_cast<T *>(scores), reinterpret_cast<T *>(p.ws + p.lay.scores_beta), K, stage_pairs,
+      nstages);
+  return cudaGetLastError();
+}
+
 template <typename T, bool FAST, bool MODIFIED>
 cudaError_t launch_staged(const Problem &p, void *scores, cudaStream_t s) {
   using P = typename Pair<T>::type;
+  {
+    const cudaError_t e = launch_skewed<T, FAST, MODIFIED>(p, scores, s);
+    if (e != cudaErrorNotSupported) return e;
+  }
   auto kernel = lattice_kernel<T, FAST, MODIFIED>;
   const int cols = p.max_u + 1;
   // rows per chunk: even, at least 2, about kChunkBytes per chunk
