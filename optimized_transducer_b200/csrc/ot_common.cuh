@@ -175,18 +175,26 @@ template <> __device__ __forceinline__ double min_log_diff<double>() { return -3
 // too negative difference returns the larger operand.
 template <typename T, bool FAST>
 __device__ __forceinline__ T log_add(T a, T b) {
-  // Written without branches: the correction is always evaluated and then
-  // selected, so a warp never diverges inside the recursion.
-  const T hi = (a < b) ? b : a;
-  const T d = (a < b) ? (a - b) : (b - a);
-  T corr;
+  // Written without branches: the correction is always evaluated, so a warp
+  // never diverges inside the recursion.
   if constexpr (FAST && sizeof(T) == 4) {
-    // ex2/lg2 approximations: absolute error of the correction < 3e-7.
-    corr = __logf(1.0f + ex2_approx(d * kLog2e));
+    // ex2/lg2 approximations: absolute error of the correction < 3e-7.  The
+    // difference is clamped instead of compared with the cut-off: below the
+    // cut-off the correction is < 1.2e-7 anyway, and the clamp also turns the
+    // NaN of (-inf) - (-inf) into "no correction" (fmaxf drops a NaN operand).
+    float hi;  // max that propagates a NaN operand: a poisoned log-prob must stay visible
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(hi) : "f"(a), "f"(b));
+    const float lo = fminf(a, b);
+    const float d = fmaxf(lo - hi, -64.0f);
+    float l2;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l2) : "f"(1.0f + ex2_approx(d * kLog2e)));
+    return fmaf(l2, 0.6931471805599453f, hi);
   } else {
-    corr = r_log1p(r_exp(d));
+    const T hi = (a < b) ? b : a;
+    const T d = (a < b) ? (a - b) : (b - a);
+    const T corr = r_log1p(r_exp(d));
+    return (d >= min_log_diff<T>()) ? hi + corr : hi;
   }
-  return (d >= min_log_diff<T>()) ? hi + corr : hi;
 }
 
 template <typename T>
