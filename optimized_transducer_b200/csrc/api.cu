@@ -133,7 +133,7 @@ Layout make_layout(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   l.split = off;        off = align256(off + (uint64_t)(N + 1) * sizeof(int64_t));
   l.cell_split = off;   off = align256(off + (uint64_t)(N + 1) * sizeof(int64_t));
   l.den = off;          off = align256(off + (mode_b ? 0 : (uint64_t)rows * es));
-  l.lp = off;           off = align256(off + cells * 2 * es);
+  l.lp = off;           off = align256(off + (cells + 1) * 2 * es);  // + 1: filled 16 bytes at a time
   l.alpha = off;        off = align256(off + cells * es);
   l.beta = off;         off = align256(off + cells * es);
   l.coef = off;         off = align256(off + (uint64_t)rows * coef_rec);

@@ -372,11 +372,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     if (nwarps > 1) bar_active(nact); else __syncwarp();
     if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);
     const unsigned span = (unsigned)(s_hi - s_lo);
-    auto mask = [&](int s, T x, T y, T &vb, T &vs) {
-      const unsigned rel = (unsigned)(s - s_lo);
-      vb = (rel - 1u < span) ? x : ninf;
-      vs = (rel <= span && u >= 1) ? y : ninf;
-    };
+    const bool first_col = (u == 0);  // has no symbol predecessor
     for (int p = 0; p < nphases; ++p) {
       if (u == 0 && p + 2 < nchunks) issue(p + 2);
       const int q = p - delay;
@@ -386,8 +382,11 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         wait_chunk(q);
         const P *rowp = stage + (int64_t)(q % nstages) * stage_pairs + uc;
         T *st = al + (int64_t)(row0 + 1) * U1 + uc;  // entry of the block's first step
-        T lb, ls;
-        mask(row0 + 1, rowp[0].x, rowp[-1].y, lb, ls);
+        // No range checks on the log-probs: entries that are no lattice cell
+        // hold -inf (stage 0 fills, stage 1 overwrites the real cells), and a
+        // column that has not started holds -inf itself.
+        T lb = rowp[0].x;
+        T ls = first_col ? ninf : rowp[-1].y;
         T e_cur = consume ? in_edge[row0 & kMask] : ninf;  // column u-1 after step row0
         for (int i = 0; i < n; ++i) {
           const int s = row0 + 1 + i;
@@ -395,19 +394,19 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
           rowp += U1;
           const bool more = i + 1 < n;
           const T x_next = more ? rowp[0].x : ninf;
-          const T y_next = more ? rowp[-1].y : ninf;
+          const T y_next = (more && !first_col) ? rowp[-1].y : ninf;
           const T e_next = (consume && more) ? in_edge[s & kMask] : ninf;
           // the chain
           T left = __shfl_up_sync(kFull, own, 1);
           left = consume ? e_cur : left;
           const T nv = log_add<T, FAST>(own + lb, left + ls);
-          const bool act = (unsigned)(s - s_lo) <= span;
-          own = act ? nv : own;
-          // stores
-          if (act) *st = nv;
+          // What a column holds after its last cell is never consumed (its
+          // neighbour's cells end one step later), so only the store is guarded.
+          if ((unsigned)(s - s_lo) <= span) *st = nv;
+          own = nv;
           st += U1;
           if (produce) out_edge[s & kMask] = own;
-          mask(s + 1, x_next, y_next, lb, ls);
+          lb = x_next; ls = y_next;
           e_cur = e_next;
         }
       }
@@ -415,7 +414,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     }
     if (u == U) {
       const int64_t fin = cell_pos<MODIFIED>(Tn - 1, U, U1);
-      scores[b] = own + lp2[fin].x;
+      scores[b] = al[fin] + lp2[fin].x;  // own store, read back
     }
   } else {
     // ------------------------------- beta ------------------------------
@@ -437,11 +436,6 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     const int hi = (u == U) ? s_hi - 1 : s_hi;  // the final cell is done
     const unsigned span = (hi >= s_lo) ? (unsigned)(hi - s_lo) : 0u;
     const bool any = hi >= s_lo;
-    auto mask = [&](int s, T x, T y, T &vb, T &vs) {
-      const bool in = any && (unsigned)(s - s_lo) <= span;
-      vb = in ? x : ninf;
-      vs = (in && u < U) ? y : ninf;
-    };
     for (int p = 0; p < nphases; ++p) {
       if (u == 0 && p + 2 < nchunks) issue(p + 2);
       const int q = p - delay;
@@ -453,8 +447,8 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         T *st = be + (int64_t)(row0 + n - 1) * U1 + uc;  // entry of the block's first step
         T lb, ls;
         {
-          const P v = rowp[0];
-          mask(row0 + n - 1, v.x, v.y, lb, ls);
+          const P v = rowp[0];  // (-inf, -inf) where (step, column) is no lattice cell
+          lb = v.x; ls = v.y;
         }
         T e_cur = consume ? in_edge[(row0 + n) & kMask] : ninf;  // column u+1 after step row0+n
         for (int i = n - 1; i >= 0; --i) {
@@ -468,17 +462,18 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
           right = consume ? e_cur : right;
           const T nv = log_add<T, FAST>(own + lb, right + ls);
           const bool act = any && (unsigned)(s - s_lo) <= span;
-          own = act ? nv : own;
           if (act) *st = nv;
+          // column U keeps the final cell until its steps begin (T == 1: never)
+          own = (u == U && !act) ? own : nv;
           st -= U1;
           if (produce) out_edge[s & kMask] = own;
-          mask(s - 1, v_next.x, v_next.y, lb, ls);
+          lb = v_next.x; ls = v_next.y;
           e_cur = e_next;
         }
       }
       if (nwarps > 1) bar_active(nact); else __syncwarp();
     }
-    if (u == 0) scores_beta[b] = own;
+    if (u == 0) scores_beta[b] = be[0];  // own store, read back
   }
 }
 

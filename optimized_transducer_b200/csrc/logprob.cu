@@ -131,7 +131,8 @@ logprob_kernel(const T *__restrict__ logits, const int32_t *__restrict__ targets
         // which makes the result that same infinity.
         const T d = (m - m == (T)0) ? r_log(group_sum<T, LPR>(s, gmask)) + m : m;
         // Gather: the group's lane 0 fetches the blank entry, lane 1 the symbol entry.
-        T g = 0;
+        // the last column has no next symbol: -inf, "no such transition"
+        T g = ninf;
         if (gl == 0) g = p[blank] - d;
         if (gl == 1 && u < U) g = p[__ldg(targets + (int64_t)b * max_u + u)] - d;
         const T g1 = __shfl_sync(gmask, g, (lane - gl) + 1);
@@ -173,7 +174,7 @@ gather_kernel(const T *__restrict__ logp, const int32_t *__restrict__ targets,
   const T *p = logp + row * (int64_t)V;
   T *q = lp + 2 * (__ldg(cell_split + b) + cell_pos<MODIFIED>(t, u, U1));
   q[0] = p[blank];
-  q[1] = (u < U) ? p[__ldg(targets + (int64_t)b * max_u + u)] : (T)0;
+  q[1] = (u < U) ? p[__ldg(targets + (int64_t)b * max_u + u)] : neg_inf<T>();
 }
 
 template <typename T, int VEC, int CH, int LPR, bool MODIFIED>

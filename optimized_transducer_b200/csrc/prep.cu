@@ -42,16 +42,29 @@ __device__ __forceinline__ long long block_exclusive_scan(long long mine, long l
   return base + incl - mine;
 }
 
-// One CTA.  Thread i owns the contiguous utterance range [i*per, (i+1)*per).
+// Block 0: the input check and the splits; thread i owns the contiguous
+// utterance range [i*per, (i+1)*per).  The other blocks only fill (see below).
 __global__ void __launch_bounds__(kPrepThreads)
 prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
                const int32_t *__restrict__ Ul, int N, int64_t rows, int V,
                int max_u, int modified, int64_t max_cells,
                int32_t *__restrict__ status, int64_t *__restrict__ split,
-               int64_t *__restrict__ cell_split) {
+               int64_t *__restrict__ cell_split, uint4 *__restrict__ lp_fill,
+               int64_t lp_fill_count, uint4 fill_pattern) {
   __shared__ long long scan_buf[kPrepThreads / kWarp];
   __shared__ int warp_maxu[kPrepThreads / kWarp];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (blockIdx.x > 0) {
+    // Blocks 1.. set every (blank, symbol) log-prob pair to -inf, 16 bytes at a
+    // time.  Stage 1 then overwrites the pairs of real lattice cells; what is
+    // left at -inf are the entries of the wavefront-ordered blocks that are no
+    // cell, which is exactly the value the recursions need to read there ("no
+    // such predecessor").
+    const int64_t stride = (int64_t)(gridDim.x - 1) * kPrepThreads;
+    for (int64_t i = (int64_t)(blockIdx.x - 1) * kPrepThreads + tid; i < lp_fill_count; i += stride)
+      lp_fill[i] = fill_pattern;
+    return;
+  }
   if (tid < kStatusWords) status[tid] = 0;
   __syncthreads();
 
@@ -233,12 +246,23 @@ cudaError_t launch_coef_t(const Problem &p, const void *scores, void *loss_out,
 }  // namespace
 
 cudaError_t launch_prepare(const Problem &p, cudaStream_t s) {
-  prepare_kernel<<<1, kPrepThreads, 0, s>>>(
+  // lp holds max_cells pairs; in 16-byte units that is max_cells/2 (float) or
+  // max_cells (double) stores of the -inf bit pattern.
+  const bool fp64 = p.flags & OT_B200_FP64;
+  const int64_t units = fp64 ? p.lay.max_cells : (p.lay.max_cells + 1) / 2;
+  uint4 pattern;
+  if (fp64) { pattern.x = 0u; pattern.y = 0xfff00000u; pattern.z = 0u; pattern.w = 0xfff00000u; }
+  else { pattern.x = pattern.y = pattern.z = pattern.w = 0xff800000u; }
+  int64_t fill_blocks = (units + kPrepThreads * 8 - 1) / (kPrepThreads * 8);
+  const int64_t cap = 2 * (int64_t)sm_count();
+  if (fill_blocks > cap) fill_blocks = cap;
+  prepare_kernel<<<(unsigned)(1 + fill_blocks), kPrepThreads, 0, s>>>(
       p.targets, p.T, p.U, p.N, p.rows, p.V, p.max_u,
       (p.flags & OT_B200_ONE_SYM_PER_FRAME) ? 1 : 0, p.lay.max_cells,
       reinterpret_cast<int32_t *>(p.ws + p.lay.status),
       reinterpret_cast<int64_t *>(p.ws + p.lay.split),
-      reinterpret_cast<int64_t *>(p.ws + p.lay.cell_split));
+      reinterpret_cast<int64_t *>(p.ws + p.lay.cell_split),
+      reinterpret_cast<uint4 *>(p.ws + p.lay.lp), units, pattern);
   return cudaGetLastError();
 }
 
