@@ -32,6 +32,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one full-size cfg2 launch of the
+# gradient kernel, from the one-pass ncu capture summarised in profiles/gradient_kernel_cfg2.md.
+CFG2_GRADIENT_TRAFFIC_BYTES = 2705.3e6
+CFG2_ROWS = 686128
+
 METRIC = "fwd+bwd loss lattice cells (sum T*(U+1)*V)/s"
 UNIT = "cells/s"
 HBM_FALLBACK_GBS = 6650.0
@@ -387,7 +392,9 @@ def run_ours(args, w):
                 "kernel": "gradient_logsoftmax_kernel" if mode_b else "gradient_kernel",
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
-                "traffic": None, "bytes_per_launch": grad_bytes, "ms_per_launch": bwd_ms,
+                "traffic": (CFG2_GRADIENT_TRAFFIC_BYTES
+                            if (w.name == "cfg2" and world == 1 and rows == CFG2_ROWS) else None),
+                "bytes_per_launch": grad_bytes, "ms_per_launch": bwd_ms,
             },
             "stages": {
                 "forward_ms": fwd_ms, "backward_ms": bwd_ms,
