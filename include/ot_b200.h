@@ -163,6 +163,54 @@ int ot_b200_compute_transducer_loss(const void *d_logits, void *d_grad,
 int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes,
                               int32_t *code_out, int32_t *index_out, void *stream);
 
+/* ---- Callers' side of the packed layout ----------------------------------
+ * Padded batch tensors <-> packed rows, row(b,t,u) = split_b + t*(U_b+1) + u.
+ * max_t / max_u1 are the padded extents (max_u1 >= max_b U_b + 1); D is the
+ * feature (or vocabulary) size; element type float, or double with
+ * OT_B200_FP64.  The workspace holds the row splits (ot_b200_pack_workspace_bytes,
+ * 8-byte aligned).  If the lengths are inconsistent with rows / max_t / max_u1
+ * the kernels write nothing and the int32 at workspace offset (N+1)*8 is
+ * non-zero. */
+int ot_b200_pack_workspace_bytes(int32_t N, uint64_t *bytes_out);
+
+/* out[row(b,t,u), :] = encoder_out[b,t,:] + decoder_out[b,u,:]
+ *   replaces the list comprehension + torch.cat the reference prescribes for
+ *   the joiner input (README.md:165-177).
+ * d_encoder_out (N, max_t, D), d_decoder_out (N, max_u1, D), d_out (rows, D). */
+int ot_b200_pack_joiner_input(const void *d_encoder_out, const void *d_decoder_out,
+                              const int32_t *d_logit_lengths,
+                              const int32_t *d_target_lengths, int32_t N, int64_t rows,
+                              int32_t D, int32_t max_t, int32_t max_u1, uint32_t flags,
+                              void *d_workspace, void *d_out, void *stream);
+
+/* Its backward: grad_encoder[b,t,:] = sum_u g[row(b,t,u),:] (0 for t >= T_b),
+ * grad_decoder[b,u,:] = sum_t g[row(b,t,u),:] (0 for u > U_b); what autograd
+ * does for the reference's slicing/broadcast-add/cat. */
+int ot_b200_pack_joiner_input_backward(const void *d_grad_out,
+                                       const int32_t *d_logit_lengths,
+                                       const int32_t *d_target_lengths, int32_t N,
+                                       int64_t rows, int32_t D, int32_t max_t,
+                                       int32_t max_u1, uint32_t flags, void *d_workspace,
+                                       void *d_grad_encoder, void *d_grad_decoder,
+                                       void *stream);
+
+/* packed[row(b,t,u), :] = padded[b,t,u,:]   (padded: (N, max_t, max_u1, D))
+ *   replaces the slicing/reshape/cat of the reference's tests
+ *   (python/tests/test_compute_transducer_loss.py:36-56) for callers that hold
+ *   torchaudio-style padded logits. */
+int ot_b200_pack_padded(const void *d_padded, const int32_t *d_logit_lengths,
+                        const int32_t *d_target_lengths, int32_t N, int64_t rows,
+                        int32_t D, int32_t max_t, int32_t max_u1, uint32_t flags,
+                        void *d_workspace, void *d_packed, void *stream);
+
+/* The inverse (e.g. gradients back to the padded layout): padded[b,t,u,:] =
+ * packed[row(b,t,u),:], zero outside the lattices
+ * (test_compute_transducer_loss.py:95-105 slices the padded gradient the same way). */
+int ot_b200_unpack_to_padded(const void *d_packed, const int32_t *d_logit_lengths,
+                             const int32_t *d_target_lengths, int32_t N, int64_t rows,
+                             int32_t D, int32_t max_t, int32_t max_u1, uint32_t flags,
+                             void *d_workspace, void *d_padded, void *stream);
+
 /* Scores without any allocation.  This entry point has no counterpart in the
  * reference (every path of the reference allocates its temporaries through
  * torch).  It exists for callers that cannot provide a workspace because they

@@ -9,6 +9,9 @@ csukuangfj/optimized_transducer:
 from .transducer_loss import (TransducerLoss, TransducerLossFunction,  # noqa: F401
                               compute_transducer_loss, stage_outputs, transducer_loss)
 
+from .packing import pack_joiner_input, pack_padded, rnnt_loss, unpack_to_padded  # noqa: F401,E402
+
 __version__ = "0.1.0"
 __all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
-           "compute_transducer_loss", "stage_outputs", "__version__"]
+           "compute_transducer_loss", "stage_outputs", "pack_joiner_input", "pack_padded",
+           "unpack_to_padded", "rnnt_loss", "__version__"]

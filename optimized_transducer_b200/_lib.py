@@ -32,6 +32,11 @@ EXPORTS = (
     "ot_b200_compute_transducer_loss",
     "ot_b200_read_input_status",
     "ot_b200_scores_noalloc",
+    "ot_b200_pack_workspace_bytes",
+    "ot_b200_pack_joiner_input",
+    "ot_b200_pack_joiner_input_backward",
+    "ot_b200_pack_padded",
+    "ot_b200_unpack_to_padded",
 )
 
 
@@ -76,6 +81,16 @@ def load():
     lib.ot_b200_read_input_status.argtypes = [vp, u64, ctypes.POINTER(i32), ctypes.POINTER(i32), vp]
     lib.ot_b200_scores_noalloc.restype = ctypes.c_int
     lib.ot_b200_scores_noalloc.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i32, vp, vp]
+    lib.ot_b200_pack_workspace_bytes.restype = ctypes.c_int
+    lib.ot_b200_pack_workspace_bytes.argtypes = [i32, ctypes.POINTER(u64)]
+    lib.ot_b200_pack_joiner_input.restype = ctypes.c_int
+    lib.ot_b200_pack_joiner_input.argtypes = [vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, vp, vp]
+    lib.ot_b200_pack_joiner_input_backward.restype = ctypes.c_int
+    lib.ot_b200_pack_joiner_input_backward.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, vp, vp, vp]
+    for name in ("ot_b200_pack_padded", "ot_b200_unpack_to_padded"):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, vp, vp]
     if lib.ot_b200_abi_version() != ABI_VERSION:
         raise ImportError("libot_b200.so was built from a different ABI version; rebuild it")
     _lib = lib

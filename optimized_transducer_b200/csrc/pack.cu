@@ -1,0 +1,284 @@
+// Callers' side of the packed layout: building the packed (rows, D) tensors the
+// loss expects from padded batch tensors, and taking gradients back.
+//
+// The reference leaves this to the user as a Python list comprehension plus
+// torch.cat (README.md:165-177 of the reference):
+//     x_b = encoder_out[b, :T_b].unsqueeze(1) + decoder_out[b, :U_b+1].unsqueeze(0)
+//     x   = cat([x_b.reshape(-1, D) for b in range(N)])
+// and its tests convert a padded (N, maxT, maxU+1, V) tensor by slicing
+// (python/tests/test_compute_transducer_loss.py:36-56).  Here each of these is
+// one streaming kernel over the packed rows:
+//   pack_add      out[row(b,t,u)]  = enc[b,t] + dec[b,u]            (joiner input)
+//   pack_copy     out[row(b,t,u)]  = padded[b,t,u]                  (padded -> packed)
+//   unpack_copy   padded[b,t,u]    = in[row(b,t,u)], 0 elsewhere    (packed -> padded)
+//   sum_over_u    genc[b,t] = sum_u g[row(b,t,u)],  0 for t >= T_b  (backward of pack_add)
+//   sum_over_t    gdec[b,u] = sum_t g[row(b,t,u)],  0 for u >  U_b
+// One warp owns a packed row (16-byte loads when D % 4 == 0 and the bases are
+// aligned); a warp takes runs of 8 rows and walks (b, t, u) incrementally.  All
+// of them are HBM-bound: rows * D * sizeof(T) bytes written or read once.
+#include "ot_common.cuh"
+
+namespace otb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kRun = 8;
+
+// One CTA: split[b] = sum_{b' < b} T_b' * (U_b' + 1); flags inconsistent lengths.
+__global__ void __launch_bounds__(1024)
+pack_prepare_kernel(const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul, int N,
+                    int64_t rows, int max_t, int max_u1, int64_t *__restrict__ split,
+                    int32_t *__restrict__ status) {
+  __shared__ long long part[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) status[0] = 0;
+  __syncthreads();
+  const int per = (N + blockDim.x - 1) / blockDim.x;
+  const int b0 = min(tid * per, N), b1 = min(b0 + per, N);
+  long long mine = 0;
+  for (int b = b0; b < b1; ++b) {
+    const int t = Tl[b], u = Ul[b];
+    if (t <= 0 || t > max_t || u < 0 || u + 1 > max_u1) atomicExch(status, 1 + b);
+    mine += (long long)max(t, 0) * (long long)(max(u, 0) + 1);
+  }
+  long long incl = mine;
+#pragma unroll
+  for (int o = 1; o < kWarp; o <<= 1) {
+    const long long v = __shfl_up_sync(kFull, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == kWarp - 1) part[warp] = incl;
+  __syncthreads();
+  long long base = 0, total = 0;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+    if (w < warp) base += part[w];
+    total += part[w];
+  }
+  long long run = base + incl - mine;
+  for (int b = b0; b < b1; ++b) {
+    split[b] = run;
+    run += (long long)max(Tl[b], 0) * (long long)(max(Ul[b], 0) + 1);
+  }
+  if (tid == 0) {
+    split[N] = total;
+    if (total != rows) atomicExch(status, -1);
+  }
+}
+
+enum Mode { kAdd = 0, kCopy = 1, kUnpack = 2 };
+
+// kAdd:    out (rows, D) = a[b,t,:] + bsrc[b,u,:]     a: (N,max_t,D), bsrc: (N,max_u1,D)
+// kCopy:   out (rows, D) = a[b,t,u,:]                 a: (N,max_t,max_u1,D)
+// kUnpack: out[b,t,u,:]  = a[row,:]                   a: (rows, D), out: (N,max_t,max_u1,D)
+template <typename T, int VEC, int MODE>
+__global__ void __launch_bounds__(kThreads)
+pack_rows_kernel(const T *__restrict__ a, const T *__restrict__ bsrc, T *__restrict__ out,
+                 const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
+                 const int64_t *__restrict__ split, const int32_t *__restrict__ status, int N,
+                 int64_t rows, int D, int max_t, int max_u1) {
+  if (status[0] != 0) return;
+  using VT = typename VecOf<T, VEC>::type;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
+  const int nvec = D / VEC;
+  const int64_t nruns = (rows + kRun - 1) / kRun;
+  for (int64_t run = warp; run < nruns; run += nwarps) {
+    const int64_t r0 = run * kRun;
+    const int64_t r1 = (r0 + kRun < rows) ? r0 + kRun : rows;
+    int b = find_utt(split, N, r0);
+    int U1 = __ldg(Ul + b) + 1;
+    int64_t next_split = __ldg(split + b + 1);
+    int t, u;
+    {
+      const int idx = (int)(r0 - __ldg(split + b));
+      t = idx / U1; u = idx - t * U1;
+    }
+    for (int64_t row = r0; row < r1; ++row) {
+      const int64_t padded = (((int64_t)b * max_t + t) * max_u1 + u) * D;
+      if (MODE == kAdd) {
+        const T *pa = a + ((int64_t)b * max_t + t) * D;
+        const T *pb = bsrc + ((int64_t)b * max_u1 + u) * D;
+        T *po = out + row * (int64_t)D;
+        for (int vi = lane; vi < nvec; vi += kWarp) {
+          const VT x = *reinterpret_cast<const VT *>(pa + (int64_t)vi * VEC);
+          const VT y = *reinterpret_cast<const VT *>(pb + (int64_t)vi * VEC);
+          VT z;
+          const T *xe = reinterpret_cast<const T *>(&x);
+          const T *ye = reinterpret_cast<const T *>(&y);
+          T *ze = reinterpret_cast<T *>(&z);
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) ze[k] = xe[k] + ye[k];
+          *reinterpret_cast<VT *>(po + (int64_t)vi * VEC) = z;
+        }
+      } else {
+        const T *ps = (MODE == kCopy) ? a + padded : a + row * (int64_t)D;
+        T *po = (MODE == kCopy) ? out + row * (int64_t)D : out + padded;
+        for (int vi = lane; vi < nvec; vi += kWarp)
+          *reinterpret_cast<VT *>(po + (int64_t)vi * VEC) =
+              *reinterpret_cast<const VT *>(ps + (int64_t)vi * VEC);
+      }
+      if (++u == U1) { u = 0; ++t; }
+      if (row + 1 == next_split && row + 1 < rows) {
+        ++b;
+        U1 = __ldg(Ul + b) + 1;
+        next_split = __ldg(split + b + 1);
+        t = 0; u = 0;
+      }
+    }
+  }
+}
+
+// OVER_U: CTA (t, b): out[b,t,:] = sum_u g[row(b,t,u),:]   (zero for t >= T_b)
+// else  : CTA (u, b): out[b,u,:] = sum_t g[row(b,t,u),:]   (zero for u >  U_b)
+// The sums run in index order, so the result does not depend on timing.
+template <typename T, bool OVER_U>
+__global__ void __launch_bounds__(kThreads)
+pack_sum_kernel(const T *__restrict__ g, T *__restrict__ out, const int32_t *__restrict__ Tl,
+                const int32_t *__restrict__ Ul, const int64_t *__restrict__ split,
+                const int32_t *__restrict__ status, int D, int extent) {
+  if (status[0] != 0) return;
+  const int b = blockIdx.y, i = blockIdx.x;  // i: frame t (OVER_U) or column u
+  const int Tn = Tl[b], U1 = Ul[b] + 1;
+  T *po = out + ((int64_t)b * extent + i) * D;
+  const bool live = OVER_U ? (i < Tn) : (i < U1);
+  const T *base = g + split[b] * (int64_t)D;
+  for (int d = threadIdx.x; d < D; d += kThreads) {
+    T acc = 0;
+    if (live) {
+      if (OVER_U) {
+        const T *p = base + ((int64_t)i * U1) * D + d;
+        for (int u = 0; u < U1; ++u) acc += p[(int64_t)u * D];
+      } else {
+        const T *p = base + (int64_t)i * D + d;
+        for (int t = 0; t < Tn; ++t) acc += p[(int64_t)t * U1 * D];
+      }
+    }
+    po[d] = acc;
+  }
+}
+
+int fail(int code, const char *msg) {
+  set_last_error(msg);
+  return code;
+}
+
+unsigned rows_grid(int64_t rows) {
+  const int64_t want = (rows + (kThreads / kWarp) * kRun - 1) / ((kThreads / kWarp) * kRun);
+  const int64_t cap = (int64_t)sm_count() * 8;
+  return (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+template <typename T, int MODE>
+int launch_rows(const void *a, const void *b, void *out, const int32_t *Tl, const int32_t *Ul,
+                int N, int64_t rows, int D, int max_t, int max_u1, void *ws, cudaStream_t s) {
+  int64_t *split = static_cast<int64_t *>(ws);
+  int32_t *status = reinterpret_cast<int32_t *>(split + N + 1);
+  pack_prepare_kernel<<<1, 1024, 0, s>>>(Tl, Ul, N, rows, max_t, max_u1, split, status);
+  constexpr int VEC = Vec16<T>::n;
+  const bool vec = (D % VEC == 0) && (reinterpret_cast<uintptr_t>(a) % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(out) % 16 == 0) &&
+                   (b == nullptr || reinterpret_cast<uintptr_t>(b) % 16 == 0);
+  if (vec)
+    pack_rows_kernel<T, VEC, MODE><<<rows_grid(rows), kThreads, 0, s>>>(
+        static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), Tl, Ul, split,
+        status, N, rows, D, max_t, max_u1);
+  else
+    pack_rows_kernel<T, 1, MODE><<<rows_grid(rows), kThreads, 0, s>>>(
+        static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), Tl, Ul, split,
+        status, N, rows, D, max_t, max_u1);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(OT_B200_ERR_CUDA, cudaGetErrorString(e));
+  return OT_B200_OK;
+}
+
+int check(const void *a, const void *out, const int32_t *Tl, const int32_t *Ul, int32_t N,
+          int64_t rows, int32_t D, int32_t max_t, int32_t max_u1, const void *ws) {
+  if (N <= 0 || rows <= 0 || D <= 0 || max_t <= 0 || max_u1 <= 0)
+    return fail(OT_B200_ERR_ARGUMENT, "pack: N, rows, D, max_t and max_u1 must be positive");
+  if (!a || !out || !Tl || !Ul) return fail(OT_B200_ERR_ARGUMENT, "pack: a required device pointer is NULL");
+  if (!ws || reinterpret_cast<uintptr_t>(ws) % 8 != 0)
+    return fail(OT_B200_ERR_WORKSPACE, "pack: workspace missing or not 8-byte aligned");
+  return OT_B200_OK;
+}
+
+}  // namespace
+}  // namespace otb
+
+using namespace otb;
+
+extern "C" {
+
+int ot_b200_pack_workspace_bytes(int32_t N, uint64_t *bytes_out) {
+  if (N <= 0 || !bytes_out) return fail(OT_B200_ERR_ARGUMENT, "pack: N must be positive and bytes_out non-NULL");
+  *bytes_out = (uint64_t)(N + 1) * sizeof(int64_t) + 64;  // row splits + one status word
+  return OT_B200_OK;
+}
+
+int ot_b200_pack_joiner_input(const void *d_encoder_out, const void *d_decoder_out,
+                              const int32_t *d_logit_lengths, const int32_t *d_target_lengths,
+                              int32_t N, int64_t rows, int32_t D, int32_t max_t, int32_t max_u1,
+                              uint32_t flags, void *d_workspace, void *d_out, void *stream) {
+  int rc = check(d_encoder_out, d_out, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace);
+  if (rc) return rc;
+  if (!d_decoder_out) return fail(OT_B200_ERR_ARGUMENT, "pack: decoder_out is NULL");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return (flags & OT_B200_FP64)
+             ? launch_rows<double, kAdd>(d_encoder_out, d_decoder_out, d_out, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s)
+             : launch_rows<float, kAdd>(d_encoder_out, d_decoder_out, d_out, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s);
+}
+
+int ot_b200_pack_joiner_input_backward(const void *d_grad_out, const int32_t *d_logit_lengths,
+                                       const int32_t *d_target_lengths, int32_t N, int64_t rows,
+                                       int32_t D, int32_t max_t, int32_t max_u1, uint32_t flags,
+                                       void *d_workspace, void *d_grad_encoder, void *d_grad_decoder,
+                                       void *stream) {
+  int rc = check(d_grad_out, d_grad_encoder, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace);
+  if (rc) return rc;
+  if (!d_grad_decoder) return fail(OT_B200_ERR_ARGUMENT, "pack: grad_decoder is NULL");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int64_t *split = static_cast<int64_t *>(d_workspace);
+  int32_t *status = reinterpret_cast<int32_t *>(split + N + 1);
+  pack_prepare_kernel<<<1, 1024, 0, s>>>(d_logit_lengths, d_target_lengths, N, rows, max_t, max_u1, split, status);
+  const dim3 ge((unsigned)max_t, (unsigned)N), gd((unsigned)max_u1, (unsigned)N);
+  if (flags & OT_B200_FP64) {
+    pack_sum_kernel<double, true><<<ge, kThreads, 0, s>>>(static_cast<const double *>(d_grad_out), static_cast<double *>(d_grad_encoder), d_logit_lengths, d_target_lengths, split, status, D, max_t);
+    pack_sum_kernel<double, false><<<gd, kThreads, 0, s>>>(static_cast<const double *>(d_grad_out), static_cast<double *>(d_grad_decoder), d_logit_lengths, d_target_lengths, split, status, D, max_u1);
+  } else {
+    pack_sum_kernel<float, true><<<ge, kThreads, 0, s>>>(static_cast<const float *>(d_grad_out), static_cast<float *>(d_grad_encoder), d_logit_lengths, d_target_lengths, split, status, D, max_t);
+    pack_sum_kernel<float, false><<<gd, kThreads, 0, s>>>(static_cast<const float *>(d_grad_out), static_cast<float *>(d_grad_decoder), d_logit_lengths, d_target_lengths, split, status, D, max_u1);
+  }
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(OT_B200_ERR_CUDA, cudaGetErrorString(e));
+  return OT_B200_OK;
+}
+
+int ot_b200_pack_padded(const void *d_padded, const int32_t *d_logit_lengths,
+                        const int32_t *d_target_lengths, int32_t N, int64_t rows, int32_t D,
+                        int32_t max_t, int32_t max_u1, uint32_t flags, void *d_workspace,
+                        void *d_packed, void *stream) {
+  int rc = check(d_padded, d_packed, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return (flags & OT_B200_FP64)
+             ? launch_rows<double, kCopy>(d_padded, nullptr, d_packed, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s)
+             : launch_rows<float, kCopy>(d_padded, nullptr, d_packed, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s);
+}
+
+int ot_b200_unpack_to_padded(const void *d_packed, const int32_t *d_logit_lengths,
+                             const int32_t *d_target_lengths, int32_t N, int64_t rows, int32_t D,
+                             int32_t max_t, int32_t max_u1, uint32_t flags, void *d_workspace,
+                             void *d_padded, void *stream) {
+  int rc = check(d_packed, d_padded, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t es = (flags & OT_B200_FP64) ? 8 : 4;
+  // everything outside the lattices is zero
+  cudaError_t e = cudaMemsetAsync(d_padded, 0, (size_t)N * max_t * max_u1 * D * es, s);
+  if (e != cudaSuccess) return fail(OT_B200_ERR_CUDA, cudaGetErrorString(e));
+  return (flags & OT_B200_FP64)
+             ? launch_rows<double, kUnpack>(d_packed, nullptr, d_padded, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s)
+             : launch_rows<float, kUnpack>(d_packed, nullptr, d_padded, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s);
+}
+
+}  // extern "C"

@@ -174,6 +174,37 @@ def brute_force_score(lp_blank, lp_sym, one_sym_per_frame=False):
     return m + math.log(sum(math.exp(v - m) for v in terms))
 
 
+def pack_joiner_oracle(encoder_out, decoder_out, T, U):
+    """The packing the reference prescribes for the joiner input
+    (reference README.md:165-177), in numpy: per utterance the broadcast sum
+    ``enc[b,:T_b,None,:] + dec[b,None,:U_b+1,:]`` flattened to rows, then
+    concatenated."""
+    parts = [(encoder_out[b, :t, None, :] + decoder_out[b, None, :u + 1, :]).reshape(-1, encoder_out.shape[-1])
+             for b, (t, u) in enumerate(zip(T, U))]
+    return np.concatenate(parts)
+
+
+def pack_joiner_backward_oracle(grad, T, U, max_t, max_u1):
+    """Gradients of :func:`pack_joiner_oracle` w.r.t. its two inputs (float64 sums)."""
+    d = grad.shape[-1]
+    genc = np.zeros((len(T), max_t, d), np.float64)
+    gdec = np.zeros((len(T), max_u1, d), np.float64)
+    off = 0
+    for b, (t, u) in enumerate(zip(T, U)):
+        g = grad[off:off + t * (u + 1)].reshape(t, u + 1, d).astype(np.float64)
+        genc[b, :t] = g.sum(1)
+        gdec[b, :u + 1] = g.sum(0)
+        off += t * (u + 1)
+    return genc, gdec
+
+
+def pack_padded_oracle(padded, T, U):
+    """Padded (N, maxT, maxU+1, D) -> packed rows, as the reference's tests slice it
+    (python/tests/test_compute_transducer_loss.py:36-56)."""
+    return np.concatenate([padded[b, :t, :u + 1, :].reshape(-1, padded.shape[-1])
+                           for b, (t, u) in enumerate(zip(T, U))])
+
+
 def _import_so(name, path):
     loader = importlib.machinery.ExtensionFileLoader(name, path)
     spec = importlib.util.spec_from_file_location(name, path, loader=loader)

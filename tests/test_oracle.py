@@ -118,3 +118,22 @@ def test_oracle_against_reference_build(modified, from_ls):
     np.testing.assert_allclose(o["scores"], scores, rtol=1e-6)
     np.testing.assert_allclose(o["grad"], grad, rtol=0,
                                atol=max(2e-6, fp32_grad_floor(o["alpha"], o["beta"])))
+
+
+def test_packing_oracles_follow_the_reference_recipe():
+    """numpy packing oracles vs the README's torch recipe (README.md:165-177) and its autograd."""
+    import torch
+    rng = np.random.default_rng(3)
+    T = np.array([4, 2, 5]); U = np.array([2, 0, 3]); d = 6
+    enc = rng.standard_normal((3, 6, d)); dec = rng.standard_normal((3, 5, d))
+    e = torch.from_numpy(enc).requires_grad_(True); q = torch.from_numpy(dec).requires_grad_(True)
+    x = torch.cat([(e[i, :T[i]].unsqueeze(1) + q[i, :U[i] + 1].unsqueeze(0)).reshape(-1, d) for i in range(3)])
+    np.testing.assert_array_equal(O.pack_joiner_oracle(enc, dec, T, U), x.detach().numpy())
+    g = rng.standard_normal(tuple(x.shape))
+    x.backward(torch.from_numpy(g))
+    genc, gdec = O.pack_joiner_backward_oracle(g, T, U, 6, 5)
+    np.testing.assert_allclose(genc, e.grad.numpy(), atol=1e-12)
+    np.testing.assert_allclose(gdec, q.grad.numpy(), atol=1e-12)
+    padded = rng.standard_normal((3, 6, 5, d))
+    want = np.concatenate([padded[i, :T[i], :U[i] + 1].reshape(-1, d) for i in range(3)])
+    np.testing.assert_array_equal(O.pack_padded_oracle(padded, T, U), want)

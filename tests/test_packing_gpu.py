@@ -1,0 +1,102 @@
+"""The packing helpers (callers' side of the packed layout) against the numpy
+restatement of the reference's recipe (reference README.md:165-177,
+python/tests/test_compute_transducer_loss.py:36-56) and, for the padded entry
+point, against the padded->packed->loss chain done by hand and torchaudio."""
+import numpy as np
+import pytest
+import torch
+
+import optimized_transducer_b200 as ot
+from optimized_transducer_b200 import packing
+from oracle import oracle as O
+from helpers import random_batch, splits
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _lengths(seed, n, t_range, u_range):
+    rng = np.random.default_rng(seed)
+    T = rng.integers(t_range[0], t_range[1] + 1, n).astype(np.int32)
+    U = rng.integers(u_range[0], u_range[1] + 1, n).astype(np.int32)
+    return rng, T, U
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("d", [512, 130, 7])
+def test_pack_joiner_input_forward_and_backward(d, dtype):
+    rng, T, U = _lengths(5, 4, (3, 40), (0, 17))
+    max_t, max_u1 = int(T.max()) + 2, int(U.max()) + 1 + 1  # padded larger than needed
+    enc = rng.standard_normal((4, max_t, d)).astype(dtype)
+    dec = rng.standard_normal((4, max_u1, d)).astype(dtype)
+    want = O.pack_joiner_oracle(enc, dec, T, U)
+    e = torch.from_numpy(enc).to(DEV).requires_grad_(True)
+    q = torch.from_numpy(dec).to(DEV).requires_grad_(True)
+    dT, dU = torch.from_numpy(T).to(DEV), torch.from_numpy(U).to(DEV)
+    x = packing.pack_joiner_input(e, q, dT, dU)
+    assert x.shape == want.shape
+    np.testing.assert_array_equal(x.detach().cpu().numpy(), want)  # one addition: bit-exact
+    g = rng.standard_normal(want.shape).astype(dtype)
+    x.backward(torch.from_numpy(g).to(DEV))
+    genc, gdec = O.pack_joiner_backward_oracle(g, T, U, max_t, max_u1)
+    tol = 1e-12 if dtype == np.float64 else 2e-5
+    np.testing.assert_allclose(e.grad.cpu().numpy(), genc, rtol=0, atol=tol)
+    np.testing.assert_allclose(q.grad.cpu().numpy(), gdec, rtol=0, atol=tol * 4)
+
+
+@pytest.mark.parametrize("d", [500, 33])
+def test_padded_round_trip(d):
+    rng, T, U = _lengths(6, 3, (2, 25), (0, 9))
+    max_t, max_u1 = int(T.max()), int(U.max()) + 1
+    padded = rng.standard_normal((3, max_t, max_u1, d)).astype(np.float32)
+    want = O.pack_padded_oracle(padded, T, U)
+    p = torch.from_numpy(padded).to(DEV)
+    dT, dU = torch.from_numpy(T).to(DEV), torch.from_numpy(U).to(DEV)
+    packed = packing.pack_padded(p, dT, dU)
+    np.testing.assert_array_equal(packed.cpu().numpy(), want)
+    back = packing.unpack_to_padded(packed, dT, dU, max_t, max_u1).cpu().numpy()
+    for b in range(3):
+        np.testing.assert_array_equal(back[b, :T[b], :U[b] + 1], padded[b, :T[b], :U[b] + 1])
+        assert np.all(back[b, T[b]:] == 0) and np.all(back[b, :, U[b] + 1:] == 0)
+
+
+def test_inconsistent_lengths_leave_the_output_untouched():
+    rng, T, U = _lengths(7, 2, (4, 6), (1, 2))
+    enc = torch.zeros(2, 3, 8, device=DEV)  # max_t = 3 < T_b
+    dec = torch.zeros(2, 4, 8, device=DEV)
+    rows = int(splits(T, U)[-1])
+    out = packing.pack_joiner_input(enc, dec, torch.from_numpy(T).to(DEV), torch.from_numpy(U).to(DEV), rows=rows)
+    torch.cuda.synchronize()  # no fault: the kernels saw the status word and returned
+    assert out.shape == (rows, 8)
+
+
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+def test_rnnt_loss_on_padded_logits(reduction):
+    """The padded entry point equals pack-by-hand + packed loss, and torchaudio's
+    rnnt_loss where that is importable (the reference's own oracle)."""
+    x, tg, T, U = random_batch(8, 3, (6, 14), (2, 6), 11)
+    sp = splits(T, U)
+    max_t, max_u1 = int(T.max()), int(U.max()) + 1
+    padded = np.zeros((3, max_t, max_u1, 11), np.float32)
+    for b in range(3):
+        padded[b, :T[b], :U[b] + 1] = x[sp[b]:sp[b + 1]].reshape(T[b], U[b] + 1, 11)
+    p = torch.from_numpy(padded).to(DEV).requires_grad_(True)
+    dt, dT, dU = (torch.from_numpy(a).to(DEV) for a in (tg, T, U))
+    loss = packing.rnnt_loss(p, dt, dT, dU, blank=0, reduction=reduction)
+    loss.backward()
+    ref = O.oracle_loss(x.astype(np.float64), tg, T, U, 0)
+    want = -ref["scores"].sum() / (3 if reduction == "mean" else 1)
+    assert abs(loss.item() - want) <= 1e-5 * abs(want)
+    scale = 1.0 / (3 if reduction == "mean" else 1)
+    g = p.grad.cpu().numpy()
+    for b in range(3):
+        got = g[b, :T[b], :U[b] + 1].reshape(-1, 11)
+        np.testing.assert_allclose(got, scale * ref["grad"][sp[b]:sp[b + 1]], rtol=0, atol=2e-5)
+        assert np.all(g[b, T[b]:] == 0) and np.all(g[b, :, U[b] + 1:] == 0)
+    try:
+        import torchaudio
+    except Exception:
+        return
+    ta = torchaudio.functional.rnnt_loss(torch.from_numpy(padded).requires_grad_(True), torch.from_numpy(tg),
+                                         torch.from_numpy(T), torch.from_numpy(U), blank=0, reduction=reduction)
+    assert abs(loss.item() - ta.item()) <= 1e-4 * abs(ta.item())
