@@ -420,6 +420,54 @@ def run_ours(args, w):
         dist.destroy_process_group()
 
 
+def run_pack(args, w):
+    """Measurement of the packing helpers (callers' side of the packed layout) on
+    the workload's shapes with D = 512 features: forward = one pass that writes
+    rows*D*4 bytes, backward = two summation passes that read them."""
+    import torch
+    from optimized_transducer_b200 import packing, synthetic
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    d = 512
+    T, U, _ = synthetic.make_lengths(w)
+    rows = synthetic.num_rows(T, U)
+    dT, dU = T.to(dev), U.to(dev)
+    enc = torch.randn(w.n, int(T.max()), d, device=dev, requires_grad=True)
+    dec = torch.randn(w.n, int(U.max()) + 1, d, device=dev, requires_grad=True)
+    g = torch.randn(rows, d, device=dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    fwd, bwd = [], []
+    for it in range(args.warmup + args.steps):
+        ev[0].record()
+        x = packing.pack_joiner_input(enc, dec, dT, dU, rows=rows)
+        ev[1].record()
+        x.backward(g)
+        ev[2].record()
+        torch.cuda.synchronize()
+        if it >= args.warmup:
+            fwd.append(ev[0].elapsed_time(ev[1]))
+            bwd.append(ev[1].elapsed_time(ev[2]))
+        enc.grad = dec.grad = None
+    peak, peak_kind = measured_hbm_peak()
+    f_ms, b_ms = statistics.median(fwd), statistics.median(bwd)
+    bytes_out = rows * d * 4
+    line = {
+        "metric": "packed joiner-input elements (rows*D)/s, forward", "value": rows * d / (f_ms * 1e-3),
+        "unit": "elements/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": f_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"pack_joiner_input on {w.name} lengths, D={d}, rows={rows}"},
+        "roofline": {"kernel": "pack_rows_kernel<add>", "bound": "hbm", "achieved": bytes_out / (f_ms * 1e-3) / 1e9,
+                     "peak": peak, "unit": "GB/s", "frac": bytes_out / (f_ms * 1e-3) / 1e9 / peak,
+                     "peak_source": f"{peak_kind} copy bandwidth", "traffic": None},
+        "backward": {"ms": b_ms, "kernels": "pack_sum_kernel x2 (+ autograd's gradient copy)",
+                     "achieved_gbs": 2 * bytes_out / (b_ms * 1e-3) / 1e9},
+        "gpu_launches": 4 * args.steps,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -432,6 +480,8 @@ def main():
                     help="utterances per step of the reference arm (bounded sample)")
     ap.add_argument("--cpu-utts", type=int, default=8,
                     help="utterances of the CPU-baseline sample of our arm")
+    ap.add_argument("--op", choices=["loss", "pack"], default="loss",
+                    help="loss: the transducer loss (default, the benchmark); pack: the packing helpers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer measurement")
     ap.add_argument("--utts", type=int, default=0,
@@ -441,7 +491,9 @@ def main():
         args.warmup = 3
     from optimized_transducer_b200 import synthetic
     w = synthetic.CONFIGS[args.workload]
-    if args.impl == "reference":
+    if args.op == "pack":
+        run_pack(args, w)
+    elif args.impl == "reference":
         run_reference_arm(args, w)
     else:
         run_ours(args, w)
