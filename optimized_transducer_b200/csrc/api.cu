@@ -9,6 +9,8 @@
 // none, unless the caller asks for the input-check status.
 #include <stdarg.h>
 #include <stdio.h>
+
+#include <chrono>
 #include <string.h>
 
 #include "ot_common.cuh"
@@ -45,11 +47,14 @@ const char *input_error_text(int code) {
   }
 }
 
-// Pinned landing pad + event for the optional status read-back, one per host
+// Mapped pinned words for the optional input-check report, one set per host
 // thread and device, created on first use and kept for the thread's lifetime.
+// Stage 0 writes {code, utterance, sequence number} into them; the host polls
+// the sequence number.  Nothing but kernels is ever enqueued on the stream.
 struct StatusSlot {
-  int32_t *host = nullptr;
-  cudaEvent_t ev = nullptr;
+  volatile int32_t *host = nullptr;
+  int32_t *dev = nullptr;
+  int32_t seq = 0;
 };
 thread_local StatusSlot g_slots[64];
 
@@ -60,10 +65,15 @@ int get_slot(StatusSlot **out) {
   if (dev < 0 || dev >= 64) return fail(OT_B200_ERR_ARGUMENT, "device ordinal %d not supported", dev);
   StatusSlot &s = g_slots[dev];
   if (!s.host) {
-    e = cudaHostAlloc(reinterpret_cast<void **>(&s.host), kStatusWords * sizeof(int32_t), cudaHostAllocDefault);
+    void *h = nullptr;
+    e = cudaHostAlloc(&h, kStatusWords * sizeof(int32_t), cudaHostAllocMapped);
     if (e != cudaSuccess) return fail_cuda(e, "cudaHostAlloc(status)");
-    e = cudaEventCreateWithFlags(&s.ev, cudaEventDisableTiming);
-    if (e != cudaSuccess) return fail_cuda(e, "cudaEventCreate(status)");
+    memset(h, 0, kStatusWords * sizeof(int32_t));
+    void *d = nullptr;
+    e = cudaHostGetDevicePointer(&d, h, 0);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaHostGetDevicePointer(status)");
+    s.host = static_cast<volatile int32_t *>(h);
+    s.dev = static_cast<int32_t *>(d);
   }
   *out = &s;
   return OT_B200_OK;
@@ -211,17 +221,12 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
     if (rc) return rc;
   }
 
+  if (slot) {
+    p.host_status = slot->dev;
+    p.host_seq = ++slot->seq;
+  }
   cudaError_t e = launch_prepare(p, s);
   if (e != cudaSuccess) return fail_cuda(e, "launch prepare");
-  if (slot) {
-    // The copy sits between stage 0 and stage 1 in stream order; the host waits
-    // for it only after everything else has been enqueued.
-    e = cudaMemcpyAsync(slot->host, p.ws + p.lay.status, 2 * sizeof(int32_t),
-                        cudaMemcpyDeviceToHost, s);
-    if (e != cudaSuccess) return fail_cuda(e, "copy status");
-    e = cudaEventRecord(slot->ev, s);
-    if (e != cudaSuccess) return fail_cuda(e, "record status event");
-  }
   e = launch_logprob(p, s);
   if (e != cudaSuccess) return fail_cuda(e, "launch logprob");
   e = launch_lattice(p, d_scores, s);
@@ -229,8 +234,19 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
   e = launch_coef(p, d_scores, d_loss, loss_scale, s);
   if (e != cudaSuccess) return fail_cuda(e, "launch coef");
   if (slot) {
-    e = cudaEventSynchronize(slot->ev);
-    if (e != cudaSuccess) return fail_cuda(e, "wait for status");
+    // Everything has been enqueued; now wait until stage 0 of THIS call has
+    // reported (it runs as soon as the stream reaches it).  Bounded: 60 s.
+    const int32_t want = slot->seq;
+    const auto t0 = std::chrono::steady_clock::now();
+    long spins = 0;
+    while (slot->host[2] != want) {
+      if ((++spins & 1023) == 0) {
+        if (cudaStreamQuery(s) == cudaSuccess && slot->host[2] != want)
+          return fail(OT_B200_ERR_CUDA, "the input check did not report although the stream is idle");
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(60))
+          return fail(OT_B200_ERR_CUDA, "timed out waiting for the input check");
+      }
+    }
     if (slot->host[kStatusCode] != 0)
       return fail(OT_B200_ERR_INPUT, "input check failed (code %d, utterance %d): %s",
                   slot->host[kStatusCode], slot->host[kStatusIndex],

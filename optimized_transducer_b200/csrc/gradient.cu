@@ -52,6 +52,8 @@ __global__ void __launch_bounds__(kThreads)
 gradient_kernel(const T *x, T *g, const CoefA<T> *__restrict__ coef,
                 const int32_t *__restrict__ status, int64_t rows, int V,
                 int blank, const T *__restrict__ d_scale, T scale_host) {
+  pdl_wait();
+  pdl_trigger();
   if (status[kStatusCode] != 0) return;
   using VT = typename VecOf<T, VEC>::type;
   const int lane = threadIdx.x & 31;
@@ -111,6 +113,8 @@ gradient_logsoftmax_kernel(T *__restrict__ g, const CoefB<T> *__restrict__ coef,
                            const int32_t *__restrict__ status, int64_t rows,
                            int V, int blank, const T *__restrict__ d_scale,
                            T scale_host) {
+  pdl_wait();
+  pdl_trigger();
   if (status[kStatusCode] != 0) return;
   using VT = typename VecOf<T, VEC>::type;
   const int lane = threadIdx.x & 31;
@@ -154,12 +158,13 @@ template <typename T, int VEC, int CH>
 cudaError_t launch_grad_a(const Problem &p, void *grad, const void *d_scale,
                           double scale_host, cudaStream_t s) {
   static int per_sm = 0;
-  gradient_kernel<T, VEC, CH><<<stream_grid(gradient_kernel<T, VEC, CH>, &per_sm, p.rows), kThreads, 0, s>>>(
+  const cudaError_t e = launch_pdl(gradient_kernel<T, VEC, CH>,
+      stream_grid(gradient_kernel<T, VEC, CH>, &per_sm, p.rows), (unsigned)kThreads, 0, s,
       static_cast<const T *>(p.logits), static_cast<T *>(grad),
       reinterpret_cast<const CoefA<T> *>(p.ws + p.lay.coef),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V,
       p.blank, static_cast<const T *>(d_scale), (T)scale_host);
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <typename T>

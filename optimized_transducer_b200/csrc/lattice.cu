@@ -108,6 +108,8 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   extern __shared__ __align__(128) unsigned char stage_mem[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ T xchg[2][kMaxWarps];
+  pdl_wait();
+  pdl_trigger();
   if (status[kStatusCode] != 0) return;
   const int b = blockIdx.x >> 1;
   const bool backward = blockIdx.x & 1;
@@ -305,6 +307,8 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   extern __shared__ __align__(128) unsigned char stage_mem[];
   __shared__ __align__(8) uint64_t full_bar[kSkewMaxStages];
   __shared__ T edge[kMaxWarps][kSkewRing];  // edge[w][s & 63]: boundary column of warp w after step s
+  pdl_wait();
+  pdl_trigger();
   if (status[kStatusCode] != 0) return;
   const int b = blockIdx.x >> 1;
   const bool backward = blockIdx.x & 1;
@@ -487,6 +491,8 @@ lattice_generic_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
                        const int64_t *__restrict__ cell_split,
                        const int32_t *__restrict__ status, T *alpha, T *beta,
                        T *__restrict__ scores, T *__restrict__ scores_beta) {
+  pdl_wait();
+  pdl_trigger();
   if (status[kStatusCode] != 0) return;
   const int b = blockIdx.x >> 1;
   const bool backward = blockIdx.x & 1;
@@ -594,14 +600,14 @@ cudaError_t launch_skewed(const Problem &p, void *scores, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     granted[dev] = smem;
   }
-  kernel<<<2u * (unsigned)p.N, (unsigned)(nwarps * kWarp), smem, s>>>(
+  const cudaError_t le = launch_pdl(kernel, 2u * (unsigned)p.N, (unsigned)(nwarps * kWarp), smem, s,
       reinterpret_cast<const T *>(p.ws + p.lay.lp), p.T, p.U,
       reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
       reinterpret_cast<int32_t *>(p.ws + p.lay.status),
       reinterpret_cast<T *>(p.ws + p.lay.alpha), reinterpret_cast<T *>(p.ws + p.lay.beta),
       static_cast<T *>(scores), reinterpret_cast<T *>(p.ws + p.lay.scores_beta), K, stage_pairs,
       nstages);
-  return cudaGetLastError();
+  return le != cudaSuccess ? le : cudaGetLastError();
 }
 
 template <typename T, bool FAST, bool MODIFIED>
@@ -629,13 +635,13 @@ cudaError_t launch_staged(const Problem &p, void *scores, cudaStream_t s) {
     granted[dev] = smem;
   }
   const unsigned block = (unsigned)((cols + kWarp - 1) / kWarp * kWarp);
-  kernel<<<2u * (unsigned)p.N, block, smem, s>>>(
+  const cudaError_t le = launch_pdl(kernel, 2u * (unsigned)p.N, block, smem, s,
       reinterpret_cast<const T *>(p.ws + p.lay.lp), p.T, p.U,
       reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
       reinterpret_cast<int32_t *>(p.ws + p.lay.status),
       reinterpret_cast<T *>(p.ws + p.lay.alpha), reinterpret_cast<T *>(p.ws + p.lay.beta),
       static_cast<T *>(scores), reinterpret_cast<T *>(p.ws + p.lay.scores_beta), R, stage_pairs);
-  return cudaGetLastError();
+  return le != cudaSuccess ? le : cudaGetLastError();
 }
 
 template <typename T>

@@ -69,6 +69,8 @@ logprob_kernel(const T *__restrict__ logits, const int32_t *__restrict__ targets
                const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
                const int32_t *__restrict__ status, int N, int64_t rows, int V,
                int max_u, int blank, T *__restrict__ den, T *__restrict__ lp) {
+  pdl_wait();
+  pdl_trigger();
   if (status[kStatusCode] != 0) return;
   using VT = typename VecOf<T, VEC>::type;
   constexpr int kGroups = kWarp / LPR;  // rows a warp works on at once
@@ -164,6 +166,8 @@ gather_kernel(const T *__restrict__ logp, const int32_t *__restrict__ targets,
               const int64_t *__restrict__ cell_split,
               const int32_t *__restrict__ status, int N, int64_t rows, int V,
               int max_u, int blank, T *__restrict__ lp) {
+  pdl_wait();
+  pdl_trigger();
   if (status[kStatusCode] != 0) return;
   const int64_t row = (int64_t)blockIdx.x * kThreads + threadIdx.x;
   if (row >= rows) return;
@@ -186,14 +190,14 @@ cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
   const int64_t want = (p.rows + rows_per_block - 1) / rows_per_block;
   const int64_t cap = (int64_t)sm_count() * per_sm;
   const unsigned grid = (unsigned)(want < cap ? want : cap);
-  kernel<<<grid, kThreads, 0, s>>>(
+  const cudaError_t e = launch_pdl(kernel, grid, (unsigned)kThreads, 0, s,
       static_cast<const T *>(p.logits), p.targets, p.T, p.U,
       reinterpret_cast<const int64_t *>(p.ws + p.lay.split),
       reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.N, p.rows, p.V,
       p.max_u, p.blank, reinterpret_cast<T *>(p.ws + p.lay.den),
       reinterpret_cast<T *>(p.ws + p.lay.lp));
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <typename T, int VEC, int CH, int LPR>

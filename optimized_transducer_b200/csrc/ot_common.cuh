@@ -97,6 +97,8 @@ struct Problem {
   uint32_t flags;
   char *ws;
   Layout lay;
+  int32_t *host_status = nullptr;  // device view of a mapped host buffer (input-check report), or NULL
+  int32_t host_seq = 0;            // value stage 0 stores into host_status[2] when the report is complete
 };
 
 // Number of SMs of the current device (cached per device).
@@ -112,6 +114,33 @@ int blocks_per_sm(K kernel, int threads) {
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) n = 1;
   return n;
 }
+
+// Programmatic dependent launch: the kernel may be scheduled while its
+// predecessor in the stream is still running (its CTAs then block in pdl_wait()
+// until the predecessor's memory is visible), which takes the launch latency
+// and the ramp-up of a full-occupancy grid out of the gap between two stages.
+template <typename... Exp, typename... Act>
+cudaError_t launch_pdl(void (*kernel)(Exp...), unsigned grid, unsigned block, size_t smem,
+                       cudaStream_t s, Act &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Exp>(args)...);
+}
+#ifdef __CUDACC__
+// First statement of every kernel that reads what an earlier kernel wrote
+// (a no-op when the kernel was launched the ordinary way) ...
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// ... and the permission for the next kernel in the stream to be scheduled.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 // Host launchers, one per stage; each returns the cudaError_t of its launch.
 cudaError_t launch_prepare(const Problem &p, cudaStream_t s);

@@ -163,9 +163,11 @@ int fail(int code, const char *msg) {
   return code;
 }
 
-unsigned rows_grid(int64_t rows) {
+// One resident wave of `kernel` (a grid-stride grid that is larger runs a partial second wave).
+template <typename K>
+unsigned rows_grid(K kernel, int64_t rows) {
   const int64_t want = (rows + (kThreads / kWarp) * kRun - 1) / ((kThreads / kWarp) * kRun);
-  const int64_t cap = (int64_t)sm_count() * 8;
+  const int64_t cap = (int64_t)sm_count() * blocks_per_sm(kernel, kThreads);
   return (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
 }
 
@@ -180,11 +182,11 @@ int launch_rows(const void *a, const void *b, void *out, const int32_t *Tl, cons
                    (reinterpret_cast<uintptr_t>(out) % 16 == 0) &&
                    (b == nullptr || reinterpret_cast<uintptr_t>(b) % 16 == 0);
   if (vec)
-    pack_rows_kernel<T, VEC, MODE><<<rows_grid(rows), kThreads, 0, s>>>(
+    pack_rows_kernel<T, VEC, MODE><<<rows_grid(pack_rows_kernel<T, VEC, MODE>, rows), kThreads, 0, s>>>(
         static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), Tl, Ul, split,
         status, N, rows, D, max_t, max_u1);
   else
-    pack_rows_kernel<T, 1, MODE><<<rows_grid(rows), kThreads, 0, s>>>(
+    pack_rows_kernel<T, 1, MODE><<<rows_grid(pack_rows_kernel<T, 1, MODE>, rows), kThreads, 0, s>>>(
         static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), Tl, Ul, split,
         status, N, rows, D, max_t, max_u1);
   const cudaError_t e = cudaGetLastError();

@@ -50,10 +50,13 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
                int max_u, int modified, int64_t max_cells,
                int32_t *__restrict__ status, int64_t *__restrict__ split,
                int64_t *__restrict__ cell_split, uint4 *__restrict__ lp_fill,
-               int64_t lp_fill_count, uint4 fill_pattern) {
+               int64_t lp_fill_count, uint4 fill_pattern,
+               volatile int32_t *host_status, int32_t host_seq) {
   __shared__ long long scan_buf[kPrepThreads / kWarp];
   __shared__ int warp_maxu[kPrepThreads / kWarp];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();     // the previous call's kernels may still be reading this workspace
+  pdl_trigger();
   if (blockIdx.x > 0) {
     // Blocks 1.. set every (blank, symbol) log-prob pair to -inf, 16 bytes at a
     // time.  Stage 1 then overwrites the pairs of real lattice cells; what is
@@ -116,6 +119,17 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
     const int b = (int)(i / max_u), u = (int)(i % max_u);
     if (v >= V || (u < Ul[b] && v < 0)) raise(status, OT_B200_INPUT_TARGET_RANGE, b);
   }
+  // Optional report straight into (mapped, pinned) host memory: the host polls
+  // the sequence word, so no copy or event has to sit in the stream.
+  if (host_status != nullptr) {
+    __syncthreads();
+    if (tid == 0) {
+      host_status[0] = status[kStatusCode];
+      host_status[1] = status[kStatusIndex];
+      __threadfence_system();
+      host_status[2] = host_seq;
+    }
+  }
 }
 
 // Thread per workspace cell, in the order alpha and beta are stored, so their
@@ -139,6 +153,8 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
             const T *__restrict__ alpha, const T *__restrict__ beta,
             void *__restrict__ coef_out, const T *__restrict__ scores,
             T *__restrict__ loss_out, double loss_scale) {
+  pdl_wait();
+  pdl_trigger();
   if (status[kStatusCode] != 0) return;
   if (blockIdx.x == 0 && threadIdx.x < kWarp && loss_out != nullptr) {
     double acc = 0;
@@ -233,14 +249,15 @@ cudaError_t launch_coef_t(const Problem &p, const void *scores, void *loss_out,
   const T *beta = reinterpret_cast<const T *>(p.ws + p.lay.beta);
   void *coef = p.ws + p.lay.coef;
   const unsigned grid = (unsigned)((p.lay.max_cells + 255) / 256);
+  cudaError_t e = cudaSuccess;
 #define OTB_COEF(MB, MOD)                                                        \
-  coef_kernel<T, MB, MOD><<<grid, 256, 0, s>>>(p.targets, p.T, p.U, split,       \
+  e = launch_pdl(coef_kernel<T, MB, MOD>, grid, 256u, 0, s, p.targets, p.T, p.U, split,   \
       csplit, status, p.N, p.max_u, p.blank, den, lp, alpha, beta, coef,         \
       static_cast<const T *>(scores), static_cast<T *>(loss_out), loss_scale)
   if (mode_b) { if (modified) OTB_COEF(true, true); else OTB_COEF(true, false); }
   else        { if (modified) OTB_COEF(false, true); else OTB_COEF(false, false); }
 #undef OTB_COEF
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace
@@ -262,7 +279,7 @@ cudaError_t launch_prepare(const Problem &p, cudaStream_t s) {
       reinterpret_cast<int32_t *>(p.ws + p.lay.status),
       reinterpret_cast<int64_t *>(p.ws + p.lay.split),
       reinterpret_cast<int64_t *>(p.ws + p.lay.cell_split),
-      reinterpret_cast<uint4 *>(p.ws + p.lay.lp), units, pattern);
+      reinterpret_cast<uint4 *>(p.ws + p.lay.lp), units, pattern, p.host_status, p.host_seq);
   return cudaGetLastError();
 }
 
