@@ -367,15 +367,15 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     const bool produce = (lane == kWarp - 1) && (warp + 1 < nwarps);
     const bool consume = (lane == 0) && (warp > 0);
     T *out_edge = edge[warp];
-    const T *in_edge = edge[consume ? warp - 1 : 0];
+    const T *in_edge = edge[consume ? warp - 1 : 0];  // lanes that do not consume read (and drop) a valid word
+    // The value of step s sits in ring entry (s-1) & 63.
     // "after step 0": columns 31, 63, ... have not started
-    if (lane == 0) out_edge[0] = ninf;
+    if (lane == 0) out_edge[kMask] = ninf;
     T *al = alpha + off;
     T own = (u == 0) ? (T)0 : ninf;
     if (u == 0) al[0] = 0;
     if (nwarps > 1) bar_active(nact); else __syncwarp();
     if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);
-    const unsigned span = (unsigned)(s_hi - s_lo);
     const bool first_col = (u == 0);  // has no symbol predecessor
     for (int p = 0; p < nphases; ++p) {
       if (u == 0 && p + 2 < nchunks) issue(p + 2);
@@ -386,32 +386,47 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         wait_chunk(q);
         const P *rowp = stage + (int64_t)(q % nstages) * stage_pairs + uc;
         T *st = al + (int64_t)(row0 + 1) * U1 + uc;  // entry of the block's first step
-        // No range checks on the log-probs: entries that are no lattice cell
-        // hold -inf (stage 0 fills, stage 1 overwrites the real cells), and a
-        // column that has not started holds -inf itself.
+        // No range checks anywhere in a step.  Log-probs: entries that are no
+        // lattice cell hold -inf (stage 0 fills, stage 1 overwrites the real
+        // cells), and a column that has not started holds -inf itself.  Stores:
+        // every (step, column) pair has an entry in the utterance's block, and
+        // what lands in the entries that are no cell is never read.
         T lb = rowp[0].x;
         T ls = first_col ? ninf : rowp[-1].y;
-        T e_cur = consume ? in_edge[row0 & kMask] : ninf;  // column u-1 after step row0
-        for (int i = 0; i < n; ++i) {
-          const int s = row0 + 1 + i;
+        T e_cur = in_edge[(row0 - 1) & kMask];  // column u-1 after step row0
+        // One step; `e_in` / `e_out` are the ring entries of this step.
+        auto step = [&](const bool more, const T *e_in, T *e_out) {
           // loads for the next step first
           rowp += U1;
-          const bool more = i + 1 < n;
-          const T x_next = more ? rowp[0].x : ninf;
-          const T y_next = (more && !first_col) ? rowp[-1].y : ninf;
-          const T e_next = (consume && more) ? in_edge[s & kMask] : ninf;
+          T x_next = ninf, y_next = ninf, e_next = ninf;
+          if (more) {
+            x_next = rowp[0].x;
+            y_next = rowp[-1].y;
+            e_next = *e_in;
+          }
+          y_next = first_col ? ninf : y_next;
           // the chain
-          T left = __shfl_up_sync(kFull, own, 1);
-          left = consume ? e_cur : left;
-          const T nv = log_add<T, FAST>(own + lb, left + ls);
+          const T up = __shfl_up_sync(kFull, own, 1);
+          const T left = consume ? e_cur : up;
           // What a column holds after its last cell is never consumed (its
-          // neighbour's cells end one step later), so only the store is guarded.
-          if ((unsigned)(s - s_lo) <= span) *st = nv;
-          own = nv;
+          // neighbour's cells end one step later).
+          own = log_add<T, FAST>(own + lb, left + ls);
+          if (col) *st = own;
           st += U1;
-          if (produce) out_edge[s & kMask] = own;
+          if (produce) *e_out = own;
           lb = x_next; ls = y_next;
           e_cur = e_next;
+        };
+        if (n == kSkewMaxK && K == kSkewMaxK) {
+          // row0 is a multiple of 16: the block's ring entries do not wrap, and
+          // with the loop unrolled they are constant offsets from one base.
+          const T *e_in = in_edge + (row0 & kMask);
+          T *e_out = out_edge + (row0 & kMask);
+#pragma unroll
+          for (int i = 0; i < kSkewMaxK; ++i) step(i + 1 < kSkewMaxK, e_in + i, e_out + i);
+        } else {
+          for (int i = 0; i < n; ++i)
+            step(i + 1 < n, in_edge + ((row0 + i) & kMask), out_edge + ((row0 + i) & kMask));
         }
       }
       if (nwarps > 1) bar_active(nact); else __syncwarp();
@@ -437,9 +452,12 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     if (lane == 0) out_edge[top & kMask] = (u == U) ? fin : ninf;
     if (nwarps > 1) bar_active(nact); else __syncwarp();
     if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);
-    const int hi = (u == U) ? s_hi - 1 : s_hi;  // the final cell is done
-    const unsigned span = (hi >= s_lo) ? (unsigned)(hi - s_lo) : 0u;
-    const bool any = hi >= s_lo;
+    // Column U starts with the final cell and computes from the first step on,
+    // unless it has no other cell (standard: T == 1; one symbol per frame:
+    // U == T-1): then it must keep the final cell for column U-1 to read.
+    const int hi = (u == U) ? s_hi - 1 : s_hi;
+    const bool keep = (u == U) && hi < s_lo;
+    const bool wr = col && !keep;
     for (int p = 0; p < nphases; ++p) {
       if (u == 0 && p + 2 < nchunks) issue(p + 2);
       const int q = p - delay;
@@ -454,25 +472,36 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
           const P v = rowp[0];  // (-inf, -inf) where (step, column) is no lattice cell
           lb = v.x; ls = v.y;
         }
-        T e_cur = consume ? in_edge[(row0 + n) & kMask] : ninf;  // column u+1 after step row0+n
-        for (int i = n - 1; i >= 0; --i) {
-          const int s = row0 + i;
+        T e_cur = in_edge[(row0 + n) & kMask];  // column u+1 after step row0+n
+        // One step (no range checks, as in the alpha sweep); the value of step
+        // s sits in ring entry s & 63.
+        auto step = [&](const bool more, const T *e_in, T *e_out) {
           rowp -= U1;
           P v_next;
           v_next.x = ninf; v_next.y = ninf;
-          if (i > 0) v_next = rowp[0];
-          const T e_next = (consume && i > 0) ? in_edge[s & kMask] : ninf;
-          T right = __shfl_down_sync(kFull, own, 1);
-          right = consume ? e_cur : right;
+          T e_next = ninf;
+          if (more) {
+            v_next = rowp[0];
+            e_next = *e_in;
+          }
+          const T dn = __shfl_down_sync(kFull, own, 1);
+          const T right = consume ? e_cur : dn;
           const T nv = log_add<T, FAST>(own + lb, right + ls);
-          const bool act = any && (unsigned)(s - s_lo) <= span;
-          if (act) *st = nv;
-          // column U keeps the final cell until its steps begin (T == 1: never)
-          own = (u == U && !act) ? own : nv;
+          own = keep ? own : nv;
+          if (wr) *st = nv;
           st -= U1;
-          if (produce) out_edge[s & kMask] = own;
+          if (produce) *e_out = own;
           lb = v_next.x; ls = v_next.y;
           e_cur = e_next;
+        };
+        if (n == kSkewMaxK && K == kSkewMaxK) {
+          const T *e_in = in_edge + (row0 & kMask);
+          T *e_out = out_edge + (row0 & kMask);
+#pragma unroll
+          for (int i = kSkewMaxK - 1; i >= 0; --i) step(i > 0, e_in + i, e_out + i);
+        } else {
+          for (int i = n - 1; i >= 0; --i)
+            step(i > 0, in_edge + ((row0 + i) & kMask), out_edge + ((row0 + i) & kMask));
         }
       }
       if (nwarps > 1) bar_active(nact); else __syncwarp();
