@@ -61,10 +61,14 @@ typedef enum ot_b200_input_error {
 #define OT_B200_FROM_LOG_SOFTMAX 1u   /* input rows are log-softmax outputs         */
 #define OT_B200_ONE_SYM_PER_FRAME 2u  /* modified transducer                        */
 #define OT_B200_FP64 4u               /* logits/scores/grad are double, not float   */
-#define OT_B200_CHECK_INPUTS 8u       /* read the input-check status back (one wait
-                                         on an event recorded before the streaming
-                                         kernels; not allowed during stream capture) */
+#define OT_B200_CHECK_INPUTS 8u       /* ot_b200_forward waits for the input-check
+                                         report (a few words stage 0 stores into
+                                         mapped host memory) before it returns; not
+                                         allowed during stream capture              */
 #define OT_B200_FAST_MATH 16u         /* approximate exp/log in the recursions      */
+#define OT_B200_SCALE_PER_UTTERANCE 32u /* ot_b200_backward only: d_scale holds one
+                                         factor per utterance (no counterpart in the
+                                         reference, which only reduces)             */
 
 /* Byte offsets of the intermediate arrays inside the workspace, for callers
  * (and tests) that want the stage outputs.  Element type is float, or double
@@ -139,7 +143,10 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
  *            read and d_grad must be a separate buffer (cuda.cu:444).
  * N, rows, max_u, flags  as given to ot_b200_forward (they fix the layout)
  * scale = scale_host * (d_scale ? *d_scale : 1); d_scale is a device scalar of
- *            the real type (e.g. the upstream gradient of the loss). */
+ *            the real type (e.g. the upstream gradient of the loss).  With
+ *            OT_B200_SCALE_PER_UTTERANCE d_scale must not be NULL and holds N
+ *            reals: the rows of utterance b are scaled by scale_host * d_scale[b]
+ *            (the upstream gradient of a per-utterance loss vector). */
 int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows,
                      int32_t V, int32_t max_u, int32_t blank, uint32_t flags,
                      const void *d_workspace, uint64_t workspace_bytes,

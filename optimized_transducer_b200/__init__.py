@@ -6,12 +6,14 @@ csukuangfj/optimized_transducer:
                                                 target_lengths, blank=0,
                                                 from_log_softmax=False)
 """
-from .transducer_loss import (TransducerLoss, TransducerLossFunction,  # noqa: F401
-                              compute_transducer_loss, stage_outputs, transducer_loss)
+from .transducer_loss import (PerUtteranceLossFunction, TransducerLoss,  # noqa: F401
+                              TransducerLossFunction, compute_transducer_loss, stage_outputs,
+                              transducer_loss, transducer_loss_per_utterance)
 
 from .packing import pack_joiner_input, pack_padded, rnnt_loss, unpack_to_padded  # noqa: F401,E402
 
 __version__ = "0.1.0"
 __all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
-           "compute_transducer_loss", "stage_outputs", "pack_joiner_input", "pack_padded",
+           "compute_transducer_loss", "stage_outputs", "transducer_loss_per_utterance",
+           "PerUtteranceLossFunction", "pack_joiner_input", "pack_padded",
            "unpack_to_padded", "rnnt_loss", "__version__"]

@@ -20,6 +20,7 @@ ONE_SYM_PER_FRAME = 2
 FP64 = 4
 CHECK_INPUTS = 8
 FAST_MATH = 16
+SCALE_PER_UTTERANCE = 32
 
 # Every symbol include/ot_b200.h declares.
 EXPORTS = (

@@ -80,7 +80,8 @@ int get_slot(StatusSlot **out) {
 }
 
 constexpr uint32_t kKnownFlags = OT_B200_FROM_LOG_SOFTMAX | OT_B200_ONE_SYM_PER_FRAME |
-                                 OT_B200_FP64 | OT_B200_CHECK_INPUTS | OT_B200_FAST_MATH;
+                                 OT_B200_FP64 | OT_B200_CHECK_INPUTS | OT_B200_FAST_MATH |
+                                 OT_B200_SCALE_PER_UTTERANCE;
 
 int check_sizes(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   if (N <= 0) return fail(OT_B200_ERR_ARGUMENT, "N must be positive, got %d", N);
@@ -267,6 +268,8 @@ int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows
   if (!mode_b && !d_logits) return fail(OT_B200_ERR_ARGUMENT, "logits pointer is NULL");
   if (mode_b && d_grad == d_logits)
     return fail(OT_B200_ERR_ARGUMENT, "with OT_B200_FROM_LOG_SOFTMAX the gradient needs its own buffer");
+  if ((flags & OT_B200_SCALE_PER_UTTERANCE) && !d_scale)
+    return fail(OT_B200_ERR_ARGUMENT, "OT_B200_SCALE_PER_UTTERANCE needs d_scale (N factors)");
   p.logits = d_logits; p.targets = nullptr; p.T = nullptr; p.U = nullptr;
   p.N = N; p.rows = rows; p.V = V; p.max_u = max_u; p.blank = blank; p.flags = flags;
   p.ws = static_cast<char *>(const_cast<void *>(d_workspace));

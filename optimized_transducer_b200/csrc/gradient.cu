@@ -37,17 +37,20 @@ __device__ __forceinline__ CoefA<T> load_coef(const CoefA<T> *p) {
   if constexpr (sizeof(T) == 4) {
     const float4 a = __ldg(reinterpret_cast<const float4 *>(p));
     r.c = a.x; r.beta = a.y; r.sub_blank = a.z; r.sub_sym = a.w;
-    r.tgt = __ldg(reinterpret_cast<const int32_t *>(p) + 4);
+    const int2 i = __ldg(reinterpret_cast<const int2 *>(p) + 2);
+    r.tgt = i.x; r.utt = i.y;
   } else {
     const double2 a = __ldg(reinterpret_cast<const double2 *>(p));
     const double2 b = __ldg(reinterpret_cast<const double2 *>(p) + 1);
     r.c = a.x; r.beta = a.y; r.sub_blank = b.x; r.sub_sym = b.y;
-    r.tgt = __ldg(reinterpret_cast<const int32_t *>(p) + 8);
+    const int2 i = __ldg(reinterpret_cast<const int2 *>(p) + 4);
+    r.tgt = i.x; r.utt = i.y;
   }
   return r;
 }
 
-template <typename T, int VEC, int CH>
+// PER_UTT: d_scale holds one factor per utterance instead of one scalar.
+template <typename T, int VEC, int CH, bool PER_UTT>
 __global__ void __launch_bounds__(kThreads)
 gradient_kernel(const T *x, T *g, const CoefA<T> *__restrict__ coef,
                 const int32_t *__restrict__ status, int64_t rows, int V,
@@ -60,11 +63,12 @@ gradient_kernel(const T *x, T *g, const CoefA<T> *__restrict__ coef,
   const int64_t warp0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const int nvec = V / VEC;
-  const T scale = d_scale ? scale_host * __ldg(d_scale) : scale_host;
+  const T scale_all = (!PER_UTT && d_scale) ? scale_host * __ldg(d_scale) : scale_host;
   const int bvec = blank / VEC, bk = blank % VEC;
 
   for (int64_t row = rows - 1 - warp0; row >= 0; row -= nwarps) {
     const CoefA<T> rec = load_coef(coef + row);
+    const T scale = PER_UTT ? scale_host * __ldg(d_scale + rec.utt) : scale_all;
     const T *px = x + row * (int64_t)V;
     T *pg = g + row * (int64_t)V;
     if (rec.tgt == kTgtZeroRow) {
@@ -107,7 +111,7 @@ gradient_kernel(const T *x, T *g, const CoefA<T> *__restrict__ coef,
   }
 }
 
-template <typename T, int VEC>
+template <typename T, int VEC, bool PER_UTT>
 __global__ void __launch_bounds__(kThreads)
 gradient_logsoftmax_kernel(T *__restrict__ g, const CoefB<T> *__restrict__ coef,
                            const int32_t *__restrict__ status, int64_t rows,
@@ -121,10 +125,11 @@ gradient_logsoftmax_kernel(T *__restrict__ g, const CoefB<T> *__restrict__ coef,
   const int64_t warp0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
   const int nvec = V / VEC;
-  const T scale = d_scale ? scale_host * __ldg(d_scale) : scale_host;
+  const T scale_all = (!PER_UTT && d_scale) ? scale_host * __ldg(d_scale) : scale_host;
   const int bvec = blank / VEC, bk = blank % VEC;
   for (int64_t row = warp0; row < rows; row += nwarps) {
     const CoefB<T> rec = coef[row];
+    const T scale = PER_UTT ? scale_host * __ldg(d_scale + rec.utt) : scale_all;
     T *pg = g + row * (int64_t)V;
     const bool zero = rec.tgt == kTgtZeroRow;
     const int tvec = (!zero && rec.tgt >= 0) ? rec.tgt / VEC : -1;
@@ -154,17 +159,37 @@ unsigned stream_grid(K kernel, int *per_sm, int64_t rows) {
   return (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
 }
 
-template <typename T, int VEC, int CH>
-cudaError_t launch_grad_a(const Problem &p, void *grad, const void *d_scale,
-                          double scale_host, cudaStream_t s) {
+template <typename T, int VEC, int CH, bool PER_UTT>
+cudaError_t launch_grad_a2(const Problem &p, void *grad, const void *d_scale,
+                           double scale_host, cudaStream_t s) {
   static int per_sm = 0;
-  const cudaError_t e = launch_pdl(gradient_kernel<T, VEC, CH>,
-      stream_grid(gradient_kernel<T, VEC, CH>, &per_sm, p.rows), (unsigned)kThreads, 0, s,
+  const cudaError_t e = launch_pdl(gradient_kernel<T, VEC, CH, PER_UTT>,
+      stream_grid(gradient_kernel<T, VEC, CH, PER_UTT>, &per_sm, p.rows), (unsigned)kThreads, 0, s,
       static_cast<const T *>(p.logits), static_cast<T *>(grad),
       reinterpret_cast<const CoefA<T> *>(p.ws + p.lay.coef),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V,
       p.blank, static_cast<const T *>(d_scale), (T)scale_host);
   return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+template <typename T, int VEC, int CH>
+cudaError_t launch_grad_a(const Problem &p, void *grad, const void *d_scale,
+                          double scale_host, cudaStream_t s) {
+  return (p.flags & OT_B200_SCALE_PER_UTTERANCE)
+             ? launch_grad_a2<T, VEC, CH, true>(p, grad, d_scale, scale_host, s)
+             : launch_grad_a2<T, VEC, CH, false>(p, grad, d_scale, scale_host, s);
+}
+
+template <typename T, int VEC, bool PER_UTT>
+cudaError_t launch_grad_b(const Problem &p, void *grad, const void *d_scale,
+                          double scale_host, cudaStream_t s) {
+  static int per_sm = 0;
+  auto kernel = gradient_logsoftmax_kernel<T, VEC, PER_UTT>;
+  kernel<<<stream_grid(kernel, &per_sm, p.rows), kThreads, 0, s>>>(
+      static_cast<T *>(grad), reinterpret_cast<const CoefB<T> *>(p.ws + p.lay.coef),
+      reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V, p.blank,
+      static_cast<const T *>(d_scale), (T)scale_host);
+  return cudaGetLastError();
 }
 
 template <typename T>
@@ -174,18 +199,12 @@ cudaError_t launch_gradient_t(const Problem &p, void *grad, const void *d_scale,
   const bool aligned = (p.V % VEC == 0) &&
                        (reinterpret_cast<uintptr_t>(grad) % 16 == 0);
   if (p.flags & OT_B200_FROM_LOG_SOFTMAX) {
-    const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
-    const CoefB<T> *coef = reinterpret_cast<const CoefB<T> *>(p.ws + p.lay.coef);
-    static int per_sm_v = 0, per_sm_1 = 0;
+    const bool per_utt = p.flags & OT_B200_SCALE_PER_UTTERANCE;
     if (aligned)
-      gradient_logsoftmax_kernel<T, VEC><<<stream_grid(gradient_logsoftmax_kernel<T, VEC>, &per_sm_v, p.rows), kThreads, 0, s>>>(
-          static_cast<T *>(grad), coef, status, p.rows, p.V, p.blank,
-          static_cast<const T *>(d_scale), (T)scale_host);
-    else
-      gradient_logsoftmax_kernel<T, 1><<<stream_grid(gradient_logsoftmax_kernel<T, 1>, &per_sm_1, p.rows), kThreads, 0, s>>>(
-          static_cast<T *>(grad), coef, status, p.rows, p.V, p.blank,
-          static_cast<const T *>(d_scale), (T)scale_host);
-    return cudaGetLastError();
+      return per_utt ? launch_grad_b<T, VEC, true>(p, grad, d_scale, scale_host, s)
+                     : launch_grad_b<T, VEC, false>(p, grad, d_scale, scale_host, s);
+    return per_utt ? launch_grad_b<T, 1, true>(p, grad, d_scale, scale_host, s)
+                   : launch_grad_b<T, 1, false>(p, grad, d_scale, scale_host, s);
   }
   const bool vec_ok = aligned && (reinterpret_cast<uintptr_t>(p.logits) % 16 == 0);
   if (vec_ok) {

@@ -309,15 +309,17 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   __shared__ T edge[kMaxWarps][kSkewRing];  // edge[w][s & 63]: boundary column of warp w after step s
   pdl_wait();
   pdl_trigger();
-  if (status[kStatusCode] != 0) return;
   const int b = blockIdx.x >> 1;
   const bool backward = blockIdx.x & 1;
+  // four independent loads, one round trip
+  const int bad = status[kStatusCode];
   const int Tn = Tl[b], U = Ul[b], U1 = U + 1;
+  const int64_t off = cell_split[b];
+  if (bad != 0) return;
   const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
   const int nwarps = (U1 + kWarp - 1) / kWarp;
   if (warp >= nwarps) return;
   const int nact = nwarps * kWarp;
-  const int64_t off = cell_split[b];
   const P *lp2 = reinterpret_cast<const P *>(lp) + off;
   P *stage = reinterpret_cast<P *>(stage_mem) + 2;  // slack: column 0 reads the pair before its row
   const bool col = u < U1;
@@ -374,8 +376,10 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     T *al = alpha + off;
     T own = (u == 0) ? (T)0 : ninf;
     if (u == 0) al[0] = 0;
+    if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);  // by the thread that initialised the barriers
+    // blank log-prob of the final cell, for the score (fetched long before it is needed)
+    const T fin_blank = (u == U) ? lp2[cell_pos<MODIFIED>(Tn - 1, U, U1)].x : (T)0;
     if (nwarps > 1) bar_active(nact); else __syncwarp();
-    if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);
     const bool first_col = (u == 0);  // has no symbol predecessor
     for (int p = 0; p < nphases; ++p) {
       if (u == 0 && p + 2 < nchunks) issue(p + 2);
@@ -431,10 +435,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       }
       if (nwarps > 1) bar_active(nact); else __syncwarp();
     }
-    if (u == U) {
-      const int64_t fin = cell_pos<MODIFIED>(Tn - 1, U, U1);
-      scores[b] = al[fin] + lp2[fin].x;  // own store, read back
-    }
+    if (u == U) scores[b] = own + fin_blank;  // column U's last step is the last step
   } else {
     // ------------------------------- beta ------------------------------
     const bool produce = (lane == 0) && (warp > 0);
@@ -450,8 +451,8 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     }
     // "after step top": the boundary column of this warp before any step
     if (lane == 0) out_edge[top & kMask] = (u == U) ? fin : ninf;
-    if (nwarps > 1) bar_active(nact); else __syncwarp();
     if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);
+    if (nwarps > 1) bar_active(nact); else __syncwarp();
     // Column U starts with the final cell and computes from the first step on,
     // unless it has no other cell (standard: T == 1; one symbol per frame:
     // U == T-1): then it must keep the final cell for column U-1 to read.
@@ -506,7 +507,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       }
       if (nwarps > 1) bar_active(nact); else __syncwarp();
     }
-    if (u == 0) scores_beta[b] = be[0];  // own store, read back
+    if (u == 0) scores_beta[b] = own;  // column 0's last step is the last step
   }
 }
 

@@ -65,6 +65,7 @@ struct alignas(32) CoefA {
   T sub_blank;  // beta of the blank successor (0 for the final cell)
   T sub_sym;    // beta of the symbol successor
   int32_t tgt;  // symbol column, or kTgtNone / kTgtZeroRow
+  int32_t utt;  // utterance the row belongs to (for a per-utterance scale)
 };
 
 // Mode B (input already log-softmax): the gradient row is zero except for at
@@ -74,6 +75,7 @@ struct alignas(16) CoefB {
   T val_blank;  // gradient at the blank column (0 if none)
   T val_sym;    // gradient at the symbol column
   int32_t tgt;  // symbol column, or kTgtNone / kTgtZeroRow
+  int32_t utt;  // utterance the row belongs to
 };
 
 struct Layout {

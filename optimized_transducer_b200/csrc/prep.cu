@@ -226,11 +226,13 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
     r.val_blank = blank_term ? -r_exp((lp[2 * cell] + c) + sub_blank) : (T)0;
     r.val_sym = sym_term ? -r_exp((lp[2 * cell + 1] + c) + sub_sym) : (T)0;
     r.tgt = zero ? kTgtZeroRow : tgt;
+    r.utt = b;
     reinterpret_cast<CoefB<T> *>(coef_out)[row] = r;
   } else {
     CoefA<T> r;
     r.c = c; r.beta = b_here; r.sub_blank = sub_blank; r.sub_sym = sub_sym;
     r.tgt = zero ? kTgtZeroRow : tgt;
+    r.utt = b;
     reinterpret_cast<CoefA<T> *>(coef_out)[row] = r;
   }
 }

@@ -34,7 +34,8 @@ import torch
 from . import _lib
 
 __all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
-           "compute_transducer_loss", "stage_outputs"]
+           "compute_transducer_loss", "stage_outputs", "transducer_loss_per_utterance",
+           "PerUtteranceLossFunction"]
 
 
 def _checks_enabled():
@@ -147,11 +148,17 @@ class _Call:
         _lib.check(rc)
         return self.scores
 
-    def backward(self, grad_out, scale_tensor=None, scale_host=1.0):
+    def backward(self, grad_out, scale_tensor=None, scale_host=1.0, per_utterance=False):
+        """Enqueues the gradient pass.  ``scale_tensor``: a device scalar, or with
+        ``per_utterance`` an (N,) tensor of per-utterance factors."""
+        flags = self.flags & ~_lib.CHECK_INPUTS
+        if per_utterance:
+            assert scale_tensor is not None and scale_tensor.numel() == self.n
+            flags |= _lib.SCALE_PER_UTTERANCE
         with torch.cuda.device(self.logits.device):
             rc = self.lib.ot_b200_backward(
                 self.logits.data_ptr(), grad_out.data_ptr(), self.n, self.rows, self.v,
-                self.max_u, self.blank, self.flags & ~_lib.CHECK_INPUTS,
+                self.max_u, self.blank, flags,
                 self.workspace.data_ptr(), int(self.layout.total_bytes),
                 scale_tensor.data_ptr() if scale_tensor is not None else None,
                 float(scale_host), self._stream())
@@ -279,6 +286,48 @@ class TransducerLossFunction(torch.autograd.Function):
         scale = loss_grad.detach().to(device=data.device, dtype=data.dtype).contiguous()
         call.backward(grad, scale_tensor=scale, scale_host=ctx.scale_host)
         return (grad,) + (None,) * 7
+
+
+class PerUtteranceLossFunction(torch.autograd.Function):
+    """``reduction="none"``: the (N,) vector of per-utterance losses.  The
+    reference has no such mode (transducer_loss.py:126-128 rejects it); its
+    native function already returns per-utterance scores, and the gradient pass
+    here takes one upstream factor per utterance."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, logit_lengths, target_lengths, blank,
+                from_log_softmax, one_sym_per_frame):
+        call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
+                     from_log_softmax, one_sym_per_frame)
+        scores = call.forward()
+        ctx.call = call if ctx.needs_input_grad[0] else None
+        return scores.neg()
+
+    @staticmethod
+    def backward(ctx, loss_grad):
+        if ctx.call is None:
+            raise RuntimeError("the gradient of this transducer loss was already consumed, "
+                               "or logits did not require grad")
+        call, ctx.call = ctx.call, None
+        assert loss_grad.numel() == call.n, (loss_grad.numel(), call.n)
+        data = call.logits
+        grad = torch.empty_like(data) if call.from_log_softmax else data
+        scale = loss_grad.detach().to(device=data.device, dtype=data.dtype).contiguous()
+        call.backward(grad, scale_tensor=scale, per_utterance=True)
+        return (grad,) + (None,) * 6
+
+
+def transducer_loss_per_utterance(logits: torch.Tensor, targets: torch.Tensor,
+                                  logit_lengths: torch.Tensor, target_lengths: torch.Tensor,
+                                  blank: int, from_log_softmax: bool,
+                                  one_sym_per_frame: bool = False) -> torch.Tensor:
+    """The unreduced transducer loss: an (N,) tensor, ``-log P(y_b | x_b)`` per
+    utterance.  Arguments as for :func:`transducer_loss`.  ``backward`` accepts
+    any (N,) upstream gradient and, like the reduced loss, overwrites ``logits``
+    with its gradient unless ``from_log_softmax`` is True."""
+    return PerUtteranceLossFunction.apply(
+        logits, targets, logit_lengths, target_lengths, blank, from_log_softmax,
+        one_sym_per_frame)
 
 
 class TransducerLoss(torch.nn.Module):

@@ -180,6 +180,33 @@ def test_autograd_surface(reduction, from_ls, modified, eager, monkeypatch):
                                    rtol=0, atol=3e-5)
 
 
+@pytest.mark.parametrize("from_ls", [False, True])
+@pytest.mark.parametrize("modified", [False, True])
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_per_utterance_loss_and_weighted_gradient(from_ls, modified, dtype):
+    """The unreduced loss (no counterpart in the reference, which rejects
+    reduction="none"): -scores of the oracle, and a gradient whose rows carry the
+    upstream factor of their utterance."""
+    x, tg, T, U = random_batch(44, 5, (6, 14), (2, 6), 9, modified=modified)
+    x = x.astype(dtype)
+    if from_ls:
+        x = (x - np.log(np.exp(x.astype(np.float64)).sum(-1, keepdims=True))).astype(dtype)
+    sp = splits(T, U)
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    leaf = dx.clone().requires_grad_(True)
+    loss = ot.transducer_loss_per_utterance(leaf * 1.0, dt, dT, dU, 0, from_ls, modified)
+    assert loss.shape == (5,)
+    w = torch.tensor([0.5, -2.0, 0.0, 3.0, 1.0], dtype=leaf.dtype, device=DEV)
+    (loss * w).sum().backward()
+    ref = O.oracle_loss(x.astype(np.float64), tg, T, U, 0, from_ls, modified)
+    tol = 1e-5 if dtype == np.float32 else 1e-10
+    np.testing.assert_allclose(loss.detach().cpu().numpy(), -ref["scores"], rtol=tol, atol=0)
+    got = leaf.grad.cpu().numpy()
+    for b in range(5):
+        np.testing.assert_allclose(got[sp[b]:sp[b + 1]], w[b].item() * ref["grad"][sp[b]:sp[b + 1]],
+                                   rtol=0, atol=3e-5 if dtype == np.float32 else 1e-10)
+
+
 def test_module_form_and_no_grad():
     x, tg, T, U = random_batch(42, 3, (5, 9), (2, 4), 6)
     dx, dt, dT, dU = to_dev(x, tg, T, U)
