@@ -311,6 +311,8 @@ def run_ours(args, w):
             ev[k][1].record()
             loss.backward()
             ev[k][2].record()
+        if world > 1:
+            sharding.wait_loss(loss)  # the last step's all-reduce ends inside the timed region
         t_end.record()
         barrier()
     elapsed_ms = t_begin.elapsed_time(t_end)
@@ -339,6 +341,8 @@ def run_ours(args, w):
             loss = ot.transducer_loss(x, g_, t_, u_, blank=0, from_log_softmax=w.from_log_softmax,
                                       one_sym_per_frame=w.one_sym_per_frame, reduction=w.reduction)
         loss.backward()
+        if world > 1:
+            sharding.wait_loss(loss)
         return float(loss.item())  # device-to-host read of the result
 
     e2e_ms = 0.0

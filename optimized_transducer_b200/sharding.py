@@ -173,8 +173,8 @@ def _side_stream(device):
 
 def wait_loss(loss: torch.Tensor) -> torch.Tensor:
     """Makes the current stream wait for the all-reduce behind a loss returned by
-    ``sharded_transducer_loss(..., overlap=True)``.  Call it before reading the
-    value if ``backward`` has not run yet."""
+    ``sharded_transducer_loss(..., overlap=True)``.  Call it before the value is
+    read (``loss.item()``, logging, a device-side consumer on another stream)."""
     if loss.is_cuda:
         # every overlapped all-reduce of this device runs on the same side stream
         torch.cuda.current_stream(loss.device).wait_stream(_side_stream(loss.device))
@@ -223,8 +223,11 @@ class _ShardedLoss(torch.autograd.Function):
             call.backward(grad, scale_tensor=g, scale_host=ctx.scale_host)
         elif ctx.empty_like is not None:
             grad = torch.zeros_like(ctx.empty_like)
-        if ctx.event is not None and loss_grad.is_cuda:
-            torch.cuda.current_stream(loss_grad.device).wait_event(ctx.event)
+        # Nothing here depends on the reduced VALUE, so the main stream does not
+        # wait for the collective: the gradient kernel fills every SM until it
+        # ends, the collective's kernel gets its slot only then, and a wait here
+        # would put its whole latency behind the gradient pass.  It now runs
+        # under whatever the main stream does next; wait_loss() orders a reader.
         return (grad,) + (None,) * 10
 
 
@@ -238,9 +241,9 @@ def sharded_transducer_loss(logits, targets, logit_lengths, target_lengths, blan
     by it; default: local count x world size).  Backward scales only the local
     rows: no gradient crosses ranks.
 
-    ``overlap=True`` issues the scalar all-reduce on a side stream so that it
-    runs under the gradient pass; the returned tensor is then complete once
-    ``backward`` has run or after :func:`wait_loss`."""
+    ``overlap=True`` issues the scalar all-reduce on a side stream, off the
+    critical path of the gradient pass; the VALUE of the returned tensor is then
+    defined only after :func:`wait_loss` (or a device synchronisation)."""
     if global_batch is None:
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         global_batch = int(logit_lengths.numel()) * world
