@@ -244,7 +244,7 @@ def run_ours(args, w):
         T, U = T[:n_global].contiguous(), U[:n_global].contiguous()
         tg = tg[:n_global, :int(U.max())].contiguous()
     if world > 1:
-        shard = sharding.shard_batch(T, U, tg, w.v, world, rank)
+        shard = sharding.shard_batch(T, U, tg, w.v, world, rank, strategy=args.partition)
         T, U, tg = shard.T, shard.U, shard.targets
     rows = synthetic.num_rows(T, U)
     cells_local = rows * w.v
@@ -360,7 +360,13 @@ def run_ours(args, w):
     # ----- max over ranks, whole-job totals
     stats = torch.tensor([elapsed_ms, e2e_ms, fwd_ms, bwd_ms], dtype=torch.float64, device=dev)
     cells = torch.tensor([float(cells_local)], dtype=torch.float64, device=dev)
+    per_rank = None
     if world > 1:
+        # every rank's own figures, for the record (the line reports the max)
+        mine = torch.tensor([elapsed_ms / args.steps, fwd_ms, bwd_ms, float(rows)], dtype=torch.float64, device=dev)
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        per_rank = [[round(v, 4) for v in g.tolist()] for g in gathered]
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         dist.all_reduce(cells, op=dist.ReduceOp.SUM)
     elapsed_ms, e2e_ms, fwd_ms, bwd_ms = stats.tolist()
@@ -382,7 +388,8 @@ def run_ours(args, w):
             "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {
                 "workload": workload_description(w, n_global, rows if world == 1 else "sharded"),
-                "sharding": "none" if world == 1 else f"{world} ranks, contiguous cost-balanced by T*(U+1)*V",
+                "sharding": "none" if world == 1 else
+                            f"{world} ranks, whole utterances, balanced by T*(U+1)*V ({args.partition} partition)",
                 "cache": "inputs larger than L2: every step reads its own pristine logits buffer",
                 "checks": os.environ.get("OT_CHECKS", "1"),
                 "gradient_schedule": "eager" if os.environ.get("OT_EAGER_GRAD", "0") == "1" else "deferred (fused into backward)",
@@ -408,6 +415,8 @@ def run_ours(args, w):
             },
             "loss": last_loss,
         }
+        if per_rank is not None:
+            line["per_rank"] = {"columns": ["ms_per_step", "forward_ms", "backward_ms", "rows"], "values": per_rank}
         if world == 1 and not args.no_cpu_baseline:
             step, c_cells, kind, cores, desc = cpu_reference_step_factory(w, min(args.cpu_utts, w.n))
             step()
@@ -480,6 +489,9 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--partition", choices=["auto", "contiguous", "lpt"], default="lpt",
+                    help="how utterances are dealt to the ranks (each rank creates its own shard, "
+                         "so the permuting, better balanced \"lpt\" costs nothing here)")
     ap.add_argument("--ref-utts", type=int, default=4,
                     help="utterances per step of the reference arm (bounded sample)")
     ap.add_argument("--cpu-utts", type=int, default=8,

@@ -66,6 +66,10 @@ typedef enum ot_b200_input_error {
                                          mapped host memory) before it returns; not
                                          allowed during stream capture              */
 #define OT_B200_FAST_MATH 16u         /* approximate exp/log in the recursions      */
+#define OT_B200_SHARE_SMS 64u          /* size the one-wave grids of the streaming
+                                         kernels one SM short: for callers that keep
+                                         another kernel resident beside this path (a
+                                         collective on a second stream)             */
 #define OT_B200_SCALE_PER_UTTERANCE 32u /* ot_b200_backward only: d_scale holds one
                                          factor per utterance (no counterpart in the
                                          reference, which only reduces)             */

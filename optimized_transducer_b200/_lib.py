@@ -21,6 +21,7 @@ FP64 = 4
 CHECK_INPUTS = 8
 FAST_MATH = 16
 SCALE_PER_UTTERANCE = 32
+SHARE_SMS = 64
 
 # Every symbol include/ot_b200.h declares.
 EXPORTS = (

@@ -152,10 +152,10 @@ gradient_logsoftmax_kernel(T *__restrict__ g, const CoefB<T> *__restrict__ coef,
 // Exactly one resident wave of `kernel` (never more warps than rows): a larger
 // grid-stride grid would run a partial second wave at the end.
 template <typename K>
-unsigned stream_grid(K kernel, int *per_sm, int64_t rows) {
+unsigned stream_grid(K kernel, int *per_sm, int64_t rows, uint32_t flags) {
   if (*per_sm == 0) *per_sm = blocks_per_sm(kernel, kThreads);
   const int64_t want = (rows + (kThreads / kWarp) - 1) / (kThreads / kWarp);
-  const int64_t cap = (int64_t)sm_count() * *per_sm;
+  const int64_t cap = (int64_t)resident_sms(flags) * *per_sm;
   return (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
 }
 
@@ -164,7 +164,7 @@ cudaError_t launch_grad_a2(const Problem &p, void *grad, const void *d_scale,
                            double scale_host, cudaStream_t s) {
   static int per_sm = 0;
   const cudaError_t e = launch_pdl(gradient_kernel<T, VEC, CH, PER_UTT>,
-      stream_grid(gradient_kernel<T, VEC, CH, PER_UTT>, &per_sm, p.rows), (unsigned)kThreads, 0, s,
+      stream_grid(gradient_kernel<T, VEC, CH, PER_UTT>, &per_sm, p.rows, p.flags), (unsigned)kThreads, 0, s,
       static_cast<const T *>(p.logits), static_cast<T *>(grad),
       reinterpret_cast<const CoefA<T> *>(p.ws + p.lay.coef),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V,
@@ -185,7 +185,7 @@ cudaError_t launch_grad_b(const Problem &p, void *grad, const void *d_scale,
                           double scale_host, cudaStream_t s) {
   static int per_sm = 0;
   auto kernel = gradient_logsoftmax_kernel<T, VEC, PER_UTT>;
-  kernel<<<stream_grid(kernel, &per_sm, p.rows), kThreads, 0, s>>>(
+  kernel<<<stream_grid(kernel, &per_sm, p.rows, p.flags), kThreads, 0, s>>>(
       static_cast<T *>(grad), reinterpret_cast<const CoefB<T> *>(p.ws + p.lay.coef),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V, p.blank,
       static_cast<const T *>(d_scale), (T)scale_host);

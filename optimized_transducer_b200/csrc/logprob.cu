@@ -188,7 +188,7 @@ cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
   if (per_sm == 0) per_sm = blocks_per_sm(kernel, kThreads);
   constexpr int rows_per_block = (kThreads / kWarp) * (kWarp / LPR);
   const int64_t want = (p.rows + rows_per_block - 1) / rows_per_block;
-  const int64_t cap = (int64_t)sm_count() * per_sm;
+  const int64_t cap = (int64_t)resident_sms(p.flags) * per_sm;
   const unsigned grid = (unsigned)(want < cap ? want : cap);
   const cudaError_t e = launch_pdl(kernel, grid, (unsigned)kThreads, 0, s,
       static_cast<const T *>(p.logits), p.targets, p.T, p.U,

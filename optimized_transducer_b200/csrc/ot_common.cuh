@@ -105,6 +105,14 @@ struct Problem {
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+// SMs the one-wave grids of the streaming kernels are sized for: all of them,
+// or one fewer with OT_B200_SHARE_SMS, so that a kernel that is resident beside
+// this path (a collective waiting for its peers) does not keep some of the
+// wave's blocks from starting with the others.
+inline int resident_sms(uint32_t flags) {
+  const int n = sm_count();
+  return ((flags & OT_B200_SHARE_SMS) && n > 1) ? n - 1 : n;
+}
 
 // Stores the message ot_b200_last_error() returns for the calling thread.
 void set_last_error(const char *msg);

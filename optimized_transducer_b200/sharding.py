@@ -188,7 +188,7 @@ class _ShardedLoss(torch.autograd.Function):
         assert reduction in ("mean", "sum")
         if logit_lengths.numel() > 0:
             call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
-                         from_log_softmax, one_sym_per_frame)
+                         from_log_softmax, one_sym_per_frame, share_sms=bool(overlap))
             local = torch.empty((), dtype=logits.dtype, device=logits.device)
             call.forward(loss_out=local, loss_scale=1.0)
         else:  # a rank without utterances still joins the collective

@@ -111,7 +111,7 @@ class _Call:
     """Pointers and sizes of one loss evaluation, plus its workspace."""
 
     def __init__(self, logits, targets, logit_lengths, target_lengths, blank,
-                 from_log_softmax, one_sym_per_frame, checks=None):
+                 from_log_softmax, one_sym_per_frame, checks=None, share_sms=False):
         _validate(logits, targets, logit_lengths, target_lengths, blank)
         if checks is None:
             checks = _checks_enabled()
@@ -125,6 +125,8 @@ class _Call:
         self.from_log_softmax = bool(from_log_softmax)
         self.modified = bool(one_sym_per_frame)
         self.flags = _flags(logits, from_log_softmax, one_sym_per_frame, checks)
+        if share_sms:  # a collective runs beside this call (sharding.py)
+            self.flags |= _lib.SHARE_SMS
         self.layout = _lib.workspace_layout(self.n, self.rows, self.max_u, self.flags)
         self.targets, self.t, self.u = targets, logit_lengths, target_lengths
         with torch.cuda.device(logits.device):
