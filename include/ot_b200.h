@@ -66,6 +66,10 @@ typedef enum ot_b200_input_error {
                                          mapped host memory) before it returns; not
                                          allowed during stream capture              */
 #define OT_B200_FAST_MATH 16u         /* approximate exp/log in the recursions      */
+#define OT_B200_BF16 128u              /* logits and gradient are bfloat16; scores,  */
+#define OT_B200_FP16 256u              /* loss, scale factors and the workspace stay
+                                         float (at most one of FP64/BF16/FP16); no
+                                         counterpart in the reference (float only)  */
 #define OT_B200_SHARE_SMS 64u          /* size the one-wave grids of the streaming
                                          kernels one SM short: for callers that keep
                                          another kernel resident beside this path (a

@@ -22,6 +22,8 @@ CHECK_INPUTS = 8
 FAST_MATH = 16
 SCALE_PER_UTTERANCE = 32
 SHARE_SMS = 64
+BF16 = 128
+FP16 = 256
 
 # Every symbol include/ot_b200.h declares.
 EXPORTS = (

@@ -81,13 +81,17 @@ int get_slot(StatusSlot **out) {
 
 constexpr uint32_t kKnownFlags = OT_B200_FROM_LOG_SOFTMAX | OT_B200_ONE_SYM_PER_FRAME |
                                  OT_B200_FP64 | OT_B200_CHECK_INPUTS | OT_B200_FAST_MATH |
-                                 OT_B200_SCALE_PER_UTTERANCE | OT_B200_SHARE_SMS;
+                                 OT_B200_SCALE_PER_UTTERANCE | OT_B200_SHARE_SMS |
+                                 OT_B200_BF16 | OT_B200_FP16;
 
 int check_sizes(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   if (N <= 0) return fail(OT_B200_ERR_ARGUMENT, "N must be positive, got %d", N);
   if (rows <= 0) return fail(OT_B200_ERR_ARGUMENT, "rows must be positive, got %lld", (long long)rows);
   if (max_u < 0) return fail(OT_B200_ERR_ARGUMENT, "max_u must not be negative, got %d", max_u);
   if (flags & ~kKnownFlags) return fail(OT_B200_ERR_ARGUMENT, "unknown bits in flags: 0x%x", flags);
+  const uint32_t types = flags & (OT_B200_FP64 | OT_B200_BF16 | OT_B200_FP16);
+  if (types & (types - 1))
+    return fail(OT_B200_ERR_ARGUMENT, "at most one of OT_B200_FP64, OT_B200_BF16, OT_B200_FP16 (flags 0x%x)", flags);
   return OT_B200_OK;
 }
 
@@ -203,7 +207,7 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
   if (!d_logits || !d_logit_lengths || !d_target_lengths || !d_scores)
     return fail(OT_B200_ERR_ARGUMENT, "a required device pointer is NULL");
   if (max_u > 0 && !d_targets) return fail(OT_B200_ERR_ARGUMENT, "targets pointer is NULL");
-  const uint64_t es = (flags & OT_B200_FP64) ? 8 : 4;
+  const uint64_t es = (flags & OT_B200_FP64) ? 8 : ((flags & (OT_B200_BF16 | OT_B200_FP16)) ? 2 : 4);
   if (reinterpret_cast<uintptr_t>(d_logits) % es != 0)
     return fail(OT_B200_ERR_ARGUMENT, "logits pointer is not aligned to its element size");
   p.logits = d_logits; p.targets = d_targets; p.T = d_logit_lengths; p.U = d_target_lengths;

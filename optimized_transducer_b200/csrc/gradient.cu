@@ -49,16 +49,19 @@ __device__ __forceinline__ CoefA<T> load_coef(const CoefA<T> *p) {
   return r;
 }
 
+// X: storage type of logits and gradient, T = Real<X>: type of the arithmetic.
 // PER_UTT: d_scale holds one factor per utterance instead of one scalar.
-template <typename T, int VEC, int CH, bool PER_UTT>
+template <typename X, int VEC, int CH, bool PER_UTT>
 __global__ void __launch_bounds__(kThreads)
-gradient_kernel(const T *x, T *g, const CoefA<T> *__restrict__ coef,
+gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restrict__ coef,
                 const int32_t *__restrict__ status, int64_t rows, int V,
-                int blank, const T *__restrict__ d_scale, T scale_host) {
+                int blank, const typename Real<X>::type *__restrict__ d_scale,
+                typename Real<X>::type scale_host) {
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
-  using VT = typename VecOf<T, VEC>::type;
+  using T = typename Real<X>::type;
+  using VT = typename VecOf<X, VEC>::type;
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
@@ -69,13 +72,13 @@ gradient_kernel(const T *x, T *g, const CoefA<T> *__restrict__ coef,
   for (int64_t row = rows - 1 - warp0; row >= 0; row -= nwarps) {
     const CoefA<T> rec = load_coef(coef + row);
     const T scale = PER_UTT ? scale_host * __ldg(d_scale + rec.utt) : scale_all;
-    const T *px = x + row * (int64_t)V;
-    T *pg = g + row * (int64_t)V;
+    const X *px = x + row * (int64_t)V;
+    X *pg = g + row * (int64_t)V;
     if (rec.tgt == kTgtZeroRow) {
       VT z;
-      T *ze = reinterpret_cast<T *>(&z);
+      X *ze = reinterpret_cast<X *>(&z);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) ze[k] = 0;
+      for (int k = 0; k < VEC; ++k) ze[k] = from_real<X>((T)0);
       for (int vi = lane; vi < nvec; vi += kWarp)
         *reinterpret_cast<VT *>(pg + (int64_t)vi * VEC) = z;
       continue;
@@ -93,16 +96,16 @@ gradient_kernel(const T *x, T *g, const CoefA<T> *__restrict__ coef,
       for (int j = 0; j < CH; ++j) {
         const int vi = base + j * kWarp + lane;
         if (vi < nvec) {
-          T *e = reinterpret_cast<T *>(&v[j]);
+          X *e = reinterpret_cast<X *>(&v[j]);
           const int bsel = (vi == bvec) ? bk : -1;
           const int tsel = (vi == tvec) ? tk : -1;
 #pragma unroll
           for (int k = 0; k < VEC; ++k) {
-            const T gv = e[k] + rec.c;
+            const T gv = to_real(e[k]) + rec.c;
             T val = s_exp(gv + rec.beta);
             if (k == bsel) val -= s_exp(gv + rec.sub_blank);
             else if (k == tsel) val -= s_exp(gv + rec.sub_sym);
-            e[k] = val * scale;
+            e[k] = from_real<X>(val * scale);
           }
           *reinterpret_cast<VT *>(pg + (int64_t)vi * VEC) = v[j];
         }
@@ -111,16 +114,17 @@ gradient_kernel(const T *x, T *g, const CoefA<T> *__restrict__ coef,
   }
 }
 
-template <typename T, int VEC, bool PER_UTT>
+template <typename X, int VEC, bool PER_UTT>
 __global__ void __launch_bounds__(kThreads)
-gradient_logsoftmax_kernel(T *__restrict__ g, const CoefB<T> *__restrict__ coef,
+gradient_logsoftmax_kernel(X *__restrict__ g, const CoefB<typename Real<X>::type> *__restrict__ coef,
                            const int32_t *__restrict__ status, int64_t rows,
-                           int V, int blank, const T *__restrict__ d_scale,
-                           T scale_host) {
+                           int V, int blank, const typename Real<X>::type *__restrict__ d_scale,
+                           typename Real<X>::type scale_host) {
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
-  using VT = typename VecOf<T, VEC>::type;
+  using T = typename Real<X>::type;
+  using VT = typename VecOf<X, VEC>::type;
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
@@ -130,19 +134,19 @@ gradient_logsoftmax_kernel(T *__restrict__ g, const CoefB<T> *__restrict__ coef,
   for (int64_t row = warp0; row < rows; row += nwarps) {
     const CoefB<T> rec = coef[row];
     const T scale = PER_UTT ? scale_host * __ldg(d_scale + rec.utt) : scale_all;
-    T *pg = g + row * (int64_t)V;
+    X *pg = g + row * (int64_t)V;
     const bool zero = rec.tgt == kTgtZeroRow;
     const int tvec = (!zero && rec.tgt >= 0) ? rec.tgt / VEC : -1;
     const int tk = rec.tgt >= 0 ? rec.tgt % VEC : 0;
     for (int vi = lane; vi < nvec; vi += kWarp) {
       VT z;
-      T *ze = reinterpret_cast<T *>(&z);
+      X *ze = reinterpret_cast<X *>(&z);
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
         T val = 0;
         if (!zero && vi == bvec && k == bk) val = rec.val_blank * scale;
         else if (vi == tvec && k == tk) val = rec.val_sym * scale;
-        ze[k] = val;
+        ze[k] = from_real<X>(val);
       }
       *reinterpret_cast<VT *>(pg + (int64_t)vi * VEC) = z;
     }
@@ -159,72 +163,76 @@ unsigned stream_grid(K kernel, int *per_sm, int64_t rows, uint32_t flags) {
   return (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
 }
 
-template <typename T, int VEC, int CH, bool PER_UTT>
+template <typename X, int VEC, int CH, bool PER_UTT>
 cudaError_t launch_grad_a2(const Problem &p, void *grad, const void *d_scale,
                            double scale_host, cudaStream_t s) {
+  using T = typename Real<X>::type;
   static int per_sm = 0;
-  const cudaError_t e = launch_pdl(gradient_kernel<T, VEC, CH, PER_UTT>,
-      stream_grid(gradient_kernel<T, VEC, CH, PER_UTT>, &per_sm, p.rows, p.flags), (unsigned)kThreads, 0, s,
-      static_cast<const T *>(p.logits), static_cast<T *>(grad),
+  const cudaError_t e = launch_pdl(gradient_kernel<X, VEC, CH, PER_UTT>,
+      stream_grid(gradient_kernel<X, VEC, CH, PER_UTT>, &per_sm, p.rows, p.flags), (unsigned)kThreads, 0, s,
+      static_cast<const X *>(p.logits), static_cast<X *>(grad),
       reinterpret_cast<const CoefA<T> *>(p.ws + p.lay.coef),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V,
       p.blank, static_cast<const T *>(d_scale), (T)scale_host);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-template <typename T, int VEC, int CH>
+template <typename X, int VEC, int CH>
 cudaError_t launch_grad_a(const Problem &p, void *grad, const void *d_scale,
                           double scale_host, cudaStream_t s) {
   return (p.flags & OT_B200_SCALE_PER_UTTERANCE)
-             ? launch_grad_a2<T, VEC, CH, true>(p, grad, d_scale, scale_host, s)
-             : launch_grad_a2<T, VEC, CH, false>(p, grad, d_scale, scale_host, s);
+             ? launch_grad_a2<X, VEC, CH, true>(p, grad, d_scale, scale_host, s)
+             : launch_grad_a2<X, VEC, CH, false>(p, grad, d_scale, scale_host, s);
 }
 
-template <typename T, int VEC, bool PER_UTT>
+template <typename X, int VEC, bool PER_UTT>
 cudaError_t launch_grad_b(const Problem &p, void *grad, const void *d_scale,
                           double scale_host, cudaStream_t s) {
+  using T = typename Real<X>::type;
   static int per_sm = 0;
-  auto kernel = gradient_logsoftmax_kernel<T, VEC, PER_UTT>;
+  auto kernel = gradient_logsoftmax_kernel<X, VEC, PER_UTT>;
   kernel<<<stream_grid(kernel, &per_sm, p.rows, p.flags), kThreads, 0, s>>>(
-      static_cast<T *>(grad), reinterpret_cast<const CoefB<T> *>(p.ws + p.lay.coef),
+      static_cast<X *>(grad), reinterpret_cast<const CoefB<T> *>(p.ws + p.lay.coef),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V, p.blank,
       static_cast<const T *>(d_scale), (T)scale_host);
   return cudaGetLastError();
 }
 
-template <typename T>
+template <typename X>
 cudaError_t launch_gradient_t(const Problem &p, void *grad, const void *d_scale,
                               double scale_host, cudaStream_t s) {
-  constexpr int VEC = Vec16<T>::n;
+  constexpr int VEC = Vec16<X>::n;
+  constexpr uintptr_t kAlign = VEC * sizeof(X);
   const bool aligned = (p.V % VEC == 0) &&
-                       (reinterpret_cast<uintptr_t>(grad) % 16 == 0);
+                       (reinterpret_cast<uintptr_t>(grad) % kAlign == 0);
   if (p.flags & OT_B200_FROM_LOG_SOFTMAX) {
     const bool per_utt = p.flags & OT_B200_SCALE_PER_UTTERANCE;
     if (aligned)
-      return per_utt ? launch_grad_b<T, VEC, true>(p, grad, d_scale, scale_host, s)
-                     : launch_grad_b<T, VEC, false>(p, grad, d_scale, scale_host, s);
-    return per_utt ? launch_grad_b<T, 1, true>(p, grad, d_scale, scale_host, s)
-                   : launch_grad_b<T, 1, false>(p, grad, d_scale, scale_host, s);
+      return per_utt ? launch_grad_b<X, VEC, true>(p, grad, d_scale, scale_host, s)
+                     : launch_grad_b<X, VEC, false>(p, grad, d_scale, scale_host, s);
+    return per_utt ? launch_grad_b<X, 1, true>(p, grad, d_scale, scale_host, s)
+                   : launch_grad_b<X, 1, false>(p, grad, d_scale, scale_host, s);
   }
-  const bool vec_ok = aligned && (reinterpret_cast<uintptr_t>(p.logits) % 16 == 0);
+  const bool vec_ok = aligned && (reinterpret_cast<uintptr_t>(p.logits) % kAlign == 0);
   if (vec_ok) {
     const int per_lane = (p.V / VEC + kWarp - 1) / kWarp;
-    if (per_lane <= 1) return launch_grad_a<T, VEC, 1>(p, grad, d_scale, scale_host, s);
-    if (per_lane <= 2) return launch_grad_a<T, VEC, 2>(p, grad, d_scale, scale_host, s);
-    return launch_grad_a<T, VEC, 4>(p, grad, d_scale, scale_host, s);
+    if (per_lane <= 1) return launch_grad_a<X, VEC, 1>(p, grad, d_scale, scale_host, s);
+    if (per_lane <= 2) return launch_grad_a<X, VEC, 2>(p, grad, d_scale, scale_host, s);
+    return launch_grad_a<X, VEC, 4>(p, grad, d_scale, scale_host, s);
   }
   const int per_lane = (p.V + kWarp - 1) / kWarp;
-  if (per_lane <= 4) return launch_grad_a<T, 1, 4>(p, grad, d_scale, scale_host, s);
-  return launch_grad_a<T, 1, 8>(p, grad, d_scale, scale_host, s);
+  if (per_lane <= 4) return launch_grad_a<X, 1, 4>(p, grad, d_scale, scale_host, s);
+  return launch_grad_a<X, 1, 8>(p, grad, d_scale, scale_host, s);
 }
 
 }  // namespace
 
 cudaError_t launch_gradient(const Problem &p, void *grad, const void *d_scale,
                             double scale_host, cudaStream_t s) {
-  return (p.flags & OT_B200_FP64)
-             ? launch_gradient_t<double>(p, grad, d_scale, scale_host, s)
-             : launch_gradient_t<float>(p, grad, d_scale, scale_host, s);
+  if (p.flags & OT_B200_FP64) return launch_gradient_t<double>(p, grad, d_scale, scale_host, s);
+  if (p.flags & OT_B200_BF16) return launch_gradient_t<__nv_bfloat16>(p, grad, d_scale, scale_host, s);
+  if (p.flags & OT_B200_FP16) return launch_gradient_t<__half>(p, grad, d_scale, scale_host, s);
+  return launch_gradient_t<float>(p, grad, d_scale, scale_host, s);
 }
 
 }  // namespace otb

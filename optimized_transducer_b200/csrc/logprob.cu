@@ -59,20 +59,23 @@ __device__ __forceinline__ T group_sum(T v, unsigned mask) {
   return v;
 }
 
-// T: element type.  VEC: elements per load (16 bytes, or 1 element when the
-// row stride or the base pointer is not 16-byte aligned).  LPR: lanes per row.
+// X: storage type of the logits, T = Real<X>: type of the arithmetic and of the
+// outputs.  VEC: elements per load (one vector of Vec16<X>, or 1 element when
+// the row stride or the base pointer is not aligned to it).  LPR: lanes per row.
 // CH: loads per lane per chunk, i.e. a chunk covers LPR*VEC*CH elements.
-template <typename T, int VEC, int CH, int LPR, bool MODIFIED>
+template <typename X, int VEC, int CH, int LPR, bool MODIFIED>
 __global__ void __launch_bounds__(kThreads)
-logprob_kernel(const T *__restrict__ logits, const int32_t *__restrict__ targets,
+logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets,
                const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
                const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
                const int32_t *__restrict__ status, int N, int64_t rows, int V,
-               int max_u, int blank, T *__restrict__ den, T *__restrict__ lp) {
+               int max_u, int blank, typename Real<X>::type *__restrict__ den,
+               typename Real<X>::type *__restrict__ lp) {
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
-  using VT = typename VecOf<T, VEC>::type;
+  using T = typename Real<X>::type;
+  using VT = typename VecOf<X, VEC>::type;
   constexpr int kGroups = kWarp / LPR;  // rows a warp works on at once
   const int lane = threadIdx.x & 31;
   const int gl = lane % LPR;            // lane within the group
@@ -97,7 +100,7 @@ logprob_kernel(const T *__restrict__ logits, const int32_t *__restrict__ targets
       t = idx / U1; u = idx - t * U1;
     }
     for (int64_t row = r0; row < r1; ++row) {
-      const T *p = logits + row * (int64_t)V;
+      const X *p = logits + row * (int64_t)V;
       bool skip = false;
       if (MODIFIED) {
         // Cells outside the band u <= t <= u + (T-1-U) are never used
@@ -113,9 +116,9 @@ logprob_kernel(const T *__restrict__ logits, const int32_t *__restrict__ targets
             const int vi = base + j * LPR + gl;
             if (vi < nvec) {
               const VT v = *reinterpret_cast<const VT *>(p + (int64_t)vi * VEC);
-              const T *e = reinterpret_cast<const T *>(&v);
+              const X *e = reinterpret_cast<const X *>(&v);
 #pragma unroll
-              for (int k = 0; k < VEC; ++k) x[j * VEC + k] = e[k];
+              for (int k = 0; k < VEC; ++k) x[j * VEC + k] = to_real(e[k]);
             } else {
 #pragma unroll
               for (int k = 0; k < VEC; ++k) x[j * VEC + k] = ninf;
@@ -135,8 +138,8 @@ logprob_kernel(const T *__restrict__ logits, const int32_t *__restrict__ targets
         // Gather: the group's lane 0 fetches the blank entry, lane 1 the symbol entry.
         // the last column has no next symbol: -inf, "no such transition"
         T g = ninf;
-        if (gl == 0) g = p[blank] - d;
-        if (gl == 1 && u < U) g = p[__ldg(targets + (int64_t)b * max_u + u)] - d;
+        if (gl == 0) g = to_real(p[blank]) - d;
+        if (gl == 1 && u < U) g = to_real(p[__ldg(targets + (int64_t)b * max_u + u)]) - d;
         const T g1 = __shfl_sync(gmask, g, (lane - gl) + 1);
         if (gl == 0) {
           den[row] = d;
@@ -159,31 +162,33 @@ logprob_kernel(const T *__restrict__ logits, const int32_t *__restrict__ targets
 }
 
 // Log-softmax input: nothing to reduce, only the gather (thread per row).
-template <typename T, bool MODIFIED>
+template <typename X, bool MODIFIED>
 __global__ void __launch_bounds__(kThreads)
-gather_kernel(const T *__restrict__ logp, const int32_t *__restrict__ targets,
+gather_kernel(const X *__restrict__ logp, const int32_t *__restrict__ targets,
               const int32_t *__restrict__ Ul, const int64_t *__restrict__ split,
               const int64_t *__restrict__ cell_split,
               const int32_t *__restrict__ status, int N, int64_t rows, int V,
-              int max_u, int blank, T *__restrict__ lp) {
+              int max_u, int blank, typename Real<X>::type *__restrict__ lp) {
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
+  using T = typename Real<X>::type;
   const int64_t row = (int64_t)blockIdx.x * kThreads + threadIdx.x;
   if (row >= rows) return;
   const int b = find_utt(split, N, row);
   const int U = __ldg(Ul + b), U1 = U + 1;
   const int idx = (int)(row - __ldg(split + b));
   const int t = idx / U1, u = idx - t * U1;
-  const T *p = logp + row * (int64_t)V;
+  const X *p = logp + row * (int64_t)V;
   T *q = lp + 2 * (__ldg(cell_split + b) + cell_pos<MODIFIED>(t, u, U1));
-  q[0] = p[blank];
-  q[1] = (u < U) ? p[__ldg(targets + (int64_t)b * max_u + u)] : neg_inf<T>();
+  q[0] = to_real(p[blank]);
+  q[1] = (u < U) ? to_real(p[__ldg(targets + (int64_t)b * max_u + u)]) : neg_inf<T>();
 }
 
-template <typename T, int VEC, int CH, int LPR, bool MODIFIED>
+template <typename X, int VEC, int CH, int LPR, bool MODIFIED>
 cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
-  auto kernel = logprob_kernel<T, VEC, CH, LPR, MODIFIED>;
+  using T = typename Real<X>::type;
+  auto kernel = logprob_kernel<X, VEC, CH, LPR, MODIFIED>;
   static int per_sm = 0;  // occupancy of this instantiation (same on every B200)
   if (per_sm == 0) per_sm = blocks_per_sm(kernel, kThreads);
   constexpr int rows_per_block = (kThreads / kWarp) * (kWarp / LPR);
@@ -191,7 +196,7 @@ cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
   const int64_t cap = (int64_t)resident_sms(p.flags) * per_sm;
   const unsigned grid = (unsigned)(want < cap ? want : cap);
   const cudaError_t e = launch_pdl(kernel, grid, (unsigned)kThreads, 0, s,
-      static_cast<const T *>(p.logits), p.targets, p.T, p.U,
+      static_cast<const X *>(p.logits), p.targets, p.T, p.U,
       reinterpret_cast<const int64_t *>(p.ws + p.lay.split),
       reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.N, p.rows, p.V,
@@ -200,51 +205,54 @@ cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-template <typename T, int VEC, int CH, int LPR>
+template <typename X, int VEC, int CH, int LPR>
 cudaError_t launch_lse(const Problem &p, cudaStream_t s) {
-  return (p.flags & OT_B200_ONE_SYM_PER_FRAME) ? launch_lse_m<T, VEC, CH, LPR, true>(p, s)
-                                               : launch_lse_m<T, VEC, CH, LPR, false>(p, s);
+  return (p.flags & OT_B200_ONE_SYM_PER_FRAME) ? launch_lse_m<X, VEC, CH, LPR, true>(p, s)
+                                               : launch_lse_m<X, VEC, CH, LPR, false>(p, s);
 }
 
-template <typename T>
+template <typename X>
 cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
+  using T = typename Real<X>::type;
   if (p.flags & OT_B200_FROM_LOG_SOFTMAX) {
     const unsigned grid = (unsigned)((p.rows + kThreads - 1) / kThreads);
-    const T *x = static_cast<const T *>(p.logits);
+    const X *x = static_cast<const X *>(p.logits);
     const int64_t *split = reinterpret_cast<const int64_t *>(p.ws + p.lay.split);
     const int64_t *csplit = reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split);
     const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
     T *lp = reinterpret_cast<T *>(p.ws + p.lay.lp);
     if (p.flags & OT_B200_ONE_SYM_PER_FRAME)
-      gather_kernel<T, true><<<grid, kThreads, 0, s>>>(x, p.targets, p.U, split, csplit, status,
+      gather_kernel<X, true><<<grid, kThreads, 0, s>>>(x, p.targets, p.U, split, csplit, status,
                                                        p.N, p.rows, p.V, p.max_u, p.blank, lp);
     else
-      gather_kernel<T, false><<<grid, kThreads, 0, s>>>(x, p.targets, p.U, split, csplit, status,
+      gather_kernel<X, false><<<grid, kThreads, 0, s>>>(x, p.targets, p.U, split, csplit, status,
                                                         p.N, p.rows, p.V, p.max_u, p.blank, lp);
     return cudaGetLastError();
   }
-  constexpr int VEC = Vec16<T>::n;
+  constexpr int VEC = Vec16<X>::n;
   const bool vec_ok = (p.V % VEC == 0) &&
-                      (reinterpret_cast<uintptr_t>(p.logits) % 16 == 0);
+                      (reinterpret_cast<uintptr_t>(p.logits) % (VEC * sizeof(X)) == 0);
   if (vec_ok) {
-    const int nvec = p.V / VEC;  // 16-byte loads per row
+    const int nvec = p.V / VEC;  // vector loads per row
     // Up to 8 loads per lane: pick the narrowest group that covers the row in
     // one chunk; rows longer than 32*8 loads loop over chunks.
-    if (nvec <= 8 * 4) return launch_lse<T, VEC, 4, 8>(p, s);
-    if (nvec <= 8 * 8) return launch_lse<T, VEC, 8, 8>(p, s);
-    if (nvec <= 16 * 8) return launch_lse<T, VEC, 8, 16>(p, s);
-    return launch_lse<T, VEC, 8, 32>(p, s);
+    if (nvec <= 8 * 4) return launch_lse<X, VEC, 4, 8>(p, s);
+    if (nvec <= 8 * 8) return launch_lse<X, VEC, 8, 8>(p, s);
+    if (nvec <= 16 * 8) return launch_lse<X, VEC, 8, 16>(p, s);
+    return launch_lse<X, VEC, 8, 32>(p, s);
   }
   const int per_lane = (p.V + kWarp - 1) / kWarp;
-  if (per_lane <= 4) return launch_lse<T, 1, 4, 32>(p, s);
-  return launch_lse<T, 1, 16, 32>(p, s);
+  if (per_lane <= 4) return launch_lse<X, 1, 4, 32>(p, s);
+  return launch_lse<X, 1, 16, 32>(p, s);
 }
 
 }  // namespace
 
 cudaError_t launch_logprob(const Problem &p, cudaStream_t s) {
-  return (p.flags & OT_B200_FP64) ? launch_logprob_t<double>(p, s)
-                                  : launch_logprob_t<float>(p, s);
+  if (p.flags & OT_B200_FP64) return launch_logprob_t<double>(p, s);
+  if (p.flags & OT_B200_BF16) return launch_logprob_t<__nv_bfloat16>(p, s);
+  if (p.flags & OT_B200_FP16) return launch_logprob_t<__half>(p, s);
+  return launch_logprob_t<float>(p, s);
 }
 
 }  // namespace otb

@@ -11,6 +11,8 @@
 //   den      per row logsumexp of the logits
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -165,16 +167,44 @@ cudaError_t launch_gradient(const Problem &p, void *grad, const void *d_scale,
 // Device helpers
 // ---------------------------------------------------------------------------
 
-// 16-byte vector of the element type.
-template <typename T> struct Vec16;
+// Storage type X of the logits / gradient -> type the arithmetic runs in.
+// 16-bit logits (OT_B200_BF16 / OT_B200_FP16) are converted on load and rounded
+// to nearest on store; everything between (logsumexp, log-probs, alpha, beta,
+// scores, loss) is float32.
+template <typename X> struct Real { using type = X; };
+template <> struct Real<__nv_bfloat16> { using type = float; };
+template <> struct Real<__half> { using type = float; };
+
+// Widest vector a streaming kernel loads: 16 bytes for float and double; 8 bytes
+// (4 elements) for the 16-bit types, whose rows are only 8-byte aligned at the
+// usual vocabulary sizes (V = 500: 1000-byte rows).
+template <typename X> struct Vec16;
 template <> struct Vec16<float> { using type = float4; static constexpr int n = 4; };
 template <> struct Vec16<double> { using type = double2; static constexpr int n = 2; };
+template <> struct Vec16<__nv_bfloat16> { using type = uint2; static constexpr int n = 4; };
+template <> struct Vec16<__half> { using type = uint2; static constexpr int n = 4; };
 
-template <typename T, int VEC> struct VecOf;
+template <typename X, int VEC> struct VecOf;
 template <> struct VecOf<float, 4> { using type = float4; };
 template <> struct VecOf<float, 1> { using type = float; };
 template <> struct VecOf<double, 2> { using type = double2; };
 template <> struct VecOf<double, 1> { using type = double; };
+template <> struct VecOf<__nv_bfloat16, 4> { using type = uint2; };
+template <> struct VecOf<__nv_bfloat16, 1> { using type = __nv_bfloat16; };
+template <> struct VecOf<__half, 4> { using type = uint2; };
+template <> struct VecOf<__half, 1> { using type = __half; };
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float to_real(float v) { return v; }
+__device__ __forceinline__ double to_real(double v) { return v; }
+__device__ __forceinline__ float to_real(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_real(__half v) { return __half2float(v); }
+template <typename X> __device__ __forceinline__ X from_real(typename Real<X>::type v);
+template <> __device__ __forceinline__ float from_real<float>(float v) { return v; }
+template <> __device__ __forceinline__ double from_real<double>(double v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_real<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_real<__half>(float v) { return __float2half_rn(v); }
+#endif
 
 template <typename T> __device__ __forceinline__ T neg_inf();
 template <> __device__ __forceinline__ float neg_inf<float>() { return -__int_as_float(0x7f800000); }

@@ -22,7 +22,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-from .transducer_loss import _Call
+from .transducer_loss import _Call, real_dtype
 
 __all__ = ["utterance_costs", "partition_contiguous", "partition_lpt", "imbalance",
            "Shard", "shard_batch", "all_reduce_sum", "sharded_transducer_loss", "wait_loss"]
@@ -189,11 +189,11 @@ class _ShardedLoss(torch.autograd.Function):
         if logit_lengths.numel() > 0:
             call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
                          from_log_softmax, one_sym_per_frame, share_sms=bool(overlap))
-            local = torch.empty((), dtype=logits.dtype, device=logits.device)
+            local = torch.empty((), dtype=real_dtype(logits), device=logits.device)
             call.forward(loss_out=local, loss_scale=1.0)
         else:  # a rank without utterances still joins the collective
             call = None
-            local = torch.zeros((), dtype=logits.dtype, device=logits.device)
+            local = torch.zeros((), dtype=real_dtype(logits), device=logits.device)
         total, event = all_reduce_sum(local, group, overlap)
         scale = 1.0
         if reduction == "mean":
@@ -219,7 +219,7 @@ class _ShardedLoss(torch.autograd.Function):
         if call is not None:
             data = call.logits
             grad = torch.empty_like(data) if call.from_log_softmax else data
-            g = loss_grad.detach().to(device=data.device, dtype=data.dtype).contiguous()
+            g = loss_grad.detach().to(device=data.device, dtype=call.real).contiguous()
             call.backward(grad, scale_tensor=g, scale_host=ctx.scale_host)
         elif ctx.empty_like is not None:
             grad = torch.zeros_like(ctx.empty_like)

@@ -58,9 +58,9 @@ def _validate(logits, targets, logit_lengths, target_lengths, blank):
     (optimized_transducer/csrc/transducer-loss.cc:33-46, 58-60, 77-79); the
     data-dependent ones (:49-56, :62-66) run on the device."""
     who = "ComputeTransducerLoss"
-    if logits.dtype not in (torch.float32, torch.float64):
+    if logits.dtype not in (torch.float32, torch.float64, torch.bfloat16, torch.float16):
         raise RuntimeError(f"{who}: expected logits to have scalar type Float "
-                           f"(Double is accepted as an extension), got {logits.dtype}")
+                           f"(Double, BFloat16 and Half are accepted as extensions), got {logits.dtype}")
     for name, t in (("targets", targets), ("logit_lengths", logit_lengths),
                     ("target_lengths", target_lengths)):
         if t.dtype != torch.int32:
@@ -92,6 +92,12 @@ def _validate(logits, targets, logit_lengths, target_lengths, blank):
         raise RuntimeError(f"{who}: empty batch")
 
 
+def real_dtype(logits):
+    """dtype of everything but the logits and their gradient: scores, loss,
+    upstream factors, workspace arrays.  16-bit logits are computed in float32."""
+    return logits.dtype if logits.dtype == torch.float64 else torch.float32
+
+
 def _flags(logits, from_log_softmax, one_sym_per_frame, checks):
     f = 0
     if from_log_softmax:
@@ -100,6 +106,10 @@ def _flags(logits, from_log_softmax, one_sym_per_frame, checks):
         f |= _lib.ONE_SYM_PER_FRAME
     if logits.dtype == torch.float64:
         f |= _lib.FP64
+    elif logits.dtype == torch.bfloat16:
+        f |= _lib.BF16
+    elif logits.dtype == torch.float16:
+        f |= _lib.FP16
     if checks:
         f |= _lib.CHECK_INPUTS
     if _fast_math():
@@ -129,10 +139,11 @@ class _Call:
             self.flags |= _lib.SHARE_SMS
         self.layout = _lib.workspace_layout(self.n, self.rows, self.max_u, self.flags)
         self.targets, self.t, self.u = targets, logit_lengths, target_lengths
+        self.real = real_dtype(logits)
         with torch.cuda.device(logits.device):
             self.workspace = torch.empty(int(self.layout.total_bytes), dtype=torch.uint8,
                                          device=logits.device)
-            self.scores = torch.empty(self.n, dtype=logits.dtype, device=logits.device)
+            self.scores = torch.empty(self.n, dtype=self.real, device=logits.device)
 
     def _stream(self):
         return ctypes.c_void_p(torch.cuda.current_stream(self.logits.device).cuda_stream)
@@ -171,7 +182,7 @@ class _Call:
         """A tensor view of one intermediate array inside the workspace, in the
         library's own order (per-cell arrays are NOT in packed-row order, see
         :meth:`cell_index`)."""
-        dt = self.logits.dtype
+        dt = self.real
         es = 8 if dt == torch.float64 else 4
         cells = int(self.layout.max_cells)
         if name in ("split", "cell_split"):
@@ -266,7 +277,7 @@ class TransducerLossFunction(torch.autograd.Function):
         call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
                      from_log_softmax, one_sym_per_frame)
         scale = (1.0 / n) if reduction == "mean" else 1.0
-        loss = torch.empty((), dtype=logits.dtype, device=logits.device)
+        loss = torch.empty((), dtype=call.real, device=logits.device)
         call.forward(loss_out=loss, loss_scale=scale)  # the reduction runs on the device too
         ctx.grad = None
         ctx.call = call if ctx.needs_input_grad[0] else None
@@ -285,7 +296,7 @@ class TransducerLossFunction(torch.autograd.Function):
         call, ctx.call = ctx.call, None  # the workspace is released after this pass
         data = call.logits
         grad = torch.empty_like(data) if call.from_log_softmax else data
-        scale = loss_grad.detach().to(device=data.device, dtype=data.dtype).contiguous()
+        scale = loss_grad.detach().to(device=data.device, dtype=call.real).contiguous()
         call.backward(grad, scale_tensor=scale, scale_host=ctx.scale_host)
         return (grad,) + (None,) * 7
 
@@ -314,7 +325,7 @@ class PerUtteranceLossFunction(torch.autograd.Function):
         assert loss_grad.numel() == call.n, (loss_grad.numel(), call.n)
         data = call.logits
         grad = torch.empty_like(data) if call.from_log_softmax else data
-        scale = loss_grad.detach().to(device=data.device, dtype=data.dtype).contiguous()
+        scale = loss_grad.detach().to(device=data.device, dtype=call.real).contiguous()
         call.backward(grad, scale_tensor=scale, per_utterance=True)
         return (grad,) + (None,) * 6
 
@@ -356,7 +367,9 @@ def transducer_loss(logits: torch.Tensor, targets: torch.Tensor,
     """Transducer (RNN-T) loss over packed logits.
 
     Args:
-      logits: (sum_b T_b*(U_b+1), V) float32 (float64 accepted), contiguous,
+      logits: (sum_b T_b*(U_b+1), V) float32 (float64, bfloat16 and float16 are
+        accepted too; 16-bit logits are computed in float32, the loss is float32
+        and the gradient is rounded back to the logits' type), contiguous,
         on a CUDA device: utterance b's (T_b, U_b+1, V) joiner output flattened
         to rows and the utterances concatenated (reference README.md:131-204).
         If it requires grad and ``from_log_softmax`` is False, ``backward``

@@ -38,7 +38,7 @@ def test_no_cpu_fallback():
 
 
 @pytest.mark.parametrize("mutate,match", [
-    (lambda a: (a[0].half(), a[1], a[2], a[3]), "scalar type Float"),
+    (lambda a: (a[0].to(torch.int32), a[1], a[2], a[3]), "scalar type Float"),
     (lambda a: (a[0], a[1].long(), a[2], a[3]), "targets to have scalar type Int"),
     (lambda a: (a[0], a[1], a[2].long(), a[3]), "logit_lengths to have scalar type Int"),
     (lambda a: (a[0].t().contiguous().t(), a[1], a[2], a[3]), "logits to be contiguous"),

@@ -207,6 +207,38 @@ def test_per_utterance_loss_and_weighted_gradient(from_ls, modified, dtype):
                                    rtol=0, atol=3e-5 if dtype == np.float32 else 1e-10)
 
 
+@pytest.mark.parametrize("modified", [False, True])
+@pytest.mark.parametrize("from_ls", [False, True])
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("vocab", [500, 37])  # 8-byte vector path / scalar path
+def test_sixteen_bit_logits_float32_math(vocab, dtype, from_ls, modified):
+    """16-bit logits in, float32 arithmetic, gradient rounded back to 16 bits
+    (no counterpart in the reference, which is float32 only).  The oracle sees
+    exactly the values the kernels see: the 16-bit numbers widened to float64."""
+    tdt = getattr(torch, dtype)
+    x, tg, T, U = random_batch(45, 4, (9, 17), (3, 7), vocab, modified=modified)
+    tx = torch.from_numpy(x)
+    if from_ls:
+        tx = tx.log_softmax(-1)
+    x16 = tx.to(tdt)                      # what the kernels read
+    xin = x16.to(torch.float64).numpy()   # the same numbers for the oracle
+    _, dt, dT, dU = to_dev(x, tg, T, U)
+    leaf = x16.to(DEV).requires_grad_(True)
+    loss = ot.transducer_loss(leaf * 1, dt, dT, dU, 0, from_ls, modified, "sum")
+    assert loss.dtype == torch.float32
+    loss.backward()
+    assert leaf.grad.dtype == tdt
+    ref = O.oracle_loss(xin, tg, T, U, 0, from_ls, modified)
+    want = -ref["scores"].sum()
+    assert abs(loss.item() - want) <= 1e-5 * abs(want)
+    got = leaf.grad.to(torch.float64).cpu().numpy()
+    # rounding to nearest: half an ulp = 2^-9 (bfloat16) / 2^-12 (float16) relative,
+    # plus the float32 error of the value that is rounded, plus float16's subnormal step
+    rel = 2.0 ** -8 if dtype == "bfloat16" else 2.0 ** -11
+    err = np.abs(got - ref["grad"])
+    assert np.all(err <= rel * np.abs(ref["grad"]) + 2e-5), float(err.max())
+
+
 def test_module_form_and_no_grad():
     x, tg, T, U = random_batch(42, 3, (5, 9), (2, 4), 6)
     dx, dt, dT, dU = to_dev(x, tg, T, U)
