@@ -250,7 +250,9 @@ def run_ours(args, w):
     cells_local = rows * w.v
     dT, dU, dtg = T.to(dev), U.to(dev), tg.to(dev)
     pristine = synthetic.make_logits(w, T, U, device=dev, seed=w.seed + 31 * rank)
-    bytes_logits = pristine.numel() * 4
+    if args.dtype != "f32":  # the 16-bit extension: same values, rounded once
+        pristine = pristine.to(torch.bfloat16 if args.dtype == "bf16" else torch.float16)
+    bytes_logits = pristine.numel() * pristine.element_size()
 
     total_steps = args.steps + args.warmup
     free, _ = torch.cuda.mem_get_info(dev)
@@ -374,7 +376,7 @@ def run_ours(args, w):
 
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
-        es = 4
+        es = pristine.element_size()
         mode_b = w.from_log_softmax
         # Gradient kernel, per launch: read + in-place write of the local logits
         # (mode A), or the dense gradient write (mode B).
@@ -385,9 +387,12 @@ def run_ours(args, w):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": args.scaling, "vs_baseline": None,
+            "dtype": "f32" if args.dtype == "f32" else f"{args.dtype} logits and gradient, f32 arithmetic",
+            "data": "synthetic",
             "config": {
-                "workload": workload_description(w, n_global, rows if world == 1 else "sharded"),
+                "workload": workload_description(w, n_global, rows if world == 1 else "sharded")
+                            + ("" if args.dtype == "f32" else f", logits stored as {args.dtype}"),
                 "sharding": "none" if world == 1 else
                             f"{world} ranks, whole utterances, balanced by T*(U+1)*V ({args.partition} partition)",
                 "cache": "inputs larger than L2: every step reads its own pristine logits buffer",
@@ -404,7 +409,8 @@ def run_ours(args, w):
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
                 "traffic": (CFG2_GRADIENT_TRAFFIC_BYTES
-                            if (w.name == "cfg2" and world == 1 and rows == CFG2_ROWS) else None),
+                            if (w.name == "cfg2" and world == 1 and rows == CFG2_ROWS
+                                and args.dtype == "f32") else None),
                 "bytes_per_launch": grad_bytes, "ms_per_launch": bwd_ms,
             },
             "stages": {
@@ -489,6 +495,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--dtype", choices=["f32", "bf16", "f16"], default="f32",
+                    help="storage type of the logits (the reference's is f32; 16-bit is an extension)")
     ap.add_argument("--partition", choices=["auto", "contiguous", "lpt"], default="lpt",
                     help="how utterances are dealt to the ranks (each rank creates its own shard, "
                          "so the permuting, better balanced \"lpt\" costs nothing here)")
