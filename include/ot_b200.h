@@ -70,6 +70,10 @@ typedef enum ot_b200_input_error {
 #define OT_B200_FP16 256u              /* loss, scale factors and the workspace stay
                                          float (at most one of FP64/BF16/FP16); no
                                          counterpart in the reference (float only)  */
+#define OT_B200_TRACE 512u             /* diagnostic: every stage stores when its first
+                                         block started and its last block ended
+                                         (%globaltimer, ns) as uint64 pairs from byte 64
+                                         of the status segment on                   */
 #define OT_B200_SHARE_SMS 64u          /* size the one-wave grids of the streaming
                                          kernels one SM short: for callers that keep
                                          another kernel resident beside this path (a

@@ -24,6 +24,7 @@ SCALE_PER_UTTERANCE = 32
 SHARE_SMS = 64
 BF16 = 128
 FP16 = 256
+TRACE = 512
 
 # Every symbol include/ot_b200.h declares.
 EXPORTS = (

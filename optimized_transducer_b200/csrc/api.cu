@@ -82,7 +82,7 @@ int get_slot(StatusSlot **out) {
 constexpr uint32_t kKnownFlags = OT_B200_FROM_LOG_SOFTMAX | OT_B200_ONE_SYM_PER_FRAME |
                                  OT_B200_FP64 | OT_B200_CHECK_INPUTS | OT_B200_FAST_MATH |
                                  OT_B200_SCALE_PER_UTTERANCE | OT_B200_SHARE_SMS |
-                                 OT_B200_BF16 | OT_B200_FP16;
+                                 OT_B200_BF16 | OT_B200_FP16 | OT_B200_TRACE;
 
 int check_sizes(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   if (N <= 0) return fail(OT_B200_ERR_ARGUMENT, "N must be positive, got %d", N);
@@ -144,7 +144,7 @@ Layout make_layout(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
                 (modified ? 0 : (int64_t)N * (int64_t)max_u * ((int64_t)max_u + 1));
   const uint64_t cells = (uint64_t)l.max_cells;
   uint64_t off = 0;
-  l.status = off;       off = align256(off + kStatusWords * sizeof(int32_t));
+  l.status = off;       off = align256(off + kStatusBlockWords * sizeof(int32_t));
   l.split = off;        off = align256(off + (uint64_t)(N + 1) * sizeof(int64_t));
   l.cell_split = off;   off = align256(off + (uint64_t)(N + 1) * sizeof(int64_t));
   l.den = off;          off = align256(off + (mode_b ? 0 : (uint64_t)rows * es));

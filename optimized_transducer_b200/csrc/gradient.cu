@@ -60,6 +60,7 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
+  if (threadIdx.x == 0) trace_begin(status, kStageGradient);
   using T = typename Real<X>::type;
   using VT = typename VecOf<X, VEC>::type;
   const int lane = threadIdx.x & 31;
@@ -112,6 +113,7 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
       }
     }
   }
+  if (threadIdx.x == 0) trace_end(status, kStageGradient);
 }
 
 template <typename X, int VEC, bool PER_UTT>

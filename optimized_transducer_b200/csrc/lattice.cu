@@ -9,8 +9,12 @@
 // One CTA per (utterance, direction): 2N CTAs, alpha and beta of an utterance
 // run concurrently.  Thread u owns lattice column u and keeps the wavefront in
 // registers: its own previous value is the t-neighbour, the u-neighbour comes
-// from the adjacent lane by a warp shuffle and across warps through two
-// shared-memory words per warp and one named barrier per step.
+// from the adjacent lane by a warp shuffle.  Across warps there are two
+// kernels: lattice_skew_kernel (the default) delays each warp by one block of
+// 16 steps against its neighbour, so the boundary values travel through a
+// shared-memory ring and the CTA meets at one barrier per block;
+// lattice_kernel keeps all warps in lockstep with one barrier per step (used
+// when the skewed kernel's stages do not fit into shared memory).
 //
 //   standard transducer : anti-diagonal wavefront, T+U-1 steps
 //   one symbol per frame: both predecessors lie in the previous frame, so the
@@ -316,6 +320,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   const int Tn = Tl[b], U = Ul[b], U1 = U + 1;
   const int64_t off = cell_split[b];
   if (bad != 0) return;
+  if (threadIdx.x == 0) trace_begin(status, kStageLattice);
   const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
   const int nwarps = (U1 + kWarp - 1) / kWarp;
   if (warp >= nwarps) return;
@@ -436,6 +441,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       if (nwarps > 1) bar_active(nact); else __syncwarp();
     }
     if (u == U) scores[b] = own + fin_blank;  // column U's last step is the last step
+    if (u == 0) trace_end(status, kStageLattice);
   } else {
     // ------------------------------- beta ------------------------------
     const bool produce = (lane == 0) && (warp > 0);
@@ -508,6 +514,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       if (nwarps > 1) bar_active(nact); else __syncwarp();
     }
     if (u == 0) scores_beta[b] = own;  // column 0's last step is the last step
+    if (u == 0) trace_end(status, kStageLattice);
   }
 }
 

@@ -74,6 +74,7 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
+  if (threadIdx.x == 0) trace_begin(status, kStageLogprob);
   using T = typename Real<X>::type;
   using VT = typename VecOf<X, VEC>::type;
   constexpr int kGroups = kWarp / LPR;  // rows a warp works on at once
@@ -159,6 +160,7 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
       }
     }
   }
+  if (threadIdx.x == 0) trace_end(status, kStageLogprob);
 }
 
 // Log-softmax input: nothing to reduce, only the gather (thread per row).

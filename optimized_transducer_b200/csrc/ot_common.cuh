@@ -27,6 +27,14 @@ constexpr unsigned kFull = 0xffffffffu;
 constexpr int kStatusCode = 0;   // ot_b200_input_error, 0 = inputs are valid
 constexpr int kStatusIndex = 1;  // utterance the code refers to
 constexpr int kStatusWords = 16;
+// Diagnostic timeline (OT_B200_TRACE): word kStatusTraceOn holds the switch;
+// from int32 word kTraceWord on, one (first block started, last block ended)
+// pair of %globaltimer values (uint64, ns) per stage.  The status segment of
+// the workspace has kStatusBlockWords words.
+constexpr int kStatusTraceOn = 3;
+constexpr int kTraceWord = 16;
+constexpr int kStatusBlockWords = 64;
+enum Stage { kStagePrepare = 0, kStageLogprob = 1, kStageLattice = 2, kStageCoef = 3, kStageGradient = 4, kStages_ = 5 };
 
 // Marker values of the `tgt` field of a gradient-coefficient record.
 constexpr int32_t kTgtNone = -1;     // no symbol column to patch in this row
@@ -147,6 +155,20 @@ cudaError_t launch_pdl(void (*kernel)(Exp...), unsigned grid, unsigned block, si
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<Exp>(args)...);
 }
 #ifdef __CUDACC__
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Called by one thread per block; a no-op unless the trace is switched on.
+__device__ __forceinline__ void trace_begin(const int32_t *status, int stage) {
+  if (status[kStatusTraceOn])
+    atomicMin(reinterpret_cast<unsigned long long *>(const_cast<int32_t *>(status) + kTraceWord) + 2 * stage, global_ns());
+}
+__device__ __forceinline__ void trace_end(const int32_t *status, int stage) {
+  if (status[kStatusTraceOn])
+    atomicMax(reinterpret_cast<unsigned long long *>(const_cast<int32_t *>(status) + kTraceWord) + 2 * stage + 1, global_ns());
+}
 // First statement of every kernel that reads what an earlier kernel wrote
 // (a no-op when the kernel was launched the ordinary way) ...
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -51,7 +51,7 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
                int32_t *__restrict__ status, int64_t *__restrict__ split,
                int64_t *__restrict__ cell_split, uint4 *__restrict__ lp_fill,
                int64_t lp_fill_count, uint4 fill_pattern,
-               volatile int32_t *host_status, int32_t host_seq) {
+               volatile int32_t *host_status, int32_t host_seq, int trace) {
   __shared__ long long scan_buf[kPrepThreads / kWarp];
   __shared__ int warp_maxu[kPrepThreads / kWarp];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -68,8 +68,13 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
       lp_fill[i] = fill_pattern;
     return;
   }
-  if (tid < kStatusWords) status[tid] = 0;
+  if (tid < kStatusBlockWords) {
+    // trace slots: "first start" begins at the maximum, "last end" at 0
+    const bool min_slot = tid >= kTraceWord && ((tid - kTraceWord) & 3) < 2;
+    status[tid] = min_slot ? -1 : (tid == kStatusTraceOn ? trace : 0);
+  }
   __syncthreads();
+  if (tid == 0) trace_begin(status, kStagePrepare);
 
   const int per = (N + kPrepThreads - 1) / kPrepThreads;
   const int b0 = min(tid * per, N), b1 = min(b0 + per, N);
@@ -114,10 +119,22 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
   // targets.max() < V over the whole (N, max_u) array, as the reference
   // checks it; in addition the entries that are used must not be negative.
   const long long cells = (long long)N * max_u;
-  for (long long i = tid; i < cells; i += kPrepThreads) {
-    const int v = targets[i];
-    const int b = (int)(i / max_u), u = (int)(i % max_u);
-    if (v >= V || (u < Ul[b] && v < 0)) raise(status, OT_B200_INPUT_TARGET_RANGE, b);
+  constexpr int kBatch = 8;  // independent loads in flight per thread
+  for (long long i0 = tid; i0 < cells; i0 += (long long)kPrepThreads * kBatch) {
+    int v[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const long long i = i0 + (long long)k * kPrepThreads;
+      v[k] = (i < cells) ? __ldg(targets + i) : 0;
+    }
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const long long i = i0 + (long long)k * kPrepThreads;
+      if (i < cells) {
+        const int b = (int)(i / max_u), u = (int)(i % max_u);
+        if (v[k] >= V || (v[k] < 0 && u < Ul[b])) raise(status, OT_B200_INPUT_TARGET_RANGE, b);
+      }
+    }
   }
   // Optional report straight into (mapped, pinned) host memory: the host polls
   // the sequence word, so no copy or event has to sit in the stream.
@@ -130,6 +147,7 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
       host_status[2] = host_seq;
     }
   }
+  if (tid == 0) trace_end(status, kStagePrepare);  // block 0 only: the fill blocks are not waited for
 }
 
 // Thread per workspace cell, in the order alpha and beta are stored, so their
@@ -156,6 +174,7 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
+  if (threadIdx.x == 0) trace_begin(status, kStageCoef);
   if (blockIdx.x == 0 && threadIdx.x < kWarp && loss_out != nullptr) {
     double acc = 0;
     for (int b = threadIdx.x; b < N; b += kWarp) acc += (double)scores[b];
@@ -235,6 +254,7 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
     r.utt = b;
     reinterpret_cast<CoefA<T> *>(coef_out)[row] = r;
   }
+  if (threadIdx.x == 0) trace_end(status, kStageCoef);  // one thread per block: cheap, close enough
 }
 
 template <typename T>
@@ -275,14 +295,19 @@ cudaError_t launch_prepare(const Problem &p, cudaStream_t s) {
   int64_t fill_blocks = (units + kPrepThreads * 8 - 1) / (kPrepThreads * 8);
   const int64_t cap = 2 * (int64_t)sm_count();
   if (fill_blocks > cap) fill_blocks = cap;
-  prepare_kernel<<<(unsigned)(1 + fill_blocks), kPrepThreads, 0, s>>>(
+  // Launched like the later stages: when the previous kernel in the stream is
+  // this library's gradient pass (training loops), the blocks are resident when
+  // it drains; behind any other kernel the attribute changes nothing.
+  const cudaError_t e = launch_pdl(prepare_kernel, (unsigned)(1 + fill_blocks), (unsigned)kPrepThreads, 0, s,
       p.targets, p.T, p.U, p.N, p.rows, p.V, p.max_u,
       (p.flags & OT_B200_ONE_SYM_PER_FRAME) ? 1 : 0, p.lay.max_cells,
       reinterpret_cast<int32_t *>(p.ws + p.lay.status),
       reinterpret_cast<int64_t *>(p.ws + p.lay.split),
       reinterpret_cast<int64_t *>(p.ws + p.lay.cell_split),
-      reinterpret_cast<uint4 *>(p.ws + p.lay.lp), units, pattern, p.host_status, p.host_seq);
-  return cudaGetLastError();
+      reinterpret_cast<uint4 *>(p.ws + p.lay.lp), units, pattern,
+      static_cast<volatile int32_t *>(p.host_status), p.host_seq,
+      (p.flags & OT_B200_TRACE) ? 1 : 0);
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 cudaError_t launch_coef(const Problem &p, const void *scores, void *loss_out,

@@ -38,6 +38,11 @@ __all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
            "PerUtteranceLossFunction"]
 
 
+# Diagnostic: set to a list (and OT_TRACE=1) to collect, per backward call, a
+# copy of the call's stage timeline (see _Call.stage("trace")).
+trace_log = None
+
+
 def _checks_enabled():
     return os.environ.get("OT_CHECKS", "1") != "0"
 
@@ -114,6 +119,8 @@ def _flags(logits, from_log_softmax, one_sym_per_frame, checks):
         f |= _lib.CHECK_INPUTS
     if _fast_math():
         f |= _lib.FAST_MATH
+    if os.environ.get("OT_TRACE", "0") == "1":
+        f |= _lib.TRACE
     return f
 
 
@@ -187,6 +194,10 @@ class _Call:
         cells = int(self.layout.max_cells)
         if name in ("split", "cell_split"):
             off, count, dtype, esz = getattr(self.layout, name + "_off"), self.n + 1, torch.int64, 8
+        elif name == "trace":
+            # with OT_TRACE=1: per stage (prepare, logprob, lattice, coef, gradient) the
+            # %globaltimer (ns) at which its first block started and its last block ended
+            off, count, dtype, esz = self.layout.status_off + 64, 10, torch.int64, 8
         elif name == "status":
             off, count, dtype, esz = self.layout.status_off, 16, torch.int32, 4
         else:
@@ -298,6 +309,8 @@ class TransducerLossFunction(torch.autograd.Function):
         grad = torch.empty_like(data) if call.from_log_softmax else data
         scale = loss_grad.detach().to(device=data.device, dtype=call.real).contiguous()
         call.backward(grad, scale_tensor=scale, scale_host=ctx.scale_host)
+        if trace_log is not None:  # diagnostic, see OT_TRACE
+            trace_log.append(call.stage("trace").clone())
         return (grad,) + (None,) * 7
 
 

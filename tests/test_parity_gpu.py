@@ -291,6 +291,41 @@ def test_scale_is_folded_into_the_gradient_pass():
     torch.testing.assert_close(g2, g1 * 0.75, rtol=1e-6, atol=1e-7)
 
 
+def test_share_sms_flag_changes_grids_not_results():
+    """OT_B200_SHARE_SMS only sizes the one-wave grids one SM short."""
+    x, tg, T, U = random_batch(53, 6, (30, 60), (8, 20), 500, 2.0)
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    outs = []
+    for share in (False, True):
+        call = _Call(dx, dt, dT, dU, 0, False, False, share_sms=share)
+        scores = call.forward().clone()
+        g = torch.empty_like(dx)
+        call.backward(g)
+        outs.append((scores, g))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+def test_stage_timeline(monkeypatch):
+    """OT_TRACE=1: every stage reports when its first block started and its last
+    block ended; the stages of one call follow one another."""
+    monkeypatch.setenv("OT_TRACE", "1")
+    x, tg, T, U = random_batch(54, 4, (30, 60), (8, 20), 64)
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    call = _Call(dx, dt, dT, dU, 0, False, False)
+    call.forward()
+    call.backward(torch.empty_like(dx))
+    torch.cuda.synchronize()
+    t = call.stage("trace").cpu().numpy().reshape(5, 2)
+    assert np.all(t[:, 0] > 0) and np.all(t[:, 1] >= t[:, 0])
+    assert np.all(t[1:, 0] >= t[:-1, 0])          # prepare, logprob, lattice, coef, gradient start in order
+    assert t[-1, 1] - t[0, 0] < 1e9                # within a second of each other (ns)
+    monkeypatch.setenv("OT_TRACE", "0")
+    call = _Call(dx, dt, dT, dU, 0, False, False)
+    call.forward()
+    torch.cuda.synchronize()
+    assert int(call.stage("trace")[1]) == 0        # off: "last end" slots stay at their initial 0
+
+
 @pytest.mark.parametrize("fast", ["0", "1"])
 def test_both_log_add_variants_stay_within_tolerance(fast, monkeypatch):
     """OT_FAST_MATH=1 (default): ex2/lg2.approx in the recursions; =0: expf/log1pf."""
