@@ -235,6 +235,16 @@ def run_ours(args, w):
         opts.is_high_priority_stream = True
         dist.init_process_group("nccl", device_id=dev, pg_options=opts)
         from optimized_transducer_b200 import sharding
+    exchange, collective = None, "none"
+    if world > 1:
+        collective = "NCCL all-reduce of the 0-dim loss on a side stream"
+        if args.collective == "peer":
+            try:  # plain peer stores/loads only: no multicast object is wanted
+                os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+                exchange = sharding.peer_exchange()
+                collective = "peer-memory exchange (two one-warp kernels, no NCCL on the data path)"
+            except Exception as e:  # symmetric memory unavailable: keep NCCL, say so
+                collective += f" (peer exchange unavailable: {type(e).__name__})"
 
     # ----- the batch (global), and this rank's shard of it
     n_global = w.n * world if args.scaling == "weak" else w.n
@@ -282,7 +292,7 @@ def run_ours(args, w):
             loss = sharding.sharded_transducer_loss(
                 x, dtg, dT, dU, blank=0, from_log_softmax=w.from_log_softmax,
                 one_sym_per_frame=w.one_sym_per_frame, reduction=w.reduction,
-                global_batch=n_global, overlap=True)
+                global_batch=n_global, overlap=True, exchange=exchange)
         else:
             loss = ot.transducer_loss(x, dtg, dT, dU, blank=0, from_log_softmax=w.from_log_softmax,
                                       one_sym_per_frame=w.one_sym_per_frame, reduction=w.reduction)
@@ -338,7 +348,7 @@ def run_ours(args, w):
             loss = sharding.sharded_transducer_loss(
                 x, g_, t_, u_, blank=0, from_log_softmax=w.from_log_softmax,
                 one_sym_per_frame=w.one_sym_per_frame, reduction=w.reduction,
-                global_batch=n_global, overlap=True)
+                global_batch=n_global, overlap=True, exchange=exchange)
         else:
             loss = ot.transducer_loss(x, g_, t_, u_, blank=0, from_log_softmax=w.from_log_softmax,
                                       one_sym_per_frame=w.one_sym_per_frame, reduction=w.reduction)
@@ -395,6 +405,7 @@ def run_ours(args, w):
                             + ("" if args.dtype == "f32" else f", logits stored as {args.dtype}"),
                 "sharding": "none" if world == 1 else
                             f"{world} ranks, whole utterances, balanced by T*(U+1)*V ({args.partition} partition)",
+                "collective": collective,
                 "cache": "inputs larger than L2: every step reads its own pristine logits buffer",
                 "checks": os.environ.get("OT_CHECKS", "1"),
                 "gradient_schedule": "eager" if os.environ.get("OT_EAGER_GRAD", "0") == "1" else "deferred (fused into backward)",
@@ -497,6 +508,8 @@ def main():
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--dtype", choices=["f32", "bf16", "f16"], default="f32",
                     help="storage type of the logits (the reference's is f32; 16-bit is an extension)")
+    ap.add_argument("--collective", choices=["peer", "nccl"], default="peer",
+                    help="how the ranks' losses are summed: over peer memory (default) or by NCCL")
     ap.add_argument("--partition", choices=["auto", "contiguous", "lpt"], default="lpt",
                     help="how utterances are dealt to the ranks (each rank creates its own shard, "
                          "so the permuting, better balanced \"lpt\" costs nothing here)")

@@ -252,6 +252,35 @@ int ot_b200_scores_noalloc(const float *d_log_probs, const int32_t *d_targets,
                            int32_t V, int32_t max_u, int32_t blank, float *d_scores,
                            void *stream);
 
+/* ---------------------------------------------------------------------------
+ * Exchange of one scalar per rank over peer memory: the sum of the per-shard
+ * losses of a batch that is sharded by utterance over the GPUs of one node.
+ * No counterpart in the reference (single GPU, transducer_loss.py:145-152
+ * reduces one tensor); it replaces an NCCL all-reduce of the 0-dim loss.
+ *
+ * Every rank owns a table of ring x world entries of 16 bytes
+ * (ot_b200_exchange_bytes), zeroed before the first use, that all ranks can
+ * address (peer-mapped device memory).  d_tables is a DEVICE array of `world`
+ * pointers: d_tables[p] = the table owned by rank p, as addressed from this rank.
+ *
+ * ot_b200_exchange_publish: one warp stores {*d_value, step + 1} into entry
+ *   [step % ring][rank] of every table (plain peer stores, value before a
+ *   system-scope release of the sequence number).  It never waits.
+ * ot_b200_exchange_gather: one warp polls the `world` entries of slot
+ *   step % ring of the caller's OWN table until each carries step + 1, then
+ *   *d_out = scale * (sum in rank order).  The poll gives up after max_wait_ns:
+ *   *d_error (set it to 0 beforehand) becomes 1 + the rank that did not arrive
+ *   (101 + rank: its entry was already overwritten by a step >= step + ring),
+ *   *d_out becomes NaN and the kernel returns.
+ * d_value / d_out are float, or double with OT_B200_FP64.  world <= 32. */
+int ot_b200_exchange_bytes(int32_t world, int32_t ring, uint64_t *bytes_out);
+int ot_b200_exchange_publish(const void *d_value, uint32_t flags, void *const *d_tables,
+                             int32_t world, int32_t rank, int32_t ring, uint64_t step,
+                             void *stream);
+int ot_b200_exchange_gather(const void *d_table, int32_t world, int32_t ring, uint64_t step,
+                            void *d_out, uint32_t flags, double scale, int32_t *d_error,
+                            uint64_t max_wait_ns, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,6 +42,9 @@ EXPORTS = (
     "ot_b200_pack_joiner_input_backward",
     "ot_b200_pack_padded",
     "ot_b200_unpack_to_padded",
+    "ot_b200_exchange_bytes",
+    "ot_b200_exchange_publish",
+    "ot_b200_exchange_gather",
 )
 
 
@@ -96,6 +99,12 @@ def load():
         fn = getattr(lib, name)
         fn.restype = ctypes.c_int
         fn.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, vp, vp]
+    lib.ot_b200_exchange_bytes.restype = ctypes.c_int
+    lib.ot_b200_exchange_bytes.argtypes = [i32, i32, ctypes.POINTER(u64)]
+    lib.ot_b200_exchange_publish.restype = ctypes.c_int
+    lib.ot_b200_exchange_publish.argtypes = [vp, u32, vp, i32, i32, i32, u64, vp]
+    lib.ot_b200_exchange_gather.restype = ctypes.c_int
+    lib.ot_b200_exchange_gather.argtypes = [vp, i32, i32, u64, vp, u32, ctypes.c_double, vp, u64, vp]
     if lib.ot_b200_abi_version() != ABI_VERSION:
         raise ImportError("libot_b200.so was built from a different ABI version; rebuild it")
     _lib = lib

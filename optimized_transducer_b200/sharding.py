@@ -181,23 +181,140 @@ def wait_loss(loss: torch.Tensor) -> torch.Tensor:
     return loss
 
 
+class PeerExchange:
+    """Sum of one scalar per rank over peer-mapped device memory, the light
+    alternative to an NCCL all-reduce of the 0-dim loss (see
+    ``csrc/exchange.cu``): a one-warp kernel stores this rank's value into every
+    rank's table, a second one-warp kernel sums the table once all values of the
+    step are there.  Neither needs the room a collective's kernel needs, so both
+    run beside the one-wave gradient kernel.
+
+    ``PeerExchange(group)`` allocates the table with
+    ``torch.distributed._symmetric_memory`` (one rendezvous, then no library
+    call on the data path).  ``PeerExchange(tables=[...], rank=r)`` takes tables
+    the caller made addressable itself (tests emulate several ranks on one
+    device with it).  Ranks must not drift apart by ``ring`` steps or more.
+    """
+
+    RING = 256
+
+    def __init__(self, group=None, device=None, tables=None, rank=None, max_wait_s=2.0):
+        from . import _lib
+        import ctypes
+        self._lib, self._ct = _lib, ctypes
+        self.lib = _lib.load()
+        self.step = 0
+        self.max_wait_ns = int(max_wait_s * 1e9)
+        if tables is not None:
+            self.world, self.rank = len(tables), int(rank)
+            self.table = tables[self.rank]
+            self._keep = list(tables)
+            ptrs = [t.data_ptr() for t in tables]
+            device = self.table.device
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+            group = group if group is not None else dist.group.WORLD
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+            device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+            self.table = symm_mem.empty(self.table_doubles(self.world), dtype=torch.float64, device=device)
+            self.table.zero_()
+            self._keep = symm_mem.rendezvous(self.table, group)
+            ptrs = [int(p) for p in self._keep.buffer_ptrs]
+            torch.cuda.synchronize(device)
+            dist.barrier(group)  # every table is zero before anyone publishes
+        self.device = device
+        self.ptrs = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self.error = torch.zeros(1, dtype=torch.int32, device=device)
+
+    @classmethod
+    def table_doubles(cls, world):
+        """Size of one rank's table in float64 elements (16 bytes per entry)."""
+        return 2 * cls.RING * world
+
+    def _stream(self, stream):
+        stream = torch.cuda.current_stream(self.device) if stream is None else stream
+        return self._ct.c_void_p(stream.cuda_stream)
+
+    def publish(self, local, step=None, stream=None):
+        """Stores ``local`` (0-dim float32/float64) into every rank's table; never waits."""
+        assert local.dtype in (torch.float32, torch.float64)
+        flags = self._lib.FP64 if local.dtype == torch.float64 else 0
+        with torch.cuda.device(self.device):
+            self._lib.check(self.lib.ot_b200_exchange_publish(
+                local.data_ptr(), flags, self.ptrs.data_ptr(), self.world, self.rank, self.RING,
+                self.step if step is None else int(step), self._stream(stream)))
+
+    def gather(self, out, scale=1.0, step=None, stream=None):
+        """``out = scale * sum over ranks`` of what they published for the step
+        (waits, bounded, for the values that are not there yet)."""
+        assert out.dtype in (torch.float32, torch.float64)
+        flags = self._lib.FP64 if out.dtype == torch.float64 else 0
+        with torch.cuda.device(self.device):
+            self._lib.check(self.lib.ot_b200_exchange_gather(
+                self.table.data_ptr(), self.world, self.RING,
+                self.step if step is None else int(step), out.data_ptr(), flags,
+                float(scale), self.error.data_ptr(), self.max_wait_ns, self._stream(stream)))
+        return out
+
+    def all_reduce_sum(self, local, out, scale=1.0, stream=None):
+        """Enqueues publish + gather of the next step on ``stream`` (default:
+        the current one): ``out = scale * sum over ranks of local``."""
+        assert local.dtype == out.dtype
+        self.publish(local, stream=stream)
+        self.gather(out, scale, stream=stream)
+        self.step += 1
+        return out
+
+    def check(self):
+        """Synchronises and raises if a gather gave up (a rank did not publish in time)."""
+        code = int(self.error.item())
+        if code:
+            what = (f"rank {code - 101}'s entry was overwritten (ranks drifted apart by {self.RING} steps)"
+                    if code > 100 else f"rank {code - 1} did not publish within {self.max_wait_ns / 1e9:.1f} s")
+            raise RuntimeError("PeerExchange: " + what)
+
+
+_PEER = {}
+
+
+def peer_exchange(group=None, device=None):
+    """The (cached) :class:`PeerExchange` of a process group; collective on first use."""
+    key = (id(group), str(device))
+    if key not in _PEER:
+        _PEER[key] = PeerExchange(group, device)
+    return _PEER[key]
+
+
 class _ShardedLoss(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, targets, logit_lengths, target_lengths, blank, from_log_softmax,
-                one_sym_per_frame, reduction, global_batch, group, overlap):
+                one_sym_per_frame, reduction, global_batch, group, overlap, exchange):
         assert reduction in ("mean", "sum")
         if logit_lengths.numel() > 0:
             call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
-                         from_log_softmax, one_sym_per_frame, share_sms=bool(overlap))
+                         from_log_softmax, one_sym_per_frame,
+                         share_sms=bool(overlap) and exchange is None)
             local = torch.empty((), dtype=real_dtype(logits), device=logits.device)
             call.forward(loss_out=local, loss_scale=1.0)
         else:  # a rank without utterances still joins the collective
             call = None
             local = torch.zeros((), dtype=real_dtype(logits), device=logits.device)
+        scale = 1.0 / float(global_batch) if reduction == "mean" else 1.0
+        if exchange is not None:
+            # peer-memory exchange: two one-warp kernels on the side stream
+            main = torch.cuda.current_stream(logits.device)
+            side = _side_stream(logits.device)
+            side.wait_stream(main)
+            total = torch.empty_like(local)
+            exchange.all_reduce_sum(local, total, scale, stream=side)
+            local.record_stream(side)
+            total.record_stream(side)
+            ctx.call = call if ctx.needs_input_grad[0] else None
+            ctx.scale_host = scale
+            ctx.empty_like = logits.detach() if call is None else None
+            return total
         total, event = all_reduce_sum(local, group, overlap)
-        scale = 1.0
         if reduction == "mean":
-            scale = 1.0 / float(global_batch)
             if event is not None:
                 with torch.cuda.stream(_side_stream(logits.device)):
                     total = total * scale
@@ -228,12 +345,13 @@ class _ShardedLoss(torch.autograd.Function):
         # ends, the collective's kernel gets its slot only then, and a wait here
         # would put its whole latency behind the gradient pass.  It now runs
         # under whatever the main stream does next; wait_loss() orders a reader.
-        return (grad,) + (None,) * 10
+        return (grad,) + (None,) * 11
 
 
 def sharded_transducer_loss(logits, targets, logit_lengths, target_lengths, blank,
                             from_log_softmax, one_sym_per_frame=False, reduction="mean",
-                            global_batch: Optional[int] = None, group=None, overlap=False):
+                            global_batch: Optional[int] = None, group=None, overlap=False,
+                            exchange: Optional[PeerExchange] = None):
     """Transducer loss of a batch that is sharded by utterance over the ranks of
     ``group``.  Every rank passes ITS utterances (packed logits, targets padded
     to the local max U, lengths); every rank gets the loss of the whole batch.
@@ -243,11 +361,16 @@ def sharded_transducer_loss(logits, targets, logit_lengths, target_lengths, blan
 
     ``overlap=True`` issues the scalar all-reduce on a side stream, off the
     critical path of the gradient pass; the VALUE of the returned tensor is then
-    defined only after :func:`wait_loss` (or a device synchronisation)."""
+    defined only after :func:`wait_loss` (or a device synchronisation).
+
+    ``exchange`` (a :class:`PeerExchange`, e.g. ``peer_exchange(group)``; GPUs of
+    one node) replaces the NCCL all-reduce by two one-warp kernels over peer
+    memory on the side stream; the value is likewise defined after
+    :func:`wait_loss`."""
     if global_batch is None:
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         global_batch = int(logit_lengths.numel()) * world
     loss = _ShardedLoss.apply(logits, targets, logit_lengths, target_lengths, blank,
                               from_log_softmax, one_sym_per_frame, reduction, global_batch,
-                              group, overlap)
+                              group, overlap, exchange)
     return loss

@@ -478,3 +478,56 @@ def test_sharded_loss_on_one_rank_equals_plain_loss(reduction):
     sharding.wait_loss(b)
     assert torch.allclose(a, b, rtol=1e-6)
     assert torch.allclose(a_leaf.grad, b_leaf.grad, rtol=0, atol=1e-7)
+
+
+# ---------------------------------------------------------------------------
+# 8. the peer-memory scalar exchange, several ranks emulated on one device
+#    (all publishes are enqueued before any gather: nothing ever waits here)
+# ---------------------------------------------------------------------------
+def _emulated_ranks(world, **kw):
+    from optimized_transducer_b200.sharding import PeerExchange
+    tables = [torch.zeros(PeerExchange.table_doubles(world), dtype=torch.float64, device=DEV)
+              for _ in range(world)]
+    return [PeerExchange(tables=tables, rank=r, **kw) for r in range(world)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_peer_exchange_sums_in_rank_order(dtype):
+    ranks = _emulated_ranks(3)
+    for step in range(300):  # wraps the ring
+        vals = [torch.tensor(v * (step + 1), dtype=dtype, device=DEV) for v in (1.5, -2.25, 4.0)]
+        for ex, v in zip(ranks, vals):
+            ex.publish(v, step=step)
+        outs = [ex.gather(torch.empty((), dtype=dtype, device=DEV), scale=0.5, step=step) for ex in ranks]
+        if step in (0, 1, 255, 256, 299):
+            want = 0.5 * ((1.5 * (step + 1) + -2.25 * (step + 1)) + 4.0 * (step + 1))
+            for o in outs:
+                assert o.item() == pytest.approx(want, rel=1e-6)
+            assert outs[0].item() == outs[1].item() == outs[2].item()  # same order, same bits
+    for ex in ranks:
+        ex.check()
+
+
+def test_peer_exchange_gives_up_on_a_rank_that_never_publishes():
+    """The wait is bounded: a flag nothing sets makes it run out; the kernel
+    reports the missing rank, writes NaN and returns, the context stays usable."""
+    ranks = _emulated_ranks(2, max_wait_s=0.002)
+    ranks[0].publish(torch.tensor(1.0, device=DEV), step=0)
+    out = ranks[0].gather(torch.zeros((), device=DEV), step=0)
+    torch.cuda.synchronize()
+    assert torch.isnan(out)
+    with pytest.raises(RuntimeError, match="rank 1 did not publish"):
+        ranks[0].check()
+    assert torch.ones(4, device=DEV).sum().item() == 4.0
+
+
+def test_peer_exchange_detects_an_overwritten_entry():
+    from optimized_transducer_b200.sharding import PeerExchange
+    ranks = _emulated_ranks(2)
+    for ex in ranks:
+        ex.publish(torch.tensor(1.0, device=DEV), step=PeerExchange.RING)  # same slot as step 0, one lap later
+    out = ranks[1].gather(torch.zeros((), device=DEV), step=0)
+    torch.cuda.synchronize()
+    assert torch.isnan(out)
+    with pytest.raises(RuntimeError, match="overwritten"):
+        ranks[1].check()
