@@ -367,6 +367,40 @@ def test_infeasible_utterance_gives_zero_gradient_rows():
     assert np.max(np.abs(out["grad"][sp[1]:] - ref["grad"])) <= 1e-5
 
 
+def test_long_utterance_replica_float64_and_float32():
+    """Four utterances of the long-utterance stress shape (T in [500,1000], U in
+    [100,200], V=1024) in float64 against the float64 restatement at 1e-10, and the
+    float32 path on the same numbers.  Lattices of 101..201 columns (4..7 warps)
+    and up to 1200 steps: the skewed recursion runs with blocks shorter than 16
+    steps here (its stages would not fit otherwise)."""
+    w = synthetic.CONFIGS["cfg5"]
+    T, U, tg = synthetic.make_lengths(w)
+    T, U = T[:4].contiguous(), U[:4].contiguous()
+    tg = tg[:4, :int(U.max())].contiguous()
+    x64 = synthetic.make_logits(w, T, U, dtype=torch.float64)
+    ref = O.oracle_loss(x64.numpy(), tg.numpy(), T.numpy(), U.numpy(), 0)
+    dt, dT, dU = tg.to(DEV), T.to(DEV), U.to(DEV)
+    for dtype, tol in ((torch.float64, 1e-10), (torch.float32, 1e-5)):
+        dx = x64.to(DEV, dtype).requires_grad_(True)
+        scores, grad = ot.compute_transducer_loss(dx, dt, dT, dU, 0, False, False)
+        got = scores.double().cpu().numpy()
+        assert np.max(np.abs(got - ref["scores"]) / np.abs(ref["scores"])) <= tol
+        gerr = float((grad.double().cpu() - torch.from_numpy(ref["grad"])).abs().max())
+        if dtype == torch.float64:
+            assert gerr <= 1e-10
+        else:
+            # float32 at |log-likelihood| ~ 5000-7500 cannot hold 1e-5 against the
+            # float64 result (nor can the reference): it must be as close to it as
+            # the reference's algorithm run in float32, and within the float32
+            # floor of that float32 result.
+            ref32 = O.oracle_loss(x64.float().numpy(), tg.numpy(), T.numpy(), U.numpy(), 0)
+            err_ref = float(np.abs(ref32["grad"].astype(np.float64) - ref["grad"]).max())
+            assert gerr <= 1.5 * err_ref + 1e-6, (gerr, err_ref)
+            g32 = float((grad.cpu() - torch.from_numpy(ref32["grad"])).abs().max())
+            assert g32 <= fp32_grad_floor(ref32["alpha"], ref32["beta"]), g32
+        del dx, grad
+
+
 # ---------------------------------------------------------------------------
 # 5. device-side input check (transducer-loss.cc:49-66) and its error path
 # ---------------------------------------------------------------------------
