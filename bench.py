@@ -461,10 +461,13 @@ def run_pack(args, w):
     torch.cuda.set_device(dev)
     d = 512
     T, U, _ = synthetic.make_lengths(w)
+    if args.utts:  # a smaller case of the same workload, for profiler captures
+        T, U = T[:args.utts].contiguous(), U[:args.utts].contiguous()
+    n_utt = int(T.numel())
     rows = synthetic.num_rows(T, U)
     dT, dU = T.to(dev), U.to(dev)
-    enc = torch.randn(w.n, int(T.max()), d, device=dev, requires_grad=True)
-    dec = torch.randn(w.n, int(U.max()) + 1, d, device=dev, requires_grad=True)
+    enc = torch.randn(n_utt, int(T.max()), d, device=dev, requires_grad=True)
+    dec = torch.randn(n_utt, int(U.max()) + 1, d, device=dev, requires_grad=True)
     g = torch.randn(rows, d, device=dev)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     fwd, bwd = [], []

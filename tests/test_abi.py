@@ -82,3 +82,13 @@ def test_argument_errors_without_touching_a_gpu():
     assert rc == _lib.ERR_ARGUMENT
     with pytest.raises(RuntimeError):
         _lib.check(rc)
+
+
+def test_exchange_table_size_and_argument_checks():
+    """Host-side part of the peer-memory exchange: 16 bytes per (slot, rank)."""
+    lib = _lib.load()
+    n = ctypes.c_uint64(0)
+    assert lib.ot_b200_exchange_bytes(8, 256, ctypes.byref(n)) == _lib.OK and n.value == 8 * 256 * 16
+    assert lib.ot_b200_exchange_bytes(33, 256, ctypes.byref(n)) == _lib.ERR_ARGUMENT
+    assert lib.ot_b200_exchange_publish(None, 0, None, 2, 0, 256, 0, None) == _lib.ERR_ARGUMENT
+    assert lib.ot_b200_exchange_gather(None, 2, 256, 0, None, 0, 1.0, None, 1000, None) == _lib.ERR_ARGUMENT
