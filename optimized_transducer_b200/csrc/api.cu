@@ -116,6 +116,15 @@ int check_common(int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blan
 
 void set_last_error(const char *msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
 
+bool wave_grids() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char *e = getenv("OT_B200_GRID");
+    cached = (e && strcmp(e, "wave") == 0) ? 1 : 0;
+  }
+  return cached == 1;
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;

@@ -193,10 +193,14 @@ cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
   auto kernel = logprob_kernel<X, VEC, CH, LPR, MODIFIED>;
   static int per_sm = 0;  // occupancy of this instantiation (same on every B200)
   if (per_sm == 0) per_sm = blocks_per_sm(kernel, kThreads);
-  constexpr int rows_per_block = (kThreads / kWarp) * (kWarp / LPR);
-  const int64_t want = (p.rows + rows_per_block - 1) / rows_per_block;
-  const int64_t cap = (int64_t)resident_sms(p.flags) * per_sm;
-  const unsigned grid = (unsigned)(want < cap ? want : cap);
+  constexpr int groups_per_block = (kThreads / kWarp) * (kWarp / LPR);
+  const int64_t nruns = (p.rows + kRun - 1) / kRun;  // a lane group takes one run at a time
+  int64_t want = (nruns + groups_per_block - 1) / groups_per_block;
+  if (wave_grids()) {
+    const int64_t cap = (int64_t)resident_sms(p.flags) * per_sm;
+    if (want > cap) want = cap;
+  }
+  const unsigned grid = (unsigned)(want < 1 ? 1 : (want < 0x7fffffff ? want : 0x7fffffff));
   const cudaError_t e = launch_pdl(kernel, grid, (unsigned)kThreads, 0, s,
       static_cast<const X *>(p.logits), p.targets, p.T, p.U,
       reinterpret_cast<const int64_t *>(p.ws + p.lay.split),

@@ -115,6 +115,12 @@ struct Problem {
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+// Grid policy of the streaming kernels.  Default: one short-lived block per
+// 8 rows (or 8 runs), as many blocks as the buffer needs.  OT_B200_GRID=wave:
+// exactly one resident wave of blocks that stride over the buffer.  On B200 the
+// same row-per-warp in-place pass moves 6.8 TB/s with the first and 5.85 TB/s
+// with the second (a read-only pass 7.5 against 7.2).
+bool wave_grids();
 // SMs the one-wave grids of the streaming kernels are sized for: all of them,
 // or one fewer with OT_B200_SHARE_SMS, so that a kernel that is resident beside
 // this path (a collective waiting for its peers) does not keep some of the

@@ -94,22 +94,48 @@ pack_rows_kernel(const T *__restrict__ a, const T *__restrict__ bsrc, T *__restr
       const int idx = (int)(r0 - __ldg(split + b));
       t = idx / U1; u = idx - t * U1;
     }
+    // Frame whose encoder vector the registers hold (rows of a run mostly share
+    // their frame: only u advances), when a row fits into one chunk.
+    constexpr int kCh = 4;
+    const bool one_chunk = nvec <= kWarp * kCh;
+    int64_t held = -1;
+    VT x[kCh];
     for (int64_t row = r0; row < r1; ++row) {
       const int64_t padded = (((int64_t)b * max_t + t) * max_u1 + u) * D;
       if (MODE == kAdd) {
-        const T *pa = a + ((int64_t)b * max_t + t) * D;
+        const int64_t frame = (int64_t)b * max_t + t;
+        const T *pa = a + frame * D;
         const T *pb = bsrc + ((int64_t)b * max_u1 + u) * D;
         T *po = out + row * (int64_t)D;
-        for (int vi = lane; vi < nvec; vi += kWarp) {
-          const VT x = *reinterpret_cast<const VT *>(pa + (int64_t)vi * VEC);
-          const VT y = *reinterpret_cast<const VT *>(pb + (int64_t)vi * VEC);
-          VT z;
-          const T *xe = reinterpret_cast<const T *>(&x);
-          const T *ye = reinterpret_cast<const T *>(&y);
-          T *ze = reinterpret_cast<T *>(&z);
+        // kCh vectors per lane at a time, all loads issued before the first
+        // add.  Both operands are small and L2-resident, but at one encoder and
+        // one decoder load per stored vector the L2 would have to deliver twice
+        // the bytes the pass writes; keeping the encoder vector halves that.
+        for (int base = 0; base < nvec; base += kWarp * kCh) {
+          VT y[kCh];
+          const bool reload = !(one_chunk && held == frame);
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) ze[k] = xe[k] + ye[k];
-          *reinterpret_cast<VT *>(po + (int64_t)vi * VEC) = z;
+          for (int j = 0; j < kCh; ++j) {
+            const int vi = base + j * kWarp + lane;
+            if (vi < nvec) {
+              if (reload) x[j] = *reinterpret_cast<const VT *>(pa + (int64_t)vi * VEC);
+              y[j] = *reinterpret_cast<const VT *>(pb + (int64_t)vi * VEC);
+            }
+          }
+          held = frame;
+#pragma unroll
+          for (int j = 0; j < kCh; ++j) {
+            const int vi = base + j * kWarp + lane;
+            if (vi < nvec) {
+              VT z;
+              const T *xe = reinterpret_cast<const T *>(&x[j]);
+              const T *ye = reinterpret_cast<const T *>(&y[j]);
+              T *ze = reinterpret_cast<T *>(&z);
+#pragma unroll
+              for (int k = 0; k < VEC; ++k) ze[k] = xe[k] + ye[k];
+              *reinterpret_cast<VT *>(po + (int64_t)vi * VEC) = z;
+            }
+          }
         }
       } else {
         const T *ps = (MODE == kCopy) ? a + padded : a + row * (int64_t)D;
@@ -163,12 +189,17 @@ int fail(int code, const char *msg) {
   return code;
 }
 
-// One resident wave of `kernel` (a grid-stride grid that is larger runs a partial second wave).
+// One warp per run of kRun rows: as many short-lived blocks as that takes, or, with
+// OT_B200_GRID=wave, at most one resident wave (the kernel loops).
 template <typename K>
 unsigned rows_grid(K kernel, int64_t rows) {
-  const int64_t want = (rows + (kThreads / kWarp) * kRun - 1) / ((kThreads / kWarp) * kRun);
-  const int64_t cap = (int64_t)sm_count() * blocks_per_sm(kernel, kThreads);
-  return (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
+  int64_t want = (rows + (kThreads / kWarp) * kRun - 1) / ((kThreads / kWarp) * kRun);
+  if (want < 1) want = 1;
+  if (wave_grids()) {
+    const int64_t cap = (int64_t)sm_count() * blocks_per_sm(kernel, kThreads);
+    if (want > cap) want = cap;
+  }
+  return (unsigned)(want < 0x7fffffff ? want : 0x7fffffff);
 }
 
 template <typename T, int MODE>
