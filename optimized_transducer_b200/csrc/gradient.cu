@@ -22,6 +22,8 @@
 // towards its start: the rows stage 1 read last are the ones still resident in
 // L2.  HBM traffic per row: V*sizeof(T) read + V*sizeof(T) written (mode A),
 // V*sizeof(T) written (mode B), plus one 32-byte (16-byte) coefficient record.
+#include <stdlib.h>
+
 #include "ot_common.cuh"
 
 namespace otb {
@@ -51,12 +53,12 @@ __device__ __forceinline__ CoefA<T> load_coef(const CoefA<T> *p) {
 
 // X: storage type of logits and gradient, T = Real<X>: type of the arithmetic.
 // PER_UTT: d_scale holds one factor per utterance instead of one scalar.
-template <typename X, int VEC, int CH, bool PER_UTT>
-__global__ void __launch_bounds__(kThreads)
+template <typename X, int VEC, int CH, bool PER_UTT, int MINB = 5>
+__global__ void __launch_bounds__(kThreads, MINB)
 gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restrict__ coef,
                 const int32_t *__restrict__ status, int64_t rows, int V,
                 int blank, const typename Real<X>::type *__restrict__ d_scale,
-                typename Real<X>::type scale_host) {
+                typename Real<X>::type scale_host, bool eager) {
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
@@ -75,6 +77,17 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
     const T scale = PER_UTT ? scale_host * __ldg(d_scale + rec.utt) : scale_all;
     const X *px = x + row * (int64_t)V;
     X *pg = g + row * (int64_t)V;
+    VT v[CH];
+    // The first chunk of the row is requested before the record is looked at, so
+    // the two round trips overlap.  (`eager` is off for the band-limited
+    // recursion, whose many zero rows would then be read for nothing.)
+    if (eager) {
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int vi = j * kWarp + lane;
+        if (vi < nvec) v[j] = *reinterpret_cast<const VT *>(px + (int64_t)vi * VEC);
+      }
+    }
     if (rec.tgt == kTgtZeroRow) {
       VT z;
       X *ze = reinterpret_cast<X *>(&z);
@@ -87,11 +100,12 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
     const int tvec = rec.tgt >= 0 ? rec.tgt / VEC : -1;
     const int tk = rec.tgt >= 0 ? rec.tgt % VEC : 0;
     for (int base = 0; base < nvec; base += kWarp * CH) {
-      VT v[CH];
+      if (!(eager && base == 0)) {
 #pragma unroll
-      for (int j = 0; j < CH; ++j) {
-        const int vi = base + j * kWarp + lane;
-        if (vi < nvec) v[j] = *reinterpret_cast<const VT *>(px + (int64_t)vi * VEC);
+        for (int j = 0; j < CH; ++j) {
+          const int vi = base + j * kWarp + lane;
+          if (vi < nvec) v[j] = *reinterpret_cast<const VT *>(px + (int64_t)vi * VEC);
+        }
       }
 #pragma unroll
       for (int j = 0; j < CH; ++j) {
@@ -175,10 +189,10 @@ gradient_logsoftmax_kernel(X *__restrict__ g, const CoefB<typename Real<X>::type
 // Blocks for `units` warp-sized units of work (8 per block): all of them, or,
 // with OT_B200_GRID=wave, at most one resident wave (the kernels loop).
 template <typename K>
-unsigned stream_grid(K kernel, int *per_sm, int64_t units, uint32_t flags) {
+unsigned stream_grid(K kernel, int *per_sm, int64_t units, uint32_t flags, bool one_wave = false) {
   int64_t want = (units + (kThreads / kWarp) - 1) / (kThreads / kWarp);
   if (want < 1) want = 1;
-  if (wave_grids()) {
+  if (one_wave || wave_grids()) {
     if (*per_sm == 0) *per_sm = blocks_per_sm(kernel, kThreads);
     const int64_t cap = (int64_t)resident_sms(flags) * *per_sm;
     if (want > cap) want = cap;
@@ -191,12 +205,22 @@ cudaError_t launch_grad_a2(const Problem &p, void *grad, const void *d_scale,
                            double scale_host, cudaStream_t s) {
   using T = typename Real<X>::type;
   static int per_sm = 0;
-  const cudaError_t e = launch_pdl(gradient_kernel<X, VEC, CH, PER_UTT>,
-      stream_grid(gradient_kernel<X, VEC, CH, PER_UTT>, &per_sm, p.rows, p.flags), (unsigned)kThreads, 0, s,
+  // Six resident blocks per SM (40 registers) for the vectorised float pass: with
+  // short-lived blocks the bytes in flight are (resident warps) x (one row), and
+  // the step from 5 to 6 blocks took the float pass from 436 to 408 us on
+  // 686 128 rows of 500; 7 or 8 blocks need spills and are slower (488 us), and so
+  // are six for the 16-bit types (348 against 309 us).
+  constexpr int kMinBlocks = (sizeof(X) == 4 && VEC == 4) ? 6 : (sizeof(X) == 8 ? 3 : 5);
+  auto kernel = gradient_kernel<X, VEC, CH, PER_UTT, kMinBlocks>;
+  // 16-bit rows are half as many bytes per warp; there one resident wave that
+  // strides over the buffer measured faster (315 against 351 us on bf16 cfg2).
+  const cudaError_t e = launch_pdl(kernel,
+      stream_grid(kernel, &per_sm, p.rows, p.flags, sizeof(X) == 2), (unsigned)kThreads, 0, s,
       static_cast<const X *>(p.logits), static_cast<X *>(grad),
       reinterpret_cast<const CoefA<T> *>(p.ws + p.lay.coef),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V,
-      p.blank, static_cast<const T *>(d_scale), (T)scale_host);
+      p.blank, static_cast<const T *>(d_scale), (T)scale_host,
+      (p.flags & OT_B200_ONE_SYM_PER_FRAME) == 0);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
