@@ -24,6 +24,9 @@
 // per row: V*sizeof(T) bytes read, 3*sizeof(T) bytes written.
 #include <stdlib.h>
 
+#include <stdlib.h>
+#include <string.h>
+
 #include "ot_common.cuh"
 
 namespace otb {
@@ -173,6 +176,130 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
   if (threadIdx.x == 0) trace_end(status, kStageLogprob);
 }
 
+// ---------------------------------------------------------------------------
+// The same stage with the rows staged through shared memory by bulk copies, for
+// the common shape: float rows of 64 < V/4 <= 128 vectors (V = 260..512,
+// V % 4 == 0), standard transducer.  A block walks over kTmaTiles consecutive
+// tiles of 16 rows; thread 0 keeps kTmaStages tiles (16 * V * 4 bytes each,
+// one contiguous piece of the packed buffer) in flight with cp.async.bulk +
+// mbarrier, the 16 lane groups of the block each reduce one row of the tile out
+// of shared memory.  What this buys: the bytes in flight no longer depend on
+// the registers a warp can hold (two blocks x 3 stages x 32 KB per SM instead
+// of 32 warps x 4 KB, and none while a warp computes), so the loads and the
+// exp-sum overlap fully.
+constexpr int kTmaRows = 16;     // rows per tile = lane groups per block
+constexpr int kTmaStages = 3;
+constexpr int kTmaTiles = 16;    // tiles per block
+constexpr int kStatusCopyTimeout = 2;  // status word: a bulk copy never arrived
+
+__global__ void __launch_bounds__(kThreads, 2)
+logprob_tma_kernel(const float *__restrict__ logits, const int32_t *__restrict__ targets,
+                   const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
+                   const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
+                   int32_t *__restrict__ status, int N, int64_t rows, int V, int max_u,
+                   int blank, float *__restrict__ den, float *__restrict__ lp) {
+  extern __shared__ __align__(128) unsigned char tile_mem[];
+  __shared__ __align__(8) uint64_t full_bar[kTmaStages];
+  pdl_wait();
+  pdl_trigger();
+  if (status[kStatusCode] != 0) return;
+  if (threadIdx.x == 0) trace_begin(status, kStageLogprob);
+  constexpr int LPR = 16, CH = 8;
+  const int lane = threadIdx.x & 31, gl = lane & (LPR - 1);
+  const int g = threadIdx.x / LPR;  // lane group = row within the tile
+  const unsigned gmask = ((1u << LPR) - 1u) << (lane - gl);
+  const int nvec = V >> 2;
+  const float ninf = neg_inf<float>();
+  const uint32_t row_bytes = (uint32_t)V * 4u;
+  const uint32_t tile_bytes = kTmaRows * row_bytes;
+  const int64_t ntiles_all = (rows + kTmaRows - 1) / kTmaRows;
+  const int64_t tile0 = (int64_t)blockIdx.x * kTmaTiles;
+  const int ntiles = (int)((ntiles_all - tile0 < kTmaTiles) ? (ntiles_all - tile0) : kTmaTiles);
+  if (ntiles <= 0) return;
+
+  auto issue = [&](int k) {  // thread 0 only
+    const int64_t r0 = (tile0 + k) * kTmaRows;
+    const int64_t nr = (rows - r0 < kTmaRows) ? (rows - r0) : kTmaRows;
+    uint64_t *bar = &full_bar[k % kTmaStages];
+    const uint32_t bytes = (uint32_t)nr * row_bytes;  // a multiple of 16: V % 4 == 0
+    mbar_expect_tx(bar, bytes);
+    tma_load_1d(tile_mem + (size_t)(k % kTmaStages) * tile_bytes, logits + r0 * (int64_t)V, bytes, bar);
+  };
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kTmaStages; ++i) mbar_init(&full_bar[i], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    for (int k = 0; k < kTmaStages && k < ntiles; ++k) issue(k);
+  }
+  __syncthreads();
+
+  // Position of this group's first row; it then advances by 16 rows per tile.
+  int64_t row = tile0 * kTmaRows + g;
+  int b = 0, Tn = 1, U = 0, U1 = 1, t = 0, u = 0;
+  int64_t next_split = 0, coff = 0;
+  auto locate = [&]() {
+    b = find_utt(split, N, row);
+    Tn = __ldg(Tl + b); U = __ldg(Ul + b); U1 = U + 1;
+    next_split = __ldg(split + b + 1);
+    coff = __ldg(cell_split + b);
+    const int idx = (int)(row - __ldg(split + b));
+    t = idx / U1; u = idx - t * U1;
+  };
+  if (row < rows) locate();
+  (void)Tn;
+
+  for (int k = 0; k < ntiles; ++k) {
+    uint64_t *bar = &full_bar[k % kTmaStages];
+    const uint32_t parity = (uint32_t)((k / kTmaStages) & 1);
+    // index of the symbol entry, fetched while the tile is still on its way
+    const int tsym = (gl == 0 && row < rows && u < U) ? __ldg(targets + (int64_t)b * max_u + u) : -1;
+    bool arrived = false;
+    for (int spin = 0; spin < (1 << 22); ++spin)  // bounded: report and carry on
+      if (mbar_try_wait(bar, parity)) { arrived = true; break; }
+    if (!arrived) atomicCAS(status + kStatusCopyTimeout, 0, 1);
+    if (row < rows) {
+      const float *p = reinterpret_cast<const float *>(tile_mem + (size_t)(k % kTmaStages) * tile_bytes) + (size_t)g * V;
+      float x[CH * 4];
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int vi = j * LPR + gl;
+        if (vi < nvec) {
+          const float4 v = *reinterpret_cast<const float4 *>(p + vi * 4);
+          x[j * 4 + 0] = v.x; x[j * 4 + 1] = v.y; x[j * 4 + 2] = v.z; x[j * 4 + 3] = v.w;
+        } else {
+          x[j * 4 + 0] = ninf; x[j * 4 + 1] = ninf; x[j * 4 + 2] = ninf; x[j * 4 + 3] = ninf;
+        }
+      }
+      float m = x[0];
+#pragma unroll
+      for (int i = 1; i < CH * 4; ++i) m = fmaxf(m, x[i]);
+      m = group_max<float, LPR>(m, gmask);
+      float s = 0;
+      if (m - m == 0.0f) s = add_exps(x, m, s);  // an infinite maximum needs no sum
+      const float d = (m - m == 0.0f) ? logf(group_sum<float, LPR>(s, gmask)) + m : m;
+      if (gl == 0) {
+        const float gb = p[blank] - d;
+        const float gs = (tsym >= 0) ? p[tsym] - d : ninf;
+        den[row] = d;
+        *reinterpret_cast<float2 *>(lp + 2 * (coff + cell_pos<false>(t, u, U1))) = make_float2(gb, gs);
+      }
+    }
+    __syncthreads();  // every group is done with this stage
+    if (threadIdx.x == 0 && k + kTmaStages < ntiles) issue(k + kTmaStages);
+    // advance by one tile
+    row += kTmaRows;
+    if (row < rows) {
+      if (row >= next_split) {
+        locate();
+      } else {
+        u += kTmaRows;
+        while (u >= U1) { u -= U1; ++t; }
+      }
+    }
+  }
+  if (threadIdx.x == 0) trace_end(status, kStageLogprob);
+}
+
 // Log-softmax input: nothing to reduce, only the gather (thread per row).
 template <typename X, bool MODIFIED>
 __global__ void __launch_bounds__(kThreads)
@@ -230,6 +357,16 @@ cudaError_t launch_lse(const Problem &p, cudaStream_t s) {
                                                : launch_lse_m<X, VEC, CH, LPR, false>(p, s);
 }
 
+// OT_B200_LOGPROB=plain keeps the register-staged kernel for every shape.
+bool plain_loads_forced() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char *e = getenv("OT_B200_LOGPROB");
+    cached = (e && strcmp(e, "plain") == 0) ? 1 : 0;
+  }
+  return cached == 1;
+}
+
 template <typename X>
 cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
   using T = typename Real<X>::type;
@@ -251,6 +388,31 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
   constexpr int VEC = Vec16<X>::n;
   const bool vec_ok = (p.V % VEC == 0) &&
                       (reinterpret_cast<uintptr_t>(p.logits) % (VEC * sizeof(X)) == 0);
+  if constexpr (sizeof(X) == 4) {
+    const int nv = p.V / 4;
+    if (vec_ok && nv > 64 && nv <= 128 && !(p.flags & OT_B200_ONE_SYM_PER_FRAME) && !plain_loads_forced()) {
+      const size_t smem = (size_t)kTmaStages * kTmaRows * p.V * 4;
+      static bool opted[64] = {false};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev < 0 || dev >= 64) dev = 0;
+      if (!opted[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(logprob_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   kTmaStages * kTmaRows * 512 * 4);
+        if (e != cudaSuccess) return e;
+        opted[dev] = true;
+      }
+      const int64_t ntiles = (p.rows + kTmaRows - 1) / kTmaRows;
+      const unsigned grid = (unsigned)((ntiles + kTmaTiles - 1) / kTmaTiles);
+      const cudaError_t e = launch_pdl(logprob_tma_kernel, grid, (unsigned)kThreads, smem, s,
+          static_cast<const float *>(p.logits), p.targets, p.T, p.U,
+          reinterpret_cast<const int64_t *>(p.ws + p.lay.split),
+          reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
+          reinterpret_cast<int32_t *>(p.ws + p.lay.status), p.N, p.rows, p.V, p.max_u, p.blank,
+          reinterpret_cast<float *>(p.ws + p.lay.den), reinterpret_cast<float *>(p.ws + p.lay.lp));
+      return e != cudaSuccess ? e : cudaGetLastError();
+    }
+  }
   if (vec_ok) {
     const int nvec = p.V / VEC;  // vector loads per row
     // Up to 8 loads per lane: pick the narrowest group that covers the row in
