@@ -344,4 +344,14 @@ __device__ __forceinline__ int find_utt(const int64_t *__restrict__ split, int N
   return lo;
 }
 
+// The same search with ordinary loads, for a table in shared memory.
+__device__ __forceinline__ int find_utt_plain(const int64_t *split, int N, int64_t row) {
+  int lo = 0, hi = N;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (split[mid] <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
 }  // namespace otb

@@ -182,21 +182,30 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
     if (threadIdx.x == 0) *loss_out = (T)(-acc * loss_scale);
   }
   const int64_t cell = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  // A block's 256 cells nearly always belong to one utterance: two threads
-  // search for the block's first and last cell, the others only search between.
-  __shared__ int b_range[2];
-  const int64_t total_cells = __ldg(cell_split + N);
-  if (threadIdx.x == 0 || threadIdx.x == kWarp) {
-    int64_t probe = (int64_t)blockIdx.x * blockDim.x + (threadIdx.x ? blockDim.x - 1 : 0);
-    if (probe >= total_cells) probe = total_cells - 1;
-    b_range[threadIdx.x ? 1 : 0] = (probe >= 0) ? find_utt(cell_split, N, probe) : 0;
+  // The chain of dependent loads decides this kernel's time (thousands of small
+  // blocks, each a few L2 round trips long), so it is kept at three: (1) the
+  // per-utterance tables of the whole batch into shared memory, one coalesced
+  // pass; (2) every per-cell value the record can need, all requested at once;
+  // (3) the store.  Batches of more than kMetaMax utterances read the tables
+  // from global memory instead.
+  constexpr int kMetaMax = 512;
+  __shared__ int64_t s_csplit[kMetaMax + 1];
+  __shared__ int64_t s_split[kMetaMax];
+  __shared__ int32_t s_T[kMetaMax], s_U[kMetaMax];
+  const bool meta = N <= kMetaMax;
+  if (meta) {
+    for (int i = threadIdx.x; i <= N; i += blockDim.x) {
+      s_csplit[i] = __ldg(cell_split + i);
+      if (i < N) { s_split[i] = __ldg(split + i); s_T[i] = __ldg(Tl + i); s_U[i] = __ldg(Ul + i); }
+    }
+    __syncthreads();
   }
-  __syncthreads();
+  const int64_t *cs = meta ? s_csplit : cell_split;
+  const int64_t total_cells = cs[N];
   if (cell >= total_cells) return;
-  int b = b_range[0];
-  while (b < b_range[1] && __ldg(cell_split + b + 1) <= cell) ++b;
-  const int64_t coff = __ldg(cell_split + b);
-  const int Tn = __ldg(Tl + b), U = __ldg(Ul + b), U1 = U + 1;
+  const int b = meta ? find_utt_plain(s_csplit, N, cell) : find_utt(cell_split, N, cell);
+  const int64_t coff = cs[b];
+  const int Tn = meta ? s_T[b] : __ldg(Tl + b), U = meta ? s_U[b] : __ldg(Ul + b), U1 = U + 1;
   const int64_t p = cell - coff;
   int t, u;
   if (MODIFIED) {
@@ -208,31 +217,39 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
     t = d - u;
     if (t < 0 || t >= Tn) return;  // no lattice cell is stored here
   }
-  const int64_t row = __ldg(split + b) + (int64_t)t * U1 + u;
+  const int64_t row = (meta ? s_split[b] : __ldg(split + b)) + (int64_t)t * U1 + u;
   const int diff = Tn - 1 - U;
+  const bool off_band = MODIFIED && (u > t || t - u > diff);
+  const bool last = (t == Tn - 1 && u == U);
+  const bool blank_ok = MODIFIED ? (t - u < diff) : (t < Tn - 1);
+  // successors: blank -> (t+1,u), symbol -> (t,u+1) or (t+1,u+1) if modified;
+  // in both storage orders they sit U1 and U1+1 entries further.  Which of them
+  // exist depends on (t, u) alone, so all loads go out together.
+  const bool live = !off_band;
   const T L = beta[coff];  // beta(0,0) is the first entry in both layouts
+  const T a_here = live ? alpha[cell] : (T)0;
+  const T b_here_v = live ? beta[cell] : (T)0;
+  const T den_v = (live && !MODE_B) ? den[row] : (T)0;
+  const int target_u = (live && u < U) ? __ldg(targets + (int64_t)b * max_u + u) : -1;
+  const T b_sym_next = (live && u < U) ? beta[cell + U1 + 1] : neg_inf<T>();
+  const T b_blank_next = (live && !last && blank_ok) ? beta[cell + U1] : neg_inf<T>();
+  T lp_b = 0, lp_s = 0;
+  if (MODE_B && live) { lp_b = lp[2 * cell]; lp_s = lp[2 * cell + 1]; }
 
-  bool zero = !(L - L == (T)0);  // inf or nan
-  if (MODIFIED && (u > t || t - u > diff)) zero = true;
+  const bool zero = off_band || !(L - L == (T)0);  // off the band, or an infinite / NaN likelihood
 
   T c = 0, b_here = 0, sub_blank = neg_inf<T>(), sub_sym = neg_inf<T>();
   int32_t tgt = kTgtNone;
   bool blank_term = false, sym_term = false;
   if (!zero) {
     const T loss = -L;
-    c = alpha[cell] + loss;
-    if (!MODE_B) c = c - den[row];
-    b_here = beta[cell];
-    const bool last = (t == Tn - 1 && u == U);
-    const bool blank_ok = MODIFIED ? (t - u < diff) : (t < Tn - 1);
-    const int target_u = (u < U) ? __ldg(targets + (int64_t)b * max_u + u) : -1;
-    // successors: blank -> (t+1,u), symbol -> (t,u+1) or (t+1,u+1) if modified;
-    // in both storage orders they sit U1 and U1+1 entries further.
-    const T b_sym_next = (u < U) ? beta[cell + U1 + 1] : neg_inf<T>();
+    c = a_here + loss;
+    if (!MODE_B) c = c - den_v;
+    b_here = b_here_v;
     if (last) {
       sub_blank = 0; blank_term = true;
     } else if (blank_ok) {
-      sub_blank = beta[cell + U1]; blank_term = true;
+      sub_blank = b_blank_next; blank_term = true;
     } else if (u < U && target_u == blank) {
       sub_blank = b_sym_next; blank_term = true;
     }
@@ -242,8 +259,8 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
   }
   if (MODE_B) {
     CoefB<T> r;
-    r.val_blank = blank_term ? -r_exp((lp[2 * cell] + c) + sub_blank) : (T)0;
-    r.val_sym = sym_term ? -r_exp((lp[2 * cell + 1] + c) + sub_sym) : (T)0;
+    r.val_blank = blank_term ? -r_exp((lp_b + c) + sub_blank) : (T)0;
+    r.val_sym = sym_term ? -r_exp((lp_s + c) + sub_sym) : (T)0;
     r.tgt = zero ? kTgtZeroRow : tgt;
     r.utt = b;
     reinterpret_cast<CoefB<T> *>(coef_out)[row] = r;
