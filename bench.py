@@ -34,7 +34,7 @@ if ROOT not in sys.path:
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one full-size cfg2 launch of the
 # gradient kernel, from the one-pass ncu capture summarised in profiles/gradient_kernel_cfg2.md.
-CFG2_GRADIENT_TRAFFIC_BYTES = 2705.3e6
+CFG2_GRADIENT_TRAFFIC_BYTES = 2706.0e6
 CFG2_ROWS = 686128
 
 METRIC = "fwd+bwd loss lattice cells (sum T*(U+1)*V)/s"
@@ -55,7 +55,7 @@ class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU through NVML (read-only)
     while the timed region runs."""
 
-    def __init__(self, index, uuid=None, period=0.004):
+    def __init__(self, index, uuid=None, period=0.001):
         self.index, self.period = index, period
         self.samples, self.reasons = [], set()
         self.max_mhz = None
