@@ -18,11 +18,12 @@
 // (division by N for reduction="mean", multiplication by the upstream
 // gradient; transducer_loss.py:150,162) into this pass.
 //
-// One warp owns a row at a time; rows are visited from the END of the buffer
+// Mode A: one warp per row, one short-lived block per 8 rows (OT_B200_GRID=wave:
+// one resident wave that strides); rows are visited from the END of the buffer
 // towards its start: the rows stage 1 read last are the ones still resident in
-// L2.  HBM traffic per row: V*sizeof(T) read + V*sizeof(T) written (mode A),
-// V*sizeof(T) written (mode B), plus one 32-byte (16-byte) coefficient record.
-#include <stdlib.h>
+// L2.  Mode B is written as one front of 2 KB chunks.  HBM traffic per row:
+// V*sizeof(X) read + V*sizeof(X) written (mode A), V*sizeof(X) written (mode B),
+// plus one 32-byte (16-byte) coefficient record.
 
 #include "ot_common.cuh"
 

@@ -16,12 +16,14 @@
 //  * a group takes runs of kRun consecutive rows and walks (b, t, u)
 //    incrementally inside a run, so the owning utterance is searched once per
 //    run, not once per row.
-// The grid is exactly one resident wave (SMs x blocks that fit per SM).  Runs
-// are dealt round-robin, so the grid sweeps the buffer front to back and the
-// rows read last are contiguous at the end, where stage 3 starts.  A row is
-// read once with 16-byte coalesced loads, all issued before the first use; the
-// two gathered entries are re-read from the lines just fetched.  HBM traffic
-// per row: V*sizeof(T) bytes read, 3*sizeof(T) bytes written.
+// One short-lived block per 128 or 256 rows (a lane group takes one run), or one
+// resident wave with OT_B200_GRID=wave.  Runs are dealt in order, so the grid
+// sweeps the buffer front to back and the rows read last are contiguous at the
+// end, where stage 3 starts.  A row is read once with 16-byte coalesced loads,
+// all issued before the first use; the two gathered entries are requested with
+// them and fall into the lines just fetched.  HBM traffic per row:
+// V*sizeof(X) bytes read, 3*sizeof(T) bytes written.  Float rows of 260..512
+// columns take the bulk-copy staged variant further down.
 #include <stdlib.h>
 
 #include <stdlib.h>
