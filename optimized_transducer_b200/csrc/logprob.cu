@@ -194,8 +194,9 @@ constexpr int kTmaStages = 3;
 constexpr int kTmaTiles = 16;    // tiles per block
 constexpr int kStatusCopyTimeout = 2;  // status word: a bulk copy never arrived
 
+template <typename X>
 __global__ void __launch_bounds__(kThreads, 2)
-logprob_tma_kernel(const float *__restrict__ logits, const int32_t *__restrict__ targets,
+logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets,
                    const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
                    const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
                    int32_t *__restrict__ status, int N, int64_t rows, int V, int max_u,
@@ -210,9 +211,10 @@ logprob_tma_kernel(const float *__restrict__ logits, const int32_t *__restrict__
   const int lane = threadIdx.x & 31, gl = lane & (LPR - 1);
   const int g = threadIdx.x / LPR;  // lane group = row within the tile
   const unsigned gmask = ((1u << LPR) - 1u) << (lane - gl);
+  using VT = typename VecOf<X, 4>::type;  // 4 elements: 16 bytes of float, 8 bytes of a 16-bit type
   const int nvec = V >> 2;
   const float ninf = neg_inf<float>();
-  const uint32_t row_bytes = (uint32_t)V * 4u;
+  const uint32_t row_bytes = (uint32_t)V * (uint32_t)sizeof(X);
   const uint32_t tile_bytes = kTmaRows * row_bytes;
   const int64_t ntiles_all = (rows + kTmaRows - 1) / kTmaRows;
   const int64_t tile0 = (int64_t)blockIdx.x * kTmaTiles;
@@ -223,7 +225,9 @@ logprob_tma_kernel(const float *__restrict__ logits, const int32_t *__restrict__
     const int64_t r0 = (tile0 + k) * kTmaRows;
     const int64_t nr = (rows - r0 < kTmaRows) ? (rows - r0) : kTmaRows;
     uint64_t *bar = &full_bar[k % kTmaStages];
-    const uint32_t bytes = (uint32_t)nr * row_bytes;  // a multiple of 16: V % 4 == 0
+    // a multiple of 16: V % 4 == 0, and for 16-bit rows the launcher requires an
+    // even row count, so every tile and the tail are whole pairs of rows
+    const uint32_t bytes = (uint32_t)nr * row_bytes;
     mbar_expect_tx(bar, bytes);
     tma_load_1d(tile_mem + (size_t)(k % kTmaStages) * tile_bytes, logits + r0 * (int64_t)V, bytes, bar);
   };
@@ -260,14 +264,16 @@ logprob_tma_kernel(const float *__restrict__ logits, const int32_t *__restrict__
       if (mbar_try_wait(bar, parity)) { arrived = true; break; }
     if (!arrived) atomicCAS(status + kStatusCopyTimeout, 0, 1);
     if (row < rows) {
-      const float *p = reinterpret_cast<const float *>(tile_mem + (size_t)(k % kTmaStages) * tile_bytes) + (size_t)g * V;
+      const X *p = reinterpret_cast<const X *>(tile_mem + (size_t)(k % kTmaStages) * tile_bytes) + (size_t)g * V;
       float x[CH * 4];
 #pragma unroll
       for (int j = 0; j < CH; ++j) {
         const int vi = j * LPR + gl;
         if (vi < nvec) {
-          const float4 v = *reinterpret_cast<const float4 *>(p + vi * 4);
-          x[j * 4 + 0] = v.x; x[j * 4 + 1] = v.y; x[j * 4 + 2] = v.z; x[j * 4 + 3] = v.w;
+          const VT v = *reinterpret_cast<const VT *>(p + vi * 4);
+          const X *e = reinterpret_cast<const X *>(&v);
+          x[j * 4 + 0] = to_real(e[0]); x[j * 4 + 1] = to_real(e[1]);
+          x[j * 4 + 2] = to_real(e[2]); x[j * 4 + 3] = to_real(e[3]);
         } else {
           x[j * 4 + 0] = ninf; x[j * 4 + 1] = ninf; x[j * 4 + 2] = ninf; x[j * 4 + 3] = ninf;
         }
@@ -280,8 +286,8 @@ logprob_tma_kernel(const float *__restrict__ logits, const int32_t *__restrict__
       if (m - m == 0.0f) s = add_exps(x, m, s);  // an infinite maximum needs no sum
       const float d = (m - m == 0.0f) ? logf(group_sum<float, LPR>(s, gmask)) + m : m;
       if (gl == 0) {
-        const float gb = p[blank] - d;
-        const float gs = (tsym >= 0) ? p[tsym] - d : ninf;
+        const float gb = to_real(p[blank]) - d;
+        const float gs = (tsym >= 0) ? to_real(p[tsym]) - d : ninf;
         den[row] = d;
         *reinterpret_cast<float2 *>(lp + 2 * (coff + cell_pos<false>(t, u, U1))) = make_float2(gb, gs);
       }
@@ -360,13 +366,9 @@ cudaError_t launch_lse(const Problem &p, cudaStream_t s) {
 }
 
 // OT_B200_LOGPROB=plain keeps the register-staged kernel for every shape.
-bool plain_loads_forced() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char *e = getenv("OT_B200_LOGPROB");
-    cached = (e && strcmp(e, "plain") == 0) ? 1 : 0;
-  }
-  return cached == 1;
+bool plain_loads_forced() {  // read on every call, so that a test can compare the two kernels
+  const char *e = getenv("OT_B200_LOGPROB");
+  return e && strcmp(e, "plain") == 0;
 }
 
 template <typename X>
@@ -390,24 +392,27 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
   constexpr int VEC = Vec16<X>::n;
   const bool vec_ok = (p.V % VEC == 0) &&
                       (reinterpret_cast<uintptr_t>(p.logits) % (VEC * sizeof(X)) == 0);
-  if constexpr (sizeof(X) == 4) {
+  if constexpr (sizeof(X) <= 4) {
     const int nv = p.V / 4;
-    if (vec_ok && nv > 64 && nv <= 128 && !(p.flags & OT_B200_ONE_SYM_PER_FRAME) && !plain_loads_forced()) {
-      const size_t smem = (size_t)kTmaStages * kTmaRows * p.V * 4;
+    // 16-bit rows: a tile is a multiple of 16 bytes only for whole pairs of rows,
+    // so the row count must be even (the last tile then ends on a pair as well)
+    const bool tiles_ok = sizeof(X) == 4 || (p.rows % 2 == 0 && reinterpret_cast<uintptr_t>(p.logits) % 16 == 0);
+    if (vec_ok && tiles_ok && nv > 64 && nv <= 128 && !(p.flags & OT_B200_ONE_SYM_PER_FRAME) && !plain_loads_forced()) {
+      const size_t smem = (size_t)kTmaStages * kTmaRows * p.V * sizeof(X);
       static bool opted[64] = {false};
       int dev = 0;
       cudaGetDevice(&dev);
       if (dev < 0 || dev >= 64) dev = 0;
       if (!opted[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(logprob_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   kTmaStages * kTmaRows * 512 * 4);
+        const cudaError_t e = cudaFuncSetAttribute(logprob_tma_kernel<X>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   kTmaStages * kTmaRows * 512 * (int)sizeof(X));
         if (e != cudaSuccess) return e;
         opted[dev] = true;
       }
       const int64_t ntiles = (p.rows + kTmaRows - 1) / kTmaRows;
       const unsigned grid = (unsigned)((ntiles + kTmaTiles - 1) / kTmaTiles);
-      const cudaError_t e = launch_pdl(logprob_tma_kernel, grid, (unsigned)kThreads, smem, s,
-          static_cast<const float *>(p.logits), p.targets, p.T, p.U,
+      const cudaError_t e = launch_pdl(logprob_tma_kernel<X>, grid, (unsigned)kThreads, smem, s,
+          static_cast<const X *>(p.logits), p.targets, p.T, p.U,
           reinterpret_cast<const int64_t *>(p.ws + p.lay.split),
           reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
           reinterpret_cast<int32_t *>(p.ws + p.lay.status), p.N, p.rows, p.V, p.max_u, p.blank,

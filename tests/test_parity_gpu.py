@@ -239,6 +239,37 @@ def test_sixteen_bit_logits_float32_math(vocab, dtype, from_ls, modified):
     assert np.all(err <= rel * np.abs(ref["grad"]) + 2e-5), float(err.max())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
+def test_bulk_copy_staged_logprob_kernel_equals_the_register_staged_one(dtype, monkeypatch):
+    """Rows of 260..512 columns reach the log-prob stage through shared memory
+    (16-row tiles fetched by bulk copies); OT_B200_LOGPROB=plain forces the
+    kernel that loads into registers.  Same arithmetic in the same order: the
+    outputs are bitwise equal, and both agree with the oracle.  33 tiles and a
+    ragged tail, utterance boundaries inside tiles; the row count is even, which
+    the 16-bit variant needs."""
+    tdt = getattr(torch, dtype)
+    T = np.array([37, 5, 64, 1, 29], np.int32)
+    U = np.array([3, 9, 2, 7, 1], np.int32)
+    rows = int((T.astype(np.int64) * (U + 1)).sum())
+    assert rows % 2 == 0 and rows > 16 * 16
+    rng = np.random.default_rng(46)
+    x = torch.from_numpy((rng.standard_normal((rows, 500)) * 2).astype(np.float32)).to(tdt).to(DEV)
+    tg = torch.from_numpy(rng.integers(1, 500, (5, 9)).astype(np.int32)).to(DEV)
+    dT, dU = torch.from_numpy(T).to(DEV), torch.from_numpy(U).to(DEV)
+    got = {}
+    for mode in ("tma", "plain"):
+        monkeypatch.setenv("OT_B200_LOGPROB", mode)
+        got[mode] = ot.stage_outputs(x, tg, dT, dU, 0, False, False)
+    for k in ("den", "lp", "scores"):
+        assert torch.equal(got["tma"][k], got["plain"][k]), k
+    st = got["tma"]
+    ref = O.oracle_loss(x.to(torch.float64).cpu().numpy(), tg.cpu().numpy(), T, U, 0)
+    assert np.max(np.abs(st["den"].double().cpu().numpy() - ref["den"]) / np.maximum(1, np.abs(ref["den"]))) <= 1e-6
+    ok = ~np.isnan(ref["lp"])
+    assert np.max(np.abs(st["lp"].double().cpu().numpy()[ok] - ref["lp"][ok])) <= 2e-5
+    assert np.max(np.abs(st["scores"].double().cpu().numpy() - ref["scores"]) / np.abs(ref["scores"])) <= 1e-5
+
+
 def test_module_form_and_no_grad():
     x, tg, T, U = random_batch(42, 3, (5, 9), (2, 4), 6)
     dx, dt, dT, dU = to_dev(x, tg, T, U)
