@@ -203,10 +203,12 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
                    int blank, float *__restrict__ den, float *__restrict__ lp) {
   extern __shared__ __align__(128) unsigned char tile_mem[];
   __shared__ __align__(8) uint64_t full_bar[kTmaStages];
-  pdl_wait();
+  // The first tiles are requested BEFORE this grid waits for stage 0: they only
+  // read the logits, which whoever ran before stage 0 has finished writing
+  // (stage 0 releases this grid after its own wait), and which are valid memory
+  // whatever the lengths turn out to be.  Stage 0's few microseconds then run
+  // under the first loads.
   pdl_trigger();
-  if (status[kStatusCode] != 0) return;
-  if (threadIdx.x == 0) trace_begin(status, kStageLogprob);
   constexpr int LPR = 16, CH = 8;
   const int lane = threadIdx.x & 31, gl = lane & (LPR - 1);
   const int g = threadIdx.x / LPR;  // lane group = row within the tile
@@ -219,7 +221,7 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
   const int64_t ntiles_all = (rows + kTmaRows - 1) / kTmaRows;
   const int64_t tile0 = (int64_t)blockIdx.x * kTmaTiles;
   const int ntiles = (int)((ntiles_all - tile0 < kTmaTiles) ? (ntiles_all - tile0) : kTmaTiles);
-  if (ntiles <= 0) return;
+  if (ntiles <= 0) return;  // cannot happen with the launcher's grid
 
   auto issue = [&](int k) {  // thread 0 only
     const int64_t r0 = (tile0 + k) * kTmaRows;
@@ -238,6 +240,18 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
     for (int k = 0; k < kTmaStages && k < ntiles; ++k) issue(k);
   }
   __syncthreads();
+  pdl_wait();  // from here on: status, splits and the -inf fill of stage 0 are visible
+  if (status[kStatusCode] != 0) {
+    // bad input: nothing is computed, but the copies in flight must land before
+    // the block gives its shared memory back (bounded wait, like every other)
+    if (threadIdx.x == 0)
+      for (int k = 0; k < kTmaStages && k < ntiles; ++k)
+        for (int spin = 0; spin < (1 << 22); ++spin)
+          if (mbar_try_wait(&full_bar[k], 0)) break;
+    __syncthreads();
+    return;
+  }
+  if (threadIdx.x == 0) trace_begin(status, kStageLogprob);
 
   // Position of this group's first row; it then advances by 16 rows per tile.
   int64_t row = tile0 * kTmaRows + g;
