@@ -168,18 +168,22 @@ gradient_logsoftmax_kernel(X *__restrict__ g, const CoefB<typename Real<X>::type
       int vi = col0 + j * kWarp + lane;
       while (vi >= nvec) { vi -= nvec; ++row; }
       const CoefB<T> rec = coef[row];  // 16 bytes shared by a whole row: L1 hits
-      const T scale = PER_UTT ? scale_host * __ldg(d_scale + rec.utt) : scale_all;
       const bool zero = rec.tgt == kTgtZeroRow;
       const int tvec = (!zero && rec.tgt >= 0) ? rec.tgt / VEC : -1;
-      const int tk = rec.tgt >= 0 ? rec.tgt % VEC : 0;
       VT z;
       X *ze = reinterpret_cast<X *>(&z);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        T val = 0;
-        if (!zero && vi == bvec && k == bk) val = rec.val_blank * scale;
-        else if (vi == tvec && k == tk) val = rec.val_sym * scale;
-        ze[k] = from_real<X>(val);
+      for (int k = 0; k < VEC; ++k) ze[k] = from_real<X>((T)0);
+      if ((vi == bvec && !zero) || vi == tvec) {  // at most two vectors of a row are not all zero
+        const T scale = PER_UTT ? scale_host * __ldg(d_scale + rec.utt) : scale_all;
+        const int tk = rec.tgt >= 0 ? rec.tgt % VEC : 0;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          T val = 0;
+          if (!zero && vi == bvec && k == bk) val = rec.val_blank * scale;
+          else if (vi == tvec && k == tk) val = rec.val_sym * scale;
+          ze[k] = from_real<X>(val);
+        }
       }
       *reinterpret_cast<VT *>(g + g_index * VEC) = z;
     }
