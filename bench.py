@@ -441,7 +441,9 @@ def run_ours(args, w):
             "e2e": None if not e2e_steps else {"value": cells_total / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": bytes_logits + 4 * (T.numel() + U.numel() + tg.numel()),
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
-            "gpu_launches": 5 * args.steps,
+            # own kernels per step and rank: prepare, logprob, lattice, coef, gradient
+            # (+ publish and gather of the peer-memory exchange)
+            "gpu_launches": (5 + (2 if exchange is not None else 0)) * args.steps,
             "roofline": {
                 "kernel": "gradient_logsoftmax_kernel" if mode_b else "gradient_kernel",
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
