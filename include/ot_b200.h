@@ -74,10 +74,12 @@ typedef enum ot_b200_input_error {
                                          block started and its last block ended
                                          (%globaltimer, ns) as uint64 pairs from byte 64
                                          of the status segment on                   */
-#define OT_B200_SHARE_SMS 64u          /* size the one-wave grids of the streaming
-                                         kernels one SM short: for callers that keep
-                                         another kernel resident beside this path (a
-                                         collective on a second stream)             */
+#define OT_B200_SHARE_SMS 64u          /* where a streaming kernel runs as one resident
+                                         wave of blocks (OT_B200_GRID=wave; the 16-bit
+                                         gradient pass), size that wave one SM short:
+                                         for callers that keep another kernel resident
+                                         beside this path (a collective on a second
+                                         stream)                                    */
 #define OT_B200_SCALE_PER_UTTERANCE 32u /* ot_b200_backward only: d_scale holds one
                                          factor per utterance (no counterpart in the
                                          reference, which only reduces)             */
