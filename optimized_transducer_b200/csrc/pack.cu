@@ -13,9 +13,11 @@
 //   unpack_copy   padded[b,t,u]    = in[row(b,t,u)], 0 elsewhere    (packed -> padded)
 //   sum_over_u    genc[b,t] = sum_u g[row(b,t,u)],  0 for t >= T_b  (backward of pack_add)
 //   sum_over_t    gdec[b,u] = sum_t g[row(b,t,u)],  0 for u >  U_b
-// One warp owns a packed row (16-byte loads when D % 4 == 0 and the bases are
-// aligned); a warp takes runs of 8 rows and walks (b, t, u) incrementally.  All
-// of them are HBM-bound: rows * D * sizeof(T) bytes written or read once.
+// The copies give one warp a packed row (16-byte loads when D % 4 == 0 and the
+// bases are aligned); a warp takes runs of 8 rows and walks (b, t, u)
+// incrementally.  pack_add writes by frames and the sums read rows a fixed stride
+// apart (see the kernels).  All of them are HBM-bound: rows * D * sizeof(T) bytes
+// written or read once.
 #include "ot_common.cuh"
 
 namespace otb {
@@ -155,38 +157,155 @@ pack_rows_kernel(const T *__restrict__ a, const T *__restrict__ bsrc, T *__restr
   }
 }
 
+constexpr int kAddCh = 4;       // decoder vectors a thread keeps in registers
+constexpr int kAddFrames = 16;  // frames one block writes
+
+// The joiner input by frames.  The packed rows of one frame (b, t) are one
+// contiguous piece of (U_b+1)*D elements, and that piece is the utterance's
+// decoder block dec[b, 0..U_b, :] (contiguous too) plus enc[b, t, :] repeated.  A
+// block takes 256*kAddCh consecutive vectors of the decoder block into registers
+// once and writes them out for kAddFrames frames; per stored vector it loads one
+// vector of the frame's 2 KB encoder row, which the first warp brings into L1.
+// The L2 then delivers a small fraction of the bytes the pass writes, where the
+// row-by-row kernel asks it for one decoder vector per stored vector.
+// Grid: x = chunk of the decoder block + chunks_max * group of frames, y =
+// utterance; blocks past their utterance's own extent leave at once.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kThreads)
+pack_add_frames_kernel(const T *__restrict__ enc, const T *__restrict__ dec, T *__restrict__ out,
+                       const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
+                       const int64_t *__restrict__ split, const int32_t *__restrict__ status,
+                       int N, int D, int max_t, int max_u1, int chunks_max) {
+  if (status[0] != 0) return;
+  using VT = typename VecOf<T, VEC>::type;
+  const int nvec = D / VEC;
+  const int chunk = (int)(blockIdx.x % (unsigned)chunks_max);
+  const int t0 = (int)(blockIdx.x / (unsigned)chunks_max) * kAddFrames;
+  const int64_t i0 = (int64_t)chunk * (kThreads * kAddCh) + threadIdx.x;
+  for (int b = blockIdx.y; b < N; b += gridDim.y) {
+    const int Tn = __ldg(Tl + b), U1 = __ldg(Ul + b) + 1;
+    const int64_t nvb = (int64_t)U1 * nvec;  // vectors in one frame's piece
+    if ((int64_t)chunk * (kThreads * kAddCh) >= nvb || t0 >= Tn) continue;
+    const int t1 = min(Tn, t0 + kAddFrames);
+    const VT *decv = reinterpret_cast<const VT *>(dec + (int64_t)b * max_u1 * D);
+    VT y[kAddCh];
+    int dv[kAddCh];
+    bool ok[kAddCh];
+#pragma unroll
+    for (int k = 0; k < kAddCh; ++k) {
+      const int64_t i = i0 + (int64_t)k * kThreads;
+      ok[k] = i < nvb;
+      dv[k] = ok[k] ? (int)(i % nvec) : 0;
+      if (ok[k]) y[k] = decv[i];
+    }
+    const VT *encv = reinterpret_cast<const VT *>(enc + ((int64_t)b * max_t + t0) * D);
+    VT *outv = reinterpret_cast<VT *>(out + (__ldg(split + b) + (int64_t)t0 * U1) * D) + i0;
+#pragma unroll 2
+    for (int t = t0; t < t1; ++t, encv += nvec, outv += nvb) {
+      VT x[kAddCh];
+#pragma unroll
+      for (int k = 0; k < kAddCh; ++k)
+        if (ok[k]) x[k] = encv[dv[k]];
+#pragma unroll
+      for (int k = 0; k < kAddCh; ++k) {
+        if (ok[k]) {
+          VT z;
+          const T *xe = reinterpret_cast<const T *>(&x[k]);
+          const T *ye = reinterpret_cast<const T *>(&y[k]);
+          T *ze = reinterpret_cast<T *>(&z);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) ze[e] = xe[e] + ye[e];
+          outv[(int64_t)k * kThreads] = z;
+        }
+      }
+    }
+  }
+}
+
+template <typename VT, typename T>
+__device__ __forceinline__ void vec_add(VT &acc, const VT &v) {
+  T *ae = reinterpret_cast<T *>(&acc);
+  const T *ve = reinterpret_cast<const T *>(&v);
+#pragma unroll
+  for (int e = 0; e < (int)(sizeof(VT) / sizeof(T)); ++e) ae[e] += ve[e];
+}
+
 // OVER_U: CTA (t, b): out[b,t,:] = sum_u g[row(b,t,u),:]   (zero for t >= T_b)
 // else  : CTA (u, b): out[b,u,:] = sum_t g[row(b,t,u),:]   (zero for u >  U_b)
-// The sums run in index order, so the result does not depend on timing.
-template <typename T, bool OVER_U>
+// Either way the CTA adds up n rows of D elements that lie `stride` apart.  With
+// nvec = D/VEC vectors per row, R = 256/nvec rows are read side by side (thread =
+// (row lane, vector)), eight rows deep per thread with all loads issued before the
+// first add; the R partial sums meet in shared memory in a fixed order, so the
+// result does not depend on timing.  Rows longer than 256 vectors: R = 1 and the
+// threads walk the row.
+template <typename T, int VEC, bool OVER_U>
 __global__ void __launch_bounds__(kThreads)
 pack_sum_kernel(const T *__restrict__ g, T *__restrict__ out, const int32_t *__restrict__ Tl,
                 const int32_t *__restrict__ Ul, const int64_t *__restrict__ split,
                 const int32_t *__restrict__ status, int D, int extent) {
   if (status[0] != 0) return;
+  using VT = typename VecOf<T, VEC>::type;
+  __shared__ VT part[kThreads];
+  constexpr int kDeep = 8;
+  const int tid = threadIdx.x;
   const int b = blockIdx.y, i = blockIdx.x;  // i: frame t (OVER_U) or column u
   const int Tn = Tl[b], U1 = Ul[b] + 1;
-  T *po = out + ((int64_t)b * extent + i) * D;
+  VT *po = reinterpret_cast<VT *>(out + ((int64_t)b * extent + i) * D);
   const bool live = OVER_U ? (i < Tn) : (i < U1);
-  const T *base = g + split[b] * (int64_t)D;
-  for (int d = threadIdx.x; d < D; d += kThreads) {
-    T acc = 0;
-    if (live) {
-      if (OVER_U) {
-        const T *p = base + ((int64_t)i * U1) * D + d;
-        for (int u = 0; u < U1; ++u) acc += p[(int64_t)u * D];
-      } else {
-        const T *p = base + (int64_t)i * D + d;
-        for (int t = 0; t < Tn; ++t) acc += p[(int64_t)t * U1 * D];
+  const int n = live ? (OVER_U ? U1 : Tn) : 0;
+  const int nvec = D / VEC;
+  // distance between consecutive rows of the sum, in vectors
+  const int64_t stride = OVER_U ? (int64_t)nvec : (int64_t)U1 * nvec;
+  const VT *base = reinterpret_cast<const VT *>(
+      g + (split[b] + (OVER_U ? (int64_t)i * U1 : (int64_t)i)) * D);
+  VT zero;
+  {
+    T *ze = reinterpret_cast<T *>(&zero);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) ze[e] = (T)0;
+  }
+  const int R = nvec <= kThreads ? kThreads / nvec : 1;
+  const int rl = nvec <= kThreads ? tid / nvec : 0;
+  const int64_t step = (int64_t)R * stride;
+  for (int dv = nvec <= kThreads ? tid - rl * nvec : tid; dv < nvec; dv += kThreads) {
+    VT acc = zero;
+    if (rl < R) {
+      const VT *p = base + (int64_t)rl * stride + dv;
+      int r = rl;
+      for (; r + (kDeep - 1) * R < n; r += kDeep * R, p += kDeep * step) {
+        VT v[kDeep];
+#pragma unroll
+        for (int j = 0; j < kDeep; ++j) v[j] = p[j * step];
+#pragma unroll
+        for (int j = 0; j < kDeep; ++j) vec_add<VT, T>(acc, v[j]);
+      }
+      for (; r < n; r += R, p += step) vec_add<VT, T>(acc, *p);
+    }
+    if (R == 1) {
+      if (rl < R) po[dv] = acc;  // nvec in (128, 256]: the threads past the row idle
+    } else {
+      if (rl < R) part[tid] = acc;
+      __syncthreads();
+      if (tid < nvec) {
+        VT s = part[tid];
+        for (int q = 1; q < R; ++q) vec_add<VT, T>(s, part[q * nvec + tid]);
+        po[tid] = s;
       }
     }
-    po[d] = acc;
+    if (nvec <= kThreads) break;  // one vector per thread in this arrangement
   }
 }
 
 int fail(int code, const char *msg) {
   set_last_error(msg);
   return code;
+}
+
+// OT_B200_PACK=rows: the joiner input row by row (pack_rows_kernel) instead of by
+// frames; read at every call, so a process can measure both.
+bool add_by_rows_forced() {
+  const char *v = getenv("OT_B200_PACK");
+  return v != nullptr && strcmp(v, "rows") == 0;
 }
 
 // One warp per run of kRun rows: as many short-lived blocks as that takes, or, with
@@ -212,7 +331,22 @@ int launch_rows(const void *a, const void *b, void *out, const int32_t *Tl, cons
   const bool vec = (D % VEC == 0) && (reinterpret_cast<uintptr_t>(a) % 16 == 0) &&
                    (reinterpret_cast<uintptr_t>(out) % 16 == 0) &&
                    (b == nullptr || reinterpret_cast<uintptr_t>(b) % 16 == 0);
-  if (vec)
+  const int nvec = vec ? D / VEC : D;
+  const int chunks_max =
+      (int)(((int64_t)max_u1 * nvec + kThreads * kAddCh - 1) / (kThreads * kAddCh));
+  const int groups_max = (max_t + kAddFrames - 1) / kAddFrames;
+  if (MODE == kAdd && !add_by_rows_forced() && (int64_t)chunks_max * groups_max < 0x7fffffff) {
+    // by frames (see pack_add_frames_kernel); OT_B200_PACK=rows keeps the row-by-row kernel
+    const dim3 grid((unsigned)((int64_t)chunks_max * groups_max), (unsigned)(N < 65535 ? N : 65535));
+    if (vec)
+      pack_add_frames_kernel<T, VEC><<<grid, kThreads, 0, s>>>(
+          static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), Tl, Ul, split,
+          status, N, D, max_t, max_u1, chunks_max);
+    else
+      pack_add_frames_kernel<T, 1><<<grid, kThreads, 0, s>>>(
+          static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), Tl, Ul, split,
+          status, N, D, max_t, max_u1, chunks_max);
+  } else if (vec)
     pack_rows_kernel<T, VEC, MODE><<<rows_grid(pack_rows_kernel<T, VEC, MODE>, rows), kThreads, 0, s>>>(
         static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), Tl, Ul, split,
         status, N, rows, D, max_t, max_u1);
@@ -274,13 +408,23 @@ int ot_b200_pack_joiner_input_backward(const void *d_grad_out, const int32_t *d_
   int32_t *status = reinterpret_cast<int32_t *>(split + N + 1);
   pack_prepare_kernel<<<1, 1024, 0, s>>>(d_logit_lengths, d_target_lengths, N, rows, max_t, max_u1, split, status);
   const dim3 ge((unsigned)max_t, (unsigned)N), gd((unsigned)max_u1, (unsigned)N);
+  const auto aligned = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool al = aligned(d_grad_out) && aligned(d_grad_encoder) && aligned(d_grad_decoder);
+#define OTB_PACK_SUM(T, VEC)                                                                        \
+  do {                                                                                              \
+    pack_sum_kernel<T, VEC, true><<<ge, kThreads, 0, s>>>(                                          \
+        static_cast<const T *>(d_grad_out), static_cast<T *>(d_grad_encoder), d_logit_lengths,      \
+        d_target_lengths, split, status, D, max_t);                                                 \
+    pack_sum_kernel<T, VEC, false><<<gd, kThreads, 0, s>>>(                                         \
+        static_cast<const T *>(d_grad_out), static_cast<T *>(d_grad_decoder), d_logit_lengths,      \
+        d_target_lengths, split, status, D, max_u1);                                                \
+  } while (0)
   if (flags & OT_B200_FP64) {
-    pack_sum_kernel<double, true><<<ge, kThreads, 0, s>>>(static_cast<const double *>(d_grad_out), static_cast<double *>(d_grad_encoder), d_logit_lengths, d_target_lengths, split, status, D, max_t);
-    pack_sum_kernel<double, false><<<gd, kThreads, 0, s>>>(static_cast<const double *>(d_grad_out), static_cast<double *>(d_grad_decoder), d_logit_lengths, d_target_lengths, split, status, D, max_u1);
+    if (al && D % 2 == 0) OTB_PACK_SUM(double, 2); else OTB_PACK_SUM(double, 1);
   } else {
-    pack_sum_kernel<float, true><<<ge, kThreads, 0, s>>>(static_cast<const float *>(d_grad_out), static_cast<float *>(d_grad_encoder), d_logit_lengths, d_target_lengths, split, status, D, max_t);
-    pack_sum_kernel<float, false><<<gd, kThreads, 0, s>>>(static_cast<const float *>(d_grad_out), static_cast<float *>(d_grad_decoder), d_logit_lengths, d_target_lengths, split, status, D, max_u1);
+    if (al && D % 4 == 0) OTB_PACK_SUM(float, 4); else OTB_PACK_SUM(float, 1);
   }
+#undef OTB_PACK_SUM
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(OT_B200_ERR_CUDA, cudaGetErrorString(e));
   return OT_B200_OK;

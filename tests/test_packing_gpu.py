@@ -44,6 +44,26 @@ def test_pack_joiner_input_forward_and_backward(d, dtype):
     np.testing.assert_allclose(q.grad.cpu().numpy(), gdec, rtol=0, atol=tol * 4)
 
 
+@pytest.mark.parametrize("d", [512, 320, 66])
+def test_pack_by_frames_and_by_rows_give_the_same_bits(d, monkeypatch):
+    """The joiner input has two kernels (by frames: the default; row by row:
+    OT_B200_PACK=rows); same additions, so the same bits, on a ragged batch whose
+    utterances span several chunks of the decoder block and several frame groups."""
+    rng, T, U = _lengths(11, 7, (1, 90), (0, 60))
+    T[0], U[0] = 1, 0      # smallest lattice
+    T[3], U[3] = 90, 60    # largest: more than one chunk and more than one frame group
+    max_t, max_u1 = int(T.max()), int(U.max()) + 1
+    enc = torch.from_numpy(rng.standard_normal((7, max_t, d)).astype(np.float32)).to(DEV)
+    dec = torch.from_numpy(rng.standard_normal((7, max_u1, d)).astype(np.float32)).to(DEV)
+    dT, dU = torch.from_numpy(T).to(DEV), torch.from_numpy(U).to(DEV)
+    monkeypatch.delenv("OT_B200_PACK", raising=False)
+    by_frames = packing.pack_joiner_input(enc, dec, dT, dU).cpu().numpy()
+    monkeypatch.setenv("OT_B200_PACK", "rows")
+    by_rows = packing.pack_joiner_input(enc, dec, dT, dU).cpu().numpy()
+    np.testing.assert_array_equal(by_frames, by_rows)
+    np.testing.assert_array_equal(by_frames, O.pack_joiner_oracle(enc.cpu().numpy(), dec.cpu().numpy(), T, U))
+
+
 @pytest.mark.parametrize("d", [500, 33])
 def test_padded_round_trip(d):
     rng, T, U = _lengths(6, 3, (2, 25), (0, 9))
