@@ -108,23 +108,68 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
           if (vi < nvec) v[j] = *reinterpret_cast<const VT *>(px + (int64_t)vi * VEC);
         }
       }
+      // The 16-bit pass is bound by instruction issue, not by bytes (half the bytes
+      // per element, the same arithmetic), so the two columns with a second term
+      // are kept out of the common code: their logits are taken out of the
+      // registers of the lanes that hold them (warp-uniform branches, one shuffle
+      // each), every element then takes the one-term formula, and the two lanes
+      // store their corrected element after their vector.  Same operations on
+      // those elements as in the general code, so the same bits.
+      X fix_b = from_real<X>((T)0), fix_t = from_real<X>((T)0);
+      bool own_b = false, own_t = false;
+      if constexpr (sizeof(X) == 2) {
+        const auto take = [&](int vec, int k) {  // logit k of vector `vec` of this chunk
+          const int jj = (vec - base) >> 5;
+          VT cand = v[0];
+#pragma unroll
+          for (int j = 1; j < CH; ++j)
+            if (j == jj) cand = v[j];
+          const X *ce = reinterpret_cast<const X *>(&cand);
+          X xs = ce[0];
+#pragma unroll
+          for (int q = 1; q < VEC; ++q)
+            if (q == k) xs = ce[q];
+          return __shfl_sync(kFull, to_real(xs), (vec - base) & 31);
+        };
+        if (bvec >= base && bvec < base + kWarp * CH && bvec < nvec) {
+          const T gv = take(bvec, bk) + rec.c;
+          fix_b = from_real<X>((s_exp(gv + rec.beta) - s_exp(gv + rec.sub_blank)) * scale);
+          own_b = ((bvec - base) & 31) == lane;
+        }
+        if (tvec >= base && tvec < base + kWarp * CH && !(tvec == bvec && tk == bk)) {
+          const T gv = take(tvec, tk) + rec.c;
+          fix_t = from_real<X>((s_exp(gv + rec.beta) - s_exp(gv + rec.sub_sym)) * scale);
+          own_t = ((tvec - base) & 31) == lane;
+        }
+      }
 #pragma unroll
       for (int j = 0; j < CH; ++j) {
         const int vi = base + j * kWarp + lane;
         if (vi < nvec) {
           X *e = reinterpret_cast<X *>(&v[j]);
-          const int bsel = (vi == bvec) ? bk : -1;
-          const int tsel = (vi == tvec) ? tk : -1;
+          if constexpr (sizeof(X) == 2) {
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) {
-            const T gv = to_real(e[k]) + rec.c;
-            T val = s_exp(gv + rec.beta);
-            if (k == bsel) val -= s_exp(gv + rec.sub_blank);
-            else if (k == tsel) val -= s_exp(gv + rec.sub_sym);
-            e[k] = from_real<X>(val * scale);
+            for (int k = 0; k < VEC; ++k)
+              e[k] = from_real<X>(s_exp((to_real(e[k]) + rec.c) + rec.beta) * scale);
+          } else {
+            const int bsel = (vi == bvec) ? bk : -1;
+            const int tsel = (vi == tvec) ? tk : -1;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+              const T gv = to_real(e[k]) + rec.c;
+              T val = s_exp(gv + rec.beta);
+              if (k == bsel) val -= s_exp(gv + rec.sub_blank);
+              else if (k == tsel) val -= s_exp(gv + rec.sub_sym);
+              e[k] = from_real<X>(val * scale);
+            }
           }
           *reinterpret_cast<VT *>(pg + (int64_t)vi * VEC) = v[j];
         }
+      }
+      if constexpr (sizeof(X) == 2) {
+        // after the vector stores of the same thread, so these land on top
+        if (own_b) pg[blank] = fix_b;
+        if (own_t) pg[rec.tgt] = fix_t;
       }
     }
   }
@@ -210,15 +255,16 @@ cudaError_t launch_grad_a2(const Problem &p, void *grad, const void *d_scale,
                            double scale_host, cudaStream_t s) {
   using T = typename Real<X>::type;
   static int per_sm = 0;
-  // Six resident blocks per SM (40 registers) for the vectorised float pass: with
+  // Six resident blocks per SM (40 registers) for the vectorised passes: with
   // short-lived blocks the bytes in flight are (resident warps) x (one row), and
   // the step from 5 to 6 blocks took the float pass from 436 to 408 us on
-  // 686 128 rows of 500; 7 or 8 blocks need spills and are slower (488 us), and so
-  // are six for the 16-bit types (348 against 309 us).
-  constexpr int kMinBlocks = (sizeof(X) == 4 && VEC == 4) ? 6 : (sizeof(X) == 8 ? 3 : 5);
+  // 686 128 rows of 500; 7 or 8 blocks need spills and are slower (488 us).  The
+  // 16-bit pass waits on memory latency most of the time once the two special
+  // columns are out of its common code, and gains too (292 -> 277 us).
+  constexpr int kMinBlocks = ((sizeof(X) == 4 || sizeof(X) == 2) && VEC == 4) ? 6 : (sizeof(X) == 8 ? 3 : 5);
   auto kernel = gradient_kernel<X, VEC, CH, PER_UTT, kMinBlocks>;
   // 16-bit rows are half as many bytes per warp; there one resident wave that
-  // strides over the buffer measured faster (315 against 351 us on bf16 cfg2).
+  // strides over the buffer measured faster (277 against 289 us on bf16 cfg2).
   const cudaError_t e = launch_pdl(kernel,
       stream_grid(kernel, &per_sm, p.rows, p.flags, sizeof(X) == 2), (unsigned)kThreads, 0, s,
       static_cast<const X *>(p.logits), static_cast<X *>(grad),
