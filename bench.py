@@ -527,7 +527,7 @@ def run_pack(args, w):
                      "peak_source": f"{peak_kind} copy bandwidth", "traffic": None},
         "backward": {"ms": b_ms, "kernels": "pack_sum_kernel x2 (+ autograd's gradient copy)",
                      "achieved_gbs": 2 * bytes_out / (b_ms * 1e-3) / 1e9},
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": 5 * args.steps,  # forward: prepare + add; backward: prepare + two sums
     }
     print(json.dumps(line), flush=True)
 
