@@ -1,7 +1,7 @@
 """Benchmark of the transducer-loss hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload cfg2] [--scaling weak|strong]
+                    [--workload cfg2] [--scaling strong|weak]
 
 A step is one forward+backward of ``transducer_loss`` over one synthetic batch.
 Metric: lattice cells per second, cells = sum_b T_b * (U_b + 1) * V (the lattice
@@ -14,13 +14,30 @@ steps never share cache lines and are far larger than L2.  ``e2e`` repeats the
 measurement with the logits in pinned host memory, the host-to-device copy and
 the device-to-host read of the loss inside the timed region.  ``roofline``
 describes the gradient kernel, the dominant one; ``cpu_baseline`` times the
-reference's CPU implementation on this box's host cores on a bounded sample.
+reference's CPU implementation on this box's host cores.
 
-``--impl reference``: the reference's CPU implementation alone (its own build
-from ``oracle/_ref`` when present, else the C port in ``oracle/``), each step a
-bounded sample of the same workload.
+With ``--gpus N`` (one process per GPU, launched by torch.distributed.run) the
+SAME batch is dealt to the ranks by utterance ("strong" scaling, the default):
+every utterance's logits depend only on the workload and the utterance's index,
+so the batch, and its loss, are the same at every N.  ``--scaling weak`` gives
+every rank a batch of the workload's size instead.  The ranks' losses are summed
+over peer memory (or by NCCL); after the timed region the line's ``loss_check``
+compares that sum with the float64 sum of the ranks' local losses.
+
+``--impl reference``: the reference's own CPU implementation through its own
+Python layer (``oracle/_ref``: its extension built from its sources plus its
+``transducer_loss.py``; else the C port in ``oracle/``), on the same workload,
+with all host threads.  Under torch.distributed.run only rank 0 works.
+
+``--record-traffic FILE``: not a measurement; reads the csv log of an ncu run of
+this script (metrics dram__bytes_read.sum, dram__bytes_write.sum) and stores the
+gradient kernel's DRAM bytes per lattice cell, with a hash of the kernel's
+source, in ``profiles/gradient_kernel_traffic.txt``, from which ``roofline.traffic``
+is taken as long as the source has not changed since.
 """
 import argparse
+import csv
+import hashlib
 import json
 import os
 import statistics
@@ -32,14 +49,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one full-size cfg2 launch of the
-# gradient kernel, from the one-pass ncu capture summarised in profiles/gradient_kernel_cfg2.md.
-CFG2_GRADIENT_TRAFFIC_BYTES = 2706.0e6
-CFG2_ROWS = 686128
-
 METRIC = "fwd+bwd loss lattice cells (sum T*(U+1)*V)/s"
 UNIT = "cells/s"
 HBM_FALLBACK_GBS = 6650.0
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "gradient_kernel_traffic.txt")
+GRADIENT_SOURCES = [os.path.join(ROOT, "optimized_transducer_b200", "csrc", f)
+                    for f in ("gradient.cu", "ot_common.cuh")]
+CACHE_NOTE = "inputs larger than cache: every step reads its own pristine copy of the logits"
 
 
 def measured_hbm_peak():
@@ -49,6 +65,63 @@ def measured_hbm_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return HBM_FALLBACK_GBS, "fallback"
+
+
+def gradient_source_hash():
+    h = hashlib.sha256()
+    for path in GRADIENT_SOURCES:
+        with open(path, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def recorded_traffic_per_cell(dtype, mode_b):
+    """DRAM bytes per lattice cell of one gradient-kernel launch, from the last
+    recorded ncu capture, or None when there is none for this kernel variant or
+    the kernel's source has changed since."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            rec = json.load(f)
+        if rec["source_sha256"] != gradient_source_hash():
+            return None
+        if rec["dtype"] != dtype or bool(rec["from_log_softmax"]) != bool(mode_b):
+            return None
+        return float(rec["dram_bytes_per_cell"])
+    except Exception:
+        return None
+
+
+def record_traffic(args, w):
+    """Parses an ncu csv log (long format: one line per launch and metric)."""
+    from optimized_transducer_b200 import synthetic
+    per_launch = {}
+    with open(args.record_traffic, newline="") as f:
+        rows = [r for r in csv.reader(f) if len(r) >= 15 and r[0].isdigit()]
+    for r in rows:
+        name, metric, value = r[4], r[12], float(r[14].replace(",", ""))
+        if "gradient" in name and metric in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+            per_launch.setdefault(r[0], {})[metric] = value
+    full = [sum(v.values()) for v in per_launch.values() if len(v) == 2]
+    if not full:
+        raise SystemExit("no gradient-kernel launch with both DRAM metrics in " + args.record_traffic)
+    T, U, _ = synthetic.make_lengths(w)
+    n = min(args.utts, w.n) if args.utts else w.n
+    cells = synthetic.num_rows(T[:n], U[:n]) * w.v
+    rec = {
+        "kernel": "gradient_logsoftmax_kernel" if w.from_log_softmax else "gradient_kernel",
+        "workload": f"{w.name}, first {n} utterances, {cells} cells", "dtype": args.dtype,
+        "from_log_softmax": w.from_log_softmax, "launches": len(full),
+        "dram_bytes_per_launch": statistics.mean(full),
+        "dram_bytes_per_cell": statistics.mean(full) / cells,
+        "source_sha256": gradient_source_hash(),
+        "sources": [os.path.relpath(p, ROOT) for p in GRADIENT_SOURCES],
+        "made_by": "python bench.py --record-traffic <ncu csv log> --workload %s --utts %d --dtype %s"
+                   % (w.name, args.utts, args.dtype),
+    }
+    with open(TRAFFIC_FILE, "w") as f:
+        json.dump(rec, f, indent=1)
+        f.write("\n")
+    print(json.dumps(rec))
 
 
 class ClockSampler:
@@ -120,52 +193,75 @@ def workload_description(w, n_utt, rows):
             f"reduction={w.reduction}, rows={rows}")
 
 
+def global_batch(args, w, world):
+    """Lengths and targets of the whole batch (CPU tensors) and the utterances
+    the benchmark uses of it."""
+    from optimized_transducer_b200 import synthetic
+    n_global = w.n * world if args.scaling == "weak" else w.n
+    T, U, tg = synthetic.make_lengths(w, n=n_global)
+    if args.utts:  # a smaller case of the same workload, for profiler captures
+        n_global = min(args.utts, n_global)
+        T, U = T[:n_global].contiguous(), U[:n_global].contiguous()
+        tg = tg[:n_global, :int(U.max())].contiguous()
+    return n_global, T, U, tg
+
+
 # ---------------------------------------------------------------------------
 # reference arm / CPU baseline
 # ---------------------------------------------------------------------------
-def cpu_reference_step_factory(w, n_sample):
+REFERENCE_SAMPLE_BYTES = 4 << 30  # the reference arm takes the whole batch up to this size
+
+
+def cpu_reference_step_factory(w, T, U, tg, n_sample):
     """Returns (step, cells, kind, cores, description) for the reference's CPU
-    implementation on the first ``n_sample`` utterances of the workload.
+    implementation on the first ``n_sample`` utterances of the batch.
     ``step()`` runs one forward+backward and returns its duration in seconds."""
     import numpy as np
     import torch
     from optimized_transducer_b200 import synthetic
     from oracle import oracle as O
 
-    T, U, tg = synthetic.make_lengths(w)
+    n_all = int(T.numel())
     T, U = T[:n_sample].contiguous(), U[:n_sample].contiguous()
     tg = tg[:n_sample, :int(U.max())].contiguous()
-    x = synthetic.make_logits(w, T, U, device="cpu")
+    x = synthetic.make_utterance_logits(w, T, U, range(n_sample), device="cpu")
     cells = synthetic.num_rows(T, U) * w.v
+    torch.set_num_threads(os.cpu_count() or 1)  # torch.distributed.run exports OMP_NUM_THREADS=1
     cores = torch.get_num_threads()
-    ref = O.load_ref()
-    if ref is not None:
-        ext = ref[0]
+    ref_py = O.load_ref_python()
+    if ref_py is not None:
         work = torch.empty_like(x)
 
+        class Feed(torch.autograd.Function):
+            """The joiner's place: hands the loss a non-leaf tensor, as the
+            reference's tests do (they torch.cat their leaves), and takes its
+            gradient."""
+
+            @staticmethod
+            def forward(ctx, buf, anchor):
+                return buf.view(buf.shape)
+
+            @staticmethod
+            def backward(ctx, grad):
+                return None, None
+
+        anchor = torch.zeros((), requires_grad=True)
+
         def step():
-            # What the reference's Python layer does around its native call
-            # (transducer_loss.py:135-170): loss = -scores, reduce, divide the
-            # gradient for "mean", multiply it by the upstream gradient.
             work.copy_(x)  # restore the input (not timed)
-            lx = work.requires_grad_(True)
             t0 = time.perf_counter()
-            scores, grad = ext.compute_transducer_loss(
-                logits=lx, targets=tg, logit_lengths=T, target_lengths=U, blank=0,
-                from_log_softmax=w.from_log_softmax, one_sym_per_frame=w.one_sym_per_frame)
-            with torch.no_grad():  # both run inside an autograd.Function there
-                loss = -1 * scores
-                if w.reduction == "mean":
-                    loss = loss.mean()
-                    grad /= T.size(0)
-                else:
-                    loss = loss.sum()
-                grad.mul_(torch.ones(()))
-            dt = time.perf_counter() - t0
-            work.requires_grad_(False)
-            return dt
+            # The reference's own Python layer over its own extension
+            # (transducer_loss.py:312-442 of the reference), then backward.
+            loss = ref_py.transducer_loss(
+                logits=Feed.apply(work, anchor), targets=tg, logit_lengths=T, target_lengths=U,
+                blank=0, reduction=w.reduction, from_log_softmax=w.from_log_softmax,
+                one_sym_per_frame=w.one_sym_per_frame)
+            loss.backward()
+            loss.item()
+            return time.perf_counter() - t0
         kind = "reference"
-        note = "only its logsumexp is multi-threaded (ATen); the rest of the reference is one thread"
+        note = ("the reference's transducer_loss + backward on its own CPU build; only its logsumexp is "
+                "multi-threaded (ATen), the rest of the reference is one thread")
     else:
         cores = O.set_threads(os.cpu_count() or 1)
         xn, tn, Tn, Un = x.numpy(), tg.numpy(), T.numpy(), U.numpy()
@@ -179,9 +275,23 @@ def cpu_reference_step_factory(w, n_sample):
             return time.perf_counter() - t0
         kind = "port"
         note = "C port of the reference's algorithm with OpenMP over rows and utterances"
-    desc = (f"first {n_sample} of {w.n} utterances of {w.name} "
-            f"({synthetic.num_rows(T, U)} rows x V={w.v}); {note}")
+    what = "all" if n_sample == n_all else f"first {n_sample} of"
+    desc = (f"{what} {n_all} utterances of {w.name} ({synthetic.num_rows(T, U)} rows x V={w.v}); {note}")
     return step, cells, kind, cores, desc
+
+
+def reference_sample_size(args, w, T, U, requested):
+    """Utterances the CPU runs take: all of them, unless the logits exceed
+    REFERENCE_SAMPLE_BYTES (then the longest prefix that fits) or a count is asked for."""
+    n = int(T.numel())
+    if requested:
+        return min(requested, n)
+    per_utt = (T.to(int) * (U.to(int) + 1) * w.v * 4).tolist()
+    total, k = 0, 0
+    while k < n and (k == 0 or total + per_utt[k] <= REFERENCE_SAMPLE_BYTES):
+        total += per_utt[k]
+        k += 1
+    return k
 
 
 def run_reference_arm(args, w):
@@ -189,19 +299,21 @@ def run_reference_arm(args, w):
     if rank != 0:
         return
     from optimized_transducer_b200 import synthetic
-    step, cells, kind, cores, desc = cpu_reference_step_factory(w, min(args.ref_utts, w.n))
+    n_global, T, U, tg = global_batch(args, w, args.gpus)
+    n_sample = reference_sample_size(args, w, T, U, args.ref_utts)
+    step, cells, kind, cores, desc = cpu_reference_step_factory(w, T, U, tg, n_sample)
     for _ in range(args.warmup):
         step()
     dt = sum(step() for _ in range(args.steps))
     value = cells * args.steps / dt
-    T, U, _ = synthetic.make_lengths(w)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
         "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": workload_description(w, w.n, synthetic.num_rows(T, U)),
-                   "device": "host CPU", "sample": desc},
+        "config": {"workload": workload_description(w, n_global, synthetic.num_rows(T, U)),
+                   "cache": CACHE_NOTE},
+        "setup": {"device": "host CPU", "sample": desc, "threads": cores},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -209,15 +321,115 @@ def run_reference_arm(args, w):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_cuda(args, w):
+    """The reference's own CUDA kernels on this GPU (its cuda.cu / kernels.cu built
+    unmodified for sm_100 by oracle/build_ref.py --cuda), through its own Python
+    layer: the like-for-like GPU comparison.  Not the reference arm the driver
+    runs (that is the CPU build); one GPU, device-resident inputs, CUDA events."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from optimized_transducer_b200 import synthetic
+    from oracle import oracle as O
+    ref_py = O.load_ref_python(cuda=True)
+    if ref_py is None:
+        print(json.dumps({"impl": "reference-cuda",
+                          "unavailable": "oracle/_ref/_optimized_transducer_cuda is not built "
+                                         "(python oracle/build_ref.py --cuda)"}), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n_global, T, U, tg = global_batch(args, w, 1)
+    rows = synthetic.num_rows(T, U)
+    if rows * w.v >= 2 ** 31:
+        print(json.dumps({"impl": "reference-cuda",
+                          "unavailable": "the reference's kernels index with 32-bit element offsets "
+                                         "(kernels.cu:49); this batch has more than 2^31 elements"}), flush=True)
+        return
+    pristine = synthetic.make_utterance_logits(w, T, U, range(n_global), device=dev)
+    dT, dU, dtg = T.to(dev), U.to(dev), tg.to(dev)
+    total = args.steps + args.warmup
+    pool = [pristine.clone() for _ in range(total)]
+
+    class Feed(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, buf, anchor):
+            return buf.view(buf.shape)
+
+        @staticmethod
+        def backward(ctx, grad):
+            return None, None
+
+    anchor = torch.zeros((), device=dev, requires_grad=True)
+
+    def step(buf):
+        loss = ref_py.transducer_loss(
+            logits=Feed.apply(buf, anchor), targets=dtg, logit_lengths=dT, target_lengths=dU, blank=0,
+            reduction=w.reduction, from_log_softmax=w.from_log_softmax,
+            one_sym_per_frame=w.one_sym_per_frame)
+        loss.backward()
+        return loss
+
+    it = iter(pool)
+    for _ in range(args.warmup):
+        step(next(it))
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = step(next(it))
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / args.steps
+    cells = rows * w.v
+    peak, peak_kind = measured_hbm_peak()
+    line = {
+        "impl": "reference-cuda", "metric": METRIC, "value": cells / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_description(w, n_global, rows), "cache": CACHE_NOTE},
+        "setup": {"device": "cuda:0", "what": "the reference's CUDA kernels (sm_35-era SIMT code compiled for "
+                  "sm_100 with its own options, -use_fast_math included) behind its Python layer; "
+                  "row ids from a stand-in for moderngpu's load_balance_search"},
+        "stages": {"whole_step_frac_of_peak": (12 if not w.from_log_softmax else 4) * cells / (ms * 1e-3) / 1e9 / peak},
+        "loss": float(loss.item()),
+    }
+    print(json.dumps(line), flush=True)
+
+
 # ---------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------
+STAGES = ("prepare", "logprob", "lattice", "coef", "gradient")
+
+
+def timeline_summary(traces):
+    """From the kernels' own %globaltimer stamps, as medians over the traced steps
+    (microseconds): when every stage began and ended, relative to the start of the
+    step's first kernel.  A call that ran as two groups of utterances has a second
+    set of stages ("b:"); stages that did not run show -1."""
+    out = {}
+    rows = [t.reshape(10, 2).tolist() for t in traces]
+    unused = -1  # a "first start" slot nobody wrote still holds its initial all-ones
+    for i in range(10):
+        name = ("b:" if i >= 5 else "") + STAGES[i % 5]
+        spans = [((r[i][0] - r[0][0]) / 1e3, (r[i][1] - r[0][0]) / 1e3) for r in rows
+                 if r[i][0] != unused and r[i][1] > 0]
+        out[name] = ([round(statistics.median(s[0] for s in spans), 1),
+                      round(statistics.median(s[1] for s in spans), 1)] if spans else [-1.0, -1.0])
+    out["step_span"] = round(statistics.median(
+        (max(r[i][1] for i in range(10)) - r[0][0]) / 1e3 for r in rows), 1)
+    return out
+
+
 def run_ours(args, w):
     import torch
     import torch.distributed as dist
 
     import optimized_transducer_b200 as ot
     from optimized_transducer_b200 import synthetic
+    from optimized_transducer_b200.transducer_loss import collect_traces
 
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py --impl ours needs a CUDA device: the loss has no CPU path")
@@ -247,28 +459,35 @@ def run_ours(args, w):
                 collective += f" (peer exchange unavailable: {type(e).__name__})"
 
     # ----- the batch (global), and this rank's shard of it
-    n_global = w.n * world if args.scaling == "weak" else w.n
-    T, U, tg = synthetic.make_lengths(w, n=n_global)
-    if args.utts:  # a smaller case of the same workload, for profiler captures
-        n_global = min(args.utts, n_global)
-        T, U = T[:n_global].contiguous(), U[:n_global].contiguous()
-        tg = tg[:n_global, :int(U.max())].contiguous()
+    n_global, gT, gU, gtg = global_batch(args, w, world)
+    rows_global = synthetic.num_rows(gT, gU)
     if world > 1:
-        shard = sharding.shard_batch(T, U, tg, w.v, world, rank, strategy=args.partition)
-        T, U, tg = shard.T, shard.U, shard.targets
+        shard = sharding.shard_batch(gT, gU, gtg, w.v, world, rank, strategy=args.partition)
+        T, U, tg, mine = shard.T, shard.U, shard.targets, shard.indices
+    else:
+        T, U, tg, mine = gT, gU, gtg, list(range(n_global))
     rows = synthetic.num_rows(T, U)
     cells_local = rows * w.v
     dT, dU, dtg = T.to(dev), U.to(dev), tg.to(dev)
-    pristine = synthetic.make_logits(w, T, U, device=dev, seed=w.seed + 31 * rank)
+    pristine = synthetic.make_utterance_logits(w, gT, gU, mine, device=dev)
     if args.dtype != "f32":  # the 16-bit extension: same values, rounded once
         pristine = pristine.to(torch.bfloat16 if args.dtype == "bf16" else torch.float16)
     bytes_logits = pristine.numel() * pristine.element_size()
 
+    # One logits buffer per step (the backward overwrites them), so that the K timed
+    # steps run back to back.  Where the device cannot hold that many (the
+    # long-utterance workload on one GPU) a few buffers rotate: each is restored
+    # from the pristine copy before it is used again, and the steps are timed one by
+    # one so that the restoring copies stay outside the timed spans.
     total_steps = args.steps + args.warmup
     free, _ = torch.cuda.mem_get_info(dev)
-    if (total_steps + 2) * bytes_logits > 0.85 * free:
-        raise RuntimeError("steps + warmup need one logits buffer each; lower --steps")
-    pool = [pristine.clone() for _ in range(total_steps)]
+    fit = int(0.6 * free // bytes_logits) - 2
+    if fit < 2:
+        raise RuntimeError("the device cannot hold three copies of this rank's logits")
+    rotating = fit < total_steps
+    if rotating:
+        args.no_e2e = True  # the host-buffer run needs two more device buffers and a pinned copy
+    pool = [pristine.clone() for _ in range(min(fit, total_steps))]
 
     class Feed(torch.autograd.Function):
         """Stands for the joiner that produces the logits in training: the loss
@@ -286,25 +505,35 @@ def run_ours(args, w):
 
     anchor = torch.zeros((), device=dev, requires_grad=True)
 
-    def one_step(buf):
-        x = Feed.apply(buf, anchor)
+    def loss_of(x, tg_, t_, u_):
         if world > 1:
-            loss = sharding.sharded_transducer_loss(
-                x, dtg, dT, dU, blank=0, from_log_softmax=w.from_log_softmax,
+            return sharding.sharded_transducer_loss(
+                x, tg_, t_, u_, blank=0, from_log_softmax=w.from_log_softmax,
                 one_sym_per_frame=w.one_sym_per_frame, reduction=w.reduction,
                 global_batch=n_global, overlap=True, exchange=exchange)
-        else:
-            loss = ot.transducer_loss(x, dtg, dT, dU, blank=0, from_log_softmax=w.from_log_softmax,
-                                      one_sym_per_frame=w.one_sym_per_frame, reduction=w.reduction)
-        return x, loss
+        return ot.transducer_loss(x, tg_, t_, u_, blank=0, from_log_softmax=w.from_log_softmax,
+                                  one_sym_per_frame=w.one_sym_per_frame, reduction=w.reduction)
+
+    def one_step(buf):
+        x = Feed.apply(buf, anchor)
+        return x, loss_of(x, dtg, dT, dU)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    def buffers():
+        used = 0
+        while True:
+            for buf in pool:
+                if used >= len(pool):
+                    buf.copy_(pristine)  # only when rotating
+                used += 1
+                yield buf
+
     # ----- warm-up
-    it = iter(pool)
+    it = buffers()
     for _ in range(args.warmup):
         x, loss = one_step(next(it))
         loss.backward()
@@ -316,22 +545,83 @@ def run_ours(args, w):
     uuid = getattr(torch.cuda.get_device_properties(dev), "uuid", None)
     with ClockSampler(local_rank, uuid) as clocks:
         barrier()
+        host_t0 = time.perf_counter()
         t_begin.record()
         for k in range(args.steps):
+            buf = next(it)
             ev[k][0].record()
-            x, loss = one_step(next(it))
+            x, loss = one_step(buf)
             ev[k][1].record()
             loss.backward()
             ev[k][2].record()
         if world > 1:
-            sharding.wait_loss(loss)  # the last step's all-reduce ends inside the timed region
+            sharding.wait_loss(loss)  # the last step's exchange ends inside the timed region
         t_end.record()
+        host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps  # host time to ENQUEUE a step
         barrier()
-    elapsed_ms = t_begin.elapsed_time(t_end)
+    elapsed_ms = (sum(e[0].elapsed_time(e[2]) for e in ev) if rotating
+                  else t_begin.elapsed_time(t_end))
+    ot.check_inputs(dev)  # a failed device-side check in any step raises here
     last_loss = float(loss.item())
     fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
     bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
-    del pool, it, x, loss
+    del pool, it, x, loss, buf
+
+    # ----- the dominant kernel by itself: CUDA events around each launch of the
+    #       gradient pass, on the stream it is launched on, directly behind the
+    #       forward kernels of the same step (as it runs inside a step; in the
+    #       default schedule the pass overlaps other stages and has no span of its own)
+    from optimized_transducer_b200.transducer_loss import _Call
+    kbufs = [pristine.clone() for _ in range(2)]
+    kout = torch.empty_like(pristine) if w.from_log_softmax else None
+    kev = []
+    for k in range(args.steps + 3):
+        kb = kbufs[k % 2]
+        kb.copy_(pristine)
+        call = _Call(kb, dtg, dT, dU, 0, w.from_log_softmax, w.one_sym_per_frame, checks="off")
+        call.forward()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record()
+        call.backward(kb if kout is None else kout)
+        k1.record()
+        kev.append((k0, k1))
+    torch.cuda.synchronize(dev)
+    kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in kev[3:])
+    del kbufs, kout, kev, call
+
+    # ----- the exchanged loss against the sum of the ranks' own losses, and a
+    #       stage timeline of a few extra steps (neither is timed)
+    loss_check, timeline = None, None
+    if world > 1:
+        buf = pristine.clone()
+        x = Feed.apply(buf, anchor)
+        total = loss_of(x, dtg, dT, dU)
+        sharding.wait_loss(total)
+        local = ot.transducer_loss(Feed.apply(pristine.clone(), anchor), dtg, dT, dU, blank=0,
+                                   from_log_softmax=w.from_log_softmax,
+                                   one_sym_per_frame=w.one_sym_per_frame, reduction="sum")
+        mine_sum = torch.tensor([float(local.item())], dtype=torch.float64, device=dev)
+        gathered = [torch.empty_like(mine_sum) for _ in range(world)]
+        dist.all_gather(gathered, mine_sum)
+        want = sum(float(g.item()) for g in gathered)  # float64, rank order, on the host
+        if w.reduction == "mean":
+            want /= n_global
+        got = float(total.item())
+        rel = abs(got - want) / max(abs(want), 1e-30)
+        loss_check = {"exchanged": got, "sum_of_locals": want, "rel": rel}
+        del buf, x, total, local
+    if not args.no_timeline:
+        os.environ["OT_TRACE"] = "1"
+        traces = []
+        collect_traces(traces)
+        for _ in range(5):
+            x, loss = one_step(pristine.clone())
+            loss.backward()
+        torch.cuda.synchronize(dev)
+        os.environ["OT_TRACE"] = "0"
+        collect_traces(None)
+        timeline = timeline_summary([t.cpu().numpy() for t in traces])
+        del x, loss
 
     # ----- end to end: logits start in pinned host memory
     host = torch.empty(pristine.shape, dtype=pristine.dtype, pin_memory=True)
@@ -366,14 +656,7 @@ def run_ours(args, w):
         for t in (dev_bufs[slot], t_, u_, g_):
             t.record_stream(main_stream)
         x = Feed.apply(dev_bufs[slot], anchor)
-        if world > 1:
-            loss = sharding.sharded_transducer_loss(
-                x, g_, t_, u_, blank=0, from_log_softmax=w.from_log_softmax,
-                one_sym_per_frame=w.one_sym_per_frame, reduction=w.reduction,
-                global_batch=n_global, overlap=True, exchange=exchange)
-        else:
-            loss = ot.transducer_loss(x, g_, t_, u_, blank=0, from_log_softmax=w.from_log_softmax,
-                                      one_sym_per_frame=w.one_sym_per_frame, reduction=w.reduction)
+        loss = loss_of(x, g_, t_, u_)
         loss.backward()
         done[slot].record(main_stream)
         if world > 1:
@@ -397,18 +680,30 @@ def run_ours(args, w):
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
     # ----- max over ranks, whole-job totals
-    stats = torch.tensor([elapsed_ms, e2e_ms, fwd_ms, bwd_ms], dtype=torch.float64, device=dev)
+    stats = torch.tensor([elapsed_ms, e2e_ms, fwd_ms, bwd_ms, host_ms, kernel_ms], dtype=torch.float64, device=dev)
     cells = torch.tensor([float(cells_local)], dtype=torch.float64, device=dev)
     per_rank = None
     if world > 1:
         # every rank's own figures, for the record (the line reports the max)
-        mine = torch.tensor([elapsed_ms / args.steps, fwd_ms, bwd_ms, float(rows)], dtype=torch.float64, device=dev)
-        gathered = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(gathered, mine)
-        per_rank = [[round(v, 4) for v in g.tolist()] for g in gathered]
+        cols = ["ms_per_step", "forward_ms", "backward_ms", "host_enqueue_ms", "rows", "utterances",
+                "longest_T_plus_U"]
+        vals = [elapsed_ms / args.steps, fwd_ms, bwd_ms, host_ms, float(rows), float(T.numel()),
+                float(int((T + U).max()))]
+        if timeline is not None:
+            for k, v in timeline.items():
+                if isinstance(v, list):
+                    cols += [f"us_{k}_begin", f"us_{k}_end"]
+                    vals += [float(v[0]), float(v[1])]
+                else:
+                    cols.append("us_" + k)
+                    vals.append(float(v))
+        mine_t = torch.tensor(vals, dtype=torch.float64, device=dev)
+        gathered = [torch.empty_like(mine_t) for _ in range(world)]
+        dist.all_gather(gathered, mine_t)
+        per_rank = {"columns": cols, "values": [[round(v, 4) for v in g.tolist()] for g in gathered]}
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         dist.all_reduce(cells, op=dist.ReduceOp.SUM)
-    elapsed_ms, e2e_ms, fwd_ms, bwd_ms = stats.tolist()
+    elapsed_ms, e2e_ms, fwd_ms, bwd_ms, host_ms, kernel_ms = stats.tolist()
     cells_total = cells.item()
 
     if rank == 0:
@@ -418,53 +713,79 @@ def run_ours(args, w):
         # Gradient kernel, per launch: read + in-place write of the local logits
         # (mode A), or the dense gradient write (mode B).
         grad_bytes = (1 if mode_b else 2) * es * cells_local
-        achieved = grad_bytes / (bwd_ms * 1e-3) / 1e9
+        achieved = grad_bytes / (kernel_ms * 1e-3) / 1e9
+        eager = os.environ.get("OT_EAGER_GRAD", "1") != "0"
+        two_groups = (eager and not mode_b and T.numel() >= 2 and bytes_logits >= (256 << 20)
+                      and os.environ.get("OT_B200_PIPELINE", "1") != "0")
+        # own kernels per step and rank: prepare, logprob, lattice, coef, gradient (twice
+        # the last four + one closing kernel when the batch runs as two groups), the
+        # scaling kernel of the eager schedule's backward, publish + gather of the exchange
+        launches = (10 if two_groups else 5) + (1 if eager else 0) + (2 if exchange is not None else 0)
         fwd_bytes = (0 if mode_b else es * cells_local)
         value = cells_total * args.steps / (elapsed_ms * 1e-3)
+        per_cell = recorded_traffic_per_cell(args.dtype, mode_b)
+        step_ms = elapsed_ms / args.steps
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
             "scaling": args.scaling, "vs_baseline": None,
             "dtype": "f32" if args.dtype == "f32" else f"{args.dtype} logits and gradient, f32 arithmetic",
             "data": "synthetic",
             "config": {
-                "workload": workload_description(w, n_global, rows if world == 1 else "sharded")
+                "workload": workload_description(w, n_global, rows_global)
                             + ("" if args.dtype == "f32" else f", logits stored as {args.dtype}"),
+                "cache": CACHE_NOTE,
+            },
+            "setup": {
+                "timed_region": ("the K steps one by one (CUDA events around each; a few logits buffers "
+                                 "rotate and are restored between the steps)") if rotating else
+                                "the K steps back to back, one pair of CUDA events",
                 "sharding": "none" if world == 1 else
-                            f"{world} ranks, whole utterances, balanced by T*(U+1)*V ({args.partition} partition)",
+                            f"{world} ranks, whole utterances of the one batch ({args.partition} partition)"
+                            if args.scaling == "strong" else
+                            f"{world} ranks, {w.n} utterances per rank ({args.partition} partition)",
                 "collective": collective,
-                "cache": "inputs larger than L2: every step reads its own pristine logits buffer",
-                "checks": os.environ.get("OT_CHECKS", "1"),
-                "gradient_schedule": "eager" if os.environ.get("OT_EAGER_GRAD", "0") == "1" else "deferred (fused into backward)",
+                "checks": {"0": "off", "2": "strict (the call waits)"}.get(
+                    os.environ.get("OT_CHECKS", "1"), "deferred (reported by a later call)"),
+                "gradient_schedule": ("deferred (one fused pass in backward)"
+                                      if os.environ.get("OT_EAGER_GRAD", "1") == "0" else
+                                      "eager (loss and gradient in one library call, as the reference; "
+                                      "backward only scales, and skips that when the upstream gradient is 1)"),
+                "stage_overlap": ("off (OT_B200_PIPELINE=0)" if os.environ.get("OT_B200_PIPELINE", "1") == "0"
+                                  else "two groups of utterances on three streams when a rank holds >= 256 MB of logits"),
+                "host_enqueue_ms_per_step": host_ms,
             },
             "clocks": clocks.summary(),
             "e2e": None if not e2e_steps else {"value": cells_total / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": bytes_logits + 4 * (T.numel() + U.numel() + tg.numel()),
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
-            # own kernels per step and rank: prepare, logprob, lattice, coef, gradient
-            # (+ publish and gather of the peer-memory exchange)
-            "gpu_launches": (5 + (2 if exchange is not None else 0)) * args.steps,
+            "gpu_launches": launches * args.steps,
             "roofline": {
                 "kernel": "gradient_logsoftmax_kernel" if mode_b else "gradient_kernel",
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
-                "traffic": (CFG2_GRADIENT_TRAFFIC_BYTES
-                            if (w.name == "cfg2" and world == 1 and rows == CFG2_ROWS
-                                and args.dtype == "f32") else None),
-                "bytes_per_launch": grad_bytes, "ms_per_launch": bwd_ms,
+                "traffic": None if per_cell is None else per_cell * cells_local,
+                "bytes_per_launch": grad_bytes, "ms_per_launch": kernel_ms,
+                "timing": "CUDA events around each launch of the kernel alone, behind the forward kernels "
+                          "of the same batch (in the timed steps it overlaps other stages)",
             },
             "stages": {
                 "forward_ms": fwd_ms, "backward_ms": bwd_ms,
                 "forward_gbs": (fwd_bytes / (fwd_ms * 1e-3) / 1e9) if fwd_bytes else None,
-                "whole_step_gbs": (fwd_bytes + grad_bytes) / ((elapsed_ms / args.steps) * 1e-3) / 1e9,
-                "whole_step_frac_of_peak": (fwd_bytes + grad_bytes) / ((elapsed_ms / args.steps) * 1e-3) / 1e9 / peak,
+                "whole_step_gbs": (fwd_bytes + grad_bytes) / (step_ms * 1e-3) / 1e9,
+                "whole_step_frac_of_peak": (fwd_bytes + grad_bytes) / (step_ms * 1e-3) / 1e9 / peak,
             },
             "loss": last_loss,
         }
+        if timeline is not None:
+            line["timeline_us"] = timeline
         if per_rank is not None:
-            line["per_rank"] = {"columns": ["ms_per_step", "forward_ms", "backward_ms", "rows"], "values": per_rank}
+            line["per_rank"] = per_rank
+        if loss_check is not None:
+            line["loss_check"] = loss_check
         if world == 1 and not args.no_cpu_baseline:
-            step, c_cells, kind, cores, desc = cpu_reference_step_factory(w, min(args.cpu_utts, w.n))
+            n_sample = reference_sample_size(args, w, gT, gU, args.cpu_utts)
+            step, c_cells, kind, cores, desc = cpu_reference_step_factory(w, gT, gU, gtg, n_sample)
             step()
             t0 = time.perf_counter()
             reps, spent = 0, 0.0
@@ -477,6 +798,8 @@ def run_ours(args, w):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if loss_check is not None and loss_check["rel"] > 1e-6:
+        raise SystemExit(f"loss check failed on rank {rank}: {loss_check}")
 
 
 def run_pack(args, w):
@@ -537,35 +860,48 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--impl", choices=["ours", "reference", "reference-cuda"], default="ours",
+                    help="ours: the sm_100a path; reference: the reference's CPU implementation (the arm "
+                         "the driver compares with); reference-cuda: the reference's own CUDA kernels on "
+                         "this GPU (an extra, like-for-like comparison)")
     ap.add_argument("--workload", default="cfg2")
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--scaling", choices=["strong", "weak"], default="strong",
+                    help="strong (default): the workload's one batch is dealt to the ranks; "
+                         "weak: every rank gets a batch of the workload's size")
     ap.add_argument("--dtype", choices=["f32", "bf16", "f16"], default="f32",
                     help="storage type of the logits (the reference's is f32; 16-bit is an extension)")
     ap.add_argument("--collective", choices=["peer", "nccl"], default="peer",
                     help="how the ranks' losses are summed: over peer memory (default) or by NCCL")
-    ap.add_argument("--partition", choices=["auto", "contiguous", "lpt"], default="lpt",
-                    help="how utterances are dealt to the ranks (each rank creates its own shard, "
-                         "so the permuting, better balanced \"lpt\" costs nothing here)")
-    ap.add_argument("--ref-utts", type=int, default=4,
-                    help="utterances per step of the reference arm (bounded sample)")
-    ap.add_argument("--cpu-utts", type=int, default=8,
-                    help="utterances of the CPU-baseline sample of our arm")
+    ap.add_argument("--partition", choices=["auto", "contiguous", "lpt", "lpt_chain"], default="lpt_chain",
+                    help="how utterances are dealt to the ranks (each rank creates its own shard, so a "
+                         "permuting partition costs nothing here); lpt_chain balances cells and the "
+                         "longest recursion per rank")
+    ap.add_argument("--ref-utts", type=int, default=0,
+                    help="utterances per step of the reference arm (0: the whole batch, up to 4 GB of logits)")
+    ap.add_argument("--cpu-utts", type=int, default=0,
+                    help="utterances of the CPU-baseline sample of our arm (0: as --ref-utts 0)")
     ap.add_argument("--op", choices=["loss", "pack"], default="loss",
                     help="loss: the transducer loss (default, the benchmark); pack: the packing helpers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer measurement")
+    ap.add_argument("--no-timeline", action="store_true", help="skip the traced extra steps")
     ap.add_argument("--utts", type=int, default=0,
                     help="use only the first UTTS utterances (small case for profiler captures)")
+    ap.add_argument("--record-traffic", default="",
+                    help="csv log of an ncu run of this script: store the gradient kernel's DRAM traffic")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     from optimized_transducer_b200 import synthetic
     w = synthetic.CONFIGS[args.workload]
-    if args.op == "pack":
+    if args.record_traffic:
+        record_traffic(args, w)
+    elif args.op == "pack":
         run_pack(args, w)
     elif args.impl == "reference":
         run_reference_arm(args, w)
+    elif args.impl == "reference-cuda":
+        run_reference_cuda(args, w)
     else:
         run_ours(args, w)
 

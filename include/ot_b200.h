@@ -9,14 +9,22 @@
  * Conventions
  *  - Plain pointers and sizes only; every pointer named `d_*` is DEVICE memory
  *    of the current CUDA device, `stream` is a cudaStream_t passed as void*.
- *  - The library allocates no device memory.  The caller provides outputs and
- *    one workspace whose size ot_b200_workspace_bytes() reports.
+ *  - The library allocates no device memory: the caller provides outputs and
+ *    one workspace whose size ot_b200_workspace_bytes() reports.  Two things
+ *    live inside the library instead: the fixed scratch array of
+ *    ot_b200_scores_noalloc (part of the library image, see there), and, per
+ *    device, a few KB of pinned, device-mapped HOST memory for the error
+ *    reports (allocated by the first call that asks for reports on a device,
+ *    kept until the process exits).
  *  - Every function returns an ot_b200_status; nothing throws, traps or
  *    asserts.  ot_b200_last_error() gives the message of the calling thread's
  *    last failure.
  *  - All work is enqueued on `stream`; functions return without synchronising
- *    unless stated.  Re-entrant: no state is shared between calls except the
- *    caller's workspace.
+ *    unless stated.  Callable from any host thread: calls share nothing but
+ *    the caller's workspace, the per-device report words above (sequence
+ *    numbers are atomic, every blocking call polls a slot of its own) and a
+ *    few per-device caches of launch parameters (atomics).  Exception:
+ *    ot_b200_scores_noalloc, whose calls share one scratch array.
  *  - Packed layout (README.md:131-204 of the reference): utterance b owns
  *    T_b*(U_b+1) consecutive rows of `logits`, row(b,t,u) = split_b + t*(U_b+1) + u,
  *    each row holding V values.  64-bit element offsets are used throughout
@@ -32,7 +40,7 @@
 extern "C" {
 #endif
 
-#define OT_B200_ABI_VERSION 2
+#define OT_B200_ABI_VERSION 3
 
 typedef enum ot_b200_status {
   OT_B200_OK = 0,
@@ -52,19 +60,39 @@ typedef enum ot_b200_input_error {
   OT_B200_INPUT_ROWS_MISMATCH = 3,      /* sum T_b*(U_b+1) != rows  (:49-51)           */
   OT_B200_INPUT_TARGET_RANGE = 4,       /* targets.max() >= V or a used target < 0 (:53-56) */
   OT_B200_INPUT_MAX_U_MISMATCH = 5,     /* targets.size(1) != max_b U_b  (:62-66)      */
-  OT_B200_INPUT_ONE_SYM_INFEASIBLE = 6  /* one_sym_per_frame with U_b > T_b - 1: no
+  OT_B200_INPUT_ONE_SYM_INFEASIBLE = 6, /* one_sym_per_frame with U_b > T_b - 1: no
                                            alignment exists; the reference returns
                                            uninitialised memory here                  */
+  /* Not input errors, but reported the same way (status word, error report): */
+  OT_B200_TOTALS_DIFFER = 7,            /* alpha(T-1,U)+blank and beta(0,0) of an utterance
+                                           are not allclose (rtol 1e-5, atol 1e-8): the
+                                           check of cpu.cc:795-797; only made when a
+                                           report is asked for                          */
+  OT_B200_COPY_TIMEOUT = 8,             /* a bounded wait for a bulk copy of the log-prob
+                                           or recursion stage ran out: results invalid  */
+  OT_B200_INPUT_PACK_LENGTHS = 9        /* a packing helper: some T_b > max_t, U_b + 1 >
+                                           max_u1, T_b <= 0, U_b < 0, or the lengths do
+                                           not add up to rows                           */
 } ot_b200_input_error;
 
 /* Bits of `flags`. */
 #define OT_B200_FROM_LOG_SOFTMAX 1u   /* input rows are log-softmax outputs         */
 #define OT_B200_ONE_SYM_PER_FRAME 2u  /* modified transducer                        */
 #define OT_B200_FP64 4u               /* logits/scores/grad are double, not float   */
-#define OT_B200_CHECK_INPUTS 8u       /* ot_b200_forward waits for the input-check
-                                         report (a few words stage 0 stores into
-                                         mapped host memory) before it returns; not
-                                         allowed during stream capture              */
+#define OT_B200_CHECK_INPUTS 8u       /* ot_b200_forward waits until the forward half
+                                         has run and returns its verdict (input check,
+                                         totals check, copy timeouts: a few words the
+                                         last forward kernel stores into mapped host
+                                         memory), like the reference, which raises
+                                         inside the call; not allowed during stream
+                                         capture                                    */
+#define OT_B200_REPORT_ERRORS 1024u   /* the same verdict without the wait: a failed
+                                         call leaves a record in mapped host memory,
+                                         and the NEXT ot_b200_forward / ot_b200_backward
+                                         on the device (or ot_b200_poll_errors) that
+                                         finds it returns OT_B200_ERR_INPUT without
+                                         launching anything.  The host never waits
+                                         for the device, so it can run ahead of it. */
 #define OT_B200_FAST_MATH 16u         /* approximate exp/log in the recursions      */
 #define OT_B200_BF16 128u              /* logits and gradient are bfloat16; scores,  */
 #define OT_B200_FP16 256u              /* loss, scale factors and the workspace stay
@@ -97,7 +125,9 @@ typedef enum ot_b200_input_error {
  * one-symbol-per-frame recursion, are undefined. */
 typedef struct ot_b200_workspace_layout {
   uint64_t total_bytes;
-  uint64_t status_off;      /* int32[16]: [0] ot_b200_input_error, [1] utterance index */
+  uint64_t status_off;      /* int32[64]: [0] ot_b200_input_error, [1] utterance index,
+                               [2] 1 + utterance whose bulk-copy wait ran out (0: none),
+                               [3] trace switch; from byte 64: the OT_B200_TRACE timeline */
   uint64_t split_off;       /* int64[N+1]: first packed row of each utterance        */
   uint64_t cell_split_off;  /* int64[N+1]: first cell of each utterance              */
   uint64_t den_off;         /* real[rows]: row-wise logsumexp          (cuda.cu:427)  */
@@ -134,9 +164,11 @@ int ot_b200_workspace_bytes(int32_t N, int64_t rows, int32_t max_u, uint32_t fla
  * d_scores        (N) real out: log P(y_b|x_b) = alpha(T-1,U) + lp_blank(T-1,U)
  * d_loss          NULL, or one real out: loss_scale * -(sum_b scores[b])
  *                 (loss_scale = 1 for reduction "sum", 1/N for "mean")
- * With OT_B200_CHECK_INPUTS a failed input check returns OT_B200_ERR_INPUT
- * (the streaming kernels then do not touch the inputs); without it the status
- * stays in the workspace and ot_b200_read_input_status() can fetch it. */
+ * Whenever the verdict of the forward half is not OT_B200_INPUT_OK the streaming
+ * kernels do not touch the inputs, *d_loss and (for input errors) d_scores are
+ * NaN and ot_b200_backward on this workspace writes nothing.  How the caller
+ * learns of it: OT_B200_CHECK_INPUTS (this call returns OT_B200_ERR_INPUT),
+ * OT_B200_REPORT_ERRORS (a later call does), or ot_b200_read_input_status(). */
 int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
                     const int32_t *d_logit_lengths,
                     const int32_t *d_target_lengths, int32_t N, int64_t rows,
@@ -166,6 +198,38 @@ int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows
                      const void *d_workspace, uint64_t workspace_bytes,
                      const void *d_scale, double scale_host, void *stream);
 
+/* Loss and gradient in one call: what TransducerLossFunction.forward of the
+ * reference does (transducer_loss.py:135-154: native call, loss = -scores,
+ * mean/sum, gradient divided by N for "mean"), without its extra pass:
+ *   d_scores[b] = log P(y_b|x_b);  *d_loss = loss_scale * -(sum_b d_scores[b])
+ *   (d_loss may be NULL);  d_grad = grad_scale * d(-sum_b scores[b])/d logits
+ *   (d_grad may be NULL: no gradient; MAY EQUAL d_logits unless
+ *   OT_B200_FROM_LOG_SOFTMAX).  Arguments otherwise as for ot_b200_forward.
+ * Because the whole step is one call, large batches (raw-logit input with a
+ * gradient, >= 256 MB of logits) run as two groups of utterances on three
+ * streams (the caller's and two the library creates per device on first use):
+ * the recursion of one group overlaps the streaming kernels of the other.  The
+ * caller's stream waits, by events, for everything before the function's last
+ * kernel; results are bitwise those of ot_b200_forward + ot_b200_backward.
+ * OT_B200_PIPELINE=0 in the environment keeps everything on the caller's stream. */
+int ot_b200_loss_and_gradient(const void *d_logits, void *d_grad, const int32_t *d_targets,
+                              const int32_t *d_logit_lengths,
+                              const int32_t *d_target_lengths, int32_t N, int64_t rows,
+                              int32_t V, int32_t max_u, int32_t blank, uint32_t flags,
+                              void *d_workspace, uint64_t workspace_bytes, void *d_scores,
+                              void *d_loss, double loss_scale, double grad_scale, void *stream);
+
+/* d_grad[i] *= *d_scale for i < count, unless *d_scale == 1 (then the buffer is
+ * not touched: the kernel's blocks return after one load).  The counterpart of
+ * `ctx.grad.mul_(loss_grad)` (transducer_loss.py:162) for a gradient that
+ * ot_b200_loss_and_gradient computed ahead of the backward pass.  d_scale: one
+ * device scalar of the arithmetic type (float; double with OT_B200_FP64);
+ * `flags`: the storage type of d_grad (OT_B200_FP64 / BF16 / FP16, else float),
+ * and optionally OT_B200_REPORT_ERRORS (a pending error record is returned
+ * instead of launching, as by ot_b200_backward). */
+int ot_b200_scale_gradient(void *d_grad, int64_t count, const void *d_scale, uint32_t flags,
+                           void *stream);
+
 /* One call with the reference's semantics, forward + (if d_grad != NULL)
  * backward with scale 1:  the counterpart of
  * _optimized_transducer.compute_transducer_loss
@@ -179,6 +243,16 @@ int ot_b200_compute_transducer_loss(const void *d_logits, void *d_grad,
                                     void *d_workspace, uint64_t workspace_bytes,
                                     void *d_scores, void *stream);
 
+/* Error record of calls made with OT_B200_REPORT_ERRORS on the current device.
+ * wait != 0: synchronises `stream` first, so every call enqueued on it has
+ * delivered its verdict.  Outputs (each may be NULL): the ot_b200_input_error
+ * code (0: no failed call since the last poll), the utterance it refers to,
+ * and the sequence number of the failed call (calls with a report are counted
+ * per device, from 1).  Clears the record.  Always returns OT_B200_OK unless a
+ * CUDA call fails; the message of a found error is left in ot_b200_last_error(). */
+int ot_b200_poll_errors(int32_t *code_out, int32_t *index_out, int32_t *seq_out,
+                        void *stream, int32_t wait);
+
 /* Copies the input-check status out of the workspace (synchronises `stream`).
  * code_out receives an ot_b200_input_error, index_out the offending utterance. */
 int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes,
@@ -187,11 +261,15 @@ int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes,
 /* ---- Callers' side of the packed layout ----------------------------------
  * Padded batch tensors <-> packed rows, row(b,t,u) = split_b + t*(U_b+1) + u.
  * max_t / max_u1 are the padded extents (max_u1 >= max_b U_b + 1); D is the
- * feature (or vocabulary) size; element type float, or double with
- * OT_B200_FP64.  The workspace holds the row splits (ot_b200_pack_workspace_bytes,
- * 8-byte aligned).  If the lengths are inconsistent with rows / max_t / max_u1
- * the kernels write nothing and the int32 at workspace offset (N+1)*8 is
- * non-zero. */
+ * feature (or vocabulary) size; element type float, or as OT_B200_FP64 /
+ * OT_B200_BF16 / OT_B200_FP16 say (16-bit data is added and summed in float and
+ * rounded once).  The workspace holds the row splits
+ * (ot_b200_pack_workspace_bytes, 8-byte aligned).  If the lengths are
+ * inconsistent with rows / max_t / max_u1 the kernels do not follow them: every
+ * output element becomes NaN (ot_b200_unpack_to_padded: zero), the int32 at
+ * workspace offset (N+1)*8 is non-zero (1 + an offending utterance, or -1 if
+ * only the sum differs from rows), and with OT_B200_REPORT_ERRORS in `flags`
+ * the failure is recorded for the next call, as for ot_b200_forward. */
 int ot_b200_pack_workspace_bytes(int32_t N, uint64_t *bytes_out);
 
 /* out[row(b,t,u), :] = encoder_out[b,t,:] + decoder_out[b,u,:]

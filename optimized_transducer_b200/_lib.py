@@ -9,7 +9,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libot_b200.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 # ot_b200_status
 OK, ERR_ARGUMENT, ERR_CUDA, ERR_WORKSPACE, ERR_INPUT = range(5)
@@ -25,6 +25,7 @@ SHARE_SMS = 64
 BF16 = 128
 FP16 = 256
 TRACE = 512
+REPORT_ERRORS = 1024
 
 # Every symbol include/ot_b200.h declares.
 EXPORTS = (
@@ -34,7 +35,10 @@ EXPORTS = (
     "ot_b200_workspace_bytes",
     "ot_b200_forward",
     "ot_b200_backward",
+    "ot_b200_loss_and_gradient",
+    "ot_b200_scale_gradient",
     "ot_b200_compute_transducer_loss",
+    "ot_b200_poll_errors",
     "ot_b200_read_input_status",
     "ot_b200_scores_noalloc",
     "ot_b200_pack_workspace_bytes",
@@ -83,8 +87,15 @@ def load():
                                     ctypes.c_double, vp]
     lib.ot_b200_backward.restype = ctypes.c_int
     lib.ot_b200_backward.argtypes = [vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, ctypes.c_double, vp]
+    lib.ot_b200_loss_and_gradient.restype = ctypes.c_int
+    lib.ot_b200_loss_and_gradient.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, vp,
+                                              ctypes.c_double, ctypes.c_double, vp]
+    lib.ot_b200_scale_gradient.restype = ctypes.c_int
+    lib.ot_b200_scale_gradient.argtypes = [vp, i64, vp, u32, vp]
     lib.ot_b200_compute_transducer_loss.restype = ctypes.c_int
     lib.ot_b200_compute_transducer_loss.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, vp]
+    lib.ot_b200_poll_errors.restype = ctypes.c_int
+    lib.ot_b200_poll_errors.argtypes = [ctypes.POINTER(i32), ctypes.POINTER(i32), ctypes.POINTER(i32), vp, i32]
     lib.ot_b200_read_input_status.restype = ctypes.c_int
     lib.ot_b200_read_input_status.argtypes = [vp, u64, ctypes.POINTER(i32), ctypes.POINTER(i32), vp]
     lib.ot_b200_scores_noalloc.restype = ctypes.c_int

@@ -10,8 +10,11 @@
 #include <stdarg.h>
 #include <stdio.h>
 
-#include <chrono>
 #include <string.h>
+
+#include <atomic>
+#include <chrono>
+#include <mutex>
 
 #include "ot_common.cuh"
 
@@ -43,46 +46,128 @@ const char *input_error_text(int code) {
     case OT_B200_INPUT_TARGET_RANGE: return "Expect targets.max() < logits.size(1) and used targets >= 0";
     case OT_B200_INPUT_MAX_U_MISMATCH: return "targets.size(1) should be equal to target_lengths.max()";
     case OT_B200_INPUT_ONE_SYM_INFEASIBLE: return "one_sym_per_frame needs target_length <= logit_length - 1";
+    case OT_B200_TOTALS_DIFFER: return "total scores computed from forward/backward passes are not equal";
+    case OT_B200_COPY_TIMEOUT: return "a bulk copy into shared memory did not complete in time";
+    case OT_B200_INPUT_PACK_LENGTHS: return "packing: the lengths do not fit rows, max_t or max_u1 (the output was filled with NaN)";
     default: return "unknown input error";
   }
 }
 
-// Mapped pinned words for the optional input-check report, one set per host
-// thread and device, created on first use and kept for the thread's lifetime.
-// Stage 0 writes {code, utterance, sequence number} into them; the host polls
-// the sequence number.  Nothing but kernels is ever enqueued on the stream.
-struct StatusSlot {
-  volatile int32_t *host = nullptr;
+// Mapped pinned host words for the error reports, one block per device, created
+// by the first call on the device that asks for a report and kept until the
+// process exits (a few KB; freeing it at exit would race with the teardown of
+// the CUDA context).  Layout, in int32 words:
+//   [4*i .. 4*i+2], i < kReportSlots   {code, utterance, sequence} of the blocking
+//                                      call whose sequence number is i mod kReportSlots
+//   [4*kReportSlots .. +2]             the record of the last FAILED call that ran
+//                                      with OT_B200_REPORT_ERRORS (code 0: none)
+// The last kernel of the forward half stores them; nothing but kernels is ever
+// enqueued on the stream.
+constexpr int kReportSlots = 64;  // blocking calls in flight at once, per device
+constexpr int kReportWords = 4 * kReportSlots + 4;
+struct ReportBlock {
+  std::atomic<int32_t *> host{nullptr};
   int32_t *dev = nullptr;
-  int32_t seq = 0;
+  std::atomic<uint32_t> seq{0};
 };
-thread_local StatusSlot g_slots[64];
+ReportBlock g_reports[kMaxDevices];
+std::mutex g_reports_mutex;
 
-int get_slot(StatusSlot **out) {
+int get_reports(ReportBlock **out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
-  if (dev < 0 || dev >= 64) return fail(OT_B200_ERR_ARGUMENT, "device ordinal %d not supported", dev);
-  StatusSlot &s = g_slots[dev];
-  if (!s.host) {
-    void *h = nullptr;
-    e = cudaHostAlloc(&h, kStatusWords * sizeof(int32_t), cudaHostAllocMapped);
-    if (e != cudaSuccess) return fail_cuda(e, "cudaHostAlloc(status)");
-    memset(h, 0, kStatusWords * sizeof(int32_t));
-    void *d = nullptr;
-    e = cudaHostGetDevicePointer(&d, h, 0);
-    if (e != cudaSuccess) return fail_cuda(e, "cudaHostGetDevicePointer(status)");
-    s.host = static_cast<volatile int32_t *>(h);
-    s.dev = static_cast<int32_t *>(d);
+  if (dev < 0 || dev >= kMaxDevices) return fail(OT_B200_ERR_ARGUMENT, "device ordinal %d not supported", dev);
+  ReportBlock &r = g_reports[dev];
+  if (r.host.load(std::memory_order_acquire) == nullptr) {
+    std::lock_guard<std::mutex> lock(g_reports_mutex);
+    if (r.host.load(std::memory_order_relaxed) == nullptr) {
+      void *h = nullptr;
+      e = cudaHostAlloc(&h, kReportWords * sizeof(int32_t), cudaHostAllocMapped);
+      if (e != cudaSuccess) return fail_cuda(e, "cudaHostAlloc(error reports)");
+      memset(h, 0, kReportWords * sizeof(int32_t));
+      void *d = nullptr;
+      e = cudaHostGetDevicePointer(&d, h, 0);
+      if (e != cudaSuccess) return fail_cuda(e, "cudaHostGetDevicePointer(error reports)");
+      r.dev = static_cast<int32_t *>(d);
+      r.host.store(static_cast<int32_t *>(h), std::memory_order_release);
+    }
   }
-  *out = &s;
+  *out = &r;
   return OT_B200_OK;
 }
+
+int fail_verdict(int code, int index) {
+  return fail(OT_B200_ERR_INPUT, "input check failed (code %d, utterance %d): %s", code, index,
+              input_error_text(code));
+}
+
+// Takes (and clears) the record of a failed OT_B200_REPORT_ERRORS call, if any.
+int take_sticky(ReportBlock *r, int32_t *index, int32_t *seq) {
+  volatile int32_t *s = r->host.load(std::memory_order_acquire) + 4 * kReportSlots;
+  const int32_t code = s[0];
+  if (code == 0) return 0;
+  *index = s[1];
+  *seq = s[2];
+  s[0] = 0;
+  return code;
+}
+
+int fail_earlier(int code, int index, int seq) {
+  return fail(OT_B200_ERR_INPUT,
+              "an earlier call on this device (number %d) failed (code %d, utterance %d): %s; "
+              "its results are NaN and it wrote no gradient",
+              seq, code, index, input_error_text(code));
+}
+
+// Resources of the two-group schedule (see run_two_groups): per device two side
+// streams and six events, created by the first call that uses the schedule and
+// kept until the process exits.  `lock` serialises the enqueue sequences of
+// concurrent host threads on one device (a sequence records and waits on the
+// shared events; it takes a few tens of microseconds and never waits for the GPU).
+struct Pipeline {
+  std::mutex lock;
+  bool ready = false;
+  cudaStream_t side = nullptr;     // the second group's streaming kernels
+  cudaStream_t urgent = nullptr;   // both groups' recursions: highest priority, so that their few
+                                   // blocks are placed ahead of the streaming kernels' thousands
+  cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+};
+Pipeline g_pipelines[kMaxDevices];
+
+cudaError_t pipeline_init(Pipeline &pl) {
+  if (pl.ready) return cudaSuccess;
+  int least = 0, greatest = 0;
+  cudaError_t e = cudaDeviceGetStreamPriorityRange(&least, &greatest);
+  if (e != cudaSuccess) return e;
+  e = cudaStreamCreateWithPriority(&pl.side, cudaStreamNonBlocking, least);
+  if (e != cudaSuccess) return e;
+  e = cudaStreamCreateWithPriority(&pl.urgent, cudaStreamNonBlocking, greatest);
+  if (e != cudaSuccess) return e;
+  for (auto &ev : pl.ev) {
+    e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) return e;
+  }
+  pl.ready = true;
+  return cudaSuccess;
+}
+
+// OT_B200_PIPELINE=0 keeps every call on the caller's stream, one stage after
+// the other (read at every call, so a process can compare the two schedules).
+bool two_groups_allowed() {
+  const char *e = getenv("OT_B200_PIPELINE");
+  return !(e && strcmp(e, "0") == 0);
+}
+
+// Batches below this many bytes of logits run as one group: the streaming
+// kernels of half the batch must outlast a recursion for the overlap to pay.
+constexpr uint64_t kTwoGroupsMinBytes = 256ull << 20;
 
 constexpr uint32_t kKnownFlags = OT_B200_FROM_LOG_SOFTMAX | OT_B200_ONE_SYM_PER_FRAME |
                                  OT_B200_FP64 | OT_B200_CHECK_INPUTS | OT_B200_FAST_MATH |
                                  OT_B200_SCALE_PER_UTTERANCE | OT_B200_SHARE_SMS |
-                                 OT_B200_BF16 | OT_B200_FP16 | OT_B200_TRACE;
+                                 OT_B200_BF16 | OT_B200_FP16 | OT_B200_TRACE |
+                                 OT_B200_REPORT_ERRORS;
 
 int check_sizes(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   if (N <= 0) return fail(OT_B200_ERR_ARGUMENT, "N must be positive, got %d", N);
@@ -116,26 +201,42 @@ int check_common(int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blan
 
 void set_last_error(const char *msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
 
+int begin_reported_call(uint32_t flags, int32_t **sticky, int32_t *seq) {
+  *sticky = nullptr;
+  *seq = 0;
+  if (!(flags & OT_B200_REPORT_ERRORS)) return OT_B200_OK;
+  ReportBlock *rep = nullptr;
+  const int rc = get_reports(&rep);
+  if (rc) return rc;
+  int32_t index = 0, failed = 0;
+  const int code = take_sticky(rep, &index, &failed);
+  if (code) return fail_earlier(code, index, failed);
+  *sticky = rep->dev + 4 * kReportSlots;
+  *seq = (int32_t)((rep->seq.fetch_add(1, std::memory_order_relaxed) + 1) & 0x7fffffffu);
+  return OT_B200_OK;
+}
+
 bool wave_grids() {
-  static int cached = -1;
-  if (cached < 0) {
+  static std::atomic<int> cached{-1};
+  int c = cached.load(std::memory_order_relaxed);
+  if (c < 0) {
     const char *e = getenv("OT_B200_GRID");
-    cached = (e && strcmp(e, "wave") == 0) ? 1 : 0;
+    c = (e && strcmp(e, "wave") == 0) ? 1 : 0;
+    cached.store(c, std::memory_order_relaxed);
   }
-  return cached == 1;
+  return c == 1;
 }
 
 int sm_count() {
-  static int cached[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (cached[dev] == 0) {
-    int n = 0;
+  static std::atomic<int> cached[kMaxDevices];  // zero-initialised
+  const int dev = current_device_slot();
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    cached[dev] = n > 0 ? n : 148;
+    n = n > 0 ? n : 148;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
 Layout make_layout(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
@@ -165,6 +266,124 @@ Layout make_layout(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   l.total = off;
   return l;
 }
+
+namespace {
+
+// Error reports for a forward half: takes a pending record of an earlier call
+// (OT_B200_REPORT_ERRORS: returns OT_B200_ERR_INPUT, nothing must be launched),
+// numbers this call and points the problem at its report words.  *slot: the
+// host words a blocking call (OT_B200_CHECK_INPUTS) polls, else NULL.
+int attach_reports(Problem *p, uint32_t flags, cudaStream_t s, volatile int32_t **slot) {
+  *slot = nullptr;
+  const bool blocking = flags & OT_B200_CHECK_INPUTS;
+  const bool deferred = flags & OT_B200_REPORT_ERRORS;
+  if (!blocking && !deferred) return OT_B200_OK;
+  if (blocking) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaError_t e = cudaStreamIsCapturing(s, &cap);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaStreamIsCapturing");
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(OT_B200_ERR_ARGUMENT, "OT_B200_CHECK_INPUTS cannot be used while the stream is being captured");
+  }
+  ReportBlock *rep = nullptr;
+  int rc = get_reports(&rep);
+  if (rc) return rc;
+  if (deferred) {
+    int32_t index = 0, seq = 0;
+    const int code = take_sticky(rep, &index, &seq);
+    if (code) return fail_earlier(code, index, seq);
+    p->sticky = rep->dev + 4 * kReportSlots;
+  }
+  const uint32_t seq = rep->seq.fetch_add(1, std::memory_order_relaxed) + 1;
+  p->report_seq = (int32_t)(seq & 0x7fffffffu);
+  if (blocking) {
+    const int i = (int)(seq % kReportSlots);
+    *slot = rep->host.load(std::memory_order_acquire) + 4 * i;
+    p->report = rep->dev + 4 * i;
+  }
+  return OT_B200_OK;
+}
+
+// The whole call as two groups of utterances on three streams, so that the
+// recursion of one group (a latency chain that keeps a few dozen SMs busy and
+// the memory system idle) runs under the streaming kernels of the other:
+//
+//   caller's stream   K0  K1(a) ..........  K3(a) .............        close
+//   side                  K1(b) ..........          K3(b) .............
+//   urgent                      K2(a) K2c(a)  K2(b) K2c(b)
+//
+// Group a = the utterances that end at or before row r1 (half the batch), group
+// b = the rest; stage 1 is cut at r1 itself.  Only events order the streams; the
+// host never waits.  What the order relies on, as measured on B200: kernels of
+// equal priority are dispatched in arrival order (a later kernel gets SM slots
+// once the earlier one has handed out all its blocks), so K1(b) fills the tail
+// of K1(a) and K3(b) that of K3(a) without slowing them; the recursions and the
+// coefficient kernels sit on a highest-priority stream, so their few blocks are
+// placed at once, under whichever streaming kernel is running.  Results are
+// bitwise those of the one-stream schedule.
+int run_two_groups(Problem p, void *d_grad, void *d_scores, void *d_loss, double loss_scale,
+                   double grad_scale, cudaStream_t s) {
+  const int dev = current_device_slot();
+  Pipeline &pl = g_pipelines[dev];
+  std::lock_guard<std::mutex> guard(pl.lock);
+  cudaError_t e = pipeline_init(pl);
+  if (e != cudaSuccess) return fail_cuda(e, "create the streams of the two-group schedule");
+  const int64_t r1 = (p.rows / 2) & ~int64_t(15);  // a multiple of the stage-1 tile height
+  p.group_row = r1;
+  Problem a = p, b = p;
+  a.group = 0; a.row_begin = 0; a.row_end = r1;
+  b.group = 1; b.row_begin = r1; b.row_end = p.rows;
+#define OTB_TRY(call, what)                          \
+  do {                                               \
+    e = (call);                                      \
+    if (e != cudaSuccess) return fail_cuda(e, what); \
+  } while (0)
+  OTB_TRY(launch_prepare(p, s), "launch prepare");
+  OTB_TRY(cudaEventRecord(pl.ev[0], s), "record");
+  OTB_TRY(launch_logprob(a, s), "launch logprob");
+  OTB_TRY(cudaEventRecord(pl.ev[1], s), "record");
+  OTB_TRY(cudaStreamWaitEvent(pl.side, pl.ev[0], 0), "wait");      // stage 1 of group b needs stage 0 only
+  OTB_TRY(launch_logprob(b, pl.side), "launch logprob");
+  OTB_TRY(cudaEventRecord(pl.ev[2], pl.side), "record");
+  OTB_TRY(cudaStreamWaitEvent(pl.urgent, pl.ev[1], 0), "wait");
+  OTB_TRY(launch_lattice(a, d_scores, pl.urgent), "launch lattice");
+  OTB_TRY(launch_coef(a, d_scores, nullptr, 1.0, pl.urgent), "launch coef");
+  OTB_TRY(cudaEventRecord(pl.ev[3], pl.urgent), "record");
+  OTB_TRY(cudaStreamWaitEvent(s, pl.ev[3], 0), "wait");
+  OTB_TRY(launch_gradient(a, d_grad, nullptr, grad_scale, s), "launch gradient");
+  // The utterance that straddles r1 belongs to group b and has rows on either
+  // side of the cut: its recursion needs both halves of stage 1 (the urgent
+  // stream has already waited for the first).
+  OTB_TRY(cudaStreamWaitEvent(pl.urgent, pl.ev[2], 0), "wait");
+  OTB_TRY(launch_lattice(b, d_scores, pl.urgent), "launch lattice");
+  OTB_TRY(launch_coef(b, d_scores, nullptr, 1.0, pl.urgent), "launch coef");
+  OTB_TRY(cudaEventRecord(pl.ev[4], pl.urgent), "record");
+  OTB_TRY(cudaStreamWaitEvent(pl.side, pl.ev[4], 0), "wait");
+  OTB_TRY(launch_gradient(b, d_grad, nullptr, grad_scale, pl.side), "launch gradient");
+  OTB_TRY(cudaEventRecord(pl.ev[5], pl.side), "record");
+  OTB_TRY(cudaStreamWaitEvent(s, pl.ev[5], 0), "wait");
+  OTB_TRY(launch_close(p, d_scores, d_loss, loss_scale, s), "launch close");
+#undef OTB_TRY
+  return OT_B200_OK;
+}
+
+// Waits (bounded) for the verdict of a call made with OT_B200_CHECK_INPUTS.
+int wait_for_verdict(volatile int32_t *slot, int32_t want, cudaStream_t s) {
+  const auto t0 = std::chrono::steady_clock::now();
+  long spins = 0;
+  while (slot[2] != want) {
+    if ((++spins & 1023) == 0) {
+      if (cudaStreamQuery(s) == cudaSuccess && slot[2] != want)
+        return fail(OT_B200_ERR_CUDA, "the forward half did not report although the stream is idle");
+      if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(60))
+        return fail(OT_B200_ERR_CUDA, "timed out waiting for the report of the forward half");
+    }
+  }
+  if (slot[kStatusCode] != 0) return fail_verdict(slot[kStatusCode], slot[kStatusIndex]);
+  return OT_B200_OK;
+}
+
+}  // namespace
 
 }  // namespace otb
 
@@ -224,21 +443,10 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
   p.ws = static_cast<char *>(d_workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  StatusSlot *slot = nullptr;
-  if (flags & OT_B200_CHECK_INPUTS) {
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    cudaError_t e = cudaStreamIsCapturing(s, &cap);
-    if (e != cudaSuccess) return fail_cuda(e, "cudaStreamIsCapturing");
-    if (cap != cudaStreamCaptureStatusNone)
-      return fail(OT_B200_ERR_ARGUMENT, "OT_B200_CHECK_INPUTS cannot be used while the stream is being captured");
-    rc = get_slot(&slot);
-    if (rc) return rc;
-  }
+  volatile int32_t *slot = nullptr;
+  rc = attach_reports(&p, flags, s, &slot);
+  if (rc) return rc;
 
-  if (slot) {
-    p.host_status = slot->dev;
-    p.host_seq = ++slot->seq;
-  }
   cudaError_t e = launch_prepare(p, s);
   if (e != cudaSuccess) return fail_cuda(e, "launch prepare");
   e = launch_logprob(p, s);
@@ -247,25 +455,10 @@ int ot_b200_forward(const void *d_logits, const int32_t *d_targets,
   if (e != cudaSuccess) return fail_cuda(e, "launch lattice");
   e = launch_coef(p, d_scores, d_loss, loss_scale, s);
   if (e != cudaSuccess) return fail_cuda(e, "launch coef");
-  if (slot) {
-    // Everything has been enqueued; now wait until stage 0 of THIS call has
-    // reported (it runs as soon as the stream reaches it).  Bounded: 60 s.
-    const int32_t want = slot->seq;
-    const auto t0 = std::chrono::steady_clock::now();
-    long spins = 0;
-    while (slot->host[2] != want) {
-      if ((++spins & 1023) == 0) {
-        if (cudaStreamQuery(s) == cudaSuccess && slot->host[2] != want)
-          return fail(OT_B200_ERR_CUDA, "the input check did not report although the stream is idle");
-        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(60))
-          return fail(OT_B200_ERR_CUDA, "timed out waiting for the input check");
-      }
-    }
-    if (slot->host[kStatusCode] != 0)
-      return fail(OT_B200_ERR_INPUT, "input check failed (code %d, utterance %d): %s",
-                  slot->host[kStatusCode], slot->host[kStatusIndex],
-                  input_error_text(slot->host[kStatusCode]));
-  }
+  // Everything has been enqueued; with OT_B200_CHECK_INPUTS wait until the last
+  // forward kernel of THIS call has delivered the verdict (bounded: the stream
+  // going idle without a report, or 60 s).
+  if (slot) return wait_for_verdict(slot, p.report_seq, s);
   return OT_B200_OK;
 }
 
@@ -283,11 +476,81 @@ int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows
     return fail(OT_B200_ERR_ARGUMENT, "with OT_B200_FROM_LOG_SOFTMAX the gradient needs its own buffer");
   if ((flags & OT_B200_SCALE_PER_UTTERANCE) && !d_scale)
     return fail(OT_B200_ERR_ARGUMENT, "OT_B200_SCALE_PER_UTTERANCE needs d_scale (N factors)");
+  if (flags & OT_B200_REPORT_ERRORS) {
+    ReportBlock *rep = nullptr;
+    rc = get_reports(&rep);
+    if (rc) return rc;
+    int32_t index = 0, seq = 0;
+    const int code = take_sticky(rep, &index, &seq);
+    if (code) return fail_earlier(code, index, seq);
+  }
   p.logits = d_logits; p.targets = nullptr; p.T = nullptr; p.U = nullptr;
   p.N = N; p.rows = rows; p.V = V; p.max_u = max_u; p.blank = blank; p.flags = flags;
   p.ws = static_cast<char *>(const_cast<void *>(d_workspace));
   cudaError_t e = launch_gradient(p, d_grad, d_scale, scale_host, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail_cuda(e, "launch gradient");
+  return OT_B200_OK;
+}
+
+int ot_b200_loss_and_gradient(const void *d_logits, void *d_grad, const int32_t *d_targets,
+                              const int32_t *d_logit_lengths, const int32_t *d_target_lengths,
+                              int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blank,
+                              uint32_t flags, void *d_workspace, uint64_t workspace_bytes,
+                              void *d_scores, void *d_loss, double loss_scale, double grad_scale,
+                              void *stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool mode_b = flags & OT_B200_FROM_LOG_SOFTMAX;
+  const uint64_t es = (flags & OT_B200_FP64) ? 8 : ((flags & (OT_B200_BF16 | OT_B200_FP16)) ? 2 : 4);
+  bool two = d_grad != nullptr && !mode_b && N >= 2 && rows >= 64 && V > 0 &&
+             (uint64_t)rows * (uint64_t)V * es >= kTwoGroupsMinBytes && two_groups_allowed();
+  if (two) {  // not while the stream is being captured: the schedule spans three streams
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) two = false;
+  }
+  if (!two) {
+    int rc = ot_b200_forward(d_logits, d_targets, d_logit_lengths, d_target_lengths, N, rows, V,
+                             max_u, blank, flags, d_workspace, workspace_bytes, d_scores, d_loss,
+                             loss_scale, stream);
+    if (rc || !d_grad) return rc;
+    return ot_b200_backward(d_logits, d_grad, N, rows, V, max_u, blank,
+                            flags & ~(OT_B200_CHECK_INPUTS | OT_B200_REPORT_ERRORS), d_workspace,
+                            workspace_bytes, nullptr, grad_scale, stream);
+  }
+  Problem p;
+  int rc = check_common(N, rows, V, max_u, blank, flags, d_workspace, workspace_bytes, &p.lay);
+  if (rc) return rc;
+  if (!d_logits || !d_logit_lengths || !d_target_lengths || !d_scores)
+    return fail(OT_B200_ERR_ARGUMENT, "a required device pointer is NULL");
+  if (max_u > 0 && !d_targets) return fail(OT_B200_ERR_ARGUMENT, "targets pointer is NULL");
+  if (reinterpret_cast<uintptr_t>(d_logits) % es != 0)
+    return fail(OT_B200_ERR_ARGUMENT, "logits pointer is not aligned to its element size");
+  p.logits = d_logits; p.targets = d_targets; p.T = d_logit_lengths; p.U = d_target_lengths;
+  p.N = N; p.rows = rows; p.V = V; p.max_u = max_u; p.blank = blank; p.flags = flags;
+  p.ws = static_cast<char *>(d_workspace);
+  volatile int32_t *slot = nullptr;
+  rc = attach_reports(&p, flags, s, &slot);
+  if (rc) return rc;
+  rc = run_two_groups(p, d_grad, d_scores, d_loss, loss_scale, grad_scale, s);
+  if (rc) return rc;
+  if (slot) return wait_for_verdict(slot, p.report_seq, s);
+  return OT_B200_OK;
+}
+
+int ot_b200_scale_gradient(void *d_grad, int64_t count, const void *d_scale, uint32_t flags,
+                           void *stream) {
+  if (!d_grad || !d_scale || count <= 0)
+    return fail(OT_B200_ERR_ARGUMENT, "ot_b200_scale_gradient: NULL pointer or count <= 0");
+  const uint32_t types = flags & (OT_B200_FP64 | OT_B200_BF16 | OT_B200_FP16);
+  if ((flags & ~(OT_B200_FP64 | OT_B200_BF16 | OT_B200_FP16 | OT_B200_REPORT_ERRORS)) || (types & (types - 1)))
+    return fail(OT_B200_ERR_ARGUMENT, "ot_b200_scale_gradient: flags may hold one of OT_B200_FP64/BF16/FP16 and OT_B200_REPORT_ERRORS");
+  {  // a pending record of a failed call (the forward half of this very loss, perhaps) is raised here
+    int32_t *sticky = nullptr;
+    int32_t seq = 0;
+    const int rc = begin_reported_call(flags, &sticky, &seq);
+    if (rc) return rc;
+  }
+  const cudaError_t e = launch_scale(d_grad, count, d_scale, flags, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda(e, "launch scale");
   return OT_B200_OK;
 }
 
@@ -298,12 +561,27 @@ int ot_b200_compute_transducer_loss(const void *d_logits, void *d_grad,
                                     int64_t rows, int32_t V, int32_t max_u, int32_t blank,
                                     uint32_t flags, void *d_workspace,
                                     uint64_t workspace_bytes, void *d_scores, void *stream) {
-  int rc = ot_b200_forward(d_logits, d_targets, d_logit_lengths, d_target_lengths, N, rows,
-                           V, max_u, blank, flags, d_workspace, workspace_bytes, d_scores,
-                           nullptr, 1.0, stream);
-  if (rc || !d_grad) return rc;
-  return ot_b200_backward(d_logits, d_grad, N, rows, V, max_u, blank, flags, d_workspace,
-                          workspace_bytes, nullptr, 1.0, stream);
+  return ot_b200_loss_and_gradient(d_logits, d_grad, d_targets, d_logit_lengths, d_target_lengths,
+                                   N, rows, V, max_u, blank, flags, d_workspace, workspace_bytes,
+                                   d_scores, nullptr, 1.0, 1.0, stream);
+}
+
+int ot_b200_poll_errors(int32_t *code_out, int32_t *index_out, int32_t *seq_out, void *stream,
+                        int32_t wait) {
+  if (wait) {
+    const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda(e, "synchronize");
+  }
+  ReportBlock *rep = nullptr;
+  const int rc = get_reports(&rep);
+  if (rc) return rc;
+  int32_t index = 0, seq = 0;
+  const int code = take_sticky(rep, &index, &seq);
+  if (code_out) *code_out = code;
+  if (index_out) *index_out = index;
+  if (seq_out) *seq_out = seq;
+  if (code) fail_earlier(code, index, seq);  // leaves the message for ot_b200_last_error()
+  return OT_B200_OK;
 }
 
 int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes,
@@ -320,9 +598,7 @@ int ot_b200_read_input_status(const void *d_workspace, uint64_t workspace_bytes,
   if (e != cudaSuccess) return fail_cuda(e, "synchronize");
   *code_out = host[0];
   if (index_out) *index_out = host[1];
-  if (host[0] != 0)
-    fail(OT_B200_ERR_INPUT, "input check failed (code %d, utterance %d): %s", host[0], host[1],
-         input_error_text(host[0]));
+  if (host[0] != 0) fail_verdict(host[0], host[1]);
   return OT_B200_OK;
 }
 

@@ -59,11 +59,20 @@ __global__ void __launch_bounds__(kThreads, MINB)
 gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restrict__ coef,
                 const int32_t *__restrict__ status, int64_t rows, int V,
                 int blank, const typename Real<X>::type *__restrict__ d_scale,
-                typename Real<X>::type scale_host, bool eager) {
+                typename Real<X>::type scale_host, bool eager,
+                const int64_t *__restrict__ split, int N, int group) {
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
-  if (threadIdx.x == 0) trace_begin(status, kStageGradient);
+  // The rows of this launch: all of them, or those of one group of utterances.
+  int64_t row_lo = 0;
+  if (group >= 0) {
+    int lo, hi;
+    group_range(status, group, N, lo, hi);
+    row_lo = __ldg(split + lo);
+    rows = __ldg(split + hi);
+  }
+  if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageGradient, group));
   using T = typename Real<X>::type;
   using VT = typename VecOf<X, VEC>::type;
   const int lane = threadIdx.x & 31;
@@ -73,7 +82,7 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
   const T scale_all = (!PER_UTT && d_scale) ? scale_host * __ldg(d_scale) : scale_host;
   const int bvec = blank / VEC, bk = blank % VEC;
 
-  for (int64_t row = rows - 1 - warp0; row >= 0; row -= nwarps) {
+  for (int64_t row = rows - 1 - warp0; row >= row_lo; row -= nwarps) {
     const CoefA<T> rec = load_coef(coef + row);
     const T scale = PER_UTT ? scale_host * __ldg(d_scale + rec.utt) : scale_all;
     const X *px = x + row * (int64_t)V;
@@ -100,6 +109,7 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
     }
     const int tvec = rec.tgt >= 0 ? rec.tgt / VEC : -1;
     const int tk = rec.tgt >= 0 ? rec.tgt % VEC : 0;
+    [[maybe_unused]] const float k2 = (float)((rec.c + rec.beta) * (T)kLog2e);  // 16-bit rows, see below
     for (int base = 0; base < nvec; base += kWarp * CH) {
       if (!(eager && base == 0)) {
 #pragma unroll
@@ -147,7 +157,19 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
         const int vi = base + j * kWarp + lane;
         if (vi < nvec) {
           X *e = reinterpret_cast<X *>(&v[j]);
-          if constexpr (sizeof(X) == 2) {
+          if constexpr (sizeof(X) == 2 && VEC == 4) {
+            // One FFMA, one ex2, one multiply per element and one conversion per
+            // pair: the row's constants are folded, 2^(x*log2e + (c+beta)*log2e).
+            // (Folding c + beta rounds once at the magnitude of the log-likelihood,
+            // as x + c does in the float pass; far below half an ulp of a 16-bit result.)
+            uint32_t *w = reinterpret_cast<uint32_t *>(&v[j]);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const float2 a = Pair16<X>::widen(w[h]);
+              w[h] = Pair16<X>::round(ex2_approx(fmaf(a.x, kLog2e, k2)) * scale,
+                                      ex2_approx(fmaf(a.y, kLog2e, k2)) * scale);
+            }
+          } else if constexpr (sizeof(X) == 2) {
 #pragma unroll
             for (int k = 0; k < VEC; ++k)
               e[k] = from_real<X>(s_exp((to_real(e[k]) + rec.c) + rec.beta) * scale);
@@ -173,7 +195,7 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
       }
     }
   }
-  if (threadIdx.x == 0) trace_end(status, kStageGradient);
+  if (threadIdx.x == 0) trace_end(status, trace_slot(kStageGradient, group));
 }
 
 template <typename X, int VEC, bool PER_UTT>
@@ -239,12 +261,16 @@ gradient_logsoftmax_kernel(X *__restrict__ g, const CoefB<typename Real<X>::type
 // Blocks for `units` warp-sized units of work (8 per block): all of them, or,
 // with OT_B200_GRID=wave, at most one resident wave (the kernels loop).
 template <typename K>
-unsigned stream_grid(K kernel, int *per_sm, int64_t units, uint32_t flags, bool one_wave = false) {
+unsigned stream_grid(K kernel, std::atomic<int> *per_sm_cache, int64_t units, uint32_t flags, bool one_wave = false) {
   int64_t want = (units + (kThreads / kWarp) - 1) / (kThreads / kWarp);
   if (want < 1) want = 1;
   if (one_wave || wave_grids()) {
-    if (*per_sm == 0) *per_sm = blocks_per_sm(kernel, kThreads);
-    const int64_t cap = (int64_t)resident_sms(flags) * *per_sm;
+    int per_sm = per_sm_cache->load(std::memory_order_relaxed);
+    if (per_sm == 0) {
+      per_sm = blocks_per_sm(kernel, kThreads);
+      per_sm_cache->store(per_sm, std::memory_order_relaxed);
+    }
+    const int64_t cap = (int64_t)resident_sms(flags) * per_sm;
     if (want > cap) want = cap;
   }
   return (unsigned)(want < 0x7fffffff ? want : 0x7fffffff);
@@ -254,7 +280,7 @@ template <typename X, int VEC, int CH, bool PER_UTT>
 cudaError_t launch_grad_a2(const Problem &p, void *grad, const void *d_scale,
                            double scale_host, cudaStream_t s) {
   using T = typename Real<X>::type;
-  static int per_sm = 0;
+  static std::atomic<int> per_sm{0};
   // Six resident blocks per SM (40 registers) for the vectorised passes: with
   // short-lived blocks the bytes in flight are (resident warps) x (one row), and
   // the step from 5 to 6 blocks took the float pass from 436 to 408 us on
@@ -265,13 +291,18 @@ cudaError_t launch_grad_a2(const Problem &p, void *grad, const void *d_scale,
   auto kernel = gradient_kernel<X, VEC, CH, PER_UTT, kMinBlocks>;
   // 16-bit rows are half as many bytes per warp; there one resident wave that
   // strides over the buffer measured faster (277 against 289 us on bf16 cfg2).
+  // A group launch is sized for the rows the host knows the group cannot exceed
+  // by much (group 0 ends at or before group_row; group 1 starts at the utterance
+  // that straddles it): the kernel strides, so a few blocks take a second row.
+  const int64_t span = p.group == 0 ? p.group_row : (p.group == 1 ? p.rows - p.group_row : p.rows);
   const cudaError_t e = launch_pdl(kernel,
-      stream_grid(kernel, &per_sm, p.rows, p.flags, sizeof(X) == 2), (unsigned)kThreads, 0, s,
+      stream_grid(kernel, &per_sm, span > 0 ? span : 1, p.flags, sizeof(X) == 2), (unsigned)kThreads, 0, s,
       static_cast<const X *>(p.logits), static_cast<X *>(grad),
       reinterpret_cast<const CoefA<T> *>(p.ws + p.lay.coef),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V,
       p.blank, static_cast<const T *>(d_scale), (T)scale_host,
-      (p.flags & OT_B200_ONE_SYM_PER_FRAME) == 0);
+      (p.flags & OT_B200_ONE_SYM_PER_FRAME) == 0,
+      reinterpret_cast<const int64_t *>(p.ws + p.lay.split), p.N, p.group);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
@@ -287,7 +318,7 @@ template <typename X, int VEC, bool PER_UTT>
 cudaError_t launch_grad_b(const Problem &p, void *grad, const void *d_scale,
                           double scale_host, cudaStream_t s) {
   using T = typename Real<X>::type;
-  static int per_sm = 0;
+  static std::atomic<int> per_sm{0};
   auto kernel = gradient_logsoftmax_kernel<X, VEC, PER_UTT>;
   const int64_t chunks = (p.rows * (int64_t)(p.V / VEC) + 127) / 128;  // 128 vectors per warp, see the kernel
   kernel<<<stream_grid(kernel, &per_sm, chunks, p.flags), kThreads, 0, s>>>(
@@ -324,7 +355,54 @@ cudaError_t launch_gradient_t(const Problem &p, void *grad, const void *d_scale,
   return launch_grad_a<X, 1, 8>(p, grad, d_scale, scale_host, s);
 }
 
+// g *= *d_scale, unless the factor is exactly 1: then every block returns after
+// one load and the buffer is not touched.  The counterpart of the reference's
+// `ctx.grad.mul_(loss_grad)` (transducer_loss.py:162) for a gradient that was
+// computed eagerly: the usual upstream gradient of a loss is 1.
+template <typename X>
+__global__ void __launch_bounds__(kThreads)
+scale_gradient_kernel(X *__restrict__ g, int64_t count, const typename Real<X>::type *__restrict__ d_scale) {
+  using T = typename Real<X>::type;
+  const T scale = __ldg(d_scale);
+  if (scale == (T)1) return;
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  const int64_t first = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  constexpr int VEC = 16 / (int)sizeof(X);
+  if (reinterpret_cast<uintptr_t>(g) % 16 == 0) {
+    const int64_t nvec = count / VEC;
+    uint4 *gv = reinterpret_cast<uint4 *>(g);
+    for (int64_t i = first; i < nvec; i += stride) {
+      uint4 v = gv[i];
+      X *e = reinterpret_cast<X *>(&v);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) e[k] = from_real<X>(to_real(e[k]) * scale);
+      gv[i] = v;
+    }
+    for (int64_t i = nvec * VEC + first; i < count; i += stride) g[i] = from_real<X>(to_real(g[i]) * scale);
+  } else {
+    for (int64_t i = first; i < count; i += stride) g[i] = from_real<X>(to_real(g[i]) * scale);
+  }
+}
+
+template <typename X>
+cudaError_t launch_scale_t(void *g, int64_t count, const void *d_scale, cudaStream_t s) {
+  // one resident wave: with the factor 1 the launch must cost next to nothing
+  const int64_t want = (count / (16 / (int64_t)sizeof(X)) + kThreads - 1) / kThreads;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  const unsigned grid = (unsigned)(want < 1 ? 1 : (want < cap ? want : cap));
+  scale_gradient_kernel<X><<<grid, kThreads, 0, s>>>(static_cast<X *>(g), count,
+      static_cast<const typename Real<X>::type *>(d_scale));
+  return cudaGetLastError();
+}
+
 }  // namespace
+
+cudaError_t launch_scale(void *g, int64_t count, const void *d_scale, uint32_t flags, cudaStream_t s) {
+  if (flags & OT_B200_FP64) return launch_scale_t<double>(g, count, d_scale, s);
+  if (flags & OT_B200_BF16) return launch_scale_t<__nv_bfloat16>(g, count, d_scale, s);
+  if (flags & OT_B200_FP16) return launch_scale_t<__half>(g, count, d_scale, s);
+  return launch_scale_t<float>(g, count, d_scale, s);
+}
 
 cudaError_t launch_gradient(const Problem &p, void *grad, const void *d_scale,
                             double scale_host, cudaStream_t s) {

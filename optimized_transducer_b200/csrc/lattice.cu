@@ -42,7 +42,6 @@ namespace {
 
 constexpr int kMaxWarps = 32;
 constexpr int kStages = 3;
-constexpr int kStatusLatticeTimeout = 2;  // status word: a bulk copy never arrived
 constexpr int kChunkBytes = 16384;         // target size of one staged chunk
 
 // Barrier over the first `nthreads` threads of the CTA (the warps that own a
@@ -82,7 +81,7 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
                const int32_t *__restrict__ Ul, const int64_t *__restrict__ cell_split,
                int32_t *__restrict__ status, T *__restrict__ alpha,
                T *__restrict__ beta, T *__restrict__ scores,
-               T *__restrict__ scores_beta, int rows_per_chunk, int stage_pairs) {
+               T *__restrict__ scores_beta, int rows_per_chunk, int stage_pairs, int group) {
   using P = typename Pair<T>::type;
   extern __shared__ __align__(128) unsigned char stage_mem[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
@@ -91,6 +90,11 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
   const int b = blockIdx.x >> 1;
+  {
+    int lo, hi;
+    group_range(status, group, (int)(gridDim.x >> 1), lo, hi);
+    if (b < lo || b >= hi) return;  // an utterance of the other group
+  }
   const bool backward = blockIdx.x & 1;
   const int Tn = Tl[b], U = Ul[b], U1 = U + 1;
   const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
@@ -148,7 +152,7 @@ lattice_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     // barriers of the steps early, so nothing can hang).
     for (int spin = 0; spin < (1 << 22); ++spin)
       if (mbar_try_wait(bar, parity)) return;
-    atomicCAS(status + kStatusLatticeTimeout, 0, 1 + b);
+    atomicCAS(status + kStatusCopyTimeout, 0, 1 + b);
   };
   int xs = 0;
   const T ninf = neg_inf<T>();
@@ -281,7 +285,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
                     const int32_t *__restrict__ Ul, const int64_t *__restrict__ cell_split,
                     int32_t *__restrict__ status, T *__restrict__ alpha,
                     T *__restrict__ beta, T *__restrict__ scores,
-                    T *__restrict__ scores_beta, int K, int stage_pairs, int nstages) {
+                    T *__restrict__ scores_beta, int K, int stage_pairs, int nstages, int group) {
   using P = typename Pair<T>::type;
   extern __shared__ __align__(128) unsigned char stage_mem[];
   __shared__ __align__(8) uint64_t full_bar[kSkewMaxStages];
@@ -295,7 +299,12 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   const int Tn = Tl[b], U = Ul[b], U1 = U + 1;
   const int64_t off = cell_split[b];
   if (bad != 0) return;
-  if (threadIdx.x == 0) trace_begin(status, kStageLattice);
+  {
+    int lo, hi;
+    group_range(status, group, (int)(gridDim.x >> 1), lo, hi);
+    if (b < lo || b >= hi) return;  // an utterance of the other group
+  }
+  if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageLattice, group));
   const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
   const int nwarps = (U1 + kWarp - 1) / kWarp;
   if (warp >= nwarps) return;
@@ -341,7 +350,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     const uint32_t parity = (uint32_t)((j / nstages) & 1);
     for (int spin = 0; spin < (1 << 22); ++spin)
       if (mbar_try_wait(bar, parity)) return;
-    atomicCAS(status + kStatusLatticeTimeout, 0, 1 + b);  // bounded: report and carry on
+    atomicCAS(status + kStatusCopyTimeout, 0, 1 + b);  // bounded: report and carry on
   };
 
   if (!backward) {
@@ -416,7 +425,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       if (nwarps > 1) bar_active(nact); else __syncwarp();
     }
     if (u == U) scores[b] = own + fin_blank;  // column U's last step is the last step
-    if (u == 0) trace_end(status, kStageLattice);
+    if (u == 0) trace_end(status, trace_slot(kStageLattice, group));
   } else {
     // ------------------------------- beta ------------------------------
     const bool produce = (lane == 0) && (warp > 0);
@@ -489,7 +498,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       if (nwarps > 1) bar_active(nact); else __syncwarp();
     }
     if (u == 0) scores_beta[b] = own;  // column 0's last step is the last step
-    if (u == 0) trace_end(status, kStageLattice);
+    if (u == 0) trace_end(status, trace_slot(kStageLattice, group));
   }
 }
 
@@ -502,11 +511,16 @@ lattice_generic_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
                        const int32_t *__restrict__ Ul,
                        const int64_t *__restrict__ cell_split,
                        const int32_t *__restrict__ status, T *alpha, T *beta,
-                       T *__restrict__ scores, T *__restrict__ scores_beta) {
+                       T *__restrict__ scores, T *__restrict__ scores_beta, int group) {
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
   const int b = blockIdx.x >> 1;
+  {
+    int lo, hi;
+    group_range(status, group, (int)(gridDim.x >> 1), lo, hi);
+    if (b < lo || b >= hi) return;  // an utterance of the other group
+  }
   const bool backward = blockIdx.x & 1;
   const int Tn = Tl[b], U = Ul[b], U1 = U + 1;
   const int64_t off = cell_split[b];
@@ -578,12 +592,14 @@ lattice_generic_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
 constexpr size_t kSkewSmemBudget = 160 * 1024;
 
 bool lockstep_forced() {
-  static int cached = -1;
-  if (cached < 0) {
+  static std::atomic<int> cached{-1};
+  int c = cached.load(std::memory_order_relaxed);
+  if (c < 0) {
     const char *e = getenv("OT_B200_LATTICE");
-    cached = (e && strcmp(e, "lockstep") == 0) ? 1 : 0;
+    c = (e && strcmp(e, "lockstep") == 0) ? 1 : 0;
+    cached.store(c, std::memory_order_relaxed);
   }
-  return cached == 1;
+  return c == 1;
 }
 
 // Returns cudaErrorNotSupported when the lattice is too wide for the skewed kernel.
@@ -603,14 +619,10 @@ cudaError_t launch_skewed(const Problem &p, void *scores, cudaStream_t s) {
     if (smem <= kSkewSmemBudget) break;
   }
   if (K < 2 || lockstep_forced()) return cudaErrorNotSupported;
-  static size_t granted[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (smem > granted[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static SmemGrant grant;  // per device: dynamic shared memory opted in so far
+  {
+    const cudaError_t e = grant.ensure(kernel, smem);
     if (e != cudaSuccess) return e;
-    granted[dev] = smem;
   }
   const cudaError_t le = launch_pdl(kernel, 2u * (unsigned)p.N, (unsigned)(nwarps * kWarp), smem, s,
       reinterpret_cast<const T *>(p.ws + p.lay.lp), p.T, p.U,
@@ -618,7 +630,7 @@ cudaError_t launch_skewed(const Problem &p, void *scores, cudaStream_t s) {
       reinterpret_cast<int32_t *>(p.ws + p.lay.status),
       reinterpret_cast<T *>(p.ws + p.lay.alpha), reinterpret_cast<T *>(p.ws + p.lay.beta),
       static_cast<T *>(scores), reinterpret_cast<T *>(p.ws + p.lay.scores_beta), K, stage_pairs,
-      nstages);
+      nstages, p.group);
   return le != cudaSuccess ? le : cudaGetLastError();
 }
 
@@ -636,15 +648,11 @@ cudaError_t launch_staged(const Problem &p, void *scores, cudaStream_t s) {
   R = (R < 2) ? 2 : (R > 256 ? 256 : (R & ~1));
   const int stage_pairs = ((R * cols + 1) & ~1) + 2;  // + slack for the 16-byte round-up
   const size_t smem = ((size_t)kStages * stage_pairs + 2) * sizeof(P);
-  static size_t granted[64] = {0};  // per device: dynamic shared memory opted in so far
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
   // always opt in: static shared memory counts against the 48 KB default as well
-  if (smem > granted[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static SmemGrant grant;
+  {
+    const cudaError_t e = grant.ensure(kernel, smem);
     if (e != cudaSuccess) return e;
-    granted[dev] = smem;
   }
   const unsigned block = (unsigned)((cols + kWarp - 1) / kWarp * kWarp);
   const cudaError_t le = launch_pdl(kernel, 2u * (unsigned)p.N, block, smem, s,
@@ -652,7 +660,7 @@ cudaError_t launch_staged(const Problem &p, void *scores, cudaStream_t s) {
       reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
       reinterpret_cast<int32_t *>(p.ws + p.lay.status),
       reinterpret_cast<T *>(p.ws + p.lay.alpha), reinterpret_cast<T *>(p.ws + p.lay.beta),
-      static_cast<T *>(scores), reinterpret_cast<T *>(p.ws + p.lay.scores_beta), R, stage_pairs);
+      static_cast<T *>(scores), reinterpret_cast<T *>(p.ws + p.lay.scores_beta), R, stage_pairs, p.group);
   return le != cudaSuccess ? le : cudaGetLastError();
 }
 
@@ -669,8 +677,8 @@ cudaError_t launch_lattice_t(const Problem &p, void *scores, cudaStream_t s) {
     T *sb = reinterpret_cast<T *>(p.ws + p.lay.scores_beta);
     T *sa = static_cast<T *>(scores);
     const unsigned grid = 2u * (unsigned)p.N;
-    if (modified) lattice_generic_kernel<T, true><<<grid, 1024, 0, s>>>(lp, p.T, p.U, csplit, status, alpha, beta, sa, sb);
-    else lattice_generic_kernel<T, false><<<grid, 1024, 0, s>>>(lp, p.T, p.U, csplit, status, alpha, beta, sa, sb);
+    if (modified) lattice_generic_kernel<T, true><<<grid, 1024, 0, s>>>(lp, p.T, p.U, csplit, status, alpha, beta, sa, sb, p.group);
+    else lattice_generic_kernel<T, false><<<grid, 1024, 0, s>>>(lp, p.T, p.U, csplit, status, alpha, beta, sa, sb, p.group);
     return cudaGetLastError();
   }
   if (fast) return modified ? launch_staged<T, true, true>(p, scores, s) : launch_staged<T, true, false>(p, scores, s);

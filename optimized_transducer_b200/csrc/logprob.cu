@@ -75,13 +75,14 @@ __global__ void __launch_bounds__(kThreads, MINB)
 logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets,
                const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
                const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
-               const int32_t *__restrict__ status, int N, int64_t rows, int V,
+               const int32_t *__restrict__ status, int N, int64_t row_begin, int64_t rows, int V,
                int max_u, int blank, typename Real<X>::type *__restrict__ den,
                typename Real<X>::type *__restrict__ lp) {
+  // This launch covers the packed rows [row_begin, rows).
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
-  if (threadIdx.x == 0) trace_begin(status, kStageLogprob);
+  if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageLogprob, row_begin > 0 ? 1 : 0));
   using T = typename Real<X>::type;
   using VT = typename VecOf<X, VEC>::type;
   constexpr int kGroups = kWarp / LPR;  // rows a warp works on at once
@@ -92,10 +93,10 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
   const int64_t ngroups = (((int64_t)gridDim.x * kThreads) >> 5) * kGroups;
   const int nvec = V / VEC;
   const T ninf = neg_inf<T>();
-  const int64_t nruns = (rows + kRun - 1) / kRun;
+  const int64_t nruns = (rows - row_begin + kRun - 1) / kRun;
 
   for (int64_t run = group; run < nruns; run += ngroups) {
-    const int64_t r0 = run * kRun;
+    const int64_t r0 = row_begin + run * kRun;
     const int64_t r1 = (r0 + kRun < rows) ? r0 + kRun : rows;
     // Position of the run's first row; afterwards (b, t, u) advance with the rows.
     int b = find_utt(split, N, r0);
@@ -175,7 +176,7 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
       }
     }
   }
-  if (threadIdx.x == 0) trace_end(status, kStageLogprob);
+  if (threadIdx.x == 0) trace_end(status, trace_slot(kStageLogprob, row_begin > 0 ? 1 : 0));
 }
 
 // ---------------------------------------------------------------------------
@@ -192,15 +193,16 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
 constexpr int kTmaRows = 16;     // rows per tile = lane groups per block
 constexpr int kTmaStages = 3;
 constexpr int kTmaTiles = 16;    // tiles per block
-constexpr int kStatusCopyTimeout = 2;  // status word: a bulk copy never arrived
 
 template <typename X>
 __global__ void __launch_bounds__(kThreads, 2)
 logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets,
                    const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
                    const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
-                   int32_t *__restrict__ status, int N, int64_t rows, int V, int max_u,
-                   int blank, float *__restrict__ den, float *__restrict__ lp) {
+                   int32_t *__restrict__ status, int N, int64_t row_begin, int64_t rows, int V,
+                   int max_u, int blank, float *__restrict__ den, float *__restrict__ lp) {
+  // This launch covers the packed rows [row_begin, rows); row_begin is a multiple
+  // of the tile height, so every tile starts on a 16-byte boundary.
   extern __shared__ __align__(128) unsigned char tile_mem[];
   __shared__ __align__(8) uint64_t full_bar[kTmaStages];
   // The first tiles are requested BEFORE this grid waits for stage 0: they only
@@ -218,13 +220,13 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
   const float ninf = neg_inf<float>();
   const uint32_t row_bytes = (uint32_t)V * (uint32_t)sizeof(X);
   const uint32_t tile_bytes = kTmaRows * row_bytes;
-  const int64_t ntiles_all = (rows + kTmaRows - 1) / kTmaRows;
+  const int64_t ntiles_all = (rows - row_begin + kTmaRows - 1) / kTmaRows;
   const int64_t tile0 = (int64_t)blockIdx.x * kTmaTiles;
   const int ntiles = (int)((ntiles_all - tile0 < kTmaTiles) ? (ntiles_all - tile0) : kTmaTiles);
   if (ntiles <= 0) return;  // cannot happen with the launcher's grid
 
   auto issue = [&](int k) {  // thread 0 only
-    const int64_t r0 = (tile0 + k) * kTmaRows;
+    const int64_t r0 = row_begin + (tile0 + k) * kTmaRows;
     const int64_t nr = (rows - r0 < kTmaRows) ? (rows - r0) : kTmaRows;
     uint64_t *bar = &full_bar[k % kTmaStages];
     // a multiple of 16: V % 4 == 0, and for 16-bit rows the launcher requires an
@@ -251,10 +253,10 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
     __syncthreads();
     return;
   }
-  if (threadIdx.x == 0) trace_begin(status, kStageLogprob);
+  if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageLogprob, row_begin > 0 ? 1 : 0));
 
   // Position of this group's first row; it then advances by 16 rows per tile.
-  int64_t row = tile0 * kTmaRows + g;
+  int64_t row = row_begin + tile0 * kTmaRows + g;
   int b = 0, Tn = 1, U = 0, U1 = 1, t = 0, u = 0;
   int64_t next_split = 0, coff = 0;
   auto locate = [&]() {
@@ -285,9 +287,15 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
         const int vi = j * LPR + gl;
         if (vi < nvec) {
           const VT v = *reinterpret_cast<const VT *>(p + vi * 4);
-          const X *e = reinterpret_cast<const X *>(&v);
-          x[j * 4 + 0] = to_real(e[0]); x[j * 4 + 1] = to_real(e[1]);
-          x[j * 4 + 2] = to_real(e[2]); x[j * 4 + 3] = to_real(e[3]);
+          if constexpr (sizeof(X) == 2) {  // two words of two elements each
+            const uint32_t *w = reinterpret_cast<const uint32_t *>(&v);
+            const float2 a = Pair16<X>::widen(w[0]), b = Pair16<X>::widen(w[1]);
+            x[j * 4 + 0] = a.x; x[j * 4 + 1] = a.y; x[j * 4 + 2] = b.x; x[j * 4 + 3] = b.y;
+          } else {
+            const X *e = reinterpret_cast<const X *>(&v);
+            x[j * 4 + 0] = to_real(e[0]); x[j * 4 + 1] = to_real(e[1]);
+            x[j * 4 + 2] = to_real(e[2]); x[j * 4 + 3] = to_real(e[3]);
+          }
         } else {
           x[j * 4 + 0] = ninf; x[j * 4 + 1] = ninf; x[j * 4 + 2] = ninf; x[j * 4 + 3] = ninf;
         }
@@ -319,7 +327,7 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
       }
     }
   }
-  if (threadIdx.x == 0) trace_end(status, kStageLogprob);
+  if (threadIdx.x == 0) trace_end(status, trace_slot(kStageLogprob, row_begin > 0 ? 1 : 0));
 }
 
 // Log-softmax input: nothing to reduce, only the gather (thread per row).
@@ -353,10 +361,15 @@ cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
   // or six blocks spills the row buffer and is slower (forward 0.341 / 0.414 ms
   // against 0.314 ms on 686 128 rows of 500).
   auto kernel = logprob_kernel<X, VEC, CH, LPR, MODIFIED, 4>;
-  static int per_sm = 0;  // occupancy of this instantiation (same on every B200)
-  if (per_sm == 0) per_sm = blocks_per_sm(kernel, kThreads);
+  static std::atomic<int> per_sm_cache{0};  // occupancy of this instantiation (same on every B200)
+  int per_sm = per_sm_cache.load(std::memory_order_relaxed);
+  if (per_sm == 0) {
+    per_sm = blocks_per_sm(kernel, kThreads);
+    per_sm_cache.store(per_sm, std::memory_order_relaxed);
+  }
   constexpr int groups_per_block = (kThreads / kWarp) * (kWarp / LPR);
-  const int64_t nruns = (p.rows + kRun - 1) / kRun;  // a lane group takes one run at a time
+  const int64_t row_end = p.row_end > 0 ? p.row_end : p.rows;
+  const int64_t nruns = (row_end - p.row_begin + kRun - 1) / kRun;  // a lane group takes one run at a time
   int64_t want = (nruns + groups_per_block - 1) / groups_per_block;
   if (wave_grids()) {
     const int64_t cap = (int64_t)resident_sms(p.flags) * per_sm;
@@ -367,7 +380,7 @@ cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
       static_cast<const X *>(p.logits), p.targets, p.T, p.U,
       reinterpret_cast<const int64_t *>(p.ws + p.lay.split),
       reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
-      reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.N, p.rows, p.V,
+      reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.N, p.row_begin, row_end, p.V,
       p.max_u, p.blank, reinterpret_cast<T *>(p.ws + p.lay.den),
       reinterpret_cast<T *>(p.ws + p.lay.lp));
   return e != cudaSuccess ? e : cudaGetLastError();
@@ -410,27 +423,24 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
     const int nv = p.V / 4;
     // 16-bit rows: a tile is a multiple of 16 bytes only for whole pairs of rows,
     // so the row count must be even (the last tile then ends on a pair as well)
-    const bool tiles_ok = sizeof(X) == 4 || (p.rows % 2 == 0 && reinterpret_cast<uintptr_t>(p.logits) % 16 == 0);
+    const int64_t row_end = p.row_end > 0 ? p.row_end : p.rows;
+    const bool tiles_ok = p.row_begin % kTmaRows == 0 &&
+                          (sizeof(X) == 4 || (row_end % 2 == 0 && reinterpret_cast<uintptr_t>(p.logits) % 16 == 0));
     if (vec_ok && tiles_ok && nv > 64 && nv <= 128 && !(p.flags & OT_B200_ONE_SYM_PER_FRAME) && !plain_loads_forced()) {
       const size_t smem = (size_t)kTmaStages * kTmaRows * p.V * sizeof(X);
-      static bool opted[64] = {false};
-      int dev = 0;
-      cudaGetDevice(&dev);
-      if (dev < 0 || dev >= 64) dev = 0;
-      if (!opted[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(logprob_tma_kernel<X>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   kTmaStages * kTmaRows * 512 * (int)sizeof(X));
+      static SmemGrant grant;
+      {
+        const cudaError_t e = grant.ensure(logprob_tma_kernel<X>, (size_t)kTmaStages * kTmaRows * 512 * sizeof(X));
         if (e != cudaSuccess) return e;
-        opted[dev] = true;
       }
-      const int64_t ntiles = (p.rows + kTmaRows - 1) / kTmaRows;
+      const int64_t ntiles = (row_end - p.row_begin + kTmaRows - 1) / kTmaRows;
       const unsigned grid = (unsigned)((ntiles + kTmaTiles - 1) / kTmaTiles);
       const cudaError_t e = launch_pdl(logprob_tma_kernel<X>, grid, (unsigned)kThreads, smem, s,
           static_cast<const X *>(p.logits), p.targets, p.T, p.U,
           reinterpret_cast<const int64_t *>(p.ws + p.lay.split),
           reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
-          reinterpret_cast<int32_t *>(p.ws + p.lay.status), p.N, p.rows, p.V, p.max_u, p.blank,
-          reinterpret_cast<float *>(p.ws + p.lay.den), reinterpret_cast<float *>(p.ws + p.lay.lp));
+          reinterpret_cast<int32_t *>(p.ws + p.lay.status), p.N, p.row_begin, row_end, p.V, p.max_u,
+          p.blank, reinterpret_cast<float *>(p.ws + p.lay.den), reinterpret_cast<float *>(p.ws + p.lay.lp));
       return e != cudaSuccess ? e : cudaGetLastError();
     }
   }

@@ -51,12 +51,21 @@ scores_noalloc_kernel(const float *__restrict__ logp, const int32_t *__restrict_
   int *flag = reinterpret_cast<int *>(scratch);
   float *cells = scratch + kHeaderFloats;
   const int b = blockIdx.x;
-  // first row of this utterance (N is small; every CTA sums the lengths before it)
+  // First row of this utterance (N is small; every CTA sums the lengths before
+  // it).  An invalid length ANYWHERE before this utterance makes its offset
+  // meaningless, so it is rejected as well: no pointer is formed from lengths
+  // that have not been checked, and the sum runs over clamped values, so it can
+  // neither go negative nor overflow.
   int64_t off = 0;
-  for (int i = 0; i < b; ++i) off += (int64_t)Tl[i] * (Ul[i] + 1);
+  bool bad = false;
+  for (int i = 0; i < b; ++i) {
+    const int ti = Tl[i], ui = Ul[i];
+    bad |= (ti <= 0 || ui < 0 || ui > max_u);
+    off += (int64_t)max(ti, 0) * (min(max(ui, 0), max_u) + 1);
+  }
   const int Tn = Tl[b], U = Ul[b], U1 = U + 1;
-  if (Tn <= 0 || U < 0 || U > max_u || off + (int64_t)Tn * U1 > rows ||
-      off + (int64_t)Tn * U1 > kMaxCells) {
+  bad |= (Tn <= 0 || U < 0 || U > max_u);
+  if (bad || off + (int64_t)Tn * U1 > rows || off + (int64_t)Tn * U1 > kMaxCells) {
     if (threadIdx.x == 0) { atomicExch(flag, 1 + b); scores[b] = __int_as_float(0x7fc00000); }
     return;
   }
@@ -89,18 +98,18 @@ scores_noalloc_kernel(const float *__restrict__ logp, const int32_t *__restrict_
 
 // Device address of the scratch on the current device, looked up once per device.
 cudaError_t scratch_address(float **out) {
-  static float *cached[64] = {nullptr};
+  static std::atomic<float *> cached[kMaxDevices];  // zero-initialised; a race only repeats the lookup
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (cached[dev] == nullptr) {
-    float *p = nullptr;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  float *p = cached[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_alpha_scratch);
     if (e != cudaSuccess) return e;
-    cached[dev] = p;
+    cached[dev].store(p, std::memory_order_release);
   }
-  *out = cached[dev];
+  *out = p;
   return cudaSuccess;
 }
 

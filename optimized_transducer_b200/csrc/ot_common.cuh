@@ -16,6 +16,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/ot_b200.h"
 
 namespace otb {
@@ -26,6 +28,7 @@ constexpr unsigned kFull = 0xffffffffu;
 // Workspace status words (int32 each).
 constexpr int kStatusCode = 0;   // ot_b200_input_error, 0 = inputs are valid
 constexpr int kStatusIndex = 1;  // utterance the code refers to
+constexpr int kStatusCopyTimeout = 2;  // 1 + utterance (or 1) whose bounded wait for a bulk copy ran out
 constexpr int kStatusWords = 16;
 // Diagnostic timeline (OT_B200_TRACE): word kStatusTraceOn holds the switch;
 // from int32 word kTraceWord on, one (first block started, last block ended)
@@ -33,8 +36,17 @@ constexpr int kStatusWords = 16;
 // the workspace has kStatusBlockWords words.
 constexpr int kStatusTraceOn = 3;
 constexpr int kTraceWord = 16;
+// Word kStatusGroupSplit: when a call runs as two groups of utterances (the
+// pipelined schedule of api.cu), the first utterance of the second group; stage 0
+// derives it from the row at which the host cut the batch.
+constexpr int kStatusGroupSplit = 4;
 constexpr int kStatusBlockWords = 64;
 enum Stage { kStagePrepare = 0, kStageLogprob = 1, kStageLattice = 2, kStageCoef = 3, kStageGradient = 4, kStages_ = 5 };
+// Timeline slot of a stage: the launches of the second group of a two-group call
+// (group == 1) use slots kStages_ .. 2*kStages_-1, everything else 0 .. kStages_-1.
+__host__ __device__ __forceinline__ int trace_slot(int stage, int group) {
+  return group == 1 ? stage + kStages_ : stage;
+}
 
 // Marker values of the `tgt` field of a gradient-coefficient record.
 constexpr int32_t kTgtNone = -1;     // no symbol column to patch in this row
@@ -109,8 +121,20 @@ struct Problem {
   uint32_t flags;
   char *ws;
   Layout lay;
-  int32_t *host_status = nullptr;  // device view of a mapped host buffer (input-check report), or NULL
-  int32_t host_seq = 0;            // value stage 0 stores into host_status[2] when the report is complete
+  // A launch covers the whole batch (group < 0) or one of two groups of
+  // utterances: group 0 = the utterances that END at or before packed row
+  // `group_row`, group 1 = the rest.  Stage 1 is cut at the row itself
+  // ([row_begin, row_end), host-known); the later stages read the utterance
+  // boundary stage 0 stored in status word kStatusGroupSplit.
+  int group = -1;
+  int64_t group_row = 0;
+  int64_t row_begin = 0;
+  int64_t row_end = 0;  // 0: `rows`
+  // Error reports (device views of mapped host words, or NULL), written by the
+  // last kernel of the forward half:
+  int32_t *report = nullptr;   // {code, utterance, sequence}: the verdict of THIS call, always stored
+  int32_t *sticky = nullptr;   // {code, utterance, sequence}: stored only when the verdict is an error
+  int32_t report_seq = 0;      // sequence number of this call
 };
 
 // Number of SMs of the current device (cached per device).
@@ -133,6 +157,14 @@ inline int resident_sms(uint32_t flags) {
 // Stores the message ot_b200_last_error() returns for the calling thread.
 void set_last_error(const char *msg);
 
+// For entry points that honour OT_B200_REPORT_ERRORS (see include/ot_b200.h).
+// Without the flag: *sticky = NULL, returns OT_B200_OK.  With it: if an earlier
+// call on this device left an error record, takes it and returns
+// OT_B200_ERR_INPUT (nothing must be launched then); otherwise *sticky is the
+// device view of the record a failing kernel fills in and *seq the number of
+// this call.
+int begin_reported_call(uint32_t flags, int32_t **sticky, int32_t *seq);
+
 // Blocks of `kernel` that fit on one SM at `threads` threads per block.
 template <typename K>
 int blocks_per_sm(K kernel, int threads) {
@@ -140,6 +172,29 @@ int blocks_per_sm(K kernel, int threads) {
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) n = 1;
   return n;
 }
+
+// Ordinal of the current device, clamped to the size of the per-device caches.
+constexpr int kMaxDevices = 64;
+inline int current_device_slot() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev < 0 || dev >= kMaxDevices) ? 0 : dev;
+}
+
+// Per-device cache of "dynamic shared memory opted in so far" for one kernel.
+// Host threads may race here; the worst case is a redundant cudaFuncSetAttribute.
+struct SmemGrant {
+  std::atomic<size_t> granted[kMaxDevices];
+  SmemGrant() { for (auto &g : granted) g.store(0, std::memory_order_relaxed); }
+  template <typename K>
+  cudaError_t ensure(K kernel, size_t bytes) {
+    const int dev = current_device_slot();
+    if (bytes <= granted[dev].load(std::memory_order_acquire)) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) granted[dev].store(bytes, std::memory_order_release);
+    return e;
+  }
+};
 
 // Programmatic dependent launch: the kernel may be scheduled while its
 // predecessor in the stream is still running (its CTAs then block in pdl_wait()
@@ -201,6 +256,14 @@ __device__ __forceinline__ void tma_load_1d(void *dst, const void *src, uint32_t
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+// Utterances [lo, hi) a launch works on (see Problem::group).
+__device__ __forceinline__ void group_range(const int32_t *status, int group, int N, int &lo, int &hi) {
+  lo = 0;
+  hi = N;
+  if (group == 0) hi = status[kStatusGroupSplit];
+  else if (group == 1) lo = status[kStatusGroupSplit];
+}
+
 // First statement of every kernel that reads what an earlier kernel wrote
 // (a no-op when the kernel was launched the ordinary way) ...
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -212,10 +275,15 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 cudaError_t launch_prepare(const Problem &p, cudaStream_t s);
 cudaError_t launch_logprob(const Problem &p, cudaStream_t s);
 cudaError_t launch_lattice(const Problem &p, void *scores, cudaStream_t s);
-cudaError_t launch_coef(const Problem &p, const void *scores, void *loss_out,
+cudaError_t launch_coef(const Problem &p, void *scores, void *loss_out,
                         double loss_scale, cudaStream_t s);
 cudaError_t launch_gradient(const Problem &p, void *grad, const void *d_scale,
                             double scale_host, cudaStream_t s);
+// In-place multiplication of a gradient by a device scalar (skipped when it is 1).
+cudaError_t launch_scale(void *g, int64_t count, const void *d_scale, uint32_t flags, cudaStream_t s);
+// After both groups of a two-group call: the loss and the error reports.
+cudaError_t launch_close(const Problem &p, void *scores, void *loss_out, double loss_scale,
+                         cudaStream_t s);
 
 // ---------------------------------------------------------------------------
 // Device helpers
@@ -258,6 +326,31 @@ template <> __device__ __forceinline__ float from_real<float>(float v) { return 
 template <> __device__ __forceinline__ double from_real<double>(double v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_real<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_real<__half>(float v) { return __float2half_rn(v); }
+#endif
+
+#ifdef __CUDACC__
+// Two 16-bit elements in one 32-bit word <-> two floats: one or two ALU
+// instructions to widen (bfloat16 is the upper half of a float), ONE conversion
+// instruction to round both back (cvt.rn.bf16x2.f32 / cvt.rn.f16x2.f32).
+template <typename X> struct Pair16;
+template <> struct Pair16<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 widen(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  }
+  static __device__ __forceinline__ uint32_t round(float lo, float hi) {
+    const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&r);
+  }
+};
+template <> struct Pair16<__half> {
+  static __device__ __forceinline__ float2 widen(uint32_t w) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(&w));
+  }
+  static __device__ __forceinline__ uint32_t round(float lo, float hi) {
+    const __half2 r = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&r);
+  }
+};
 #endif
 
 template <typename T> __device__ __forceinline__ T neg_inf();

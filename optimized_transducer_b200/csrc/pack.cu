@@ -26,11 +26,27 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kRun = 8;
 
-// One CTA: split[b] = sum_{b' < b} T_b' * (U_b' + 1); flags inconsistent lengths.
+// What a kernel of this file does when the lengths are inconsistent (status != 0):
+// it must not follow them, but it does not leave its output uninitialised either.
+// Every element it was to produce becomes NaN, so a caller that has not looked at
+// the status cannot mistake the result for data.  `count` elements, all blocks of
+// the grid take part.
+template <typename T>
+__device__ __forceinline__ void poison(T *out, int64_t count) {
+  const int64_t nthreads = (int64_t)gridDim.x * gridDim.y * blockDim.x;
+  const int64_t first = ((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;
+  const T nan = from_real<T>((typename Real<T>::type)__int_as_float(0x7fc00000));
+  for (int64_t i = first; i < count; i += nthreads) out[i] = nan;
+}
+
+// One CTA: split[b] = sum_{b' < b} T_b' * (U_b' + 1); flags inconsistent lengths
+// (status word: 1 + the first offending utterance found, or -1 when only the sum
+// differs from `rows`).  `sticky`: NULL, or the device view of the mapped host
+// record of the last failed call (see api.cu), written on failure.
 __global__ void __launch_bounds__(1024)
 pack_prepare_kernel(const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul, int N,
                     int64_t rows, int max_t, int max_u1, int64_t *__restrict__ split,
-                    int32_t *__restrict__ status) {
+                    int32_t *__restrict__ status, volatile int32_t *sticky, int32_t seq) {
   __shared__ long long part[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) status[0] = 0;
@@ -61,9 +77,16 @@ pack_prepare_kernel(const int32_t *__restrict__ Tl, const int32_t *__restrict__ 
     split[b] = run;
     run += (long long)max(Tl[b], 0) * (long long)(max(Ul[b], 0) + 1);
   }
+  __syncthreads();  // every thread's verdict on its utterances is in
   if (tid == 0) {
     split[N] = total;
-    if (total != rows) atomicExch(status, -1);
+    if (status[0] == 0 && total != rows) status[0] = -1;
+    if (sticky != nullptr && status[0] != 0) {
+      sticky[1] = status[0] > 0 ? status[0] - 1 : 0;
+      sticky[2] = seq;
+      __threadfence_system();
+      sticky[0] = OT_B200_INPUT_PACK_LENGTHS;
+    }
   }
 }
 
@@ -78,8 +101,12 @@ pack_rows_kernel(const T *__restrict__ a, const T *__restrict__ bsrc, T *__restr
                  const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
                  const int64_t *__restrict__ split, const int32_t *__restrict__ status, int N,
                  int64_t rows, int D, int max_t, int max_u1) {
-  if (status[0] != 0) return;
+  if (status[0] != 0) {
+    if (MODE != kUnpack) poison(out, rows * (int64_t)D);  // the padded output was zeroed and stays so
+    return;
+  }
   using VT = typename VecOf<T, VEC>::type;
+  using R = typename Real<T>::type;
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
@@ -134,7 +161,7 @@ pack_rows_kernel(const T *__restrict__ a, const T *__restrict__ bsrc, T *__restr
               const T *ye = reinterpret_cast<const T *>(&y[j]);
               T *ze = reinterpret_cast<T *>(&z);
 #pragma unroll
-              for (int k = 0; k < VEC; ++k) ze[k] = xe[k] + ye[k];
+              for (int k = 0; k < VEC; ++k) ze[k] = from_real<T>((R)(to_real(xe[k]) + to_real(ye[k])));
               *reinterpret_cast<VT *>(po + (int64_t)vi * VEC) = z;
             }
           }
@@ -175,9 +202,13 @@ __global__ void __launch_bounds__(kThreads)
 pack_add_frames_kernel(const T *__restrict__ enc, const T *__restrict__ dec, T *__restrict__ out,
                        const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
                        const int64_t *__restrict__ split, const int32_t *__restrict__ status,
-                       int N, int D, int max_t, int max_u1, int chunks_max) {
-  if (status[0] != 0) return;
+                       int N, int64_t rows, int D, int max_t, int max_u1, int chunks_max) {
+  if (status[0] != 0) {
+    poison(out, rows * (int64_t)D);
+    return;
+  }
   using VT = typename VecOf<T, VEC>::type;
+  using R = typename Real<T>::type;
   const int nvec = D / VEC;
   const int chunk = (int)(blockIdx.x % (unsigned)chunks_max);
   const int t0 = (int)(blockIdx.x / (unsigned)chunks_max) * kAddFrames;
@@ -214,7 +245,7 @@ pack_add_frames_kernel(const T *__restrict__ enc, const T *__restrict__ dec, T *
           const T *ye = reinterpret_cast<const T *>(&y[k]);
           T *ze = reinterpret_cast<T *>(&z);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) ze[e] = xe[e] + ye[e];
+          for (int e = 0; e < VEC; ++e) ze[e] = from_real<T>((R)(to_real(xe[e]) + to_real(ye[e])));
           outv[(int64_t)k * kThreads] = z;
         }
       }
@@ -222,12 +253,16 @@ pack_add_frames_kernel(const T *__restrict__ enc, const T *__restrict__ dec, T *
   }
 }
 
-template <typename VT, typename T>
-__device__ __forceinline__ void vec_add(VT &acc, const VT &v) {
-  T *ae = reinterpret_cast<T *>(&acc);
+// acc[e] += element e of the vector v, in the arithmetic type R.
+template <typename T, int VEC>
+struct Acc {
+  typename Real<T>::type v[VEC];
+};
+template <typename T, int VEC, typename VT>
+__device__ __forceinline__ void acc_add(Acc<T, VEC> &acc, const VT &v) {
   const T *ve = reinterpret_cast<const T *>(&v);
 #pragma unroll
-  for (int e = 0; e < (int)(sizeof(VT) / sizeof(T)); ++e) ae[e] += ve[e];
+  for (int e = 0; e < VEC; ++e) acc.v[e] += to_real(ve[e]);
 }
 
 // OVER_U: CTA (t, b): out[b,t,:] = sum_u g[row(b,t,u),:]   (zero for t >= T_b)
@@ -237,18 +272,26 @@ __device__ __forceinline__ void vec_add(VT &acc, const VT &v) {
 // (row lane, vector)), eight rows deep per thread with all loads issued before the
 // first add; the R partial sums meet in shared memory in a fixed order, so the
 // result does not depend on timing.  Rows longer than 256 vectors: R = 1 and the
-// threads walk the row.
+// threads walk the row.  The sums are kept in the arithmetic type (float for
+// 16-bit storage) and rounded once, on the store.
 template <typename T, int VEC, bool OVER_U>
 __global__ void __launch_bounds__(kThreads)
 pack_sum_kernel(const T *__restrict__ g, T *__restrict__ out, const int32_t *__restrict__ Tl,
                 const int32_t *__restrict__ Ul, const int64_t *__restrict__ split,
                 const int32_t *__restrict__ status, int D, int extent) {
-  if (status[0] != 0) return;
   using VT = typename VecOf<T, VEC>::type;
-  __shared__ VT part[kThreads];
-  constexpr int kDeep = 8;
+  using A = Acc<T, VEC>;
+  using Rt = typename Real<T>::type;
   const int tid = threadIdx.x;
   const int b = blockIdx.y, i = blockIdx.x;  // i: frame t (OVER_U) or column u
+  if (status[0] != 0) {  // this block's own D outputs
+    T *o = out + ((int64_t)b * extent + i) * D;
+    const T nan = from_real<T>((Rt)__int_as_float(0x7fc00000));
+    for (int d = tid; d < D; d += kThreads) o[d] = nan;
+    return;
+  }
+  __shared__ A part[kThreads];
+  constexpr int kDeep = 8;
   const int Tn = Tl[b], U1 = Ul[b] + 1;
   VT *po = reinterpret_cast<VT *>(out + ((int64_t)b * extent + i) * D);
   const bool live = OVER_U ? (i < Tn) : (i < U1);
@@ -258,17 +301,21 @@ pack_sum_kernel(const T *__restrict__ g, T *__restrict__ out, const int32_t *__r
   const int64_t stride = OVER_U ? (int64_t)nvec : (int64_t)U1 * nvec;
   const VT *base = reinterpret_cast<const VT *>(
       g + (split[b] + (OVER_U ? (int64_t)i * U1 : (int64_t)i)) * D);
-  VT zero;
-  {
-    T *ze = reinterpret_cast<T *>(&zero);
+  A zero;
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) ze[e] = (T)0;
-  }
+  for (int e = 0; e < VEC; ++e) zero.v[e] = (Rt)0;
+  const auto store = [&](VT *dst, const A &a) {
+    VT z;
+    T *ze = reinterpret_cast<T *>(&z);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) ze[e] = from_real<T>(a.v[e]);
+    *dst = z;
+  };
   const int R = nvec <= kThreads ? kThreads / nvec : 1;
   const int rl = nvec <= kThreads ? tid / nvec : 0;
   const int64_t step = (int64_t)R * stride;
   for (int dv = nvec <= kThreads ? tid - rl * nvec : tid; dv < nvec; dv += kThreads) {
-    VT acc = zero;
+    A acc = zero;
     if (rl < R) {
       const VT *p = base + (int64_t)rl * stride + dv;
       int r = rl;
@@ -277,19 +324,23 @@ pack_sum_kernel(const T *__restrict__ g, T *__restrict__ out, const int32_t *__r
 #pragma unroll
         for (int j = 0; j < kDeep; ++j) v[j] = p[j * step];
 #pragma unroll
-        for (int j = 0; j < kDeep; ++j) vec_add<VT, T>(acc, v[j]);
+        for (int j = 0; j < kDeep; ++j) acc_add<T, VEC>(acc, v[j]);
       }
-      for (; r < n; r += R, p += step) vec_add<VT, T>(acc, *p);
+      for (; r < n; r += R, p += step) acc_add<T, VEC>(acc, *p);
     }
     if (R == 1) {
-      if (rl < R) po[dv] = acc;  // nvec in (128, 256]: the threads past the row idle
+      if (rl < R) store(po + dv, acc);  // nvec in (128, 256]: the threads past the row idle
     } else {
       if (rl < R) part[tid] = acc;
       __syncthreads();
       if (tid < nvec) {
-        VT s = part[tid];
-        for (int q = 1; q < R; ++q) vec_add<VT, T>(s, part[q * nvec + tid]);
-        po[tid] = s;
+        A s = part[tid];
+        for (int q = 1; q < R; ++q) {
+          const A &o = part[q * nvec + tid];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) s.v[e] += o.v[e];
+        }
+        store(po + tid, s);
       }
     }
     if (nvec <= kThreads) break;  // one vector per thread in this arrangement
@@ -323,10 +374,17 @@ unsigned rows_grid(K kernel, int64_t rows) {
 
 template <typename T, int MODE>
 int launch_rows(const void *a, const void *b, void *out, const int32_t *Tl, const int32_t *Ul,
-                int N, int64_t rows, int D, int max_t, int max_u1, void *ws, cudaStream_t s) {
+                int N, int64_t rows, int D, int max_t, int max_u1, void *ws, uint32_t flags,
+                cudaStream_t s) {
   int64_t *split = static_cast<int64_t *>(ws);
   int32_t *status = reinterpret_cast<int32_t *>(split + N + 1);
-  pack_prepare_kernel<<<1, 1024, 0, s>>>(Tl, Ul, N, rows, max_t, max_u1, split, status);
+  int32_t *sticky = nullptr;
+  int32_t seq = 0;
+  {
+    const int rc = begin_reported_call(flags, &sticky, &seq);
+    if (rc) return rc;
+  }
+  pack_prepare_kernel<<<1, 1024, 0, s>>>(Tl, Ul, N, rows, max_t, max_u1, split, status, sticky, seq);
   constexpr int VEC = Vec16<T>::n;
   const bool vec = (D % VEC == 0) && (reinterpret_cast<uintptr_t>(a) % 16 == 0) &&
                    (reinterpret_cast<uintptr_t>(out) % 16 == 0) &&
@@ -341,11 +399,11 @@ int launch_rows(const void *a, const void *b, void *out, const int32_t *Tl, cons
     if (vec)
       pack_add_frames_kernel<T, VEC><<<grid, kThreads, 0, s>>>(
           static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), Tl, Ul, split,
-          status, N, D, max_t, max_u1, chunks_max);
+          status, N, rows, D, max_t, max_u1, chunks_max);
     else
       pack_add_frames_kernel<T, 1><<<grid, kThreads, 0, s>>>(
           static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), Tl, Ul, split,
-          status, N, D, max_t, max_u1, chunks_max);
+          status, N, rows, D, max_t, max_u1, chunks_max);
   } else if (vec)
     pack_rows_kernel<T, VEC, MODE><<<rows_grid(pack_rows_kernel<T, VEC, MODE>, rows), kThreads, 0, s>>>(
         static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), Tl, Ul, split,
@@ -360,9 +418,12 @@ int launch_rows(const void *a, const void *b, void *out, const int32_t *Tl, cons
 }
 
 int check(const void *a, const void *out, const int32_t *Tl, const int32_t *Ul, int32_t N,
-          int64_t rows, int32_t D, int32_t max_t, int32_t max_u1, const void *ws) {
+          int64_t rows, int32_t D, int32_t max_t, int32_t max_u1, const void *ws, uint32_t flags) {
   if (N <= 0 || rows <= 0 || D <= 0 || max_t <= 0 || max_u1 <= 0)
     return fail(OT_B200_ERR_ARGUMENT, "pack: N, rows, D, max_t and max_u1 must be positive");
+  const uint32_t types = flags & (OT_B200_FP64 | OT_B200_BF16 | OT_B200_FP16);
+  if ((flags & ~(OT_B200_FP64 | OT_B200_BF16 | OT_B200_FP16 | OT_B200_REPORT_ERRORS)) || (types & (types - 1)))
+    return fail(OT_B200_ERR_ARGUMENT, "pack: flags may hold one of OT_B200_FP64/BF16/FP16 and OT_B200_REPORT_ERRORS");
   if (!a || !out || !Tl || !Ul) return fail(OT_B200_ERR_ARGUMENT, "pack: a required device pointer is NULL");
   if (!ws || reinterpret_cast<uintptr_t>(ws) % 8 != 0)
     return fail(OT_B200_ERR_WORKSPACE, "pack: workspace missing or not 8-byte aligned");
@@ -373,6 +434,15 @@ int check(const void *a, const void *out, const int32_t *Tl, const int32_t *Ul, 
 }  // namespace otb
 
 using namespace otb;
+
+// return FN<element type selected by the flags, MODE>(args...)
+#define OTB_PACK_BY_TYPE(flags, FN, MODE, ...)                                  \
+  do {                                                                          \
+    if ((flags) & OT_B200_FP64) return FN<double, MODE>(__VA_ARGS__);           \
+    if ((flags) & OT_B200_BF16) return FN<__nv_bfloat16, MODE>(__VA_ARGS__);    \
+    if ((flags) & OT_B200_FP16) return FN<__half, MODE>(__VA_ARGS__);           \
+    return FN<float, MODE>(__VA_ARGS__);                                        \
+  } while (0)
 
 extern "C" {
 
@@ -386,13 +456,12 @@ int ot_b200_pack_joiner_input(const void *d_encoder_out, const void *d_decoder_o
                               const int32_t *d_logit_lengths, const int32_t *d_target_lengths,
                               int32_t N, int64_t rows, int32_t D, int32_t max_t, int32_t max_u1,
                               uint32_t flags, void *d_workspace, void *d_out, void *stream) {
-  int rc = check(d_encoder_out, d_out, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace);
+  int rc = check(d_encoder_out, d_out, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, flags);
   if (rc) return rc;
   if (!d_decoder_out) return fail(OT_B200_ERR_ARGUMENT, "pack: decoder_out is NULL");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return (flags & OT_B200_FP64)
-             ? launch_rows<double, kAdd>(d_encoder_out, d_decoder_out, d_out, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s)
-             : launch_rows<float, kAdd>(d_encoder_out, d_decoder_out, d_out, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s);
+  OTB_PACK_BY_TYPE(flags, launch_rows, kAdd, d_encoder_out, d_decoder_out, d_out, d_logit_lengths,
+                   d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, flags, s);
 }
 
 int ot_b200_pack_joiner_input_backward(const void *d_grad_out, const int32_t *d_logit_lengths,
@@ -400,13 +469,17 @@ int ot_b200_pack_joiner_input_backward(const void *d_grad_out, const int32_t *d_
                                        int32_t D, int32_t max_t, int32_t max_u1, uint32_t flags,
                                        void *d_workspace, void *d_grad_encoder, void *d_grad_decoder,
                                        void *stream) {
-  int rc = check(d_grad_out, d_grad_encoder, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace);
+  int rc = check(d_grad_out, d_grad_encoder, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, flags);
   if (rc) return rc;
   if (!d_grad_decoder) return fail(OT_B200_ERR_ARGUMENT, "pack: grad_decoder is NULL");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int64_t *split = static_cast<int64_t *>(d_workspace);
   int32_t *status = reinterpret_cast<int32_t *>(split + N + 1);
-  pack_prepare_kernel<<<1, 1024, 0, s>>>(d_logit_lengths, d_target_lengths, N, rows, max_t, max_u1, split, status);
+  int32_t *sticky = nullptr;
+  int32_t seq = 0;
+  rc = begin_reported_call(flags, &sticky, &seq);
+  if (rc) return rc;
+  pack_prepare_kernel<<<1, 1024, 0, s>>>(d_logit_lengths, d_target_lengths, N, rows, max_t, max_u1, split, status, sticky, seq);
   const dim3 ge((unsigned)max_t, (unsigned)N), gd((unsigned)max_u1, (unsigned)N);
   const auto aligned = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool al = aligned(d_grad_out) && aligned(d_grad_encoder) && aligned(d_grad_decoder);
@@ -421,6 +494,10 @@ int ot_b200_pack_joiner_input_backward(const void *d_grad_out, const int32_t *d_
   } while (0)
   if (flags & OT_B200_FP64) {
     if (al && D % 2 == 0) OTB_PACK_SUM(double, 2); else OTB_PACK_SUM(double, 1);
+  } else if (flags & OT_B200_BF16) {
+    if (al && D % 4 == 0) OTB_PACK_SUM(__nv_bfloat16, 4); else OTB_PACK_SUM(__nv_bfloat16, 1);
+  } else if (flags & OT_B200_FP16) {
+    if (al && D % 4 == 0) OTB_PACK_SUM(__half, 4); else OTB_PACK_SUM(__half, 1);
   } else {
     if (al && D % 4 == 0) OTB_PACK_SUM(float, 4); else OTB_PACK_SUM(float, 1);
   }
@@ -434,28 +511,26 @@ int ot_b200_pack_padded(const void *d_padded, const int32_t *d_logit_lengths,
                         const int32_t *d_target_lengths, int32_t N, int64_t rows, int32_t D,
                         int32_t max_t, int32_t max_u1, uint32_t flags, void *d_workspace,
                         void *d_packed, void *stream) {
-  int rc = check(d_padded, d_packed, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace);
+  int rc = check(d_padded, d_packed, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, flags);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return (flags & OT_B200_FP64)
-             ? launch_rows<double, kCopy>(d_padded, nullptr, d_packed, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s)
-             : launch_rows<float, kCopy>(d_padded, nullptr, d_packed, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s);
+  OTB_PACK_BY_TYPE(flags, launch_rows, kCopy, d_padded, nullptr, d_packed, d_logit_lengths,
+                   d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, flags, s);
 }
 
 int ot_b200_unpack_to_padded(const void *d_packed, const int32_t *d_logit_lengths,
                              const int32_t *d_target_lengths, int32_t N, int64_t rows, int32_t D,
                              int32_t max_t, int32_t max_u1, uint32_t flags, void *d_workspace,
                              void *d_padded, void *stream) {
-  int rc = check(d_packed, d_padded, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace);
+  int rc = check(d_packed, d_padded, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, flags);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const size_t es = (flags & OT_B200_FP64) ? 8 : 4;
+  const size_t es = (flags & OT_B200_FP64) ? 8 : ((flags & (OT_B200_BF16 | OT_B200_FP16)) ? 2 : 4);
   // everything outside the lattices is zero
   cudaError_t e = cudaMemsetAsync(d_padded, 0, (size_t)N * max_t * max_u1 * D * es, s);
   if (e != cudaSuccess) return fail(OT_B200_ERR_CUDA, cudaGetErrorString(e));
-  return (flags & OT_B200_FP64)
-             ? launch_rows<double, kUnpack>(d_packed, nullptr, d_padded, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s)
-             : launch_rows<float, kUnpack>(d_packed, nullptr, d_padded, d_logit_lengths, d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, s);
+  OTB_PACK_BY_TYPE(flags, launch_rows, kUnpack, d_packed, nullptr, d_padded, d_logit_lengths,
+                   d_target_lengths, N, rows, D, max_t, max_u1, d_workspace, flags, s);
 }
 
 }  // extern "C"

@@ -50,10 +50,10 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
                int max_u, int modified, int64_t max_cells,
                int32_t *__restrict__ status, int64_t *__restrict__ split,
                int64_t *__restrict__ cell_split, uint4 *__restrict__ lp_fill,
-               int64_t lp_fill_count, uint4 fill_pattern,
-               volatile int32_t *host_status, int32_t host_seq, int trace) {
+               int64_t lp_fill_count, uint4 fill_pattern, int trace, int64_t group_row) {
   __shared__ long long scan_buf[kPrepThreads / kWarp];
   __shared__ int warp_maxu[kPrepThreads / kWarp];
+  __shared__ int group_count;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_wait();     // the previous call's kernels may still be reading this workspace
   pdl_trigger();
@@ -70,9 +70,10 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
   }
   if (tid < kStatusBlockWords) {
     // trace slots: "first start" begins at the maximum, "last end" at 0
-    const bool min_slot = tid >= kTraceWord && ((tid - kTraceWord) & 3) < 2;
+    const bool min_slot = tid >= kTraceWord && tid < kTraceWord + 4 * 2 * kStages_ && ((tid - kTraceWord) & 3) < 2;
     status[tid] = min_slot ? -1 : (tid == kStatusTraceOn ? trace : 0);
   }
+  if (tid == 0) group_count = 0;
   __syncthreads();
   if (tid == 0) trace_begin(status, kStagePrepare);
 
@@ -98,13 +99,19 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
   for (int o = 16; o > 0; o >>= 1) wmax = max(wmax, __shfl_xor_sync(kFull, wmax, o));
   if (lane == 0) warp_maxu[warp] = wmax;
   __syncthreads();
+  int ends_early = 0;  // my utterances that end at or before the group row
   for (int b = b0; b < b1; ++b) {
     split[b] = run_rows;
     cell_split[b] = run_cells;
     const int tc = max(Tl[b], 0), uc = min(max(Ul[b], 0), max_u);
     run_rows += (long long)tc * (uc + 1);
     run_cells += cell_block(tc, uc, modified != 0);
+    ends_early += (run_rows <= group_row) ? 1 : 0;
   }
+  // Utterance ends grow with b, so the count IS the first utterance of group 1.
+  if (ends_early) atomicAdd(&group_count, ends_early);
+  __syncthreads();
+  if (tid == 0) status[kStatusGroupSplit] = group_count;
   if (tid == 0) {
     int maxu_all = -1;
     for (int w = 0; w < kPrepThreads / kWarp; ++w) maxu_all = max(maxu_all, warp_maxu[w]);
@@ -136,17 +143,6 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
       }
     }
   }
-  // Optional report straight into (mapped, pinned) host memory: the host polls
-  // the sequence word, so no copy or event has to sit in the stream.
-  if (host_status != nullptr) {
-    __syncthreads();
-    if (tid == 0) {
-      host_status[0] = status[kStatusCode];
-      host_status[1] = status[kStatusIndex];
-      __threadfence_system();
-      host_status[2] = host_seq;
-    }
-  }
   if (tid == 0) trace_end(status, kStagePrepare);  // block 0 only: the fill blocks are not waited for
 }
 
@@ -159,28 +155,133 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
 // A non-finite log-likelihood zeroes the utterance's rows
 // (optimized_transducer/csrc/kernels.cu:556-563).
 //
-// Block 0 also reduces the scores to the loss:
+// Warp 0 of block 0 also closes the forward half: it settles the verdict of the
+// call, reduces the scores to the loss
 //   *loss_out = loss_scale * -(sum_b scores[b])      (transducer_loss.py:145-152)
+// and delivers the optional reports into mapped host memory (the host polls the
+// sequence word, or looks at the record of the last failed call: no copy or
+// event has to sit in the stream).  The verdict is the input check of stage 0,
+// then a bulk-copy wait that ran out in stage 1 or 2, then (only when a report
+// is asked for) the reference's consistency check of the two total scores,
+// torch::allclose(alpha-total, beta-total) (cpu.cc:795-797: rtol 1e-5, atol
+// 1e-8; equal infinities and NaNs pass here, they give zero gradient rows).
+// A verdict other than 0 is stored into the status word, so the gradient pass
+// writes nothing; the loss becomes NaN, and so do the scores if no recursion
+// ran.
+template <typename T>
+__device__ __forceinline__ T quiet_nan();
+template <> __device__ __forceinline__ float quiet_nan<float>() { return __int_as_float(0x7fc00000); }
+template <> __device__ __forceinline__ double quiet_nan<double>() { return __longlong_as_double(0x7ff8000000000000LL); }
+
+// Warp 0 of block 0, step 1: the verdict over the utterances [lo, hi) of this
+// launch.  Returns it (warp-uniform) and stores it into the status word if it is
+// new there.
+template <typename T>
+__device__ __forceinline__ int settle(int32_t *status, int lo, int hi,
+                                      const int64_t *__restrict__ cell_split,
+                                      const T *__restrict__ beta, const T *__restrict__ scores,
+                                      bool check_totals) {
+  const int lane = threadIdx.x;
+  int code = status[kStatusCode], index = status[kStatusIndex];
+  const int was = code;
+  if (code == 0 && status[kStatusCopyTimeout] != 0) {
+    code = OT_B200_COPY_TIMEOUT;
+    index = status[kStatusCopyTimeout] - 1;
+  }
+  if (code == 0 && check_totals) {
+    int first_bad = 0x7fffffff;
+    for (int b = lo + lane; b < hi; b += kWarp) {
+      const T a = scores[b];
+      const T l = beta[cell_split[b]];  // beta(0,0): the first entry of the utterance's block
+      const bool fa = (a - a == (T)0), fl = (l - l == (T)0);
+      const bool differ = (fa && fl) ? (fabs((double)a - (double)l) > 1e-8 + 1e-5 * fabs((double)l))
+                                     : (fa != fl);
+      if (differ && b < first_bad) first_bad = b;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) first_bad = min(first_bad, __shfl_xor_sync(kFull, first_bad, o));
+    if (first_bad != 0x7fffffff) { code = OT_B200_TOTALS_DIFFER; index = first_bad; }
+  }
+  if (lane == 0 && code != was) {
+    status[kStatusIndex] = index;
+    status[kStatusCode] = code;
+  }
+  return code;
+}
+
+// Step 2, once per call: the loss, NaN scores where no recursion ran, the reports.
+template <typename T>
+__device__ __forceinline__ void deliver(const int32_t *status, int code, int N, T *__restrict__ scores,
+                                        T *__restrict__ loss_out, double loss_scale,
+                                        volatile int32_t *report, volatile int32_t *sticky,
+                                        int32_t report_seq) {
+  const int lane = threadIdx.x;
+  double acc = 0;
+  if (code == 0) {
+    for (int b = lane; b < N; b += kWarp) acc += (double)scores[b];
+    acc = warp_sum(acc);
+  } else if (code <= OT_B200_INPUT_ONE_SYM_INFEASIBLE) {  // an input error: no recursion ran
+    for (int b = lane; b < N; b += kWarp) scores[b] = quiet_nan<T>();
+  }
+  if (lane == 0) {
+    if (loss_out != nullptr) *loss_out = code != 0 ? quiet_nan<T>() : (T)(-acc * loss_scale);
+    if (sticky != nullptr && code != 0) {
+      sticky[1] = status[kStatusIndex];
+      sticky[2] = report_seq;
+      __threadfence_system();
+      sticky[0] = code;
+    }
+    if (report != nullptr) {
+      report[0] = code;
+      report[1] = status[kStatusIndex];
+      __threadfence_system();
+      report[2] = report_seq;
+    }
+  }
+}
+
+// The closing step alone, for calls that ran as two groups: one warp.
+template <typename T>
+__global__ void __launch_bounds__(kWarp)
+close_kernel(int32_t *status, int N, T *scores, T *__restrict__ loss_out, double loss_scale,
+             int32_t *report, int32_t *sticky, int32_t report_seq) {
+  pdl_wait();
+  pdl_trigger();
+  int code = status[kStatusCode];
+  if (code == 0 && status[kStatusCopyTimeout] != 0) {
+    code = OT_B200_COPY_TIMEOUT;
+    if (threadIdx.x == 0) {
+      status[kStatusIndex] = status[kStatusCopyTimeout] - 1;
+      status[kStatusCode] = code;
+    }
+    __syncwarp();
+  }
+  deliver<T>(status, code, N, scores, loss_out, loss_scale, report, sticky, report_seq);
+}
+
 template <typename T, bool MODE_B, bool MODIFIED>
 __global__ void __launch_bounds__(256)
 coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
             const int32_t *__restrict__ Ul, const int64_t *__restrict__ split,
             const int64_t *__restrict__ cell_split,
-            const int32_t *__restrict__ status, int N, int max_u, int blank,
+            int32_t *status, int N, int max_u, int blank,
             const T *__restrict__ den, const T *__restrict__ lp,
             const T *__restrict__ alpha, const T *__restrict__ beta,
-            void *__restrict__ coef_out, const T *__restrict__ scores,
-            T *__restrict__ loss_out, double loss_scale) {
+            void *__restrict__ coef_out, T *scores,
+            T *__restrict__ loss_out, double loss_scale,
+            int32_t *report, int32_t *sticky, int32_t report_seq, int group) {
   pdl_wait();
   pdl_trigger();
-  if (status[kStatusCode] != 0) return;
-  if (threadIdx.x == 0) trace_begin(status, kStageCoef);
-  if (blockIdx.x == 0 && threadIdx.x < kWarp && loss_out != nullptr) {
-    double acc = 0;
-    for (int b = threadIdx.x; b < N; b += kWarp) acc += (double)scores[b];
-    acc = warp_sum(acc);
-    if (threadIdx.x == 0) *loss_out = (T)(-acc * loss_scale);
+  const bool bad_input = status[kStatusCode] != 0;
+  int lo, hi;
+  group_range(status, group, N, lo, hi);
+  if (blockIdx.x == 0 && threadIdx.x < kWarp) {
+    const int code = settle<T>(status, lo, hi, cell_split, beta, scores, report != nullptr || sticky != nullptr);
+    // a call that runs as two groups closes in close_kernel, after both
+    if (group < 0) deliver<T>(status, code, N, scores, loss_out, loss_scale, report, sticky, report_seq);
   }
+  if (bad_input) return;
+  if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageCoef, group));
   const int64_t cell = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   // The chain of dependent loads decides this kernel's time (thousands of small
   // blocks, each a few L2 round trips long), so it is kept at three: (1) the
@@ -201,8 +302,7 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
     __syncthreads();
   }
   const int64_t *cs = meta ? s_csplit : cell_split;
-  const int64_t total_cells = cs[N];
-  if (cell >= total_cells) return;
+  if (cell < cs[lo] || cell >= cs[hi]) return;  // not a cell of this launch's utterances
   const int b = meta ? find_utt_plain(s_csplit, N, cell) : find_utt(cell_split, N, cell);
   const int64_t coff = cs[b];
   const int Tn = meta ? s_T[b] : __ldg(Tl + b), U = meta ? s_U[b] : __ldg(Ul + b), U1 = U + 1;
@@ -271,15 +371,15 @@ coef_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ Tl,
     r.utt = b;
     reinterpret_cast<CoefA<T> *>(coef_out)[row] = r;
   }
-  if (threadIdx.x == 0) trace_end(status, kStageCoef);  // one thread per block: cheap, close enough
+  if (threadIdx.x == 0) trace_end(status, trace_slot(kStageCoef, group));  // one thread per block: cheap, close enough
 }
 
 template <typename T>
-cudaError_t launch_coef_t(const Problem &p, const void *scores, void *loss_out,
+cudaError_t launch_coef_t(const Problem &p, void *scores, void *loss_out,
                           double loss_scale, cudaStream_t s) {
   const bool mode_b = p.flags & OT_B200_FROM_LOG_SOFTMAX;
   const bool modified = p.flags & OT_B200_ONE_SYM_PER_FRAME;
-  const int32_t *status = reinterpret_cast<const int32_t *>(p.ws + p.lay.status);
+  int32_t *status = reinterpret_cast<int32_t *>(p.ws + p.lay.status);
   const int64_t *split = reinterpret_cast<const int64_t *>(p.ws + p.lay.split);
   const int64_t *csplit = reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split);
   const T *den = reinterpret_cast<const T *>(p.ws + p.lay.den);
@@ -292,7 +392,8 @@ cudaError_t launch_coef_t(const Problem &p, const void *scores, void *loss_out,
 #define OTB_COEF(MB, MOD)                                                        \
   e = launch_pdl(coef_kernel<T, MB, MOD>, grid, 256u, 0, s, p.targets, p.T, p.U, split,   \
       csplit, status, p.N, p.max_u, p.blank, den, lp, alpha, beta, coef,         \
-      static_cast<const T *>(scores), static_cast<T *>(loss_out), loss_scale)
+      static_cast<T *>(scores), static_cast<T *>(loss_out), loss_scale,          \
+      p.report, p.sticky, p.report_seq, p.group)
   if (mode_b) { if (modified) OTB_COEF(true, true); else OTB_COEF(true, false); }
   else        { if (modified) OTB_COEF(false, true); else OTB_COEF(false, false); }
 #undef OTB_COEF
@@ -322,15 +423,27 @@ cudaError_t launch_prepare(const Problem &p, cudaStream_t s) {
       reinterpret_cast<int64_t *>(p.ws + p.lay.split),
       reinterpret_cast<int64_t *>(p.ws + p.lay.cell_split),
       reinterpret_cast<uint4 *>(p.ws + p.lay.lp), units, pattern,
-      static_cast<volatile int32_t *>(p.host_status), p.host_seq,
-      (p.flags & OT_B200_TRACE) ? 1 : 0);
+      (p.flags & OT_B200_TRACE) ? 1 : 0, p.group_row);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-cudaError_t launch_coef(const Problem &p, const void *scores, void *loss_out,
+cudaError_t launch_coef(const Problem &p, void *scores, void *loss_out,
                         double loss_scale, cudaStream_t s) {
   return (p.flags & OT_B200_FP64) ? launch_coef_t<double>(p, scores, loss_out, loss_scale, s)
                                   : launch_coef_t<float>(p, scores, loss_out, loss_scale, s);
+}
+
+cudaError_t launch_close(const Problem &p, void *scores, void *loss_out, double loss_scale,
+                         cudaStream_t s) {
+  int32_t *status = reinterpret_cast<int32_t *>(p.ws + p.lay.status);
+  cudaError_t e;
+  if (p.flags & OT_B200_FP64)
+    e = launch_pdl(close_kernel<double>, 1u, (unsigned)kWarp, 0, s, status, p.N, static_cast<double *>(scores),
+                   static_cast<double *>(loss_out), loss_scale, p.report, p.sticky, p.report_seq);
+  else
+    e = launch_pdl(close_kernel<float>, 1u, (unsigned)kWarp, 0, s, status, p.N, static_cast<float *>(scores),
+                   static_cast<float *>(loss_out), loss_scale, p.report, p.sticky, p.report_seq);
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace otb

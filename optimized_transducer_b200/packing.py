@@ -15,13 +15,22 @@ kernel of ``libot_b200.so``, differentiable through ``torch.autograd``:
 ``rows = sum_b T_b * (U_b + 1)`` must be known on the host to size the result;
 pass it if you have it, otherwise it is read from the lengths (one
 device-to-host copy, as the reference's own loop does N times).
+
+Lengths that do not fit the tensors (``T_b > maxT``, ``U_b + 1 > maxU+1``, a sum
+that is not ``rows``) are found on the device.  The kernels then do not follow
+them and fill their outputs with NaN (zero for :func:`unpack_to_padded`), and
+the failure reaches the caller the way the loss's input errors do
+(``OT_CHECKS``, see ``transducer_loss.py``): raised by the next call into the
+library (default), by the call itself (``OT_CHECKS=2``), or not at all (``0``).
+float32, float64, bfloat16 and float16 are accepted; 16-bit data is added and
+summed in float32 and rounded once.
 """
 import ctypes
 
 import torch
 
 from . import _lib
-from .transducer_loss import transducer_loss
+from .transducer_loss import _CHECK_FLAG, _DTYPE_FLAG, _check_mode, _on_device, transducer_loss
 
 __all__ = ["pack_joiner_input", "pack_padded", "unpack_to_padded", "rnnt_loss", "packed_rows"]
 
@@ -34,8 +43,8 @@ def packed_rows(logit_lengths, target_lengths):
 def _check(x, logit_lengths, target_lengths, ndim, who):
     if not x.is_cuda:
         raise RuntimeError(f"{who}: CUDA tensors only (sm_100a kernels, no CPU path)")
-    if x.dtype not in (torch.float32, torch.float64):
-        raise RuntimeError(f"{who}: expected float32 or float64, got {x.dtype}")
+    if x.dtype not in _DTYPE_FLAG:
+        raise RuntimeError(f"{who}: expected float32, float64, bfloat16 or float16, got {x.dtype}")
     if x.dim() != ndim or not x.is_contiguous():
         raise RuntimeError(f"{who}: expected a contiguous {ndim}-D tensor")
     for name, t in (("logit_lengths", logit_lengths), ("target_lengths", target_lengths)):
@@ -52,11 +61,24 @@ def _workspace(n, device):
 
 
 def _flags(x):
-    return _lib.FP64 if x.dtype == torch.float64 else 0
+    mode = _check_mode()
+    return _DTYPE_FLAG[x.dtype] | (_CHECK_FLAG["deferred"] if mode == "deferred" else 0)
 
 
 def _stream(x):
     return ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+
+
+def _finish(rc, ws, n, who):
+    """Raises for a failed call; with strict checks also for lengths the device
+    found inconsistent (reads the status word of the workspace: one synchronisation)."""
+    _lib.check(rc)
+    if _check_mode() == "strict":
+        code = int(ws[(n + 1) * 8:(n + 1) * 8 + 4].view(torch.int32).item())
+        if code:
+            where = f"utterance {code - 1}" if code > 0 else "their sum differs from rows"
+            raise RuntimeError(f"{who}: the lengths do not fit rows, max_t or max_u1 ({where}); "
+                               "the output was filled with NaN")
 
 
 class _PackJoiner(torch.autograd.Function):
@@ -66,11 +88,11 @@ class _PackJoiner(torch.autograd.Function):
         max_u1 = dec.size(1)
         out = torch.empty(rows, d, dtype=enc.dtype, device=enc.device)
         ws = _workspace(n, enc.device)
-        with torch.cuda.device(enc.device):
+        with _on_device(enc.device.index):
             rc = _lib.load().ot_b200_pack_joiner_input(
                 enc.data_ptr(), dec.data_ptr(), T.data_ptr(), U.data_ptr(), n, rows, d, max_t,
                 max_u1, _flags(enc), ws.data_ptr(), out.data_ptr(), _stream(enc))
-        _lib.check(rc)
+        _finish(rc, ws, n, "pack_joiner_input")
         ctx.meta = (T, U, n, rows, d, max_t, max_u1, enc.dtype)
         return out
 
@@ -81,11 +103,11 @@ class _PackJoiner(torch.autograd.Function):
         genc = torch.empty(n, max_t, d, dtype=dtype, device=g.device)
         gdec = torch.empty(n, max_u1, d, dtype=dtype, device=g.device)
         ws = _workspace(n, g.device)
-        with torch.cuda.device(g.device):
+        with _on_device(g.device.index):
             rc = _lib.load().ot_b200_pack_joiner_input_backward(
                 g.data_ptr(), T.data_ptr(), U.data_ptr(), n, rows, d, max_t, max_u1, _flags(g),
                 ws.data_ptr(), genc.data_ptr(), gdec.data_ptr(), _stream(g))
-        _lib.check(rc)
+        _finish(rc, ws, n, "pack_joiner_input (backward)")
         return genc, gdec, None, None, None
 
 
@@ -107,11 +129,11 @@ def pack_joiner_input(encoder_out, decoder_out, logit_lengths, target_lengths, r
 def _copy(fn_name, src, out, T, U, rows):
     n, max_t, max_u1, d = (out.shape if fn_name == "ot_b200_unpack_to_padded" else src.shape)
     ws = _workspace(n, src.device)
-    with torch.cuda.device(src.device):
+    with _on_device(src.device.index):
         rc = getattr(_lib.load(), fn_name)(src.data_ptr(), T.data_ptr(), U.data_ptr(), n, rows, d,
                                            max_t, max_u1, _flags(src), ws.data_ptr(),
                                            out.data_ptr(), _stream(src))
-    _lib.check(rc)
+    _finish(rc, ws, n, fn_name[len("ot_b200_"):])
     return out
 
 

@@ -8,7 +8,9 @@ exchange step: an all-reduce of the scalar loss.  Gradients never leave the
 rank that owns the rows.
 
 * :func:`partition_contiguous` / :func:`partition_lpt` split utterances by the
-  streaming cost ``T_b * (U_b + 1) * V``.
+  streaming cost ``T_b * (U_b + 1) * V``; :func:`partition_lpt` can also weigh
+  in the length ``T_b + U_b`` of the longest recursion of a shard, which is
+  what a rank with only a few utterances waits for.
 * :func:`shard_batch` gives one rank its lengths, targets (re-padded to the
   shard's own max U, which the loss requires) and its row range.
 * :func:`sharded_transducer_loss` evaluates the loss of the local shard with
@@ -22,9 +24,9 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-from .transducer_loss import _Call, real_dtype
+from .transducer_loss import _Call, _eager_grad, _record_trace, real_dtype
 
-__all__ = ["utterance_costs", "partition_contiguous", "partition_lpt", "imbalance",
+__all__ = ["utterance_costs", "chain_lengths", "shard_time", "partition_contiguous", "partition_lpt", "imbalance",
            "Shard", "shard_batch", "all_reduce_sum", "sharded_transducer_loss", "wait_loss"]
 
 
@@ -63,16 +65,96 @@ def partition_contiguous(costs: Sequence[int], world: int) -> List[Tuple[int, in
     return bounds
 
 
-def partition_lpt(costs: Sequence[int], world: int) -> List[List[int]]:
+# Step-time model of one rank: (12 bytes per cell) / (HBM bandwidth) for the
+# three streaming passes over its cells, plus the dependent chain of the longest
+# alpha/beta recursion it holds (one log-add per step of T+U).  Only the RATIO of
+# the two constants matters for a partition; they are the measured B200 figures
+# (6.5 TB/s copy bandwidth, 93 ns per recursion step).
+SECONDS_PER_CELL = 12.0 / 6.5e12
+SECONDS_PER_CHAIN_STEP = 93e-9
+
+
+def chain_lengths(T, U) -> List[int]:
+    """Steps of each utterance's alpha/beta recursion (standard transducer): T + U."""
+    return [int(t) + int(u) for t, u in zip(T.tolist(), U.tolist())]
+
+
+def shard_time(cost: float, chain: float) -> float:
+    """Modelled step time of a shard with ``cost`` cells and a longest recursion of ``chain`` steps."""
+    return cost * SECONDS_PER_CELL + chain * SECONDS_PER_CHAIN_STEP
+
+
+def partition_lpt(costs: Sequence[int], world: int,
+                  chains: Optional[Sequence[int]] = None) -> List[List[int]]:
     """Longest-processing-time bin packing: utterances in decreasing cost order,
-    each to the least loaded rank.  Returns the (sorted) index list per rank."""
+    each to the rank whose load stays smallest.  Returns the (sorted) index list
+    per rank.
+
+    Without ``chains`` the load of a rank is the sum of its costs.  With
+    ``chains`` (``T_b + U_b`` per utterance) it is the modelled step time
+    :func:`shard_time` of (sum of costs, longest chain): with a handful of
+    utterances per rank the recursion of the longest one is a fixed latency no
+    other work hides, so long utterances are dealt first (ties in cost broken by
+    chain length) and a rank that already holds a long chain takes more cells
+    than one that does not."""
+    n = len(costs)
     loads = [0] * world
+    tails = [0] * world
     out: List[List[int]] = [[] for _ in range(world)]
-    for b in sorted(range(len(costs)), key=lambda i: (-costs[i], i)):
-        r = min(range(world), key=lambda k: (loads[k], k))
+    if chains is None:
+        order = sorted(range(n), key=lambda i: (-costs[i], i))
+    else:
+        order = sorted(range(n), key=lambda i: (-shard_time(costs[i], chains[i]), -chains[i], i))
+    for b in order:
+        if chains is None:
+            r = min(range(world), key=lambda k: (loads[k], k))
+        else:
+            r = min(range(world),
+                    key=lambda k: (shard_time(loads[k] + costs[b], max(tails[k], chains[b])), k))
+            tails[r] = max(tails[r], chains[b])
         out[r].append(b)
         loads[r] += costs[b]
+    if chains is not None:
+        out = _refine(out, costs, chains)
     return [sorted(ix) for ix in out]
+
+
+def _refine(parts, costs, chains, rounds=200):
+    """Local search on a chain-aware partition: move one utterance off the slowest
+    rank, or swap it against one of another rank, while that lowers the slowest
+    rank's modelled time.  The greedy deal is within a few percent of the
+    optimum; with a handful of utterances per rank these few percent are a
+    whole utterance."""
+    parts = [list(p) for p in parts]
+
+    def time_of(p):
+        return shard_time(sum(costs[b] for b in p), max((chains[b] for b in p), default=0))
+
+    for _ in range(rounds):
+        times = [time_of(p) for p in parts]
+        worst = max(range(len(parts)), key=lambda k: times[k])
+        best = (times[worst], None)
+        for b in parts[worst]:
+            rest = [x for x in parts[worst] if x != b]
+            for k, other in enumerate(parts):
+                if k == worst:
+                    continue
+                cand = max(time_of(rest), time_of(other + [b]))       # move b to rank k
+                if cand < best[0] - 1e-12:
+                    best = (cand, (b, k, None))
+                for c in other:                                          # swap b against c
+                    cand = max(time_of(rest + [c]), time_of([x for x in other if x != c] + [b]))
+                    if cand < best[0] - 1e-12:
+                        best = (cand, (b, k, c))
+        if best[1] is None:
+            break
+        b, k, c = best[1]
+        parts[worst].remove(b)
+        parts[k].append(b)
+        if c is not None:
+            parts[k].remove(c)
+            parts[worst].append(c)
+    return parts
 
 
 def imbalance(costs: Sequence[int], parts: Sequence[Sequence[int]]) -> float:
@@ -101,13 +183,17 @@ def shard_batch(T: torch.Tensor, U: torch.Tensor, targets: torch.Tensor, V: int,
 
     ``strategy``: "contiguous" keeps the utterance order, so the shard's rows
     are one slice of the packed logits (a view, and the in-place gradient lands
-    in the caller's buffer); "lpt" balances better but permutes; "auto" uses
-    contiguous unless its imbalance exceeds ``max_imbalance``."""
+    in the caller's buffer); "lpt" balances the cells better but permutes;
+    "lpt_chain" also accounts for the longest recursion per rank (see
+    :func:`partition_lpt`), the choice when a rank gets only a few utterances;
+    "auto" uses contiguous unless its imbalance exceeds ``max_imbalance``."""
     costs = utterance_costs(T, U, V)
     bounds = partition_contiguous(costs, world)
     parts = [list(range(a, b)) for a, b in bounds]
     contiguous = True
-    if strategy == "lpt" or (strategy == "auto" and imbalance(costs, parts) > max_imbalance):
+    if strategy == "lpt_chain":
+        parts, contiguous = partition_lpt(costs, world, chain_lengths(T, U)), False
+    elif strategy == "lpt" or (strategy == "auto" and imbalance(costs, parts) > max_imbalance):
         lpt = partition_lpt(costs, world)
         if strategy == "lpt" or imbalance(costs, lpt) < imbalance(costs, parts):
             parts, contiguous = lpt, False
@@ -290,16 +376,24 @@ class _ShardedLoss(torch.autograd.Function):
     def forward(ctx, logits, targets, logit_lengths, target_lengths, blank, from_log_softmax,
                 one_sym_per_frame, reduction, global_batch, group, overlap, exchange):
         assert reduction in ("mean", "sum")
+        scale = 1.0 / float(global_batch) if reduction == "mean" else 1.0
+        ctx.grad = None
         if logit_lengths.numel() > 0:
             call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
                          from_log_softmax, one_sym_per_frame,
                          share_sms=bool(overlap) and exchange is None)
             local = torch.empty((), dtype=real_dtype(logits), device=logits.device)
-            call.forward(loss_out=local, loss_scale=1.0)
+            if _eager_grad():
+                # one library call: local loss and gradient (the 1/N of "mean" uses
+                # the GLOBAL batch size, known up front); see transducer_loss.py
+                if ctx.needs_input_grad[0]:
+                    ctx.grad = torch.empty_like(call.logits) if call.from_log_softmax else call.logits
+                call.loss_and_gradient(ctx.grad, local, loss_scale=1.0, grad_scale=scale)
+            else:
+                call.forward(loss_out=local, loss_scale=1.0)
         else:  # a rank without utterances still joins the collective
             call = None
             local = torch.zeros((), dtype=real_dtype(logits), device=logits.device)
-        scale = 1.0 / float(global_batch) if reduction == "mean" else 1.0
         if exchange is not None:
             # peer-memory exchange: two one-warp kernels on the side stream
             main = torch.cuda.current_stream(logits.device)
@@ -333,11 +427,15 @@ class _ShardedLoss(torch.autograd.Function):
         assert loss_grad.numel() == 1, loss_grad.numel()
         call, ctx.call = ctx.call, None
         grad = None
-        if call is not None:
+        if ctx.grad is not None:  # computed in forward: only the upstream factor is left
+            grad, ctx.grad = ctx.grad, None
+            call.scale_gradient(grad, loss_grad)
+            _record_trace(call)
+        elif call is not None:
             data = call.logits
             grad = torch.empty_like(data) if call.from_log_softmax else data
-            g = loss_grad.detach().to(device=data.device, dtype=call.real).contiguous()
-            call.backward(grad, scale_tensor=g, scale_host=ctx.scale_host)
+            call.backward(grad, scale_tensor=call.upstream(loss_grad), scale_host=ctx.scale_host)
+            _record_trace(call)  # diagnostic, see OT_TRACE
         elif ctx.empty_like is not None:
             grad = torch.zeros_like(ctx.empty_like)
         # Nothing here depends on the reduced VALUE, so the main stream does not

@@ -64,3 +64,22 @@ def make_logits(w: Workload, T, U, device="cpu", dtype=torch.float32, seed=None)
     if w.from_log_softmax:
         x = torch.log_softmax(x, dim=-1)
     return x
+
+
+def make_utterance_logits(w: Workload, T, U, indices, device="cpu", dtype=torch.float32):
+    """Packed logits of the utterances ``indices`` of the workload's batch, in
+    that order.  Every utterance has a generator of its own, seeded by the
+    workload and the utterance's index in the WHOLE batch (``T`` and ``U`` are
+    the whole batch's lengths): whichever rank holds an utterance, and however
+    the batch is dealt, it consists of the same numbers."""
+    dev = torch.device(device)
+    parts = []
+    for b in indices:
+        g = torch.Generator(device=dev).manual_seed(w.seed * 1000003 + 7919 + int(b))
+        x = torch.randn(int(T[b]) * (int(U[b]) + 1), w.v, generator=g, device=dev, dtype=dtype)
+        if w.scale != 1.0:
+            x *= w.scale
+        if w.from_log_softmax:
+            x = torch.log_softmax(x, dim=-1)
+        parts.append(x)
+    return torch.cat(parts) if len(parts) != 1 else parts[0]

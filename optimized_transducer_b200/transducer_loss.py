@@ -16,15 +16,41 @@ All arithmetic runs in the sm_100a kernels of ``libot_b200.so``; PyTorch only
 provides device memory and the current stream.  There is no CPU path: tensors
 must live on a CUDA device.
 
+Input checks.  The data-dependent checks of the reference (lengths against the
+number of rows, target range, ...) and its comparison of the two total scores
+run on the device.  ``OT_CHECKS`` selects how a failure reaches the caller:
+
+* ``1`` (default), "deferred": the call that failed returns a NaN loss and
+  writes no gradient; the failure is raised as ``RuntimeError`` by the next
+  call into this module on the same device that finds the report (usually the
+  ``backward`` of the same loss, at the latest the next ``transducer_loss``),
+  or by :func:`check_inputs`.  The host never waits for the GPU, so a training
+  loop can run ahead of the device.
+* ``2``, "strict": the call itself waits for its forward kernels and raises, as
+  the reference does.  :func:`compute_transducer_loss` and
+  :func:`stage_outputs` always work this way unless checks are off.
+* ``0``: nothing is reported (the kernels still refuse to touch memory on
+  inconsistent inputs, and the loss is NaN).
+
 Gradient scheduling.  The reference computes the gradient inside ``forward``
 (overwriting ``logits`` there), divides it by N for ``reduction="mean"`` in a
-second pass and multiplies it by the upstream gradient in a third.  Here
-``forward`` stops after the alpha/beta recursions and ``backward`` runs one
-fused pass that applies both factors while it overwrites ``logits``; the
-observable results (loss, ``.grad`` of the leaves, ``logits`` overwritten by
-its gradient after ``backward``) are the same.  ``OT_EAGER_GRAD=1`` restores
-the reference's schedule, for callers that read ``logits`` between ``forward``
-and ``backward``.
+second pass and multiplies it by the upstream gradient in a third.  Two
+schedules exist here, selected by ``OT_EAGER_GRAD``:
+
+* ``1`` (default), the reference's: ``forward`` is ONE library call that
+  computes loss and gradient (the 1/N of "mean" folded in), which lets the
+  library overlap the stages of a large batch (see ``ot_b200_loss_and_gradient``);
+  ``backward`` multiplies by the upstream gradient with a kernel that returns at
+  once when that gradient is 1, the usual case, so the reference's two extra
+  passes are gone.  An upstream gradient other than 1 (loss scaling) costs one
+  extra pass.
+* ``0``, deferred: ``forward`` stops after the alpha/beta recursions and
+  ``backward`` runs one fused pass that applies both factors while it overwrites
+  ``logits``: the cheapest schedule when the upstream gradient is not 1, and
+  ``logits`` stays intact until ``backward``.
+
+The observable results (loss, ``.grad`` of the leaves, ``logits`` holding its
+gradient after ``backward``) are the same in both.
 """
 import ctypes
 import os
@@ -35,35 +61,81 @@ from . import _lib
 
 __all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
            "compute_transducer_loss", "stage_outputs", "transducer_loss_per_utterance",
-           "PerUtteranceLossFunction"]
+           "PerUtteranceLossFunction", "check_inputs"]
 
 
-# Diagnostic: set to a list (and OT_TRACE=1) to collect, per backward call, a
-# copy of the call's stage timeline (see _Call.stage("trace")).
+# Diagnostic: with OT_TRACE=1 and a list set here (collect_traces), every
+# backward call appends a copy of its call's stage timeline (_Call.stage("trace")).
 trace_log = None
 
 
-def _checks_enabled():
-    return os.environ.get("OT_CHECKS", "1") != "0"
+def collect_traces(into):
+    """``into``: a list that receives one stage timeline per backward call, or
+    None to stop collecting.  (The package exports the FUNCTION transducer_loss
+    under this module's name, so the module attribute is set through here.)"""
+    global trace_log
+    trace_log = into
+
+
+def _record_trace(call):
+    if trace_log is not None:
+        trace_log.append(call.stage("trace").clone())
+
+
+def _check_mode(default="deferred"):
+    """"off", "deferred" or "strict", from ``OT_CHECKS`` (0 / 1 / 2)."""
+    v = os.environ.get("OT_CHECKS", "1")
+    if v == "0":
+        return "off"
+    if v == "2":
+        return "strict"
+    return default
 
 
 def _eager_grad():
-    return os.environ.get("OT_EAGER_GRAD", "0") == "1"
+    return os.environ.get("OT_EAGER_GRAD", "1") != "0"
 
 
-def _fast_math():
-    # Hardware ex2/lg2 in the alpha/beta recursions (float32 only).  On by
-    # default: every parity test passes with it at the same tolerances, and the
-    # recursions are a latency chain in which the library exp/log1p cost ~20 %.
-    return os.environ.get("OT_FAST_MATH", "1") != "0"
+def _fast_math(from_log_softmax=False):
+    # Hardware ex2/lg2 in the alpha/beta recursions (float32 only).  OT_FAST_MATH=1
+    # / 0 force it on / off.  Unset: on for raw logits (the recursions are a latency
+    # chain in which the library exp/log1p cost ~20 %, and against the reference's
+    # own build the approximations add less than a third to a gradient difference
+    # that the order of the logsumexp sums dominates), off for log-softmax input
+    # (no logsumexp there: with the exact log-add the gradient matches the
+    # reference's to 2.5e-5 on the large-vocabulary benchmark batch, with the
+    # approximations to 4.9e-4).
+    v = os.environ.get("OT_FAST_MATH")
+    if v is None or v == "":
+        return not from_log_softmax
+    return v != "0"
+
+
+_LOGIT_DTYPES = (torch.float32, torch.float64, torch.bfloat16, torch.float16)
 
 
 def _validate(logits, targets, logit_lengths, target_lengths, blank):
     """The metadata checks of ot::ComputeTransducerLoss
     (optimized_transducer/csrc/transducer-loss.cc:33-46, 58-60, 77-79); the
     data-dependent ones (:49-56, :62-66) run on the device."""
+    dev = logits.device
+    if (logits.dtype in _LOGIT_DTYPES and targets.dtype == torch.int32
+            and logit_lengths.dtype == torch.int32 and target_lengths.dtype == torch.int32
+            and logits.dim() == 2 and targets.dim() == 2 and logit_lengths.dim() == 1
+            and target_lengths.dim() == 1 and logits.is_cuda and targets.device == dev
+            and logit_lengths.device == dev and target_lengths.device == dev
+            and logits.is_contiguous() and targets.is_contiguous()
+            and logit_lengths.is_contiguous() and target_lengths.is_contiguous()
+            and logit_lengths.size(0) == target_lengths.size(0) == targets.size(0) > 0
+            and logits.size(0) > 0 and 0 <= blank < logits.size(1)):
+        return  # the common case: one pass over the metadata
+    _explain_invalid(logits, targets, logit_lengths, target_lengths, blank)
+
+
+def _explain_invalid(logits, targets, logit_lengths, target_lengths, blank):
+    """Raises the error for the first check of :func:`_validate` that fails."""
     who = "ComputeTransducerLoss"
-    if logits.dtype not in (torch.float32, torch.float64, torch.bfloat16, torch.float16):
+    if logits.dtype not in _LOGIT_DTYPES:
         raise RuntimeError(f"{who}: expected logits to have scalar type Float "
                            f"(Double, BFloat16 and Half are accepted as extensions), got {logits.dtype}")
     for name, t in (("targets", targets), ("logit_lengths", logit_lengths),
@@ -93,8 +165,7 @@ def _validate(logits, targets, logit_lengths, target_lengths, blank):
     if not (0 <= blank < logits.size(1)):
         raise RuntimeError(f"blank vs logits.size(1) is {blank} vs {logits.size(1)}. "
                            "Expect 0 <= blank < logits.size(1)")
-    if logits.size(0) == 0 or logit_lengths.size(0) == 0:
-        raise RuntimeError(f"{who}: empty batch")
+    raise RuntimeError(f"{who}: empty batch")
 
 
 def real_dtype(logits):
@@ -103,25 +174,71 @@ def real_dtype(logits):
     return logits.dtype if logits.dtype == torch.float64 else torch.float32
 
 
+_DTYPE_FLAG = {torch.float32: 0, torch.float64: _lib.FP64, torch.bfloat16: _lib.BF16,
+               torch.float16: _lib.FP16}
+_CHECK_FLAG = {"off": 0, "deferred": _lib.REPORT_ERRORS, "strict": _lib.CHECK_INPUTS,
+               False: 0, True: _lib.CHECK_INPUTS}
+_LAYOUT_BITS = _lib.FROM_LOG_SOFTMAX | _lib.ONE_SYM_PER_FRAME | _lib.FP64
+_LAYOUTS = {}  # (N, rows, max_u, layout bits) -> workspace layout: shapes repeat from step to step
+
+
 def _flags(logits, from_log_softmax, one_sym_per_frame, checks):
-    f = 0
+    f = _DTYPE_FLAG[logits.dtype] | _CHECK_FLAG[checks]
     if from_log_softmax:
         f |= _lib.FROM_LOG_SOFTMAX
     if one_sym_per_frame:
         f |= _lib.ONE_SYM_PER_FRAME
-    if logits.dtype == torch.float64:
-        f |= _lib.FP64
-    elif logits.dtype == torch.bfloat16:
-        f |= _lib.BF16
-    elif logits.dtype == torch.float16:
-        f |= _lib.FP16
-    if checks:
-        f |= _lib.CHECK_INPUTS
-    if _fast_math():
+    if _fast_math(from_log_softmax):
         f |= _lib.FAST_MATH
     if os.environ.get("OT_TRACE", "0") == "1":
         f |= _lib.TRACE
     return f
+
+
+def _layout(n, rows, max_u, flags):
+    key = (n, rows, max_u, flags & _LAYOUT_BITS)
+    lay = _LAYOUTS.get(key)
+    if lay is None:
+        if len(_LAYOUTS) > 4096:
+            _LAYOUTS.clear()
+        lay = _LAYOUTS[key] = _lib.workspace_layout(n, rows, max_u, key[3])
+    return lay
+
+
+class _on_device:
+    """``with _on_device(index):`` makes the device current for the library call
+    if it is not already (the library launches on the current device)."""
+    __slots__ = ("index", "prev")
+
+    def __init__(self, index):
+        self.index = index
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        self.prev = cur if cur != self.index else -1
+        if self.prev >= 0:
+            torch.cuda.set_device(self.index)
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+def check_inputs(device=None, wait=True):
+    """Raises ``RuntimeError`` if a loss evaluated on ``device`` (default: the
+    current one) with deferred checks (``OT_CHECKS=1``) failed its device-side
+    checks since the last report.  ``wait=True`` first waits for the kernels on
+    the device's current stream, so every loss enqueued so far has reported."""
+    lib = _lib.load()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    code = ctypes.c_int32(0)
+    with _on_device(index):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(index).cuda_stream)
+        _lib.check(lib.ot_b200_poll_errors(ctypes.byref(code), None, None, stream, 1 if wait else 0))
+    if code.value:
+        raise RuntimeError(_lib.last_error())
 
 
 class _Call:
@@ -131,41 +248,42 @@ class _Call:
                  from_log_softmax, one_sym_per_frame, checks=None, share_sms=False):
         _validate(logits, targets, logit_lengths, target_lengths, blank)
         if checks is None:
-            checks = _checks_enabled()
+            checks = _check_mode()
         self.lib = _lib.load()
         self.logits = logits
-        self.n = int(logit_lengths.size(0))
-        self.rows = int(logits.size(0))
-        self.v = int(logits.size(1))
-        self.max_u = int(targets.size(1))
+        self.n = logit_lengths.size(0)
+        self.rows, self.v = logits.shape
+        self.max_u = targets.size(1)
         self.blank = int(blank)
         self.from_log_softmax = bool(from_log_softmax)
         self.modified = bool(one_sym_per_frame)
         self.flags = _flags(logits, from_log_softmax, one_sym_per_frame, checks)
         if share_sms:  # a collective runs beside this call (sharding.py)
             self.flags |= _lib.SHARE_SMS
-        self.layout = _lib.workspace_layout(self.n, self.rows, self.max_u, self.flags)
+        self.layout = _layout(self.n, self.rows, self.max_u, self.flags)
+        self.bytes = int(self.layout.total_bytes)
         self.targets, self.t, self.u = targets, logit_lengths, target_lengths
         self.real = real_dtype(logits)
-        with torch.cuda.device(logits.device):
-            self.workspace = torch.empty(int(self.layout.total_bytes), dtype=torch.uint8,
-                                         device=logits.device)
-            self.scores = torch.empty(self.n, dtype=self.real, device=logits.device)
+        self.device = logits.device
+        self.index = logits.device.index
+        self.workspace = torch.empty(self.bytes, dtype=torch.uint8, device=self.device)
+        self.scores = torch.empty(self.n, dtype=self.real, device=self.device)
 
     def _stream(self):
-        return ctypes.c_void_p(torch.cuda.current_stream(self.logits.device).cuda_stream)
+        return torch.cuda.current_stream(self.index).cuda_stream
 
     def forward(self, loss_out=None, loss_scale=1.0):
         """Enqueues the forward half.  ``loss_out``: optional 0-dim tensor that
         receives ``loss_scale * -(sum of scores)``."""
-        with torch.cuda.device(self.logits.device):
+        with _on_device(self.index):
             rc = self.lib.ot_b200_forward(
                 self.logits.data_ptr(), self.targets.data_ptr() if self.max_u else None,
                 self.t.data_ptr(), self.u.data_ptr(), self.n, self.rows, self.v, self.max_u,
-                self.blank, self.flags, self.workspace.data_ptr(), int(self.layout.total_bytes),
+                self.blank, self.flags, self.workspace.data_ptr(), self.bytes,
                 self.scores.data_ptr(), loss_out.data_ptr() if loss_out is not None else None,
-                float(loss_scale), self._stream())
-        _lib.check(rc)
+                loss_scale, self._stream())
+        if rc:
+            _lib.check(rc)
         return self.scores
 
     def backward(self, grad_out, scale_tensor=None, scale_host=1.0, per_utterance=False):
@@ -175,15 +293,49 @@ class _Call:
         if per_utterance:
             assert scale_tensor is not None and scale_tensor.numel() == self.n
             flags |= _lib.SCALE_PER_UTTERANCE
-        with torch.cuda.device(self.logits.device):
+        with _on_device(self.index):
             rc = self.lib.ot_b200_backward(
                 self.logits.data_ptr(), grad_out.data_ptr(), self.n, self.rows, self.v,
-                self.max_u, self.blank, flags,
-                self.workspace.data_ptr(), int(self.layout.total_bytes),
+                self.max_u, self.blank, flags, self.workspace.data_ptr(), self.bytes,
                 scale_tensor.data_ptr() if scale_tensor is not None else None,
-                float(scale_host), self._stream())
-        _lib.check(rc)
+                scale_host, self._stream())
+        if rc:
+            _lib.check(rc)
         return grad_out
+
+    def loss_and_gradient(self, grad_out=None, loss_out=None, loss_scale=1.0, grad_scale=1.0):
+        """Enqueues the whole step as one library call: scores, the reduced loss
+        (``loss_out``, optional) and, into ``grad_out`` (optional; may be the
+        logits), ``grad_scale`` times the gradient of ``-scores.sum()``."""
+        with _on_device(self.index):
+            rc = self.lib.ot_b200_loss_and_gradient(
+                self.logits.data_ptr(), grad_out.data_ptr() if grad_out is not None else None,
+                self.targets.data_ptr() if self.max_u else None, self.t.data_ptr(), self.u.data_ptr(),
+                self.n, self.rows, self.v, self.max_u, self.blank, self.flags,
+                self.workspace.data_ptr(), self.bytes, self.scores.data_ptr(),
+                loss_out.data_ptr() if loss_out is not None else None, loss_scale, grad_scale,
+                self._stream())
+        if rc:
+            _lib.check(rc)
+        return self.scores
+
+    def scale_gradient(self, grad, loss_grad):
+        """``grad *= loss_grad`` on the device; a no-op kernel when the factor is 1."""
+        g = self.upstream(loss_grad)
+        with _on_device(self.index):
+            rc = self.lib.ot_b200_scale_gradient(grad.data_ptr(), grad.numel(), g.data_ptr(),
+                                                 _DTYPE_FLAG[grad.dtype] | (self.flags & _lib.REPORT_ERRORS),
+                                                 self._stream())
+        if rc:
+            _lib.check(rc)
+        return grad
+
+    def upstream(self, loss_grad):
+        """The upstream gradient as a device tensor of the arithmetic type."""
+        g = loss_grad.detach()
+        if g.dtype != self.real or g.device != self.device:
+            g = g.to(device=self.device, dtype=self.real)
+        return g if g.is_contiguous() else g.contiguous()
 
     def stage(self, name):
         """A tensor view of one intermediate array inside the workspace, in the
@@ -196,8 +348,9 @@ class _Call:
             off, count, dtype, esz = getattr(self.layout, name + "_off"), self.n + 1, torch.int64, 8
         elif name == "trace":
             # with OT_TRACE=1: per stage (prepare, logprob, lattice, coef, gradient) the
-            # %globaltimer (ns) at which its first block started and its last block ended
-            off, count, dtype, esz = self.layout.status_off + 64, 10, torch.int64, 8
+            # %globaltimer (ns) at which its first block started and its last block ended;
+            # then the same five pairs for the second group of a two-group call
+            off, count, dtype, esz = self.layout.status_off + 64, 20, torch.int64, 8
         elif name == "status":
             off, count, dtype, esz = self.layout.status_off, 16, torch.int32, 4
         else:
@@ -236,13 +389,12 @@ def compute_transducer_loss(logits, targets, logit_lengths, target_lengths, blan
     is a new tensor (``cuda.cu:444``).
     """
     call = _Call(logits, targets, logit_lengths, target_lengths, blank,
-                 from_log_softmax, one_sym_per_frame)
-    scores = call.forward()
+                 from_log_softmax, one_sym_per_frame, checks=_check_mode("strict"))
     grad = None
     if logits.requires_grad:
         data = logits.detach()
         grad = data if not from_log_softmax else torch.empty_like(data)
-        call.backward(grad)
+    scores = call.loss_and_gradient(grad)
     return scores, grad
 
 
@@ -253,7 +405,7 @@ def stage_outputs(logits, targets, logit_lengths, target_lengths, blank,
     (rows, 2), ``alpha``, ``beta`` (rows) and ``split`` (N+1).  For tests and
     debugging; cells outside the band of the modified recursion are undefined."""
     call = _Call(logits, targets, logit_lengths, target_lengths, blank,
-                 from_log_softmax, one_sym_per_frame)
+                 from_log_softmax, one_sym_per_frame, checks=_check_mode("strict"))
     scores = call.forward()
     cell = call.cell_index()
     out = {"scores": scores.clone(), "scores_beta": call.stage("scores_beta").clone(),
@@ -270,19 +422,20 @@ class TransducerLossFunction(torch.autograd.Function):
         assert reduction in ("mean", "sum")
         n = logit_lengths.size(0)
         if _eager_grad():
-            # The reference's schedule (transducer_loss.py:135-154).
-            scores, grad = compute_transducer_loss(
-                logits, targets, logit_lengths, target_lengths, blank,
-                from_log_softmax, one_sym_per_frame)
-            loss = -1 * scores
-            if reduction == "mean":
-                loss = loss.mean()
-                if grad is not None:
-                    grad /= n
-            else:
-                loss = loss.sum()
+            # The reference's schedule (transducer_loss.py:135-154): the gradient is
+            # computed here, over the logits, with the 1/N of "mean" already applied.
+            data = logits.detach()
+            call = _Call(data, targets, logit_lengths, target_lengths, blank,
+                         from_log_softmax, one_sym_per_frame)
+            scale = (1.0 / n) if reduction == "mean" else 1.0
+            grad = None
+            if ctx.needs_input_grad[0]:
+                grad = torch.empty_like(data) if from_log_softmax else data
+            loss = torch.empty((), dtype=call.real, device=logits.device)
+            call.loss_and_gradient(grad, loss, loss_scale=scale, grad_scale=scale)
             ctx.grad = grad
             ctx.call = None
+            ctx.eager = call if grad is not None else None
             return loss
 
         call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
@@ -302,15 +455,16 @@ class TransducerLossFunction(torch.autograd.Function):
             if ctx.grad is None:
                 raise RuntimeError("the gradient of this transducer loss was already consumed, "
                                    "or logits did not require grad")
-            grad = ctx.grad.mul_(loss_grad)  # reference transducer_loss.py:162
+            grad, ctx.grad = ctx.grad, None
+            call, ctx.eager = ctx.eager, None  # the workspace is released after this
+            call.scale_gradient(grad, loss_grad)  # reference transducer_loss.py:162
+            _record_trace(call)
             return (grad,) + (None,) * 7
         call, ctx.call = ctx.call, None  # the workspace is released after this pass
         data = call.logits
         grad = torch.empty_like(data) if call.from_log_softmax else data
-        scale = loss_grad.detach().to(device=data.device, dtype=call.real).contiguous()
-        call.backward(grad, scale_tensor=scale, scale_host=ctx.scale_host)
-        if trace_log is not None:  # diagnostic, see OT_TRACE
-            trace_log.append(call.stage("trace").clone())
+        call.backward(grad, scale_tensor=call.upstream(loss_grad), scale_host=ctx.scale_host)
+        _record_trace(call)  # diagnostic, see OT_TRACE
         return (grad,) + (None,) * 7
 
 
@@ -338,8 +492,7 @@ class PerUtteranceLossFunction(torch.autograd.Function):
         assert loss_grad.numel() == call.n, (loss_grad.numel(), call.n)
         data = call.logits
         grad = torch.empty_like(data) if call.from_log_softmax else data
-        scale = loss_grad.detach().to(device=data.device, dtype=call.real).contiguous()
-        call.backward(grad, scale_tensor=scale, per_utterance=True)
+        call.backward(grad, scale_tensor=call.upstream(loss_grad), per_utterance=True)
         return (grad,) + (None,) * 6
 
 

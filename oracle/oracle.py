@@ -228,6 +228,46 @@ def load_ref():
     return _REF["mods"]
 
 
+def load_ref_python(cuda=False):
+    """The reference's own Python layer (``transducer_loss.py`` as installed under
+    ``oracle/_ref/python`` by ``build_ref.py``) bound to the reference's own
+    extension, or None when either is missing.  ``cuda=True`` binds it to the
+    build that includes the reference's CUDA kernels
+    (``oracle/_ref/_optimized_transducer_cuda``, ``build_ref.build_cuda``) instead
+    of the CPU-only one.  The module does ``import _optimized_transducer`` at
+    import time; that name is bound to the reference build for the duration of
+    the import only."""
+    key = "py_cuda" if cuda else "py"
+    if key not in _REF:
+        path = os.path.join(HERE, "_ref", "python", "transducer_loss.py")
+        if cuda:
+            so = os.path.join(HERE, "_ref", "_optimized_transducer_cuda", "_optimized_transducer.so")
+            ext = None
+            if os.path.isfile(so):
+                import torch  # noqa: F401
+                ext = _import_so("_optimized_transducer", so)
+        else:
+            mods = load_ref()
+            ext = None if mods is None else mods[0]
+        if ext is None or not os.path.isfile(path):
+            _REF[key] = None
+        else:
+            import sys
+            saved = sys.modules.get("_optimized_transducer")
+            sys.modules["_optimized_transducer"] = ext
+            try:
+                spec = importlib.util.spec_from_file_location("_ot_reference_transducer_loss_" + key, path)
+                mod = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(mod)
+            finally:
+                if saved is None:
+                    sys.modules.pop("_optimized_transducer", None)
+                else:
+                    sys.modules["_optimized_transducer"] = saved
+            _REF[key] = mod
+    return _REF[key]
+
+
 def ref_loss(x, targets, T, U, blank, from_log_softmax=False,
              one_sym_per_frame=False, want_grad=True):
     """Calls the reference's own ``compute_transducer_loss`` (float32, CPU).

@@ -92,3 +92,28 @@ def test_exchange_table_size_and_argument_checks():
     assert lib.ot_b200_exchange_bytes(33, 256, ctypes.byref(n)) == _lib.ERR_ARGUMENT
     assert lib.ot_b200_exchange_publish(None, 0, None, 2, 0, 256, 0, None) == _lib.ERR_ARGUMENT
     assert lib.ot_b200_exchange_gather(None, 2, 256, 0, None, 0, 1.0, None, 1000, None) == _lib.ERR_ARGUMENT
+
+
+def test_reference_side_adapter_compiles_against_the_header():
+    """``include/examples/reference_adapter.cc`` is the function a maintainer of the
+    reference would put in place of ot::ComputeTransducerLossCuda (it is also the
+    snippet shown in INTEGRATION.md).  It must stay valid C++ against the current
+    ``ot_b200.h`` and torch headers: syntax-checked here (no linking, no GPU)."""
+    import shutil
+    import subprocess
+    import sysconfig
+    from torch.utils.cpp_extension import include_paths
+    if shutil.which("g++") is None:
+        pytest.skip("g++ not available")
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    if not os.path.isfile(os.path.join(cuda_inc, "cuda_runtime_api.h")):
+        pytest.skip("CUDA headers not available")
+    inc = include_paths() + [sysconfig.get_paths()["include"], cuda_inc, os.path.join(ROOT, "include")]
+    src = os.path.join(ROOT, "include", "examples", "reference_adapter.cc")
+    cmd = ["g++", "-fsyntax-only", "-std=c++17"] + [f"-I{p}" for p in inc] + [src]
+    done = subprocess.run(cmd, capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr[-2000:]
+    # and the snippet in INTEGRATION.md is that function
+    body = open(src).read().split("namespace ot {", 1)[1].rsplit("}  // namespace ot", 1)[0].strip()
+    doc = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    assert body in doc

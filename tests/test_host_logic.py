@@ -75,3 +75,32 @@ def test_synthetic_logits_shape():
     T, U, _ = synthetic.make_lengths(w)
     x = synthetic.make_logits(w, T, U)
     assert x.shape == (synthetic.num_rows(T, U), w.v) and x.dtype == torch.float32
+
+
+def test_reference_import_names_are_served():
+    """``optimized_transducer`` exports what the reference package exports
+    (python/optimized_transducer/__init__.py:11 of the reference) and
+    ``_optimized_transducer.compute_transducer_loss`` has the argument names of the
+    reference's pybind function (python/csrc/optimized_transducer.cc:15-19)."""
+    import inspect
+    import _optimized_transducer
+    import optimized_transducer
+    assert optimized_transducer.transducer_loss is ot.transducer_loss
+    assert optimized_transducer.TransducerLoss is ot.TransducerLoss
+    assert isinstance(optimized_transducer.__version__, str)
+    sig = inspect.signature(_optimized_transducer.compute_transducer_loss)
+    assert list(sig.parameters) == ["logits", "targets", "logit_lengths", "target_lengths", "blank",
+                                    "from_log_softmax", "one_sym_per_frame"]
+
+
+def test_check_modes(monkeypatch):
+    from optimized_transducer_b200 import _lib
+    from optimized_transducer_b200.transducer_loss import _CHECK_FLAG, _check_mode
+    for env, want in (("0", "off"), ("1", "deferred"), ("2", "strict")):
+        monkeypatch.setenv("OT_CHECKS", env)
+        assert _check_mode() == want
+    monkeypatch.setenv("OT_CHECKS", "1")
+    assert _check_mode("strict") == "strict"   # the default of the native-style entry points
+    monkeypatch.delenv("OT_CHECKS")
+    assert _check_mode() == "deferred"
+    assert _CHECK_FLAG["deferred"] == _lib.REPORT_ERRORS and _CHECK_FLAG["strict"] == _lib.CHECK_INPUTS

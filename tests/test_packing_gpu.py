@@ -80,14 +80,18 @@ def test_padded_round_trip(d):
         assert np.all(back[b, T[b]:] == 0) and np.all(back[b, :, U[b] + 1:] == 0)
 
 
-def test_inconsistent_lengths_leave_the_output_untouched():
+def test_inconsistent_lengths_do_not_fault_with_reports_off(monkeypatch):
+    """OT_CHECKS=0: nothing is reported, but the kernels still do not follow lengths
+    that exceed the padded tensors (max_t = 3 < T_b): no fault, NaN output."""
+    monkeypatch.setenv("OT_CHECKS", "0")
     rng, T, U = _lengths(7, 2, (4, 6), (1, 2))
-    enc = torch.zeros(2, 3, 8, device=DEV)  # max_t = 3 < T_b
+    enc = torch.zeros(2, 3, 8, device=DEV)
     dec = torch.zeros(2, 4, 8, device=DEV)
     rows = int(splits(T, U)[-1])
     out = packing.pack_joiner_input(enc, dec, torch.from_numpy(T).to(DEV), torch.from_numpy(U).to(DEV), rows=rows)
-    torch.cuda.synchronize()  # no fault: the kernels saw the status word and returned
-    assert out.shape == (rows, 8)
+    torch.cuda.synchronize()
+    assert out.shape == (rows, 8) and bool(torch.isnan(out).all())
+    ot.check_inputs(DEV)  # nothing was recorded
 
 
 @pytest.mark.parametrize("reduction", ["mean", "sum"])
@@ -120,3 +124,70 @@ def test_rnnt_loss_on_padded_logits(reduction):
     ta = torchaudio.functional.rnnt_loss(torch.from_numpy(padded).requires_grad_(True), torch.from_numpy(tg),
                                          torch.from_numpy(T), torch.from_numpy(U), blank=0, reduction=reduction)
     assert abs(loss.item() - ta.item()) <= 1e-4 * abs(ta.item())
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("d", [512, 66, 7])
+def test_sixteen_bit_packing(d, dtype):
+    """16-bit features (the loss accepts 16-bit logits, so the helpers before it do
+    too): the joiner input is the float32 sum rounded once, which is what the
+    reference's recipe gives in PyTorch; the backward sums in float32 and rounds
+    once.  The oracle sees the 16-bit values widened to float64."""
+    tdt = getattr(torch, dtype)
+    rng, T, U = _lengths(12, 5, (2, 30), (0, 11))
+    max_t, max_u1 = int(T.max()), int(U.max()) + 1
+    enc = torch.from_numpy(rng.standard_normal((5, max_t, d)).astype(np.float32)).to(tdt)
+    dec = torch.from_numpy(rng.standard_normal((5, max_u1, d)).astype(np.float32)).to(tdt)
+    want = torch.from_numpy(O.pack_joiner_oracle(enc.double().numpy(), dec.double().numpy(), T, U)).to(tdt)
+    e = enc.to(DEV).requires_grad_(True)
+    q = dec.to(DEV).requires_grad_(True)
+    dT, dU = torch.from_numpy(T).to(DEV), torch.from_numpy(U).to(DEV)
+    x = packing.pack_joiner_input(e, q, dT, dU)
+    assert x.dtype == tdt and torch.equal(x.detach().cpu(), want)
+    g = torch.from_numpy(rng.standard_normal(tuple(want.shape)).astype(np.float32)).to(tdt)
+    x.backward(g.to(DEV))
+    genc, gdec = O.pack_joiner_backward_oracle(g.double().numpy(), T, U, max_t, max_u1)
+    rel = 2.0 ** -8 if dtype == "bfloat16" else 2.0 ** -11   # half an ulp of the rounded sum, doubled
+    for got, ref in ((e.grad, genc), (q.grad, gdec)):
+        err = np.abs(got.double().cpu().numpy() - ref)
+        assert np.all(err <= rel * np.abs(ref) + 1e-4), float(err.max())
+    # padded <-> packed copies are exact in any type
+    padded = torch.from_numpy(rng.standard_normal((5, max_t, max_u1, d)).astype(np.float32)).to(tdt).to(DEV)
+    packed = packing.pack_padded(padded, dT, dU)
+    assert torch.equal(packed.cpu(), torch.from_numpy(O.pack_padded_oracle(padded.float().cpu().numpy(), T, U)).to(tdt))
+    back = packing.unpack_to_padded(packed, dT, dU, max_t, max_u1)
+    assert torch.equal(packing.pack_padded(back, dT, dU), packed)
+
+
+@pytest.mark.parametrize("mode", ["1", "2"])
+def test_lengths_that_do_not_fit_are_reported_and_the_output_is_nan(mode, monkeypatch):
+    """An utterance longer than the padded tensor: the kernels must not follow the
+    lengths.  The output is NaN (never uninitialised memory), and the failure is
+    raised by the call itself (OT_CHECKS=2) or by the next call into the library
+    (OT_CHECKS=1) - for rnnt_loss that is the loss right behind the packing."""
+    monkeypatch.setenv("OT_CHECKS", mode)
+    rng, T, U = _lengths(13, 3, (4, 9), (1, 4))
+    max_t, max_u1, d = int(T.max()), int(U.max()) + 1, 8
+    enc = torch.from_numpy(rng.standard_normal((3, max_t, d)).astype(np.float32)).to(DEV)
+    dec = torch.from_numpy(rng.standard_normal((3, max_u1, d)).astype(np.float32)).to(DEV)
+    Tbad = T.copy(); Tbad[1] = max_t + 1                    # T_b > max_t, rows still consistent
+    rows = int(splits(Tbad, U)[-1])
+    dT, dU = torch.from_numpy(Tbad).to(DEV), torch.from_numpy(U).to(DEV)
+    if mode == "2":
+        with pytest.raises(RuntimeError, match="do not fit"):
+            packing.pack_joiner_input(enc, dec, dT, dU, rows=rows)
+    else:
+        x = packing.pack_joiner_input(enc, dec, dT, dU, rows=rows)   # no exception yet
+        torch.cuda.synchronize()
+        assert bool(torch.isnan(x).all())
+        with pytest.raises(RuntimeError, match="do not fit"):
+            ot.check_inputs(DEV, wait=False)
+        # the padded entry point: the loss behind the packing finds the record
+        v = 6
+        padded = torch.zeros(3, max_t, max_u1, v, device=DEV)
+        tg = torch.ones(3, int(U.max()), dtype=torch.int32, device=DEV)
+        with pytest.raises(RuntimeError, match="do not fit"):
+            loss = packing.rnnt_loss(padded, tg, dT, dU, blank=0)
+            torch.cuda.synchronize()
+            ot.check_inputs(DEV)
+    ot.check_inputs(DEV)

@@ -346,7 +346,7 @@ def test_stage_timeline(monkeypatch):
     call.forward()
     call.backward(torch.empty_like(dx))
     torch.cuda.synchronize()
-    t = call.stage("trace").cpu().numpy().reshape(5, 2)
+    t = call.stage("trace").cpu().numpy().reshape(10, 2)[:5]
     assert np.all(t[:, 0] > 0) and np.all(t[:, 1] >= t[:, 0])
     assert np.all(t[1:, 0] >= t[:-1, 0])          # prepare, logprob, lattice, coef, gradient start in order
     assert t[-1, 1] - t[0, 0] < 1e9                # within a second of each other (ns)
@@ -359,7 +359,7 @@ def test_stage_timeline(monkeypatch):
 
 @pytest.mark.parametrize("fast", ["0", "1"])
 def test_both_log_add_variants_stay_within_tolerance(fast, monkeypatch):
-    """OT_FAST_MATH=1 (default): ex2/lg2.approx in the recursions; =0: expf/log1pf."""
+    """OT_FAST_MATH=1 (the default for raw logits): ex2/lg2.approx in the recursions; =0: expf/log1pf."""
     x, tg, T, U = random_batch(53, 3, (30, 60), (10, 40), 50)
     ref = O.oracle_loss(x, tg, T, U, 0)
     monkeypatch.setenv("OT_FAST_MATH", fast)
@@ -459,6 +459,75 @@ def test_input_errors_are_reported_not_faulted():
     _expect_input_error(x2, np.ones((2, 3), np.int32), T2, U2, "one_sym_per_frame", modified=True)
 
 
+def test_deferred_check_reports_at_a_later_call_and_never_touches_the_logits(monkeypatch):
+    """OT_CHECKS=1 (the default): the failing call returns a NaN loss without
+    waiting for the device; the error is raised by a later call into the module
+    (here: check_inputs, then the backward of a second failing loss), the logits
+    are never written, and the next valid call works."""
+    monkeypatch.setenv("OT_CHECKS", "1")
+    x, tg, T, U = random_batch(63, 3, (4, 6), (2, 3), 5)
+    bad = tg.copy(); bad[2, 0] = 77
+    dx, dt, dT, dU = to_dev(x, bad, T, U)
+    before = dx.clone()
+    leaf = dx.clone().requires_grad_(True)
+    logits = leaf * 1.0
+    loss = ot.transducer_loss(logits, dt, dT, dU, 0, False)   # no exception here
+    with pytest.raises(RuntimeError, match="targets.max\\(\\)"):
+        ot.check_inputs(DEV)                                   # waits for the device, then reports
+    assert torch.isnan(loss).item()
+    ot.check_inputs(DEV)                                       # the record was consumed
+    # the same failure, found by the backward of the loss that failed
+    loss2 = ot.transducer_loss(leaf * 1.0, dt, dT, dU, 0, False)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="an earlier call on this device"):
+        loss2.backward()
+    assert torch.equal(dx, before)
+    # a valid call afterwards is not affected
+    _, good, _, _ = to_dev(x, tg, T, U)
+    ref = O.oracle_loss(x, tg, T, U, 0)
+    ok = ot.transducer_loss(leaf * 1.0, good, dT, dU, 0, False, reduction="sum")
+    ok.backward()
+    assert abs(ok.item() + ref["scores"].sum()) <= 1e-5 * abs(ref["scores"].sum())
+    ot.check_inputs(DEV)
+
+
+def test_strict_check_raises_inside_the_call(monkeypatch):
+    """OT_CHECKS=2: the reference's behaviour, the call itself raises."""
+    monkeypatch.setenv("OT_CHECKS", "2")
+    x, tg, T, U = random_batch(64, 2, (4, 6), (2, 3), 5)
+    Tz = T.copy(); Tz[0] += 1
+    dx, dt, dT, dU = to_dev(x, tg, Tz, U)
+    with pytest.raises(RuntimeError, match="logits.size\\(0\\)"):
+        ot.transducer_loss(dx, dt, dT, dU, 0, False)
+
+
+def test_native_module_alias_and_reference_import_name():
+    """``import optimized_transducer`` / ``import _optimized_transducer``, used the
+    way the reference's python/tests/test_cuda.py:36-60 uses them (keyword
+    arguments, leaves concatenated into the packed logits)."""
+    import _optimized_transducer
+    import optimized_transducer
+    x, tg, T, U = random_batch(65, 2, (3, 4), (3, 3), 3)
+    sp = splits(T, U)
+    ref = O.oracle_loss(x, tg, T, U, 0)
+    _, dt, dT, dU = to_dev(x, tg, T, U)
+    leaves = [torch.from_numpy(x[sp[i]:sp[i + 1]]).to(DEV).requires_grad_(True) for i in range(2)]
+    loss = optimized_transducer.transducer_loss(
+        logits=torch.cat(leaves), targets=dt, logit_lengths=dT, target_lengths=dU, blank=0,
+        reduction="sum", from_log_softmax=False)
+    loss.backward()
+    assert abs(loss.item() + ref["scores"].sum()) <= 1e-5 * abs(ref["scores"].sum())
+    for i in range(2):
+        assert np.max(np.abs(leaves[i].grad.cpu().numpy() - ref["grad"][sp[i]:sp[i + 1]])) <= 1e-5
+    dx = torch.from_numpy(x).to(DEV).requires_grad_(True)
+    scores, grad = _optimized_transducer.compute_transducer_loss(
+        logits=dx, targets=dt, logit_lengths=dT, target_lengths=dU, blank=0,
+        from_log_softmax=False, one_sym_per_frame=False)
+    assert np.max(np.abs(scores.cpu().numpy() - ref["scores"]) / np.abs(ref["scores"])) <= 1e-5
+    assert grad.data_ptr() == dx.data_ptr()
+    assert np.max(np.abs(grad.detach().cpu().numpy() - ref["grad"])) <= 1e-5
+
+
 def test_status_word_without_the_blocking_check(monkeypatch):
     monkeypatch.setenv("OT_CHECKS", "0")
     x, tg, T, U = random_batch(62, 2, (4, 6), (2, 3), 5)
@@ -500,6 +569,46 @@ def test_full_size_configs(name):
         assert abs(scores[b].item() - ref["scores"][0]) <= 1e-5 * abs(ref["scores"][0])
         gb = grad[sp[b]:sp[b + 1]].cpu().numpy()
         assert np.max(np.abs(gb - ref["grad"])) <= max(1e-5, fp32_grad_floor(ref["alpha"], ref["beta"]))
+
+
+@pytest.mark.parametrize("shape", ["cfg2", "cfg3", "one utterance straddles the cut", "bf16"])
+def test_two_group_schedule_gives_the_same_bits(shape, monkeypatch):
+    """A batch of >= 256 MB that is evaluated in one library call (the default
+    schedule of transducer_loss) runs as two groups of utterances on three streams.
+    Same kernels on the same data: scores, loss and gradient carry the bits of the
+    one-stream schedule (OT_B200_PIPELINE=0).  Covered: the benchmark batches, a
+    batch of two utterances whose first one reaches past the cut (the first group
+    is then empty), and 16-bit rows."""
+    if shape in ("cfg2", "cfg3", "bf16"):
+        w = synthetic.CONFIGS["cfg3" if shape == "cfg3" else "cfg2"]
+        T, U, tg = synthetic.make_lengths(w)
+        x = synthetic.make_logits(w, T, U, device=DEV)
+        if shape == "bf16":
+            x = x.to(torch.bfloat16)
+        modified, reduction = w.one_sym_per_frame, w.reduction
+    else:
+        T = torch.tensor([700, 650], dtype=torch.int32)
+        U = torch.tensor([200, 190], dtype=torch.int32)
+        tg = torch.randint(1, 500, (2, 200), dtype=torch.int32, generator=torch.Generator().manual_seed(3))
+        x = torch.randn(synthetic.num_rows(T, U), 500, device=DEV, generator=torch.Generator(device=DEV).manual_seed(4))
+        modified, reduction = False, "mean"
+    assert x.numel() * x.element_size() >= 256 << 20
+    dT, dU, dt = T.to(DEV), U.to(DEV), tg.to(DEV)
+    got = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("OT_B200_PIPELINE", mode)
+        leaf = x.clone().requires_grad_(True)
+        logits = leaf * 1
+        loss = ot.transducer_loss(logits, dt, dT, dU, 0, False, modified, reduction)
+        loss.backward()
+        scores, _ = ot.compute_transducer_loss(x.clone(), dt, dT, dU, 0, False, modified)
+        got[mode] = (loss.detach().clone(), leaf.grad.clone(), scores.clone())
+        del leaf, logits, loss
+    torch.cuda.synchronize()
+    ot.check_inputs(DEV)
+    for a, b in zip(got["0"], got["1"]):
+        assert torch.equal(a, b)
+    assert torch.isfinite(got["1"][0]).item()
 
 
 def test_offsets_beyond_2_to_the_31_elements():

@@ -45,7 +45,32 @@ def test_lpt_covers_every_utterance_once_and_balances():
     assert sharding.imbalance(costs, cont) < 1.25
 
 
-@pytest.mark.parametrize("strategy", ["contiguous", "lpt", "auto"])
+def test_chain_aware_partition_lowers_the_modelled_step_time():
+    """With a handful of utterances per rank the step time is (cells streamed) +
+    (the longest recursion of the rank): the chain-aware deal must cover every
+    utterance once and be no slower, in that model, than the deal by cells alone."""
+    for name, world in (("cfg2", 8), ("cfg2", 4), ("cfg3", 8), ("cfg5", 8)):
+        w = synthetic.CONFIGS[name]
+        T, U, _ = synthetic.make_lengths(w)
+        costs = sharding.utterance_costs(T, U, w.v)
+        chains = sharding.chain_lengths(T, U)
+
+        def slowest(parts):
+            return max(sharding.shard_time(sum(costs[b] for b in p), max(chains[b] for b in p)) for p in parts)
+
+        plain = sharding.partition_lpt(costs, world)
+        aware = sharding.partition_lpt(costs, world, chains)
+        assert sorted(b for p in aware for b in p) == list(range(w.n))
+        assert all(p == sorted(p) and p for p in aware)
+        assert slowest(aware) <= slowest(plain) + 1e-12
+    # few, unequal utterances: the rank that holds the long chain takes fewer cells
+    costs, chains = [100_000_000] * 6, [1200, 200, 200, 200, 200, 200]
+    parts = sharding.partition_lpt(costs, 2, chains)
+    with_long = next(p for p in parts if 0 in p)
+    assert len(with_long) <= 3
+
+
+@pytest.mark.parametrize("strategy", ["contiguous", "lpt", "lpt_chain", "auto"])
 def test_shards_tile_the_batch(strategy):
     w = synthetic.CONFIGS["cfg2"]
     T, U, tg = synthetic.make_lengths(w)
