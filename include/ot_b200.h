@@ -219,6 +219,29 @@ int ot_b200_loss_and_gradient(const void *d_logits, void *d_grad, const int32_t 
                               void *d_workspace, uint64_t workspace_bytes, void *d_scores,
                               void *d_loss, double loss_scale, double grad_scale, void *stream);
 
+/* The forward half WITHOUT logits: the joiner's output projection is fused
+ * into stage 1, so the (rows, V) tensor the reference materialises and reads
+ * back (logits.logsumexp(1), cuda.cu:427; ComputeLogProbs, kernels.cu:30-60;
+ * README.md:3-5 on its memory) never exists:
+ *   logits[r,v] = sum_d x[r,d] * w[v,d] (+ bias[v])   in float accumulators
+ *   d_x (rows, D) bfloat16: the packed joiner activations;  d_w (V, D) bfloat16:
+ *   the projection's weight (torch.nn.Linear layout);  d_bias (V) float or NULL.
+ * D a multiple of 8, d_x and d_w 16-byte aligned.  A tcgen05 (5th-generation
+ * tensor core) kernel: TMA-staged operands, accumulators in tensor memory, the
+ * epilogue keeps per row the running (max, sum) and the blank / target entries.
+ * Then the recursions and the closing stage run as in ot_b200_forward; den, lp,
+ * alpha, beta in the workspace and d_scores, d_loss are the same quantities.
+ * Standard transducer only; `flags` may hold OT_B200_CHECK_INPUTS,
+ * OT_B200_REPORT_ERRORS, OT_B200_FAST_MATH, OT_B200_TRACE.  Forward only: the
+ * gradient pass needs logits (ot_b200_backward), so this entry serves scoring
+ * and validation; size the workspace with flags = 0. */
+int ot_b200_forward_linear(const void *d_x, const void *d_w, const float *d_bias,
+                           const int32_t *d_targets, const int32_t *d_logit_lengths,
+                           const int32_t *d_target_lengths, int32_t N, int64_t rows, int32_t D,
+                           int32_t V, int32_t max_u, int32_t blank, uint32_t flags,
+                           void *d_workspace, uint64_t workspace_bytes, void *d_scores, void *d_loss,
+                           double loss_scale, void *stream);
+
 /* d_grad[i] *= *d_scale for i < count, unless *d_scale == 1 (then the buffer is
  * not touched: the kernel's blocks return after one load).  The counterpart of
  * `ctx.grad.mul_(loss_grad)` (transducer_loss.py:162) for a gradient that

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libot_b200.so")
 SOURCES = ["api.cu", "prep.cu", "logprob.cu", "lattice.cu", "gradient.cu", "noalloc.cu", "pack.cu",
-           "exchange.cu"]
+           "exchange.cu", "fused_linear.cu"]
 HEADERS = [os.path.join(CSRC, "ot_common.cuh"),
            os.path.join(HERE, os.pardir, "include", "ot_b200.h")]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

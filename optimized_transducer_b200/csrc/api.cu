@@ -536,6 +536,46 @@ int ot_b200_loss_and_gradient(const void *d_logits, void *d_grad, const int32_t 
   return OT_B200_OK;
 }
 
+int ot_b200_forward_linear(const void *d_x, const void *d_w, const float *d_bias,
+                           const int32_t *d_targets, const int32_t *d_logit_lengths,
+                           const int32_t *d_target_lengths, int32_t N, int64_t rows, int32_t D,
+                           int32_t V, int32_t max_u, int32_t blank, uint32_t flags,
+                           void *d_workspace, uint64_t workspace_bytes, void *d_scores, void *d_loss,
+                           double loss_scale, void *stream) {
+  if (flags & (OT_B200_FROM_LOG_SOFTMAX | OT_B200_ONE_SYM_PER_FRAME | OT_B200_FP64 | OT_B200_BF16 | OT_B200_FP16))
+    return fail(OT_B200_ERR_ARGUMENT, "ot_b200_forward_linear: standard transducer, bfloat16 operands, float results; "
+                                      "flags may hold OT_B200_CHECK_INPUTS, OT_B200_REPORT_ERRORS, OT_B200_FAST_MATH, OT_B200_TRACE");
+  Problem p;
+  int rc = check_common(N, rows, V, max_u, blank, flags, d_workspace, workspace_bytes, &p.lay);
+  if (rc) return rc;
+  if (!d_x || !d_w || !d_logit_lengths || !d_target_lengths || !d_scores)
+    return fail(OT_B200_ERR_ARGUMENT, "a required device pointer is NULL");
+  if (max_u > 0 && !d_targets) return fail(OT_B200_ERR_ARGUMENT, "targets pointer is NULL");
+  if (D <= 0 || D % 8 != 0)
+    return fail(OT_B200_ERR_ARGUMENT, "ot_b200_forward_linear: D must be a positive multiple of 8 (rows of 16-byte units), got %d", D);
+  if (reinterpret_cast<uintptr_t>(d_x) % 16 != 0 || reinterpret_cast<uintptr_t>(d_w) % 16 != 0)
+    return fail(OT_B200_ERR_ARGUMENT, "ot_b200_forward_linear: x and w must be 16-byte aligned");
+  p.logits = nullptr; p.targets = d_targets; p.T = d_logit_lengths; p.U = d_target_lengths;
+  p.N = N; p.rows = rows; p.V = V; p.max_u = max_u; p.blank = blank; p.flags = flags;
+  p.ws = static_cast<char *>(d_workspace);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  volatile int32_t *slot = nullptr;
+  rc = attach_reports(&p, flags, s, &slot);
+  if (rc) return rc;
+  cudaError_t e = launch_prepare(p, s);
+  if (e != cudaSuccess) return fail_cuda(e, "launch prepare");
+  e = launch_linear_logprob(p, d_x, d_w, d_bias, D, s);
+  if (e == cudaErrorNotSupported)
+    return fail(OT_B200_ERR_CUDA, "ot_b200_forward_linear: the driver's tensor-map encoder is not available or refused the operands");
+  if (e != cudaSuccess) return fail_cuda(e, "launch linear+logprob");
+  e = launch_lattice(p, d_scores, s);
+  if (e != cudaSuccess) return fail_cuda(e, "launch lattice");
+  e = launch_coef(p, d_scores, d_loss, loss_scale, s);
+  if (e != cudaSuccess) return fail_cuda(e, "launch coef");
+  if (slot) return wait_for_verdict(slot, p.report_seq, s);
+  return OT_B200_OK;
+}
+
 int ot_b200_scale_gradient(void *d_grad, int64_t count, const void *d_scale, uint32_t flags,
                            void *stream) {
   if (!d_grad || !d_scale || count <= 0)

@@ -25,6 +25,9 @@
 // V*sizeof(X) read + V*sizeof(X) written (mode A), V*sizeof(X) written (mode B),
 // plus one 32-byte (16-byte) coefficient record.
 
+#include <stdlib.h>
+#include <string.h>
+
 #include "ot_common.cuh"
 
 namespace otb {
@@ -198,6 +201,118 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
   if (threadIdx.x == 0) trace_end(status, trace_slot(kStageGradient, group));
 }
 
+// The same pass for 16-bit rows of at most 512 columns (V % 4 == 0, 8-byte
+// aligned rows), software-pipelined.  A 16-bit row is half as many bytes per warp
+// as a float row, so with one row per warp in flight the pass waits on memory
+// latency (measured: 5.1 TB/s, long-scoreboard stalls, DRAM half idle).  Here a
+// warp requests its NEXT row (record and vectors) before it works on the current
+// one, which doubles the bytes it keeps in flight; one resident wave of blocks
+// strides over the buffer from its end, so the next row is known.  Arithmetic:
+// one FFMA, one ex2 and one multiply per element with the row's constants folded
+// (2^(x*log2e + (c+beta)*log2e)), one conversion per pair; the two columns that
+// carry a second term are rewritten by the lanes that own them after their
+// vector store (same thread, so the later store lands on top).
+template <typename X, bool PER_UTT>
+__global__ void __launch_bounds__(kThreads, 5)
+gradient16_kernel(const X *x, X *g, const CoefA<float> *__restrict__ coef,
+                  const int32_t *__restrict__ status, int64_t rows, int V, int blank,
+                  const float *__restrict__ d_scale, float scale_host,
+                  const int64_t *__restrict__ split, int N, int group) {
+  pdl_wait();
+  pdl_trigger();
+  if (status[kStatusCode] != 0) return;
+  int64_t row_lo = 0;
+  if (group >= 0) {
+    int lo, hi;
+    group_range(status, group, N, lo, hi);
+    row_lo = __ldg(split + lo);
+    rows = __ldg(split + hi);
+  }
+  if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageGradient, group));
+  constexpr int CH = 4;  // vectors of 4 elements per lane: 512 columns
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
+  const int nvec = V >> 2;
+  const float scale_all = (!PER_UTT && d_scale) ? scale_host * __ldg(d_scale) : scale_host;
+  const int b_lane = (blank >> 2) & 31, b_j = blank >> 7, b_k = blank & 3;
+
+  const auto fetch = [&](int64_t row, CoefA<float> &rec, uint2 (&v)[CH]) {
+    rec = load_coef(coef + row);
+    const uint2 *px = reinterpret_cast<const uint2 *>(x + row * (int64_t)V);
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+      const int vi = j * kWarp + lane;
+      if (vi < nvec) v[j] = px[vi];
+    }
+  };
+  // element k (0..3) of vector j of this lane, widened
+  const auto element = [&](const uint2 (&v)[CH], int j, int k) {
+    uint2 cand = v[0];
+#pragma unroll
+    for (int q = 1; q < CH; ++q)
+      if (q == j) cand = v[q];
+    const float2 p = Pair16<X>::widen((k & 2) ? cand.y : cand.x);
+    return (k & 1) ? p.y : p.x;
+  };
+  const auto finish = [&](int64_t row, const CoefA<float> &rec, uint2 (&v)[CH]) {
+    uint2 *pg = reinterpret_cast<uint2 *>(g + row * (int64_t)V);
+    if (rec.tgt == kTgtZeroRow) {
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int vi = j * kWarp + lane;
+        if (vi < nvec) pg[vi] = make_uint2(0u, 0u);  // +0 in both 16-bit formats
+      }
+      return;
+    }
+    const float scale = PER_UTT ? scale_host * __ldg(d_scale + rec.utt) : scale_all;
+    // the two special columns, from the unmodified logits of the lanes that own them
+    X fix_b = from_real<X>(0.f), fix_t = from_real<X>(0.f);
+    const bool own_b = lane == b_lane && (b_j * kWarp + lane) < nvec;
+    const bool own_t = rec.tgt >= 0 && rec.tgt != blank && lane == ((rec.tgt >> 2) & 31);
+    if (own_b) {
+      const float gv = element(v, b_j, b_k) + rec.c;
+      fix_b = from_real<X>((s_exp(gv + rec.beta) - s_exp(gv + rec.sub_blank)) * scale);
+    }
+    if (own_t) {
+      const float gv = element(v, rec.tgt >> 7, rec.tgt & 3) + rec.c;
+      fix_t = from_real<X>((s_exp(gv + rec.beta) - s_exp(gv + rec.sub_sym)) * scale);
+    }
+    const float k2 = (rec.c + rec.beta) * kLog2e;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+      const int vi = j * kWarp + lane;
+      if (vi < nvec) {
+        const float2 a = Pair16<X>::widen(v[j].x), b = Pair16<X>::widen(v[j].y);
+        uint2 o;
+        o.x = Pair16<X>::round(ex2_approx(fmaf(a.x, kLog2e, k2)) * scale, ex2_approx(fmaf(a.y, kLog2e, k2)) * scale);
+        o.y = Pair16<X>::round(ex2_approx(fmaf(b.x, kLog2e, k2)) * scale, ex2_approx(fmaf(b.y, kLog2e, k2)) * scale);
+        pg[vi] = o;
+      }
+    }
+    X *pe = g + row * (int64_t)V;
+    if (own_b) pe[blank] = fix_b;
+    if (own_t) pe[rec.tgt] = fix_t;
+  };
+
+  // Two register sets alternate between "being fetched" and "being finished".
+  CoefA<float> rec_a, rec_b;
+  uint2 va[CH], vb[CH];
+  int64_t row = rows - 1 - warp0;
+  if (row >= row_lo) fetch(row, rec_a, va);
+  while (row >= row_lo) {
+    const int64_t next = row - nwarps;
+    if (next >= row_lo) fetch(next, rec_b, vb);
+    finish(row, rec_a, va);
+    if (next < row_lo) break;
+    const int64_t after = next - nwarps;
+    if (after >= row_lo) fetch(after, rec_a, va);
+    finish(next, rec_b, vb);
+    row = after;
+  }
+  if (threadIdx.x == 0) trace_end(status, trace_slot(kStageGradient, group));
+}
+
 template <typename X, int VEC, bool PER_UTT>
 __global__ void __launch_bounds__(kThreads)
 gradient_logsoftmax_kernel(X *__restrict__ g, const CoefB<typename Real<X>::type> *__restrict__ coef,
@@ -306,9 +421,34 @@ cudaError_t launch_grad_a2(const Problem &p, void *grad, const void *d_scale,
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
+// OT_B200_GRAD16=plain keeps the general kernel for 16-bit rows (for comparison).
+bool grad16_plain_forced() {
+  const char *e = getenv("OT_B200_GRAD16");
+  return e && strcmp(e, "plain") == 0;
+}
+
+template <typename X, bool PER_UTT>
+cudaError_t launch_grad16(const Problem &p, void *grad, const void *d_scale, double scale_host,
+                          cudaStream_t s) {
+  static std::atomic<int> per_sm{0};
+  auto kernel = gradient16_kernel<X, PER_UTT>;
+  const cudaError_t e = launch_pdl(kernel, stream_grid(kernel, &per_sm, p.rows, p.flags, true),
+      (unsigned)kThreads, 0, s, static_cast<const X *>(p.logits), static_cast<X *>(grad),
+      reinterpret_cast<const CoefA<float> *>(p.ws + p.lay.coef),
+      reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V, p.blank,
+      static_cast<const float *>(d_scale), (float)scale_host,
+      reinterpret_cast<const int64_t *>(p.ws + p.lay.split), p.N, p.group);
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 template <typename X, int VEC, int CH>
 cudaError_t launch_grad_a(const Problem &p, void *grad, const void *d_scale,
                           double scale_host, cudaStream_t s) {
+  if constexpr (sizeof(X) == 2 && VEC == 4) {
+    if (p.V <= 512 && !grad16_plain_forced())
+      return (p.flags & OT_B200_SCALE_PER_UTTERANCE) ? launch_grad16<X, true>(p, grad, d_scale, scale_host, s)
+                                                     : launch_grad16<X, false>(p, grad, d_scale, scale_host, s);
+  }
   return (p.flags & OT_B200_SCALE_PER_UTTERANCE)
              ? launch_grad_a2<X, VEC, CH, true>(p, grad, d_scale, scale_host, s)
              : launch_grad_a2<X, VEC, CH, false>(p, grad, d_scale, scale_host, s);

@@ -200,9 +200,15 @@ struct SmemGrant {
 // predecessor in the stream is still running (its CTAs then block in pdl_wait()
 // until the predecessor's memory is visible), which takes the launch latency
 // and the ramp-up of a full-occupancy grid out of the gap between two stages.
+// `programmatic` = false is the ordinary launch: the kernel starts when its
+// predecessor in the stream has completed.  It is what a kernel with many blocks
+// needs behind a kernel with few on a high-priority stream: launched
+// programmatically its blocks would become resident at once, wait inside
+// pdl_wait() and keep the SM slots from the streaming kernel of another stream
+// that should be running there.
 template <typename... Exp, typename... Act>
-cudaError_t launch_pdl(void (*kernel)(Exp...), unsigned grid, unsigned block, size_t smem,
-                       cudaStream_t s, Act &&...args) {
+cudaError_t launch_maybe_pdl(bool programmatic, void (*kernel)(Exp...), unsigned grid, unsigned block,
+                             size_t smem, cudaStream_t s, Act &&...args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(block);
@@ -212,8 +218,13 @@ cudaError_t launch_pdl(void (*kernel)(Exp...), unsigned grid, unsigned block, si
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = programmatic ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<Exp>(args)...);
+}
+template <typename... Exp, typename... Act>
+cudaError_t launch_pdl(void (*kernel)(Exp...), unsigned grid, unsigned block, size_t smem,
+                       cudaStream_t s, Act &&...args) {
+  return launch_maybe_pdl(true, kernel, grid, block, smem, s, static_cast<Act &&>(args)...);
 }
 #ifdef __CUDACC__
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -279,6 +290,10 @@ cudaError_t launch_coef(const Problem &p, void *scores, void *loss_out,
                         double loss_scale, cudaStream_t s);
 cudaError_t launch_gradient(const Problem &p, void *grad, const void *d_scale,
                             double scale_host, cudaStream_t s);
+// Stage 1 computed from the joiner's operands (x: (rows, D), w: (V, D), bfloat16)
+// instead of from logits; fills den and lp like launch_logprob.
+cudaError_t launch_linear_logprob(const Problem &p, const void *x, const void *w, const float *bias,
+                                  int D, cudaStream_t s);
 // In-place multiplication of a gradient by a device scalar (skipped when it is 1).
 cudaError_t launch_scale(void *g, int64_t count, const void *d_scale, uint32_t flags, cudaStream_t s);
 // After both groups of a two-group call: the loss and the error reports.

@@ -389,8 +389,10 @@ cudaError_t launch_coef_t(const Problem &p, void *scores, void *loss_out,
   void *coef = p.ws + p.lay.coef;
   const unsigned grid = (unsigned)((p.lay.max_cells + 255) / 256);
   cudaError_t e = cudaSuccess;
+  // A group launch sits on the high-priority stream behind the group's recursion:
+  // an ordinary launch there (see launch_maybe_pdl).
 #define OTB_COEF(MB, MOD)                                                        \
-  e = launch_pdl(coef_kernel<T, MB, MOD>, grid, 256u, 0, s, p.targets, p.T, p.U, split,   \
+  e = launch_maybe_pdl(p.group < 0, coef_kernel<T, MB, MOD>, grid, 256u, 0, s, p.targets, p.T, p.U, split,   \
       csplit, status, p.N, p.max_u, p.blank, den, lp, alpha, beta, coef,         \
       static_cast<T *>(scores), static_cast<T *>(loss_out), loss_scale,          \
       p.report, p.sticky, p.report_seq, p.group)

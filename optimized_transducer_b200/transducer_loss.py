@@ -61,7 +61,7 @@ from . import _lib
 
 __all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
            "compute_transducer_loss", "stage_outputs", "transducer_loss_per_utterance",
-           "PerUtteranceLossFunction", "check_inputs"]
+           "PerUtteranceLossFunction", "check_inputs", "joiner_scores"]
 
 
 # Diagnostic: with OT_TRACE=1 and a list set here (collect_traces), every
@@ -413,6 +413,74 @@ def stage_outputs(logits, targets, logit_lengths, target_lengths, blank,
            "lp": call.stage("lp").view(-1, 2)[cell], "alpha": call.stage("alpha")[cell],
            "beta": call.stage("beta")[cell], "split": call.stage("split").clone()}
     return out
+
+
+def joiner_scores(joiner_in, weight, bias, targets, logit_lengths, target_lengths, blank,
+                  reduction=None, stages=False):
+    """Scores (or the reduced loss) straight from the joiner's last projection,
+    WITHOUT materialising the logits: ``logits = joiner_in @ weight.T + bias`` is
+    computed tile by tile on the tensor cores and reduced to the row logsumexp and
+    the two gathered log-probabilities inside the same kernel
+    (``ot_b200_forward_linear``); the (rows, V) tensor the reference needs never
+    exists.  Forward only (scoring, validation): no gradient is defined.
+
+    ``joiner_in`` (rows, D) bfloat16, packed like the logits would be; ``weight``
+    (V, D) bfloat16 (the layout of ``torch.nn.Linear.weight``); ``bias`` (V,)
+    float32 or None; D a multiple of 8; standard transducer.  Returns the (N,)
+    scores ``log P(y_b | x_b)`` (float32), or with ``reduction`` "mean" / "sum" the
+    0-dim loss.  ``stages=True`` returns a dict with scores, den, lp, alpha, beta in
+    packed-row order instead (for tests)."""
+    who = "joiner_scores"
+    if joiner_in.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise RuntimeError(f"{who}: joiner_in and weight must be bfloat16")
+    if joiner_in.dim() != 2 or weight.dim() != 2 or joiner_in.size(1) != weight.size(1):
+        raise RuntimeError(f"{who}: expected joiner_in (rows, D) and weight (V, D)")
+    if not (joiner_in.is_cuda and joiner_in.is_contiguous() and weight.is_contiguous()
+            and weight.device == joiner_in.device):
+        raise RuntimeError(f"{who}: contiguous CUDA tensors on one device are required (sm_100a kernels, no CPU path)")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != weight.size(0)
+                             or bias.device != joiner_in.device or not bias.is_contiguous()):
+        raise RuntimeError(f"{who}: bias must be a contiguous float32 tensor of V entries")
+    if joiner_in.size(1) % 8 != 0:
+        raise RuntimeError(f"{who}: D must be a multiple of 8, got {joiner_in.size(1)}")
+    assert reduction in (None, "mean", "sum")
+    rows, d = joiner_in.shape
+    v = weight.size(0)
+    proxy = torch.empty((rows, v), dtype=torch.float32, device="meta")  # shapes for the shared checks only
+    for name, t in (("targets", targets), ("logit_lengths", logit_lengths), ("target_lengths", target_lengths)):
+        if t.dtype != torch.int32 or not t.is_contiguous() or t.device != joiner_in.device:
+            raise RuntimeError(f"{who}: expected {name} to be a contiguous int32 tensor on {joiner_in.device}")
+    if targets.dim() != 2 or logit_lengths.dim() != 1 or logit_lengths.shape != target_lengths.shape \
+            or targets.size(0) != logit_lengths.size(0) or not (0 <= blank < v) or rows == 0:
+        raise RuntimeError(f"{who}: inconsistent argument shapes, or blank outside [0, V)")
+    del proxy
+    lib = _lib.load()
+    n, max_u = int(logit_lengths.size(0)), int(targets.size(1))
+    flags = _CHECK_FLAG[_check_mode("strict")] | (_lib.FAST_MATH if _fast_math(False) else 0)
+    lay = _layout(n, rows, max_u, 0)
+    dev = joiner_in.device
+    ws = torch.empty(int(lay.total_bytes), dtype=torch.uint8, device=dev)
+    scores = torch.empty(n, dtype=torch.float32, device=dev)
+    loss = torch.empty((), dtype=torch.float32, device=dev) if reduction else None
+    scale = (1.0 / n) if reduction == "mean" else 1.0
+    with _on_device(dev.index):
+        rc = lib.ot_b200_forward_linear(
+            joiner_in.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+            targets.data_ptr() if max_u else None, logit_lengths.data_ptr(), target_lengths.data_ptr(),
+            n, rows, d, v, max_u, int(blank), flags, ws.data_ptr(), int(lay.total_bytes),
+            scores.data_ptr(), loss.data_ptr() if loss is not None else None, scale,
+            torch.cuda.current_stream(dev.index).cuda_stream)
+    if rc:
+        _lib.check(rc)
+    if not stages:
+        return loss if reduction else scores
+    # the stage arrays, through a _Call-shaped view of the same workspace
+    view = _Call.__new__(_Call)
+    view.layout, view.workspace, view.real, view.n, view.rows = lay, ws, torch.float32, n, rows
+    view.t, view.u, view.modified, view.logits = logit_lengths, target_lengths, False, joiner_in
+    cell = view.cell_index()
+    return {"scores": scores, "den": view.stage("den").clone(), "lp": view.stage("lp").view(-1, 2)[cell],
+            "alpha": view.stage("alpha")[cell], "beta": view.stage("beta")[cell]}
 
 
 class TransducerLossFunction(torch.autograd.Function):

@@ -1,0 +1,74 @@
+"""The forward half computed from the joiner's operands (``ot_b200_forward_linear``,
+a tcgen05 tensor-core kernel) against the path through materialised logits.
+
+Oracle: ``logits = x @ W^T + b`` evaluated in float64 from the bfloat16 operands
+(products of bfloat16 numbers are exact in float32; only the order of the
+D-term sums differs), then the CPU oracle of the loss on those logits.
+Tolerances: den and the log-probs to 1e-5 relative to max(1, |value|) plus the
+float32 accumulation error of a D-term dot product (2e-5 absolute); scores to
+1e-5 relative.
+"""
+import numpy as np
+import pytest
+import torch
+
+import optimized_transducer_b200 as ot
+from oracle import oracle as O
+from helpers import splits
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _case(seed, n, t_range, u_range, d, v, bias):
+    rng = np.random.default_rng(seed)
+    T = rng.integers(t_range[0], t_range[1] + 1, n).astype(np.int32)
+    U = rng.integers(u_range[0], u_range[1] + 1, n).astype(np.int32)
+    rows = int(splits(T, U)[-1])
+    x = torch.from_numpy(rng.standard_normal((rows, d)).astype(np.float32)).to(torch.bfloat16)
+    w = torch.from_numpy((rng.standard_normal((v, d)) / np.sqrt(d) * 2).astype(np.float32)).to(torch.bfloat16)
+    b = torch.from_numpy(rng.standard_normal(v).astype(np.float32)) if bias else None
+    tg = rng.integers(1, v, (n, int(U.max()))).astype(np.int32)
+    logits = x.double() @ w.double().T
+    if b is not None:
+        logits = logits + b.double()
+    return x, w, b, tg, T, U, logits.numpy()
+
+
+@pytest.mark.parametrize("shape", [
+    # seed, N, T range, U range, D, V, bias
+    (1, 3, (5, 12), (2, 6), 64, 40, False),      # one K block, one column tile, a partial row tile
+    (2, 4, (20, 40), (5, 12), 512, 500, True),   # the benchmark's shape of operands: 8 K blocks, 2 column tiles
+    (3, 2, (30, 50), (3, 9), 200, 1030, True),   # D not a multiple of 64, five column tiles with a ragged last one
+    (4, 5, (60, 90), (10, 30), 256, 300, False), # many row tiles per CTA
+])
+def test_scores_from_the_joiner_operands(shape):
+    seed, n, tr, ur, d, v, bias = shape
+    x, w, b, tg, T, U, logits = _case(seed, n, tr, ur, d, v, bias)
+    ref = O.oracle_loss(logits, tg, T, U, 0)
+    dx, dw = x.to(DEV), w.to(DEV)
+    db = b.to(DEV) if b is not None else None
+    dt, dT, dU = (torch.from_numpy(a).to(DEV) for a in (tg, T, U))
+    out = ot.joiner_scores(dx, dw, db, dt, dT, dU, 0, stages=True)
+    torch.cuda.synchronize()
+    den = out["den"].double().cpu().numpy()
+    assert np.max(np.abs(den - ref["den"]) / np.maximum(1, np.abs(ref["den"]))) <= 1e-5 + 2e-5
+    ok = ~np.isnan(ref["lp"])
+    lp = out["lp"].double().cpu().numpy()
+    assert np.max(np.abs(lp[ok] - ref["lp"][ok]) / np.maximum(1, np.abs(ref["lp"][ok]))) <= 1e-5 + 4e-5
+    s = out["scores"].double().cpu().numpy()
+    assert np.max(np.abs(s - ref["scores"]) / np.abs(ref["scores"])) <= 1e-5
+    # and the reduced loss equals the loss of the materialised float32 logits
+    loss = ot.joiner_scores(dx, dw, db, dt, dT, dU, 0, reduction="mean")
+    dense = (dx.float() @ dw.float().T) + (db if db is not None else 0)
+    want = ot.transducer_loss(dense.contiguous(), dt, dT, dU, 0, False, reduction="mean")
+    assert abs(loss.item() - want.item()) <= 2e-5 * abs(want.item())
+
+
+def test_bad_lengths_are_reported_not_followed():
+    x, w, b, tg, T, U, _ = _case(5, 3, (5, 9), (2, 4), 64, 20, False)
+    Tb = T.copy(); Tb[1] += 1
+    with pytest.raises(RuntimeError, match="logits.size\\(0\\)"):
+        ot.joiner_scores(x.to(DEV), w.to(DEV), None, torch.from_numpy(tg).to(DEV),
+                         torch.from_numpy(Tb).to(DEV), torch.from_numpy(U).to(DEV), 0)
+    torch.cuda.synchronize()
