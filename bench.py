@@ -92,31 +92,36 @@ def recorded_traffic_per_cell(dtype, mode_b):
 
 
 def record_traffic(args, w):
-    """Parses an ncu csv log (long format: one line per launch and metric)."""
-    from optimized_transducer_b200 import synthetic
+    """Parses an ncu csv log (long format: one line per launch and metric).  The
+    cells a gradient launch covers follow from its grid: one block per 8 rows (a
+    launch of a two-group call covers about half the batch)."""
     per_launch = {}
     with open(args.record_traffic, newline="") as f:
         rows = [r for r in csv.reader(f) if len(r) >= 15 and r[0].isdigit()]
     for r in rows:
-        name, metric, value = r[4], r[12], float(r[14].replace(",", ""))
-        if "gradient" in name and metric in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
-            per_launch.setdefault(r[0], {})[metric] = value
-    full = [sum(v.values()) for v in per_launch.values() if len(v) == 2]
+        name, grid, metric, value = r[4], r[8], r[12], float(r[14].replace(",", ""))
+        if "gradient_kernel" in name and "scale" not in name and \
+                metric in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+            rec = per_launch.setdefault(r[0], {"blocks": int(grid.strip("()").split(",")[0])})
+            rec[metric] = value
+    full = [v for v in per_launch.values() if len(v) == 3]
     if not full:
         raise SystemExit("no gradient-kernel launch with both DRAM metrics in " + args.record_traffic)
-    T, U, _ = synthetic.make_lengths(w)
-    n = min(args.utts, w.n) if args.utts else w.n
-    cells = synthetic.num_rows(T[:n], U[:n]) * w.v
+    total_bytes = sum(v["dram__bytes_read.sum"] + v["dram__bytes_write.sum"] for v in full)
+    total_cells = sum(v["blocks"] * 8 * w.v for v in full)
     rec = {
         "kernel": "gradient_logsoftmax_kernel" if w.from_log_softmax else "gradient_kernel",
-        "workload": f"{w.name}, first {n} utterances, {cells} cells", "dtype": args.dtype,
-        "from_log_softmax": w.from_log_softmax, "launches": len(full),
-        "dram_bytes_per_launch": statistics.mean(full),
-        "dram_bytes_per_cell": statistics.mean(full) / cells,
+        "workload": f"{w.name}" + (f", first {args.utts} utterances" if args.utts else ", whole batch"),
+        "dtype": args.dtype, "from_log_softmax": w.from_log_softmax, "launches": len(full),
+        "cells_per_launch": total_cells / len(full),
+        "dram_bytes_per_launch": total_bytes / len(full),
+        "dram_bytes_per_cell": total_bytes / total_cells,
         "source_sha256": gradient_source_hash(),
         "sources": [os.path.relpath(p, ROOT) for p in GRADIENT_SOURCES],
-        "made_by": "python bench.py --record-traffic <ncu csv log> --workload %s --utts %d --dtype %s"
-                   % (w.name, args.utts, args.dtype),
+        "made_by": "python bench.py --record-traffic <csv log of: ncu --metrics gpu__time_duration.sum,"
+                   "dram__bytes_read.sum,dram__bytes_write.sum --clock-control none --csv --log-file <csv> "
+                   "python bench.py --workload %s%s --dtype %s --steps 3 --warmup 3 --no-cpu-baseline "
+                   "--no-e2e --no-timeline>" % (w.name, f" --utts {args.utts}" if args.utts else "", args.dtype),
     }
     with open(TRAFFIC_FILE, "w") as f:
         json.dump(rec, f, indent=1)
@@ -717,7 +722,7 @@ def run_ours(args, w):
         grad_bytes = (1 if mode_b else 2) * es * cells_local
         achieved = grad_bytes / (kernel_ms * 1e-3) / 1e9
         eager = os.environ.get("OT_EAGER_GRAD", "1") != "0"
-        two_groups = (eager and not mode_b and T.numel() >= 2 and bytes_logits >= (256 << 20)
+        two_groups = (eager and not mode_b and T.numel() >= 2 and cells_local >= (192 << 20)
                       and os.environ.get("OT_B200_PIPELINE", "1") != "0")
         # own kernels per step and rank: prepare, logprob, lattice, coef, gradient (twice
         # the last four + one closing kernel when the batch runs as two groups), the
@@ -754,7 +759,7 @@ def run_ours(args, w):
                                       "eager (loss and gradient in one library call, as the reference; "
                                       "backward only scales, and skips that when the upstream gradient is 1)"),
                 "stage_overlap": ("off (OT_B200_PIPELINE=0)" if os.environ.get("OT_B200_PIPELINE", "1") == "0"
-                                  else "two groups of utterances on three streams when a rank holds >= 256 MB of logits"),
+                                  else "two groups of utterances on three streams when a rank holds >= 192 Mi lattice cells (768 MB of float logits)"),
                 "host_enqueue_ms_per_step": host_ms,
             },
             "clocks": clocks.summary(),
@@ -857,6 +862,64 @@ def run_pack(args, w):
     print(json.dumps(line), flush=True)
 
 
+def run_fused(args, w):
+    """The forward half computed from the joiner's operands (no logits): D = 512
+    bfloat16 features on the workload's lengths, weight (V, 512).  The bound of the
+    fused kernel is the tensor pipe: 2*rows*D*V flops against the measured dense
+    bfloat16 peak."""
+    import torch
+    import optimized_transducer_b200 as ot
+    from optimized_transducer_b200 import synthetic
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    d = 512
+    T, U, tg = synthetic.make_lengths(w)
+    if args.utts:
+        n = min(args.utts, w.n)
+        T, U = T[:n].contiguous(), U[:n].contiguous()
+        tg = tg[:n, :int(U.max())].contiguous()
+    rows = synthetic.num_rows(T, U)
+    g = torch.Generator(device=dev).manual_seed(w.seed)
+    x = torch.randn(rows, d, device=dev, generator=g).to(torch.bfloat16)
+    wt = (torch.randn(w.v, d, device=dev, generator=g) * (w.scale / d ** 0.5)).to(torch.bfloat16)
+    bias = torch.zeros(w.v, device=dev)
+    dT, dU, dtg = T.to(dev), U.to(dev), tg.to(dev)
+    os.environ["OT_TRACE"] = "1"
+    os.environ.setdefault("OT_CHECKS", "0")
+    n_it = args.warmup + args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(n_it)]
+    spans = []
+    for it in range(n_it):
+        ev[it][0].record()
+        out = ot.joiner_scores(x, wt, bias, dtg, dT, dU, 0, stages=False, reduction="sum", _trace=spans)
+        ev[it][1].record()
+    torch.cuda.synchronize()
+    ms = statistics.median(ev[it][0].elapsed_time(ev[it][1]) for it in range(args.warmup, n_it))
+    k_us = statistics.median((int(t[3]) - int(t[2])) / 1e3 for t in (s.cpu() for s in spans[args.warmup:]))
+    flops = 2.0 * rows * d * w.v
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, kind = float(json.load(f)["bf16_tflops"]), "measured (burst)"
+    except Exception:
+        peak, kind = 1590.0, "fallback"
+    line = {
+        "metric": "lattice rows/s of the logits-free forward half (projection + logsumexp + recursions)",
+        "value": rows / (ms * 1e-3), "unit": "rows/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 operands, f32 accumulators", "data": "synthetic",
+        "config": {"workload": f"joiner_scores on {w.name} lengths: rows={rows}, D={d}, V={w.v}"},
+        "roofline": {"kernel": "linear_logprob_kernel", "bound": "tensor", "achieved": flops / (k_us * 1e-6) / 1e12,
+                     "peak": peak, "unit": "TFLOP/s", "frac": flops / (k_us * 1e-6) / 1e12 / peak,
+                     "peak_source": f"{kind} dense bf16 GEMM", "traffic": None,
+                     "us_per_launch": k_us, "timing": "the kernel's own %globaltimer span (first block start to last block end)"},
+        "bytes_never_written": rows * w.v * 4,
+        "gpu_launches": 4 * args.steps,
+        "loss": float(out.item()),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -882,8 +945,9 @@ def main():
                     help="utterances per step of the reference arm (0: the whole batch, up to 4 GB of logits)")
     ap.add_argument("--cpu-utts", type=int, default=0,
                     help="utterances of the CPU-baseline sample of our arm (0: as --ref-utts 0)")
-    ap.add_argument("--op", choices=["loss", "pack"], default="loss",
-                    help="loss: the transducer loss (default, the benchmark); pack: the packing helpers")
+    ap.add_argument("--op", choices=["loss", "pack", "fused"], default="loss",
+                    help="loss: the transducer loss (default, the benchmark); pack: the packing helpers; "
+                         "fused: the logits-free forward half (projection fused with the logsumexp)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer measurement")
     ap.add_argument("--no-timeline", action="store_true", help="skip the traced extra steps")
@@ -900,6 +964,8 @@ def main():
         record_traffic(args, w)
     elif args.op == "pack":
         run_pack(args, w)
+    elif args.op == "fused":
+        run_fused(args, w)
     elif args.impl == "reference":
         run_reference_arm(args, w)
     elif args.impl == "reference-cuda":

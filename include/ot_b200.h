@@ -206,7 +206,7 @@ int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows
  *   (d_grad may be NULL: no gradient; MAY EQUAL d_logits unless
  *   OT_B200_FROM_LOG_SOFTMAX).  Arguments otherwise as for ot_b200_forward.
  * Because the whole step is one call, large batches (raw-logit input with a
- * gradient, >= 256 MB of logits) run as two groups of utterances on three
+ * gradient, >= 192 Mi lattice cells = rows * V) run as two groups of utterances on three
  * streams (the caller's and two the library creates per device on first use):
  * the recursion of one group overlaps the streaming kernels of the other.  The
  * caller's stream waits, by events, for everything before the function's last
@@ -375,8 +375,21 @@ int ot_b200_scores_noalloc(const float *d_log_probs, const int32_t *d_targets,
  *   *d_error (set it to 0 beforehand) becomes 1 + the rank that did not arrive
  *   (101 + rank: its entry was already overwritten by a step >= step + ring),
  *   *d_out becomes NaN and the kernel returns.
- * d_value / d_out are float, or double with OT_B200_FP64.  world <= 32. */
+ * d_value / d_out are float, or double with OT_B200_FP64.  world <= 32.
+ *
+ * ot_b200_exchange_allreduce: publish + gather of one step in ONE call, on a
+ *   highest-priority stream the library keeps per device (created on first use):
+ *   that stream first waits (by an event) for what `stream` holds so far, i.e.
+ *   for *d_value; nothing in `stream` waits for the exchange.  *d_out is defined
+ *   once ot_b200_exchange_wait(reader_stream) has made the reader's stream wait
+ *   for the most recent all-reduce of the device.  d_value and d_out must stay
+ *   valid until then (the Python layer keeps a ring of slots for them). */
 int ot_b200_exchange_bytes(int32_t world, int32_t ring, uint64_t *bytes_out);
+int ot_b200_exchange_allreduce(const void *d_value, void *d_out, uint32_t flags, void *const *d_tables,
+                               const void *d_table, int32_t world, int32_t rank, int32_t ring,
+                               uint64_t step, double scale, int32_t *d_error, uint64_t max_wait_ns,
+                               void *stream);
+int ot_b200_exchange_wait(void *stream);
 int ot_b200_exchange_publish(const void *d_value, uint32_t flags, void *const *d_tables,
                              int32_t world, int32_t rank, int32_t ring, uint64_t step,
                              void *stream);

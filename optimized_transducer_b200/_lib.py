@@ -48,6 +48,8 @@ EXPORTS = (
     "ot_b200_pack_padded",
     "ot_b200_unpack_to_padded",
     "ot_b200_exchange_bytes",
+    "ot_b200_exchange_allreduce",
+    "ot_b200_exchange_wait",
     "ot_b200_exchange_publish",
     "ot_b200_exchange_gather",
 )
@@ -116,6 +118,10 @@ def load():
         fn.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, vp, vp]
     lib.ot_b200_exchange_bytes.restype = ctypes.c_int
     lib.ot_b200_exchange_bytes.argtypes = [i32, i32, ctypes.POINTER(u64)]
+    lib.ot_b200_exchange_allreduce.restype = ctypes.c_int
+    lib.ot_b200_exchange_allreduce.argtypes = [vp, vp, u32, vp, vp, i32, i32, i32, u64, ctypes.c_double, vp, u64, vp]
+    lib.ot_b200_exchange_wait.restype = ctypes.c_int
+    lib.ot_b200_exchange_wait.argtypes = [vp]
     lib.ot_b200_exchange_publish.restype = ctypes.c_int
     lib.ot_b200_exchange_publish.argtypes = [vp, u32, vp, i32, i32, i32, u64, vp]
     lib.ot_b200_exchange_gather.restype = ctypes.c_int

@@ -23,11 +23,40 @@
 // before any rank publishes (seq 0 = nothing); step k uses slot k % ring and
 // seq k + 1, so a gather can tell an entry that was overwritten by a rank more
 // than `ring` steps ahead (error 2) from one that has not arrived (error 1).
+#include <mutex>
+
 #include "ot_common.cuh"
 
 namespace otb {
 
 namespace {
+
+// Resources of ot_b200_exchange_allreduce: per device one highest-priority stream
+// (the two one-warp kernels must be placed beside whatever streaming kernel fills
+// the SMs) and two events, created on first use and kept until the process exits.
+struct ExchangeLane {
+  std::mutex lock;
+  bool ready = false;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, done = nullptr;
+  bool pending = false;  // `done` has been recorded at least once
+};
+ExchangeLane g_lanes[kMaxDevices];
+
+cudaError_t lane_init(ExchangeLane &l) {
+  if (l.ready) return cudaSuccess;
+  int least = 0, greatest = 0;
+  cudaError_t e = cudaDeviceGetStreamPriorityRange(&least, &greatest);
+  if (e != cudaSuccess) return e;
+  e = cudaStreamCreateWithPriority(&l.stream, cudaStreamNonBlocking, greatest);
+  if (e != cudaSuccess) return e;
+  e = cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming);
+  if (e != cudaSuccess) return e;
+  e = cudaEventCreateWithFlags(&l.done, cudaEventDisableTiming);
+  if (e != cudaSuccess) return e;
+  l.ready = true;
+  return cudaSuccess;
+}
 
 struct alignas(16) ExEntry {
   double value;
@@ -116,6 +145,50 @@ int ot_b200_exchange_publish(const void *d_value, uint32_t flags, void *const *d
   else
     exchange_publish_kernel<float><<<1, 32, 0, s>>>(static_cast<const float *>(d_value), tables, world, rank, slot, step + 1);
   const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return OT_B200_ERR_CUDA;
+  }
+  return OT_B200_OK;
+}
+
+int ot_b200_exchange_allreduce(const void *d_value, void *d_out, uint32_t flags, void *const *d_tables,
+                               const void *d_table, int32_t world, int32_t rank, int32_t ring,
+                               uint64_t step, double scale, int32_t *d_error, uint64_t max_wait_ns,
+                               void *stream) {
+  if (!d_value || !d_out || !d_tables || !d_table || !d_error || world < 1 || world > 32 || rank < 0 ||
+      rank >= world || ring < 1) {
+    set_last_error("ot_b200_exchange_allreduce: bad argument");
+    return OT_B200_ERR_ARGUMENT;
+  }
+  ExchangeLane &l = g_lanes[current_device_slot()];
+  std::lock_guard<std::mutex> guard(l.lock);
+  cudaError_t e = lane_init(l);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (e == cudaSuccess) e = cudaEventRecord(l.fork, s);             // the value is ready in `stream` order
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(l.stream, l.fork, 0);
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return OT_B200_ERR_CUDA;
+  }
+  int rc = ot_b200_exchange_publish(d_value, flags, d_tables, world, rank, ring, step, l.stream);
+  if (rc) return rc;
+  rc = ot_b200_exchange_gather(d_table, world, ring, step, d_out, flags, scale, d_error, max_wait_ns, l.stream);
+  if (rc) return rc;
+  e = cudaEventRecord(l.done, l.stream);
+  if (e != cudaSuccess) {
+    set_last_error(cudaGetErrorString(e));
+    return OT_B200_ERR_CUDA;
+  }
+  l.pending = true;
+  return OT_B200_OK;
+}
+
+int ot_b200_exchange_wait(void *stream) {
+  ExchangeLane &l = g_lanes[current_device_slot()];
+  std::lock_guard<std::mutex> guard(l.lock);
+  if (!l.pending) return OT_B200_OK;
+  const cudaError_t e = cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), l.done, 0);
   if (e != cudaSuccess) {
     set_last_error(cudaGetErrorString(e));
     return OT_B200_ERR_CUDA;

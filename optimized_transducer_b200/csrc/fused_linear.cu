@@ -24,8 +24,11 @@
 //   warp 1      MMA issuer: 4 MMAs (M=128, N=256, K=16) per K block into one of two
 //               256-column TMEM accumulators; tcgen05.commit releases the stage /
 //               publishes the accumulator
-//   warps 2-5   epilogue: thread = row (TMEM lane); reads its 256 columns of the
-//               finished accumulator while the MMA warp fills the other one
+//   warps 2-9   epilogue: two warps per TMEM lane quarter, thread = row; each takes
+//               every other 32-column chunk of the finished accumulator (bias from
+//               shared memory, running max and sum, the blank / target entries picked
+//               by a select tree) while the MMA warp fills the other accumulator;
+//               the two halves of a row meet in shared memory at the end of its tile
 //
 // Every wait on an mbarrier is bounded; on expiry the CTA raises its abort flag,
 // records status word kStatusCopyTimeout, all roles leave their loops, the
@@ -44,7 +47,9 @@ constexpr int kTileN = 256;     // columns per MMA = half of TMEM
 constexpr int kBlockK = 64;     // bfloat16 elements per K block = one 128-byte swizzle row
 constexpr int kMmaK = 16;       // K of one tcgen05.mma for 16-bit operands
 constexpr int kRing = 4;        // shared-memory stages
-constexpr int kFusedThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kFusedThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kMaxBiasColumns = 7680;  // bias staged in shared memory behind the ring: vocabularies up to this size
 constexpr uint32_t kBytesA = kTileM * kBlockK * 2;   // 16 KB
 constexpr uint32_t kBytesB = kTileN * kBlockK * 2;   // 32 KB
 constexpr uint32_t kStageBytes = kBytesA + kBytesB;  // 48 KB
@@ -127,10 +132,25 @@ struct FusedShared {
   uint64_t full[kRing];        // TMA -> MMA: the stage's two boxes have landed
   uint64_t empty[kRing];       // MMA -> TMA: the stage's MMAs have completed
   uint64_t acc_full[2];        // MMA -> epilogue: the accumulator is complete
-  uint64_t acc_empty[2];       // epilogue -> MMA: the accumulator has been read (128 arrivals)
+  uint64_t acc_empty[2];       // epilogue -> MMA: the accumulator has been read (one arrival per epilogue thread)
   uint32_t tmem_base;
   volatile int abort;
+  float4 half[kTileM];         // (max, sum, blank entry, target entry) of the rows' second halves
 };
+
+// Element idx (0..31, may differ per lane) of a register array: a tree of selects.
+__device__ __forceinline__ float pick32(const float (&x)[32], int idx) {
+  float a[16], b[8], c[4], d[2];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) a[i] = (idx & 16) ? x[i + 16] : x[i];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) b[i] = (idx & 8) ? a[i + 8] : a[i];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) c[i] = (idx & 4) ? b[i + 4] : b[i];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) d[i] = (idx & 2) ? c[i + 2] : c[i];
+  return (idx & 1) ? d[1] : d[0];
+}
 
 __global__ void __launch_bounds__(kFusedThreads, 1)
 linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -144,12 +164,19 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned char *ring = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(ring_mem) + 1023) & ~uintptr_t(1023));  // swizzle atoms are 1024-byte aligned
+  // behind the ring: the bias of every column, padded with zeros to whole column tiles
+  float *bias_s = reinterpret_cast<float *>(ring + (size_t)kRing * kStageBytes);
+  {
+    const int padded = ((V + kTileN - 1) / kTileN) * kTileN;
+    for (int i = threadIdx.x; i < padded; i += kFusedThreads)
+      bias_s[i] = (bias != nullptr && i < V) ? __ldg(bias + i) : 0.f;
+  }
 
   pdl_wait();     // stage 0 (splits, status, the -inf fill of lp) is complete
   pdl_trigger();
   if (threadIdx.x == 0) {
     for (int i = 0; i < kRing; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh.acc_full[i], 1); mbar_init(&sh.acc_empty[i], kTileM); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh.acc_full[i], 1); mbar_init(&sh.acc_empty[i], 32 * kEpilogueWarps); }
     sh.abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -164,6 +191,7 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = sh.tmem_base;
   const bool run = status[kStatusCode] == 0;  // bad inputs: nothing is computed
+  if (run && threadIdx.x == 0) trace_begin(status, kStageLogprob);
 
   const int64_t row_tiles = (rows + kTileM - 1) / kTileM;
   const int col_tiles = (V + kTileN - 1) / kTileN;
@@ -219,8 +247,10 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     if (sh.abort) atomicCAS(status + kStatusCopyTimeout, 0, 1);
   } else if (run && warp >= 2) {
     // -------------------------------- epilogue --------------------------------
-    // TMEM lanes 32*(warp % 4) .. +31 are the ones this warp may read.
+    // TMEM lanes 32*(warp % 4) .. +31 are the ones a warp may read; the two warps of
+    // a quarter take the even / the odd 32-column chunks.
     const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;  // 0: even chunks, writes the row; 1: odd chunks
     const int r_in_tile = quarter * 32 + lane;
     const float ninf = neg_inf<float>();
     uint32_t acc_it = 0;
@@ -244,46 +274,66 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kTileN);
 #pragma unroll 1
-        for (int c = 0; c < kTileN / 32; ++c) {
+        for (int c = part; c < kTileN / 32; c += 2) {
+          const int col0 = ct * kTileN + c * 32;
+          if (col0 >= V) break;  // only padding columns from here on (warp-uniform)
           float x[32];
           tmem_load_32(taddr + (uint32_t)(c * 32), x);
-          const int col0 = ct * kTileN + c * 32;
-          if (col0 >= V) continue;  // a chunk of padding columns (warp-uniform)
-          float cm = ninf;
+          const float4 *bs = reinterpret_cast<const float4 *>(bias_s + col0);  // broadcast loads
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = col0 + i;
-            float v = x[i];
-            if (bias != nullptr && col < V) v += __ldg(bias + col);
-            v = col < V ? v : ninf;  // columns past V are padding
-            x[i] = v;
-            cm = fmaxf(cm, v);
+          for (int i = 0; i < 8; ++i) {
+            const float4 bv = bs[i];
+            x[4 * i + 0] += bv.x; x[4 * i + 1] += bv.y; x[4 * i + 2] += bv.z; x[4 * i + 3] += bv.w;
+          }
+          if (col0 + 32 > V) {  // the chunk that straddles V: its padding columns drop out
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = (col0 + i < V) ? x[i] : ninf;
           }
           // the two gathered entries, when this chunk holds them
-          if (blank >= col0 && blank < col0 + 32) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (col0 + i == blank) g_blank = x[i];
+          if ((unsigned)(blank - col0) < 32u) g_blank = pick32(x, blank - col0);
+          if (__any_sync(kFull, (unsigned)(tsym - col0) < 32u)) {
+            const float v = pick32(x, (tsym - col0) & 31);
+            if ((unsigned)(tsym - col0) < 32u) g_sym = v;
           }
-          if (tsym >= col0 && tsym < col0 + 32) {
+          // running maximum and sum, four independent chains each
+          float c0 = fmaxf(x[0], x[1]), c1 = fmaxf(x[2], x[3]), c2 = fmaxf(x[4], x[5]), c3 = fmaxf(x[6], x[7]);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) if (col0 + i == tsym) g_sym = x[i];
+          for (int i = 8; i < 32; i += 4) {
+            c0 = fmaxf(c0, x[i]); c1 = fmaxf(c1, x[i + 1]); c2 = fmaxf(c2, x[i + 2]); c3 = fmaxf(c3, x[i + 3]);
           }
+          const float cm = fmaxf(fmaxf(c0, c1), fmaxf(c2, c3));
           if (cm > m) { ssum *= ex2_approx((m - cm) * kLog2e); m = cm; }  // first chunk: ssum is 0
           if (m - m == 0.f) {  // an infinite maximum needs no sum
             const float mneg = -m * kLog2e;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ssum += ex2_approx(fmaf(x[i], kLog2e, mneg));
+            for (int i = 0; i < 32; i += 4) {
+              s0 += ex2_approx(fmaf(x[i], kLog2e, mneg));
+              s1 += ex2_approx(fmaf(x[i + 1], kLog2e, mneg));
+              s2 += ex2_approx(fmaf(x[i + 2], kLog2e, mneg));
+              s3 += ex2_approx(fmaf(x[i + 3], kLog2e, mneg));
+            }
+            ssum += (s0 + s1) + (s2 + s3);
           }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(&sh.acc_empty[buf]);  // 128 arrivals: every row of the accumulator has been read
+        mbar_arrive(&sh.acc_empty[buf]);  // one arrival per epilogue thread: the accumulator has been read
       }
-      if (sh.abort) break;
-      if (live) {
-        const float d = (m - m == 0.f) ? logf(ssum) + m : m;
+      // The two halves of a row meet: part 1 leaves its (max, sum, entries), part 0 merges and writes.
+      if (part == 1) sh.half[r_in_tile] = make_float4(m, ssum, g_blank, g_sym);
+      asm volatile("bar.sync 2, %0;" ::"r"(32 * kEpilogueWarps) : "memory");
+      if (part == 0 && live && !sh.abort) {
+        const float4 o = sh.half[r_in_tile];
+        const float mm = fmaxf(m, o.x);
+        float tot = 0.f;
+        if (mm - mm == 0.f)
+          tot = ssum * ex2_approx((m - mm) * kLog2e) + o.y * ex2_approx((o.x - mm) * kLog2e);
+        const float d = (mm - mm == 0.f) ? logf(tot) + mm : mm;
+        const float gb = fmaxf(g_blank, o.z), gs = fmaxf(g_sym, o.w);  // the half that did not see it holds -inf
         den[row] = d;
-        *reinterpret_cast<float2 *>(lp + 2 * cell) = make_float2(g_blank - d, tsym >= 0 ? g_sym - d : ninf);
+        *reinterpret_cast<float2 *>(lp + 2 * cell) = make_float2(gb - d, tsym >= 0 ? gs - d : ninf);
       }
+      asm volatile("bar.sync 2, %0;" ::"r"(32 * kEpilogueWarps) : "memory");  // half[] may be overwritten again
     }
     if (sh.abort && lane == 0) atomicCAS(status + kStatusCopyTimeout, 0, 1);
   }
@@ -291,6 +341,7 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (run && threadIdx.x == 0) trace_end(status, kStageLogprob);
   if (warp == 1)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
 }
@@ -341,7 +392,10 @@ cudaError_t launch_linear_logprob(const Problem &p, const void *x, const void *w
   if (!make_map(&map_x, x, (uint64_t)p.rows, (uint64_t)D, kTileM) ||
       !make_map(&map_w, w, (uint64_t)p.V, (uint64_t)D, kTileN))
     return cudaErrorNotSupported;
-  const size_t smem = (size_t)kRing * kStageBytes + 1024;  // + room to align the ring to 1024 bytes
+  if (p.V > kMaxBiasColumns) return cudaErrorNotSupported;
+  const int padded = ((p.V + kTileN - 1) / kTileN) * kTileN;
+  // the ring, room to align it to 1024 bytes, and the bias of every (padded) column
+  const size_t smem = (size_t)kRing * kStageBytes + 1024 + (size_t)padded * sizeof(float);
   static SmemGrant grant;
   cudaError_t e = grant.ensure(linear_logprob_kernel, smem);
   if (e != cudaSuccess) return e;

@@ -209,9 +209,8 @@ gradient_kernel(const X *x, X *g, const CoefA<typename Real<X>::type> *__restric
 // one, which doubles the bytes it keeps in flight; one resident wave of blocks
 // strides over the buffer from its end, so the next row is known.  Arithmetic:
 // one FFMA, one ex2 and one multiply per element with the row's constants folded
-// (2^(x*log2e + (c+beta)*log2e)), one conversion per pair; the two columns that
-// carry a second term are rewritten by the lanes that own them after their
-// vector store (same thread, so the later store lands on top).
+// (2^(x*log2e + (c+beta)*log2e + log2 scale)), one conversion per pair; the two
+// columns that carry a second term get a per-row factor (see `finish`).
 template <typename X, bool PER_UTT>
 __global__ void __launch_bounds__(kThreads, 5)
 gradient16_kernel(const X *x, X *g, const CoefA<float> *__restrict__ coef,
@@ -246,15 +245,15 @@ gradient16_kernel(const X *x, X *g, const CoefA<float> *__restrict__ coef,
       if (vi < nvec) v[j] = px[vi];
     }
   };
-  // element k (0..3) of vector j of this lane, widened
-  const auto element = [&](const uint2 (&v)[CH], int j, int k) {
-    uint2 cand = v[0];
-#pragma unroll
-    for (int q = 1; q < CH; ++q)
-      if (q == j) cand = v[q];
-    const float2 p = Pair16<X>::widen((k & 2) ? cand.y : cand.x);
-    return (k & 1) ? p.y : p.x;
-  };
+  // One row.  FOLD: the scale is positive and finite, so it moves into the exponent
+  // (scale * 2^y = 2^(y + log2 scale)) and the multiply per element disappears.
+  // The two columns that carry a second term: with y = scale * exp(x + c + beta)
+  // already computed for every element,
+  //     scale * (exp(x+c+beta) - exp(x+c+sub)) = y * (1 - exp(sub - beta)),
+  // so the row needs two factors (warp-uniform, one ex2 each) and the lane that
+  // owns such a column multiplies its element before it is rounded; where that
+  // element sits (vector, word, half) is warp-uniform, so the patch is a uniform
+  // branch taken once per row, not a select per element.
   const auto finish = [&](int64_t row, const CoefA<float> &rec, uint2 (&v)[CH]) {
     uint2 *pg = reinterpret_cast<uint2 *>(g + row * (int64_t)V);
     if (rec.tgt == kTgtZeroRow) {
@@ -266,33 +265,32 @@ gradient16_kernel(const X *x, X *g, const CoefA<float> *__restrict__ coef,
       return;
     }
     const float scale = PER_UTT ? scale_host * __ldg(d_scale + rec.utt) : scale_all;
-    // the two special columns, from the unmodified logits of the lanes that own them
-    X fix_b = from_real<X>(0.f), fix_t = from_real<X>(0.f);
-    const bool own_b = lane == b_lane && (b_j * kWarp + lane) < nvec;
-    const bool own_t = rec.tgt >= 0 && rec.tgt != blank && lane == ((rec.tgt >> 2) & 31);
-    if (own_b) {
-      const float gv = element(v, b_j, b_k) + rec.c;
-      fix_b = from_real<X>((s_exp(gv + rec.beta) - s_exp(gv + rec.sub_blank)) * scale);
-    }
-    if (own_t) {
-      const float gv = element(v, rec.tgt >> 7, rec.tgt & 3) + rec.c;
-      fix_t = from_real<X>((s_exp(gv + rec.beta) - s_exp(gv + rec.sub_sym)) * scale);
-    }
-    const float k2 = (rec.c + rec.beta) * kLog2e;
+    const bool fold = scale > 0.f && scale < 3.0e38f;
+    const float mul = fold ? 1.f : scale;
+    const float k2 = (rec.c + rec.beta) * kLog2e + (fold ? __log2f(scale) : 0.f);
+    const bool reachable = rec.beta > neg_inf<float>();  // else every term of the row is 0
+    const float f_b = reachable ? 1.f - ex2_approx((rec.sub_blank - rec.beta) * kLog2e) : 1.f;
+    const float f_t = reachable ? 1.f - ex2_approx((rec.sub_sym - rec.beta) * kLog2e) : 1.f;
+    const int t_j = rec.tgt >= 0 ? rec.tgt >> 7 : -1, t_lane = (rec.tgt >> 2) & 31, t_k = rec.tgt & 3;
 #pragma unroll
     for (int j = 0; j < CH; ++j) {
       const int vi = j * kWarp + lane;
       if (vi < nvec) {
         const float2 a = Pair16<X>::widen(v[j].x), b = Pair16<X>::widen(v[j].y);
-        uint2 o;
-        o.x = Pair16<X>::round(ex2_approx(fmaf(a.x, kLog2e, k2)) * scale, ex2_approx(fmaf(a.y, kLog2e, k2)) * scale);
-        o.y = Pair16<X>::round(ex2_approx(fmaf(b.x, kLog2e, k2)) * scale, ex2_approx(fmaf(b.y, kLog2e, k2)) * scale);
-        pg[vi] = o;
+        float y0 = ex2_approx(fmaf(a.x, kLog2e, k2)), y1 = ex2_approx(fmaf(a.y, kLog2e, k2));
+        float y2 = ex2_approx(fmaf(b.x, kLog2e, k2)), y3 = ex2_approx(fmaf(b.y, kLog2e, k2));
+        if (!fold) { y0 *= mul; y1 *= mul; y2 *= mul; y3 *= mul; }  // uniform: rare
+        if (j == b_j) {  // uniform: the vector that holds the blank column
+          const float f = lane == b_lane ? f_b : 1.f;
+          y0 *= b_k == 0 ? f : 1.f; y1 *= b_k == 1 ? f : 1.f; y2 *= b_k == 2 ? f : 1.f; y3 *= b_k == 3 ? f : 1.f;
+        }
+        if (j == t_j) {  // uniform: the vector that holds the target column
+          const float f = lane == t_lane ? f_t : 1.f;
+          y0 *= t_k == 0 ? f : 1.f; y1 *= t_k == 1 ? f : 1.f; y2 *= t_k == 2 ? f : 1.f; y3 *= t_k == 3 ? f : 1.f;
+        }
+        pg[vi] = make_uint2(Pair16<X>::round(y0, y1), Pair16<X>::round(y2, y3));
       }
     }
-    X *pe = g + row * (int64_t)V;
-    if (own_b) pe[blank] = fix_b;
-    if (own_t) pe[rec.tgt] = fix_t;
   };
 
   // Two register sets alternate between "being fetched" and "being finished".

@@ -24,7 +24,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-from .transducer_loss import _Call, _eager_grad, _record_trace, real_dtype
+from .transducer_loss import _Call, _eager_grad, _on_device, _record_trace, real_dtype
 
 __all__ = ["utterance_costs", "chain_lengths", "shard_time", "partition_contiguous", "partition_lpt", "imbalance",
            "Shard", "shard_batch", "all_reduce_sum", "sharded_transducer_loss", "wait_loss"]
@@ -262,8 +262,12 @@ def wait_loss(loss: torch.Tensor) -> torch.Tensor:
     ``sharded_transducer_loss(..., overlap=True)``.  Call it before the value is
     read (``loss.item()``, logging, a device-side consumer on another stream)."""
     if loss.is_cuda:
-        # every overlapped all-reduce of this device runs on the same side stream
+        # every overlapped NCCL all-reduce of this device runs on the same side stream ...
         torch.cuda.current_stream(loss.device).wait_stream(_side_stream(loss.device))
+        # ... and every peer-memory exchange on the library's own
+        from . import _lib
+        with torch.cuda.device(loss.device):
+            _lib.check(_lib.load().ot_b200_exchange_wait(torch.cuda.current_stream(loss.device).cuda_stream))
     return loss
 
 
@@ -311,6 +315,11 @@ class PeerExchange:
         self.device = device
         self.ptrs = torch.tensor(ptrs, dtype=torch.int64, device=device)
         self.error = torch.zeros(1, dtype=torch.int32, device=device)
+        # Persistent slots for the values the one-call all-reduce reads and writes on
+        # the library's own stream (step k uses slot k % RING): nothing the caching
+        # allocator could hand to someone else while the exchange is still pending.
+        self._slot_mem = torch.zeros(2 * self.RING, dtype=torch.float64, device=device)
+        self._slots = {}
 
     @classmethod
     def table_doubles(cls, world):
@@ -351,6 +360,30 @@ class PeerExchange:
         self.step += 1
         return out
 
+    def slots(self, dtype):
+        """Per step slot k % RING: (0-dim tensor the local value is written to,
+        0-dim tensor the sum arrives in), views of persistent memory."""
+        views = self._slots.get(dtype)
+        if views is None:
+            mem = self._slot_mem.view(dtype).view(2 * self.RING, -1)  # row i: the 8 bytes of slot i
+            views = self._slots[dtype] = [(mem[2 * i, 0], mem[2 * i + 1, 0]) for i in range(self.RING)]
+        return views[self.step % self.RING]
+
+    def all_reduce_next(self, local, out, scale=1.0):
+        """One library call: publish + gather of the next step on the library's own
+        high-priority stream, which first waits for what the current stream holds
+        (i.e. for ``local``).  ``local`` / ``out`` should be a pair from
+        :meth:`slots`; ``out`` is defined after :func:`wait_loss`."""
+        flags = self._lib.FP64 if local.dtype == torch.float64 else 0
+        rc = self.lib.ot_b200_exchange_allreduce(
+            local.data_ptr(), out.data_ptr(), flags, self.ptrs.data_ptr(), self.table.data_ptr(),
+            self.world, self.rank, self.RING, self.step, scale, self.error.data_ptr(), self.max_wait_ns,
+            torch.cuda.current_stream(self.device).cuda_stream)
+        if rc:
+            self._lib.check(rc)
+        self.step += 1
+        return out
+
     def check(self):
         """Synchronises and raises if a gather gave up (a rank did not publish in time)."""
         code = int(self.error.item())
@@ -382,7 +415,10 @@ class _ShardedLoss(torch.autograd.Function):
             call = _Call(logits.detach(), targets, logit_lengths, target_lengths, blank,
                          from_log_softmax, one_sym_per_frame,
                          share_sms=bool(overlap) and exchange is None)
-            local = torch.empty((), dtype=real_dtype(logits), device=logits.device)
+            if exchange is not None:
+                local, total = exchange.slots(real_dtype(logits))
+            else:
+                local = torch.empty((), dtype=real_dtype(logits), device=logits.device)
             if _eager_grad():
                 # one library call: local loss and gradient (the 1/N of "mean" uses
                 # the GLOBAL batch size, known up front); see transducer_loss.py
@@ -393,16 +429,15 @@ class _ShardedLoss(torch.autograd.Function):
                 call.forward(loss_out=local, loss_scale=1.0)
         else:  # a rank without utterances still joins the collective
             call = None
-            local = torch.zeros((), dtype=real_dtype(logits), device=logits.device)
+            if exchange is not None:
+                local, total = exchange.slots(real_dtype(logits))
+                local.zero_()
+            else:
+                local = torch.zeros((), dtype=real_dtype(logits), device=logits.device)
         if exchange is not None:
-            # peer-memory exchange: two one-warp kernels on the side stream
-            main = torch.cuda.current_stream(logits.device)
-            side = _side_stream(logits.device)
-            side.wait_stream(main)
-            total = torch.empty_like(local)
-            exchange.all_reduce_sum(local, total, scale, stream=side)
-            local.record_stream(side)
-            total.record_stream(side)
+            # peer-memory exchange: two one-warp kernels on the library's own stream, one call
+            with _on_device(logits.device.index):
+                exchange.all_reduce_next(local, total, scale)
             ctx.call = call if ctx.needs_input_grad[0] else None
             ctx.scale_host = scale
             ctx.empty_like = logits.detach() if call is None else None
@@ -463,8 +498,10 @@ def sharded_transducer_loss(logits, targets, logit_lengths, target_lengths, blan
 
     ``exchange`` (a :class:`PeerExchange`, e.g. ``peer_exchange(group)``; GPUs of
     one node) replaces the NCCL all-reduce by two one-warp kernels over peer
-    memory on the side stream; the value is likewise defined after
-    :func:`wait_loss`."""
+    memory on a stream of the library's own; the value is likewise defined after
+    :func:`wait_loss`.  The returned tensor then lives in one of the exchange's
+    ``PeerExchange.RING`` persistent slots: it is overwritten that many steps
+    later (clone it to keep it longer)."""
     if global_batch is None:
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         global_batch = int(logit_lengths.numel()) * world

@@ -416,7 +416,7 @@ def stage_outputs(logits, targets, logit_lengths, target_lengths, blank,
 
 
 def joiner_scores(joiner_in, weight, bias, targets, logit_lengths, target_lengths, blank,
-                  reduction=None, stages=False):
+                  reduction=None, stages=False, _trace=None):
     """Scores (or the reduced loss) straight from the joiner's last projection,
     WITHOUT materialising the logits: ``logits = joiner_in @ weight.T + bias`` is
     computed tile by tile on the tensor cores and reduced to the row logsumexp and
@@ -457,6 +457,8 @@ def joiner_scores(joiner_in, weight, bias, targets, logit_lengths, target_length
     lib = _lib.load()
     n, max_u = int(logit_lengths.size(0)), int(targets.size(1))
     flags = _CHECK_FLAG[_check_mode("strict")] | (_lib.FAST_MATH if _fast_math(False) else 0)
+    if os.environ.get("OT_TRACE", "0") == "1":
+        flags |= _lib.TRACE
     lay = _layout(n, rows, max_u, 0)
     dev = joiner_in.device
     ws = torch.empty(int(lay.total_bytes), dtype=torch.uint8, device=dev)
@@ -472,6 +474,8 @@ def joiner_scores(joiner_in, weight, bias, targets, logit_lengths, target_length
             torch.cuda.current_stream(dev.index).cuda_stream)
     if rc:
         _lib.check(rc)
+    if _trace is not None:  # diagnostic (OT_TRACE=1): the stage timeline of this call
+        _trace.append(ws[int(lay.status_off) + 64:int(lay.status_off) + 64 + 160].view(torch.int64).clone())
     if not stages:
         return loss if reduction else scores
     # the stage arrays, through a _Call-shaped view of the same workspace
