@@ -430,7 +430,19 @@ cudaError_t launch_grad16(const Problem &p, void *grad, const void *d_scale, dou
                           cudaStream_t s) {
   static std::atomic<int> per_sm{0};
   auto kernel = gradient16_kernel<X, PER_UTT>;
-  const cudaError_t e = launch_pdl(kernel, stream_grid(kernel, &per_sm, p.rows, p.flags, true),
+  unsigned grid = stream_grid(kernel, &per_sm, p.rows, p.flags, true);
+  if (p.group >= 0) {
+    // In a two-group call the other group's recursion and coefficient kernels must
+    // find room UNDER this resident wave (measured with five blocks per SM: the
+    // coefficient kernel of group b started 42 us late, when the first blocks of
+    // this kernel retired): leave one block slot per SM free.
+    const int blocks = per_sm.load(std::memory_order_relaxed);
+    if (blocks > 1) {
+      const unsigned smaller = (unsigned)(sm_count() * (blocks - 1));
+      if (grid > smaller) grid = smaller;
+    }
+  }
+  const cudaError_t e = launch_pdl(kernel, grid,
       (unsigned)kThreads, 0, s, static_cast<const X *>(p.logits), static_cast<X *>(grad),
       reinterpret_cast<const CoefA<float> *>(p.ws + p.lay.coef),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.rows, p.V, p.blank,
