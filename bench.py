@@ -523,6 +523,21 @@ def run_ours(args, w):
         x = Feed.apply(buf, anchor)
         return x, loss_of(x, dtg, dT, dU)
 
+    def run_step(buf, tg_, t_, u_, api):
+        """One pass of the hot path over one batch: loss AND gradient (over ``buf``
+        for raw logits).  "call": the one-call entry, the shape of the reference's
+        native function; "autograd": transducer_loss(...) + loss.backward()."""
+        if api == "autograd":
+            loss = loss_of(Feed.apply(buf, anchor), tg_, t_, u_)
+            loss.backward()
+            return loss
+        if world > 1:
+            return sharding.sharded_loss_and_grad(
+                buf, tg_, t_, u_, 0, w.from_log_softmax, w.one_sym_per_frame, w.reduction,
+                global_batch=n_global, exchange=exchange)[0]
+        return ot.transducer_loss_and_grad(buf, tg_, t_, u_, 0, w.from_log_softmax,
+                                           w.one_sym_per_frame, w.reduction)[0]
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -540,12 +555,11 @@ def run_ours(args, w):
     # ----- warm-up
     it = buffers()
     for _ in range(args.warmup):
-        x, loss = one_step(next(it))
-        loss.backward()
+        run_step(next(it), dtg, dT, dU, args.api)
     barrier()
 
     # ----- timed region: K steps, device resident
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     uuid = getattr(torch.cuda.get_device_properties(dev), "uuid", None)
     with ClockSampler(local_rank, uuid) as clocks:
@@ -554,22 +568,47 @@ def run_ours(args, w):
         t_begin.record()
         for k in range(args.steps):
             buf = next(it)
-            ev[k][0].record()
-            x, loss = one_step(buf)
-            ev[k][1].record()
-            loss.backward()
-            ev[k][2].record()
+            if rotating:
+                ev[k][0].record()
+            loss = run_step(buf, dtg, dT, dU, args.api)
+            if rotating:
+                ev[k][1].record()
         if world > 1:
             sharding.wait_loss(loss)  # the last step's exchange ends inside the timed region
         t_end.record()
         host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps  # host time to ENQUEUE a step
         barrier()
-    elapsed_ms = (sum(e[0].elapsed_time(e[2]) for e in ev) if rotating
+    elapsed_ms = (sum(e[0].elapsed_time(e[1]) for e in ev) if rotating
                   else t_begin.elapsed_time(t_end))
     ot.check_inputs(dev)  # a failed device-side check in any step raises here
     last_loss = float(loss.item())
-    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
-    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+
+    # ----- the same K steps through the autograd surface (transducer_loss +
+    #       loss.backward()), for the record: forward / backward split and what the
+    #       autograd graph costs per step.  Not the headline when --api call.
+    for b_ in pool:
+        b_.copy_(pristine)
+    it = buffers()
+    for _ in range(min(args.warmup, 3)):
+        run_step(next(it), dtg, dT, dU, "autograd")
+    barrier()
+    n_auto = min(args.steps, len(pool) - min(args.warmup, 3)) if not rotating else args.steps
+    ev3 = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_auto)]
+    for k in range(n_auto):
+        buf = next(it)
+        ev3[k][0].record()
+        x, loss = one_step(buf)
+        ev3[k][1].record()
+        loss.backward()
+        ev3[k][2].record()
+    if world > 1:
+        sharding.wait_loss(loss)
+    barrier()
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev3)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev3)
+    autograd_ms = (sum(e[0].elapsed_time(e[2]) for e in ev3) if rotating
+                   else ev3[0][0].elapsed_time(ev3[-1][2])) / n_auto
+    ot.check_inputs(dev)
     kbufs = pool[:2] if rotating else None
     del pool, it, x, loss, buf
 
@@ -601,8 +640,7 @@ def run_ours(args, w):
     loss_check, timeline = None, None
     if world > 1:
         buf = pristine.clone()
-        x = Feed.apply(buf, anchor)
-        total = loss_of(x, dtg, dT, dU)
+        total = run_step(buf, dtg, dT, dU, args.api)
         sharding.wait_loss(total)
         local = ot.transducer_loss(Feed.apply(pristine.clone(), anchor), dtg, dT, dU, blank=0,
                                    from_log_softmax=w.from_log_softmax,
@@ -616,19 +654,18 @@ def run_ours(args, w):
         got = float(total.item())
         rel = abs(got - want) / max(abs(want), 1e-30)
         loss_check = {"exchanged": got, "sum_of_locals": want, "rel": rel}
-        del buf, x, total, local
+        del buf, total, local
     if not args.no_timeline:
         os.environ["OT_TRACE"] = "1"
         traces = []
         collect_traces(traces)
         for _ in range(5):
-            x, loss = one_step(pristine.clone())
-            loss.backward()
+            loss = run_step(pristine.clone(), dtg, dT, dU, args.api)
         torch.cuda.synchronize(dev)
         os.environ["OT_TRACE"] = "0"
         collect_traces(None)
         timeline = timeline_summary([t.cpu().numpy() for t in traces])
-        del x, loss
+        del loss
 
     # ----- end to end: logits start in pinned host memory
     host = torch.empty(pristine.shape, dtype=pristine.dtype, pin_memory=True)
@@ -662,9 +699,7 @@ def run_ours(args, w):
         t_, u_, g_ = staged[slot]
         for t in (dev_bufs[slot], t_, u_, g_):
             t.record_stream(main_stream)
-        x = Feed.apply(dev_bufs[slot], anchor)
-        loss = loss_of(x, g_, t_, u_)
-        loss.backward()
+        loss = run_step(dev_bufs[slot], g_, t_, u_, args.api)
         done[slot].record(main_stream)
         if world > 1:
             sharding.wait_loss(loss)
@@ -687,7 +722,7 @@ def run_ours(args, w):
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
     # ----- max over ranks, whole-job totals
-    stats = torch.tensor([elapsed_ms, e2e_ms, fwd_ms, bwd_ms, host_ms, kernel_ms], dtype=torch.float64, device=dev)
+    stats = torch.tensor([elapsed_ms, e2e_ms, fwd_ms, bwd_ms, host_ms, kernel_ms, autograd_ms], dtype=torch.float64, device=dev)
     cells = torch.tensor([float(cells_local)], dtype=torch.float64, device=dev)
     per_rank = None
     if world > 1:
@@ -710,7 +745,7 @@ def run_ours(args, w):
         per_rank = {"columns": cols, "values": [[round(v, 4) for v in g.tolist()] for g in gathered]}
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
         dist.all_reduce(cells, op=dist.ReduceOp.SUM)
-    elapsed_ms, e2e_ms, fwd_ms, bwd_ms, host_ms, kernel_ms = stats.tolist()
+    elapsed_ms, e2e_ms, fwd_ms, bwd_ms, host_ms, kernel_ms, autograd_ms = stats.tolist()
     cells_total = cells.item()
 
     if rank == 0:
@@ -727,7 +762,9 @@ def run_ours(args, w):
         # own kernels per step and rank: prepare, logprob, lattice, coef, gradient (twice
         # the last four + one closing kernel when the batch runs as two groups), the
         # scaling kernel of the eager schedule's backward, publish + gather of the exchange
-        launches = (10 if two_groups else 5) + (1 if eager else 0) + (2 if exchange is not None else 0)
+        one_call = args.api == "call"
+        launches = ((10 if two_groups else 5) + (1 if eager and not one_call else 0)
+                    + (2 if exchange is not None else 0))
         fwd_bytes = (0 if mode_b else es * cells_local)
         value = cells_total * args.steps / (elapsed_ms * 1e-3)
         per_cell = recorded_traffic_per_cell(args.dtype, mode_b)
@@ -754,7 +791,13 @@ def run_ours(args, w):
                 "collective": collective,
                 "checks": {"0": "off", "2": "strict (the call waits)"}.get(
                     os.environ.get("OT_CHECKS", "1"), "deferred (reported by a later call)"),
-                "gradient_schedule": ("deferred (one fused pass in backward)"
+                "api": ("transducer_loss_and_grad: loss and in-place gradient from one call, no autograd graph "
+                        "(the shape of the reference's native compute_transducer_loss, which returns scores "
+                        "and gradient together)") if one_call else
+                       "transducer_loss(...) + loss.backward() through torch.autograd",
+                "autograd_api_ms_per_step": autograd_ms,
+                "gradient_schedule": "eager (loss and gradient in one library call, as the reference)" if one_call else
+                                     ("deferred (one fused pass in backward)"
                                       if os.environ.get("OT_EAGER_GRAD", "1") == "0" else
                                       "eager (loss and gradient in one library call, as the reference; "
                                       "backward only scales, and skips that when the upstream gradient is 1)"),
@@ -777,6 +820,7 @@ def run_ours(args, w):
                           "of the same batch (in the timed steps it overlaps other stages)",
             },
             "stages": {
+                "measured_through": "transducer_loss + loss.backward() (CUDA events between them)",
                 "forward_ms": fwd_ms, "backward_ms": bwd_ms,
                 "forward_gbs": (fwd_bytes / (fwd_ms * 1e-3) / 1e9) if fwd_bytes else None,
                 "whole_step_gbs": (fwd_bytes + grad_bytes) / (step_ms * 1e-3) / 1e9,
@@ -937,6 +981,10 @@ def main():
                     help="storage type of the logits (the reference's is f32; 16-bit is an extension)")
     ap.add_argument("--collective", choices=["peer", "nccl"], default="peer",
                     help="how the ranks' losses are summed: over peer memory (default) or by NCCL")
+    ap.add_argument("--api", choices=["call", "autograd"], default="call",
+                    help="the timed step: 'call' = transducer_loss_and_grad (one call, loss + in-place gradient, "
+                         "no autograd graph); 'autograd' = transducer_loss(...) + loss.backward().  The other "
+                         "one is measured too and reported under setup / stages")
     ap.add_argument("--partition", choices=["auto", "contiguous", "lpt", "lpt_chain"], default="lpt_chain",
                     help="how utterances are dealt to the ranks (each rank creates its own shard, so a "
                          "permuting partition costs nothing here); lpt_chain balances cells and the "

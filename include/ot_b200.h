@@ -94,6 +94,13 @@ typedef enum ot_b200_input_error {
                                          launching anything.  The host never waits
                                          for the device, so it can run ahead of it. */
 #define OT_B200_FAST_MATH 16u         /* approximate exp/log in the recursions      */
+#define OT_B200_LINEAR_DOMAIN 2048u    /* float recursions in a scaled linear domain
+                                          (each value m * 2^e) instead of the
+                                          reference's log domain: alpha/beta within
+                                          one float rounding of the double recursion
+                                          (the log-domain float recursion drifts by
+                                          about ten), at 1.6x the recursion time.
+                                          Ignored for double                        */
 #define OT_B200_BF16 128u              /* logits and gradient are bfloat16; scores,  */
 #define OT_B200_FP16 256u              /* loss, scale factors and the workspace stay
                                          float (at most one of FP64/BF16/FP16); no

@@ -26,6 +26,7 @@ BF16 = 128
 FP16 = 256
 TRACE = 512
 REPORT_ERRORS = 1024
+LINEAR_DOMAIN = 2048
 
 # Every symbol include/ot_b200.h declares.
 EXPORTS = (

@@ -170,7 +170,7 @@ constexpr uint32_t kKnownFlags = OT_B200_FROM_LOG_SOFTMAX | OT_B200_ONE_SYM_PER_
                                  OT_B200_FP64 | OT_B200_CHECK_INPUTS | OT_B200_FAST_MATH |
                                  OT_B200_SCALE_PER_UTTERANCE | OT_B200_SHARE_SMS |
                                  OT_B200_BF16 | OT_B200_FP16 | OT_B200_TRACE |
-                                 OT_B200_REPORT_ERRORS;
+                                 OT_B200_REPORT_ERRORS | OT_B200_LINEAR_DOMAIN;
 
 int check_sizes(int32_t N, int64_t rows, int32_t max_u, uint32_t flags) {
   if (N <= 0) return fail(OT_B200_ERR_ARGUMENT, "N must be positive, got %d", N);

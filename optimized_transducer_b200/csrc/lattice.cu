@@ -31,6 +31,23 @@
 //
 // Lattices wider than 1024 columns use the generic kernel at the end of the
 // file (several columns per thread, wavefront kept in global memory).
+//
+// Arithmetic of the skewed kernel (struct Num below).  The reference adds in the
+// log domain: every step is max, subtract, exp, log1p, and every partial sum is
+// rounded at ulp(|alpha|); that is the default here too, and it reproduces the
+// reference's alpha/beta almost rounding by rounding.  OT_B200_LINEAR_DOMAIN
+// (float) carries each value as m * 2^e instead (float m, int e): a step is two
+// multiplies, an exponent alignment (integer subtract, clamp, shift) and one
+// fused multiply-add; the exp of the two log-probs a step consumes is taken one
+// step early and the log only when a value is stored.  Its rounding error is
+// relative to m (2^-24), so alpha and beta land within one float rounding of the
+// float64 recursion, about ten times closer than the log-domain float recursion
+// (the reference's included).  It is the SLOWER of the two: the recursion is one
+// warp per 32 columns issuing in order at about five cycles per instruction
+// (measured: issue slots 17-21 % busy, stalls split between fixed-latency
+// dependencies and the scoreboard), so the step time follows the instruction
+// count, 63 per step against 35 (88 us against 56 us on four benchmark
+// utterances), not the length of the dependency chain.
 #include <stdlib.h>
 #include <string.h>
 
@@ -72,6 +89,85 @@ __device__ __forceinline__ T neighbour(T own, T (*xchg)[kMaxWarps], int xs,
 template <typename T> struct Pair;
 template <> struct Pair<float> { using type = float2; };
 template <> struct Pair<double> { using type = double2; };
+
+// The value a column carries through the recursion.  ARITH 0: log domain with
+// the reference's exact log-add; 1: log domain, ex2/lg2 approximations; 2
+// (float only): scaled linear domain, value = m * 2^e.
+constexpr int kArithLog = 0, kArithLogFast = 1, kArithLinear = 2;
+
+template <typename T, int ARITH>
+struct Num {
+  T v;
+  static __device__ __forceinline__ Num zero() { return {neg_inf<T>()}; }
+  static __device__ __forceinline__ Num from_log(T x) { return {x}; }
+  __device__ __forceinline__ T log() const { return v; }
+  __device__ __forceinline__ Num up() const { return {__shfl_up_sync(kFull, v, 1)}; }
+  __device__ __forceinline__ Num down() const { return {__shfl_down_sync(kFull, v, 1)}; }
+  // a * pa + b * pb
+  static __device__ __forceinline__ Num mad2(Num a, Num pa, Num b, Num pb) {
+    return {log_add<T, ARITH == kArithLogFast>(a.v + pa.v, b.v + pb.v)};
+  }
+  static __device__ __forceinline__ Num pick(bool c, Num a, Num b) { return {c ? a.v : b.v}; }
+  __device__ __forceinline__ void renorm() {}
+};
+
+template <>
+struct Num<float, kArithLinear> {
+  float m;  // >= 0 (or NaN: a poisoned log-prob stays visible)
+  int e;
+  // Exponent of a zero: far below every real exponent, so that a zero never wins
+  // the alignment in mad2, and small enough that 17 of them add up inside int.
+  static constexpr int kZeroExp = -(1 << 21);
+  static constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: float <-> int without cvt
+  static __device__ __forceinline__ Num zero() { return {0.0f, kZeroExp}; }
+  // exp(x) as m * 2^e with m in [2^-0.5, 2^0.5]; -inf (no lattice cell) gives (0, kZeroExp)
+  static __device__ __forceinline__ Num from_log(float x) {
+    const float v = fmaxf(x * kLog2e, (float)kZeroExp);
+    const float r = v + kMagic;   // the integer nearest to v sits in the low mantissa bits
+    const float fl = r - kMagic;
+    Num n;
+    n.e = __float_as_int(r) - __float_as_int(kMagic);
+    // x*log2(e) - fl with the product unrounded; log2(e) in two pieces
+    float f = fmaf(x, 1.4426950216293335f, -fl);
+    f = fmaf(x, 1.9259629911e-8f, f);
+    n.m = ex2_approx(f);
+    return n;
+  }
+  __device__ __forceinline__ float log() const {
+    float l2;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l2) : "f"(m));
+    const float ef = __int_as_float(e + __float_as_int(kMagic)) - kMagic;  // (float)e, |e| < 2^22; any finite value for a zero
+    // (l2 + e) * ln 2, ln 2 in two pieces, the large term through the fma unrounded
+    return fmaf(ef, 0.693147182464599609375f, fmaf(ef, -1.904654323148236e-9f, l2 * 0.6931471805599453f));
+  }
+  __device__ __forceinline__ Num up() const {
+    return {__shfl_up_sync(kFull, m, 1), __shfl_up_sync(kFull, e, 1)};
+  }
+  __device__ __forceinline__ Num down() const {
+    return {__shfl_down_sync(kFull, m, 1), __shfl_down_sync(kFull, e, 1)};
+  }
+  static __device__ __forceinline__ Num mad2(Num a, Num pa, Num b, Num pb) {
+    const float ma = a.m * pa.m, mb = b.m * pb.m;
+    const int ea = a.e + pa.e, eb = b.e + pb.e;
+    const int d = ea - eb;
+    const int nd = max(min(d, -d), -127);                  // -|d|; 2^-127 is written as 0
+    const float sc = __int_as_float((nd + 127) << 23);     // 2^nd
+    const bool a_big = d >= 0;
+    const float big = a_big ? ma : mb, small = a_big ? mb : ma;
+    return {fmaf(small, sc, big), max(ea, eb)};
+  }
+  static __device__ __forceinline__ Num pick(bool c, Num a, Num b) {
+    return {c ? a.m : b.m, c ? a.e : b.e};
+  }
+  // m back into [1, 2).  Between two calls m grows by at most 2*sqrt(2) per step
+  // and shrinks by at most sqrt(2): call at least every 16 steps.
+  __device__ __forceinline__ void renorm() {
+    const int bits = __float_as_int(m);
+    const bool finite = bits > 0 && bits < 0x7f800000;
+    e = finite ? e + ((bits >> 23) - 127) : (m == 0.0f ? kZeroExp : e);
+    m = finite ? __int_as_float((bits & 0x007fffff) | 0x3f800000) : m;
+  }
+};
 
 // `rows_per_chunk` (even) wavefront rows are staged per bulk copy; the dynamic
 // shared memory holds kStages chunks of rows_per_chunk * (max_u+1) pairs.
@@ -279,7 +375,7 @@ constexpr int kSkewRing = 64;   // ring entries per warp boundary; >= 4*K
 constexpr int kSkewMaxK = 16;
 constexpr int kSkewMaxStages = kMaxWarps + 3;
 
-template <typename T, bool FAST, bool MODIFIED>
+template <typename T, int ARITH, bool MODIFIED>
 __global__ void __launch_bounds__(1024)
 lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
                     const int32_t *__restrict__ Ul, const int64_t *__restrict__ cell_split,
@@ -287,9 +383,10 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
                     T *__restrict__ beta, T *__restrict__ scores,
                     T *__restrict__ scores_beta, int K, int stage_pairs, int nstages, int group) {
   using P = typename Pair<T>::type;
+  using N = Num<T, ARITH>;
   extern __shared__ __align__(128) unsigned char stage_mem[];
   __shared__ __align__(8) uint64_t full_bar[kSkewMaxStages];
-  __shared__ T edge[kMaxWarps][kSkewRing];  // edge[w][s & 63]: boundary column of warp w after step s
+  __shared__ N edge[kMaxWarps][kSkewRing];  // edge[w][s & 63]: boundary column of warp w after step s
   pdl_wait();
   pdl_trigger();
   const int b = blockIdx.x >> 1;
@@ -357,13 +454,13 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     // ------------------------------ alpha ------------------------------
     const bool produce = (lane == kWarp - 1) && (warp + 1 < nwarps);
     const bool consume = (lane == 0) && (warp > 0);
-    T *out_edge = edge[warp];
-    const T *in_edge = edge[consume ? warp - 1 : 0];  // lanes that do not consume read (and drop) a valid word
+    N *out_edge = edge[warp];
+    const N *in_edge = edge[consume ? warp - 1 : 0];  // lanes that do not consume read (and drop) a valid word
     // The value of step s sits in ring entry (s-1) & 63.
     // "after step 0": columns 31, 63, ... have not started
-    if (lane == 0) out_edge[kMask] = ninf;
+    if (lane == 0) out_edge[kMask] = N::zero();
     T *al = alpha + off;
-    T own = (u == 0) ? (T)0 : ninf;
+    N own = (u == 0) ? N::from_log((T)0) : N::zero();
     if (u == 0) al[0] = 0;
     if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);  // by the thread that initialised the barriers
     // blank log-prob of the final cell, for the score (fetched long before it is needed)
@@ -384,63 +481,66 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         // cells), and a column that has not started holds -inf itself.  Stores:
         // every (step, column) pair has an entry in the utterance's block, and
         // what lands in the entries that are no cell is never read.
-        T lb = rowp[0].x;
-        T ls = first_col ? ninf : rowp[-1].y;
-        T e_cur = in_edge[(row0 - 1) & kMask];  // column u-1 after step row0
+        N lb = N::from_log(rowp[0].x);
+        N ls = N::from_log(first_col ? ninf : rowp[-1].y);
+        N e_cur = in_edge[(row0 - 1) & kMask];  // column u-1 after step row0
         // One step; `e_in` / `e_out` are the ring entries of this step.
-        auto step = [&](const bool more, const T *e_in, T *e_out) {
-          // loads for the next step first
+        auto step = [&](const bool more, const N *e_in, N *e_out) {
+          // loads (and the conversion of the log-probs) for the next step first
           rowp += U1;
-          T x_next = ninf, y_next = ninf, e_next = ninf;
+          T x_next = ninf, y_next = ninf;
+          N e_next = N::zero();
           if (more) {
             x_next = rowp[0].x;
             y_next = rowp[-1].y;
             e_next = *e_in;
           }
           y_next = first_col ? ninf : y_next;
+          const N lb_next = N::from_log(x_next), ls_next = N::from_log(y_next);
           // the chain
-          const T up = __shfl_up_sync(kFull, own, 1);
-          const T left = consume ? e_cur : up;
+          const N up = own.up();
+          const N left = N::pick(consume, e_cur, up);
           // What a column holds after its last cell is never consumed (its
           // neighbour's cells end one step later).
-          own = log_add<T, FAST>(own + lb, left + ls);
-          if (col) *st = own;
+          own = N::mad2(own, lb, left, ls);
+          if (col) *st = own.log();
           st += U1;
           if (produce) *e_out = own;
-          lb = x_next; ls = y_next;
+          lb = lb_next; ls = ls_next;
           e_cur = e_next;
         };
         if (n == kSkewMaxK && K == kSkewMaxK) {
           // row0 is a multiple of 16: the block's ring entries do not wrap, and
           // with the loop unrolled they are constant offsets from one base.
-          const T *e_in = in_edge + (row0 & kMask);
-          T *e_out = out_edge + (row0 & kMask);
+          const N *e_in = in_edge + (row0 & kMask);
+          N *e_out = out_edge + (row0 & kMask);
 #pragma unroll
           for (int i = 0; i < kSkewMaxK; ++i) step(i + 1 < kSkewMaxK, e_in + i, e_out + i);
         } else {
           for (int i = 0; i < n; ++i)
             step(i + 1 < n, in_edge + ((row0 + i) & kMask), out_edge + ((row0 + i) & kMask));
         }
+        own.renorm();  // K <= 16 steps since the last one
       }
       if (nwarps > 1) bar_active(nact); else __syncwarp();
     }
-    if (u == U) scores[b] = own + fin_blank;  // column U's last step is the last step
+    if (u == U) scores[b] = own.log() + fin_blank;  // column U's last step is the last step
     if (u == 0) trace_end(status, trace_slot(kStageLattice, group));
   } else {
     // ------------------------------- beta ------------------------------
     const bool produce = (lane == 0) && (warp > 0);
     const bool consume = (lane == kWarp - 1) && (warp + 1 < nwarps);
-    T *out_edge = edge[warp];
-    const T *in_edge = edge[consume ? warp + 1 : 0];
+    N *out_edge = edge[warp];
+    const N *in_edge = edge[consume ? warp + 1 : 0];
     T *be = beta + off;
     const T fin = lp2[(int64_t)top * U1 + U].x;  // beta(T-1,U)
-    T own = ninf;
+    N own = N::zero();
     if (u == U) {
-      own = fin;
-      be[(int64_t)top * U1 + U] = own;
+      own = N::from_log(fin);
+      be[(int64_t)top * U1 + U] = fin;
     }
     // "after step top": the boundary column of this warp before any step
-    if (lane == 0) out_edge[top & kMask] = (u == U) ? fin : ninf;
+    if (lane == 0) out_edge[top & kMask] = own;  // column U: the final cell; every other column: nothing yet
     if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);
     if (nwarps > 1) bar_active(nact); else __syncwarp();
     // Column U starts with the final cell and computes from the first step on,
@@ -458,46 +558,48 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         wait_chunk(q);
         const P *rowp = stage + (int64_t)(q % nstages) * stage_pairs + (int64_t)(n - 1) * U1 + uc;
         T *st = be + (int64_t)(row0 + n - 1) * U1 + uc;  // entry of the block's first step
-        T lb, ls;
+        N lb, ls;
         {
           const P v = rowp[0];  // (-inf, -inf) where (step, column) is no lattice cell
-          lb = v.x; ls = v.y;
+          lb = N::from_log(v.x); ls = N::from_log(v.y);
         }
-        T e_cur = in_edge[(row0 + n) & kMask];  // column u+1 after step row0+n
+        N e_cur = in_edge[(row0 + n) & kMask];  // column u+1 after step row0+n
         // One step (no range checks, as in the alpha sweep); the value of step
         // s sits in ring entry s & 63.
-        auto step = [&](const bool more, const T *e_in, T *e_out) {
+        auto step = [&](const bool more, const N *e_in, N *e_out) {
           rowp -= U1;
           P v_next;
           v_next.x = ninf; v_next.y = ninf;
-          T e_next = ninf;
+          N e_next = N::zero();
           if (more) {
             v_next = rowp[0];
             e_next = *e_in;
           }
-          const T dn = __shfl_down_sync(kFull, own, 1);
-          const T right = consume ? e_cur : dn;
-          const T nv = log_add<T, FAST>(own + lb, right + ls);
-          own = keep ? own : nv;
-          if (wr) *st = nv;
+          const N lb_next = N::from_log(v_next.x), ls_next = N::from_log(v_next.y);
+          const N dn = own.down();
+          const N right = N::pick(consume, e_cur, dn);
+          const N nv = N::mad2(own, lb, right, ls);
+          own = N::pick(keep, own, nv);
+          if (wr) *st = nv.log();
           st -= U1;
           if (produce) *e_out = own;
-          lb = v_next.x; ls = v_next.y;
+          lb = lb_next; ls = ls_next;
           e_cur = e_next;
         };
         if (n == kSkewMaxK && K == kSkewMaxK) {
-          const T *e_in = in_edge + (row0 & kMask);
-          T *e_out = out_edge + (row0 & kMask);
+          const N *e_in = in_edge + (row0 & kMask);
+          N *e_out = out_edge + (row0 & kMask);
 #pragma unroll
           for (int i = kSkewMaxK - 1; i >= 0; --i) step(i > 0, e_in + i, e_out + i);
         } else {
           for (int i = n - 1; i >= 0; --i)
             step(i > 0, in_edge + ((row0 + i) & kMask), out_edge + ((row0 + i) & kMask));
         }
+        own.renorm();
       }
       if (nwarps > 1) bar_active(nact); else __syncwarp();
     }
-    if (u == 0) scores_beta[b] = own;  // column 0's last step is the last step
+    if (u == 0) scores_beta[b] = own.log();  // column 0's last step is the last step
     if (u == 0) trace_end(status, trace_slot(kStageLattice, group));
   }
 }
@@ -603,10 +705,10 @@ bool lockstep_forced() {
 }
 
 // Returns cudaErrorNotSupported when the lattice is too wide for the skewed kernel.
-template <typename T, bool FAST, bool MODIFIED>
+template <typename T, int ARITH, bool MODIFIED>
 cudaError_t launch_skewed(const Problem &p, void *scores, cudaStream_t s) {
   using P = typename Pair<T>::type;
-  auto kernel = lattice_skew_kernel<T, FAST, MODIFIED>;
+  auto kernel = lattice_skew_kernel<T, ARITH, MODIFIED>;
   const int cols = p.max_u + 1;
   const int nwarps = (cols + kWarp - 1) / kWarp;
   const int nstages = nwarps + 3;
@@ -638,7 +740,16 @@ template <typename T, bool FAST, bool MODIFIED>
 cudaError_t launch_staged(const Problem &p, void *scores, cudaStream_t s) {
   using P = typename Pair<T>::type;
   {
-    const cudaError_t e = launch_skewed<T, FAST, MODIFIED>(p, scores, s);
+    // float: the scaled linear arithmetic when the caller asks for it
+    constexpr bool kCanLinear = sizeof(T) == 4;
+    cudaError_t e;
+    if constexpr (kCanLinear) {
+      e = (p.flags & OT_B200_LINEAR_DOMAIN)
+              ? launch_skewed<T, kArithLinear, MODIFIED>(p, scores, s)
+              : launch_skewed<T, FAST ? kArithLogFast : kArithLog, MODIFIED>(p, scores, s);
+    } else {
+      e = launch_skewed<T, FAST ? kArithLogFast : kArithLog, MODIFIED>(p, scores, s);
+    }
     if (e != cudaErrorNotSupported) return e;
   }
   auto kernel = lattice_kernel<T, FAST, MODIFIED>;

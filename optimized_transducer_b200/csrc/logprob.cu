@@ -182,8 +182,9 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
 // ---------------------------------------------------------------------------
 // The same stage with the rows staged through shared memory by bulk copies, for
 // the common shape: float rows of 64 < V/4 <= 128 vectors (V = 260..512,
-// V % 4 == 0), standard transducer.  A block walks over kTmaTiles consecutive
-// tiles of 16 rows; thread 0 keeps kTmaStages tiles (16 * V * 4 bytes each,
+// V % 4 == 0), standard transducer.  A block walks over `tiles_per_block`
+// consecutive tiles of 16 rows (16 of them, fewer in a launch of at most three
+// waves: see the launcher); thread 0 keeps kTmaStages tiles (16 * V * 4 bytes each,
 // one contiguous piece of the packed buffer) in flight with cp.async.bulk +
 // mbarrier, the 16 lane groups of the block each reduce one row of the tile out
 // of shared memory.  What this buys: the bytes in flight no longer depend on
@@ -192,7 +193,7 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
 // exp-sum overlap fully.
 constexpr int kTmaRows = 16;     // rows per tile = lane groups per block
 constexpr int kTmaStagesMax = 3;
-constexpr int kTmaTiles = 16;    // tiles per block
+constexpr int kTmaTiles = 16;    // tiles per block in a launch of many waves
 
 // kTmaStages: tiles in flight per block (three are used; see the launcher).
 template <typename X, int kTmaStages>
@@ -201,7 +202,8 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
                    const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
                    const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
                    int32_t *__restrict__ status, int N, int64_t row_begin, int64_t rows, int V,
-                   int max_u, int blank, float *__restrict__ den, float *__restrict__ lp) {
+                   int max_u, int blank, float *__restrict__ den, float *__restrict__ lp,
+                   int tiles_per_block) {
   // This launch covers the packed rows [row_begin, rows); row_begin is a multiple
   // of the tile height, so every tile starts on a 16-byte boundary.
   extern __shared__ __align__(128) unsigned char tile_mem[];
@@ -222,8 +224,8 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
   const uint32_t row_bytes = (uint32_t)V * (uint32_t)sizeof(X);
   const uint32_t tile_bytes = kTmaRows * row_bytes;
   const int64_t ntiles_all = (rows - row_begin + kTmaRows - 1) / kTmaRows;
-  const int64_t tile0 = (int64_t)blockIdx.x * kTmaTiles;
-  const int ntiles = (int)((ntiles_all - tile0 < kTmaTiles) ? (ntiles_all - tile0) : kTmaTiles);
+  const int64_t tile0 = (int64_t)blockIdx.x * tiles_per_block;
+  const int ntiles = (int)((ntiles_all - tile0 < tiles_per_block) ? (ntiles_all - tile0) : tiles_per_block);
   if (ntiles <= 0) return;  // cannot happen with the launcher's grid
 
   auto issue = [&](int k) {  // thread 0 only
@@ -441,14 +443,29 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
         if (e != cudaSuccess) return e;
       }
       const int64_t ntiles = (row_end - p.row_begin + kTmaRows - 1) / kTmaRows;
-      const unsigned grid = (unsigned)((ntiles + kTmaTiles - 1) / kTmaTiles);
+      // Tiles per block.  Two blocks are resident per SM; a launch of a few waves of
+      // 16-tile blocks ends with a mostly empty last wave (85 000 rows: 334 blocks on
+      // 296 slots, 46 us against 36 us with every slot filled once), so such a launch
+      // is cut into as few full waves as blocks of at most 24 tiles allow: equal
+      // blocks, at least 4 tiles each so that the three-stage pipeline still fills.
+      int tiles_per_block = kTmaTiles;
+      {
+        const int64_t slots = 2 * (int64_t)sm_count();
+        if (ntiles <= 3 * slots * kTmaTiles) {
+          const int64_t waves = (ntiles + slots * 24 - 1) / (slots * 24);
+          const int64_t even = (ntiles + slots * waves - 1) / (slots * waves);
+          tiles_per_block = (int)(even < 4 ? 4 : even);
+        }
+      }
+      const unsigned grid = (unsigned)((ntiles + tiles_per_block - 1) / tiles_per_block);
       const cudaError_t e = launch_pdl(stages == 2 ? logprob_tma_kernel<X, 2> : logprob_tma_kernel<X, 3>,
           grid, (unsigned)kThreads, smem, s,
           static_cast<const X *>(p.logits), p.targets, p.T, p.U,
           reinterpret_cast<const int64_t *>(p.ws + p.lay.split),
           reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
           reinterpret_cast<int32_t *>(p.ws + p.lay.status), p.N, p.row_begin, row_end, p.V, p.max_u,
-          p.blank, reinterpret_cast<float *>(p.ws + p.lay.den), reinterpret_cast<float *>(p.ws + p.lay.lp));
+          p.blank, reinterpret_cast<float *>(p.ws + p.lay.den), reinterpret_cast<float *>(p.ws + p.lay.lp),
+          tiles_per_block);
       return e != cudaSuccess ? e : cudaGetLastError();
     }
   }

@@ -24,10 +24,12 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-from .transducer_loss import _Call, _eager_grad, _on_device, _record_trace, real_dtype
+from .transducer_loss import (_Call, _eager_grad, _on_device, _planned_call, _record_trace,
+                              real_dtype)
 
 __all__ = ["utterance_costs", "chain_lengths", "shard_time", "partition_contiguous", "partition_lpt", "imbalance",
-           "Shard", "shard_batch", "all_reduce_sum", "sharded_transducer_loss", "wait_loss"]
+           "Shard", "shard_batch", "all_reduce_sum", "sharded_transducer_loss", "sharded_loss_and_grad",
+           "wait_loss"]
 
 
 def utterance_costs(T, U, V: int) -> List[int]:
@@ -509,3 +511,44 @@ def sharded_transducer_loss(logits, targets, logit_lengths, target_lengths, blan
                               from_log_softmax, one_sym_per_frame, reduction, global_batch,
                               group, overlap, exchange)
     return loss
+
+
+def sharded_loss_and_grad(logits, targets, logit_lengths, target_lengths, blank,
+                          from_log_softmax, one_sym_per_frame=False, reduction="mean",
+                          global_batch: Optional[int] = None, group=None,
+                          exchange: Optional[PeerExchange] = None):
+    """:func:`sharded_transducer_loss` without an autograd graph: one library call
+    for this rank's loss and gradient (see ``transducer_loss_and_grad``) and one
+    for the exchange of the scalar.  Returns ``(loss, grad)``: the loss of the
+    WHOLE batch on every rank (defined after :func:`wait_loss` when ``exchange``
+    is given) and the gradient of that loss with respect to this rank's rows
+    (``logits`` itself for raw logits).  No gradient crosses ranks; the only
+    coupling is the sum the reference's Python layer takes over the batch
+    (transducer_loss.py:147-152 of the reference)."""
+    assert reduction in ("mean", "sum")
+    if global_batch is None:
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        global_batch = int(logit_lengths.numel()) * world
+    scale = 1.0 / float(global_batch) if reduction == "mean" else 1.0
+    data = logits.detach() if logits.requires_grad else logits
+    dtype = real_dtype(data)
+    if exchange is not None:
+        local, total = exchange.slots(dtype)
+    else:
+        local = torch.empty((), dtype=dtype, device=data.device)
+    if logit_lengths.numel() > 0:
+        call = _planned_call(data, targets, logit_lengths, target_lengths, blank,
+                             from_log_softmax, one_sym_per_frame)
+        grad = torch.empty_like(data) if from_log_softmax else data
+        call.loss_and_gradient(grad, local, loss_scale=1.0, grad_scale=scale)
+        _record_trace(call)
+    else:  # a rank without utterances still joins the exchange
+        local.zero_()
+        grad = torch.zeros_like(data)
+    if exchange is not None:
+        with _on_device(data.device.index):
+            exchange.all_reduce_next(local, total, scale)
+        return total, grad
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(local, group=group)
+    return (local * scale if reduction == "mean" else local), grad

@@ -61,7 +61,8 @@ from . import _lib
 
 __all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
            "compute_transducer_loss", "stage_outputs", "transducer_loss_per_utterance",
-           "PerUtteranceLossFunction", "check_inputs", "joiner_scores"]
+           "PerUtteranceLossFunction", "check_inputs", "joiner_scores",
+           "transducer_loss_and_grad"]
 
 
 # Diagnostic: with OT_TRACE=1 and a list set here (collect_traces), every
@@ -96,15 +97,25 @@ def _eager_grad():
     return os.environ.get("OT_EAGER_GRAD", "1") != "0"
 
 
+def _linear_domain():
+    # OT_LATTICE=linear: float32 recursions in a scaled linear domain (every value
+    # carried as m * 2^e) instead of the reference's log domain: alpha/beta land
+    # within one float32 rounding of the float64 recursion and the gradient about
+    # six to ten times closer to the float64 gradient than the reference's own
+    # float32 output, for a recursion that takes 1.6 times as long.  Default: the
+    # log domain, which repeats the reference's roundings almost step by step.
+    return os.environ.get("OT_LATTICE", "log") == "linear"
+
+
 def _fast_math(from_log_softmax=False):
-    # Hardware ex2/lg2 in the alpha/beta recursions (float32 only).  OT_FAST_MATH=1
-    # / 0 force it on / off.  Unset: on for raw logits (the recursions are a latency
-    # chain in which the library exp/log1p cost ~20 %, and against the reference's
-    # own build the approximations add less than a third to a gradient difference
-    # that the order of the logsumexp sums dominates), off for log-softmax input
-    # (no logsumexp there: with the exact log-add the gradient matches the
-    # reference's to 2.5e-5 on the large-vocabulary benchmark batch, with the
-    # approximations to 4.9e-4).
+    # Hardware ex2/lg2 in the log-adds of the recursions (float32, log domain).
+    # OT_FAST_MATH=1 / 0 force it on / off.  Unset: on for raw logits (the
+    # recursions are a latency chain in which the library exp/log1p cost ~20 %, and
+    # against the reference's own build the approximations add less than a third to
+    # a gradient difference that the order of the logsumexp sums dominates), off for
+    # log-softmax input (no logsumexp there: with the exact log-add the gradient
+    # matches the reference's to 2.5e-5 on the large-vocabulary benchmark batch,
+    # with the approximations to 4.9e-4).
     v = os.environ.get("OT_FAST_MATH")
     if v is None or v == "":
         return not from_log_softmax
@@ -190,6 +201,8 @@ def _flags(logits, from_log_softmax, one_sym_per_frame, checks):
         f |= _lib.ONE_SYM_PER_FRAME
     if _fast_math(from_log_softmax):
         f |= _lib.FAST_MATH
+    if _linear_domain():
+        f |= _lib.LINEAR_DOMAIN
     if os.environ.get("OT_TRACE", "0") == "1":
         f |= _lib.TRACE
     return f
@@ -398,6 +411,66 @@ def compute_transducer_loss(logits, targets, logit_lengths, target_lengths, blan
     return scores, grad
 
 
+_PLANS = {}  # shape key -> _Call whose workspace the next call of that shape on that stream reuses
+
+
+def _planned_call(logits, targets, logit_lengths, target_lengths, blank, from_log_softmax,
+                  one_sym_per_frame, share_sms=False):
+    """A :class:`_Call` for a step that is complete after ONE library call
+    (``loss_and_gradient``), with the workspace of the previous such call of the
+    same shape on the same stream: calls on one stream run in order, the step's
+    kernels are the workspace's only readers, and a call that splits into groups
+    on the library's own streams joins them before it ends.  Training batches
+    repeat their shapes (bucketed sampling); a new shape costs one allocation."""
+    _validate(logits, targets, logit_lengths, target_lengths, blank)
+    index = logits.device.index
+    env = os.environ
+    key = (logits.shape, logits.dtype, index, torch.cuda.current_stream(index).cuda_stream,
+           targets.size(1), logit_lengths.size(0), blank, from_log_softmax, one_sym_per_frame,
+           share_sms, env.get("OT_CHECKS"), env.get("OT_FAST_MATH"), env.get("OT_LATTICE"),
+           env.get("OT_TRACE"))
+    call = _PLANS.get(key)
+    if call is None:
+        if len(_PLANS) >= 64:
+            _PLANS.clear()
+        call = _PLANS[key] = _Call(logits, targets, logit_lengths, target_lengths, blank,
+                                   from_log_softmax, one_sym_per_frame, share_sms=share_sms)
+    else:
+        call.logits, call.targets, call.t, call.u = logits, targets, logit_lengths, target_lengths
+        call.scores = torch.empty(call.n, dtype=call.real, device=call.device)
+    return call
+
+
+def transducer_loss_and_grad(logits, targets, logit_lengths, target_lengths, blank,
+                             from_log_softmax, one_sym_per_frame=False, reduction="mean"):
+    """Loss AND gradient in one library call, without an autograd graph: the
+    shape of the reference's native function, which returns its scores together
+    with the gradient (``_optimized_transducer.compute_transducer_loss``,
+    python/csrc/optimized_transducer.cc:15-19 and csrc/cuda.cu:402-457 of the
+    reference), with the reduction of its Python layer (transducer_loss.py:
+    135-154) folded in.
+
+    Returns ``(loss, grad)``: the reduced loss as a 0-dim tensor and the gradient
+    of that loss with respect to ``logits``: ``logits`` itself, overwritten, for
+    raw logits; a new tensor for log-softmax input.  A training loop hands it to
+    the joiner with ``joiner_out.backward(grad)``.  Arguments, checks
+    (``OT_CHECKS``) and numerics are those of :func:`transducer_loss`, whose
+    ``loss.backward()`` leaves the same values; what is saved is the autograd
+    engine's and this module's per-step host work (about 130 us, against 40 us
+    here), which decides the step time of a batch of a few utterances per GPU.
+    The workspace is reused from call to call (same shape, same stream)."""
+    assert reduction in ("mean", "sum")
+    data = logits.detach() if logits.requires_grad else logits
+    call = _planned_call(data, targets, logit_lengths, target_lengths, blank,
+                         from_log_softmax, one_sym_per_frame)
+    scale = (1.0 / call.n) if reduction == "mean" else 1.0
+    grad = torch.empty_like(data) if from_log_softmax else data
+    loss = torch.empty((), dtype=call.real, device=call.device)
+    call.loss_and_gradient(grad, loss, loss_scale=scale, grad_scale=scale)
+    _record_trace(call)
+    return loss, grad
+
+
 def stage_outputs(logits, targets, logit_lengths, target_lengths, blank,
                   from_log_softmax=False, one_sym_per_frame=False):
     """Runs the forward half and returns its intermediate arrays (copies):
@@ -456,7 +529,8 @@ def joiner_scores(joiner_in, weight, bias, targets, logit_lengths, target_length
     del proxy
     lib = _lib.load()
     n, max_u = int(logit_lengths.size(0)), int(targets.size(1))
-    flags = _CHECK_FLAG[_check_mode("strict")] | (_lib.FAST_MATH if _fast_math(False) else 0)
+    flags = (_CHECK_FLAG[_check_mode("strict")] | (_lib.FAST_MATH if _fast_math(False) else 0)
+             | (_lib.LINEAR_DOMAIN if _linear_domain() else 0))
     if os.environ.get("OT_TRACE", "0") == "1":
         flags |= _lib.TRACE
     lay = _layout(n, rows, max_u, 0)

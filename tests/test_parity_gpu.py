@@ -357,18 +357,57 @@ def test_stage_timeline(monkeypatch):
     assert int(call.stage("trace")[1]) == 0        # off: "last end" slots stay at their initial 0
 
 
-@pytest.mark.parametrize("fast", ["0", "1"])
-def test_both_log_add_variants_stay_within_tolerance(fast, monkeypatch):
-    """OT_FAST_MATH=1 (the default for raw logits): ex2/lg2.approx in the recursions; =0: expf/log1pf."""
+@pytest.mark.parametrize("arith", ["linear", "log0", "log1"])
+def test_all_recursion_arithmetics_stay_within_tolerance(arith, monkeypatch):
+    """The reference's log domain with ex2/lg2.approx (OT_FAST_MATH=1) or
+    expf/log1pf (=0) in the log-add, and the optional scaled linear domain
+    (OT_LATTICE=linear, values m * 2^e).  The log domain is held against the
+    float32 restatement of the reference (whose roundings it repeats), the linear
+    domain against the float64 one (the float32 restatement is itself further
+    from float64 than the bound allows)."""
+    wide = (lambda a: a.astype(np.float64)) if arith == "linear" else (lambda a: a)
     x, tg, T, U = random_batch(53, 3, (30, 60), (10, 40), 50)
-    ref = O.oracle_loss(x, tg, T, U, 0)
-    monkeypatch.setenv("OT_FAST_MATH", fast)
+    ref = O.oracle_loss(wide(x), tg, T, U, 0)
+    monkeypatch.setenv("OT_LATTICE", "linear" if arith == "linear" else "log")
+    if arith != "linear":
+        monkeypatch.setenv("OT_FAST_MATH", arith[-1])
     out = run_cuda(x, tg, T, U, 0)
     check_against(out, ref)
     x, tg, T, U = random_batch(31, 2, (200, 300), (40, 80), 500, 2.0)
-    ref = O.oracle_loss(x, tg, T, U, 0)
+    ref = O.oracle_loss(wide(x), tg, T, U, 0)
     out = run_cuda(x, tg, T, U, 0)
     check_against(out, ref)
+
+
+@pytest.mark.parametrize("modified", [False, True])
+def test_linear_arithmetic_on_log_probs_far_outside_the_float_exponent_range(modified, monkeypatch):
+    """Log-softmax input whose target log-probs are -300 apiece (exp(-300) is not a
+    float32, and the likelihood of an utterance is about exp(-300 U)), some targets
+    at -inf (masked symbols) on cells that a path can avoid, and blanks near 0: the
+    scaled linear recursion keeps an integer exponent beside each value, so alpha,
+    beta and the scores must still match the float64 restatement at 1e-5, across
+    several warps of columns (U up to 70)."""
+    rng = np.random.default_rng(97)
+    n, v = 3, 12
+    T = np.array([90, 75, 80], np.int32)
+    U = np.array([70, 33, 5], np.int32)
+    if modified:
+        U = np.minimum(U, T - 1).astype(np.int32)
+    tg = rng.integers(1, v, (n, int(U.max()))).astype(np.int32)
+    rows = int((T.astype(np.int64) * (U + 1)).sum())
+    x = np.full((rows, v), -300.0, np.float32) + rng.standard_normal((rows, v)).astype(np.float32) * 20
+    x[:, 0] = -np.abs(rng.standard_normal(rows)).astype(np.float32) * 1e-2  # blank: nearly certain
+    sp = splits(T, U)
+    # utterance 1: its first target symbol is impossible (-inf) in every second frame
+    U1 = int(U[1]) + 1
+    for t in range(1, int(T[1]), 2):
+        x[sp[1] + t * U1 + 0, tg[1, 0]] = -np.inf
+    ref = O.oracle_loss(x.astype(np.float64), tg, T, U, 0, True, modified)
+    assert np.all(np.isfinite(ref["scores"])) and ref["scores"].min() < -5000
+    monkeypatch.setenv("OT_LATTICE", "linear")
+    out = run_cuda(x, tg, T, U, 0, from_ls=True, modified=modified)
+    band = O.band_mask(T, U) if modified else None
+    check_against(out, ref, band=band)
 
 
 def test_wide_lattice_uses_generic_recursion():
@@ -637,6 +676,76 @@ def test_offsets_beyond_2_to_the_31_elements():
 # ---------------------------------------------------------------------------
 # 7. the sharded entry point on one rank (multi-rank logic: tests/test_sharding.py)
 # ---------------------------------------------------------------------------
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+@pytest.mark.parametrize("from_ls", [False, True])
+@pytest.mark.parametrize("modified", [False, True])
+def test_one_call_loss_and_grad_equals_the_oracle_and_the_autograd_surface(reduction, from_ls, modified):
+    """transducer_loss_and_grad: (loss, gradient) of one library call, no autograd
+    graph; three calls in a row reuse one workspace (different inputs each time)
+    and each must match the fp64 oracle and, bit for bit, transducer_loss +
+    backward on the same input."""
+    _, tg, T, U = random_batch(51, 3, (9, 14), (3, 6), 40, modified=modified)
+    rows = int((T.astype(np.int64) * (U + 1)).sum())
+    for seed in (51, 52, 53):
+        x = np.random.default_rng(seed).standard_normal((rows, 40)).astype(np.float32)
+        if from_ls:
+            m = x.max(1, keepdims=True)
+            x = (x - (m + np.log(np.exp(x - m).sum(1, keepdims=True)))).astype(np.float32)
+        dx, dt, dT, dU = to_dev(x, tg, T, U)
+        leaf = dx.clone().requires_grad_(True)
+        want = ot.transducer_loss(leaf * 1.0, dt, dT, dU, 0, from_ls, modified, reduction)
+        want.backward()
+        buf = dx.clone()
+        loss, grad = ot.transducer_loss_and_grad(buf, dt, dT, dU, 0, from_ls, modified, reduction)
+        assert (grad.data_ptr() == buf.data_ptr()) == (not from_ls)
+        assert torch.equal(loss, want.detach())
+        assert torch.equal(grad, leaf.grad)
+        if from_ls:
+            assert torch.equal(buf, dx)  # log-softmax input is left alone
+        ref = O.oracle_loss(x.astype(np.float64), tg, T, U, 0, from_ls, modified)
+        div = 3 if reduction == "mean" else 1
+        want_loss = -ref["scores"].sum() / div
+        assert abs(loss.item() - want_loss) <= 1e-5 * abs(want_loss)
+        np.testing.assert_allclose(grad.cpu().numpy(), ref["grad"] / div, rtol=0, atol=2e-5)
+    ot.check_inputs()
+
+
+def test_one_call_loss_and_grad_reports_bad_lengths_like_the_autograd_surface(monkeypatch):
+    monkeypatch.setenv("OT_CHECKS", "1")
+    x, tg, T, U = random_batch(54, 3, (9, 14), (3, 6), 40)
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    bad = dT.clone()
+    bad[1] += 1  # the lengths no longer add up to the number of rows
+    buf = dx.clone()
+    loss, grad = ot.transducer_loss_and_grad(buf, dt, bad, dU, 0, False)
+    assert torch.isnan(loss).item()
+    assert torch.equal(buf, dx)  # nothing was written
+    with pytest.raises(RuntimeError, match="an earlier call on this device"):
+        ot.check_inputs()
+    # and the cached plan still serves a good call afterwards
+    loss, grad = ot.transducer_loss_and_grad(buf, dt, dT, dU, 0, False)
+    assert torch.isfinite(loss).item()
+    ot.check_inputs()
+
+
+def test_sharded_one_call_entry_on_one_rank():
+    from optimized_transducer_b200 import sharding
+    ex = _emulated_ranks(1)[0]
+    x, tg, T, U = random_batch(73, 3, (10, 20), (3, 8), 40)
+    dx, dt, dT, dU = to_dev(x, tg, T, U)
+    for reduction in ("mean", "sum"):
+        a_buf, b_buf, c_buf = dx.clone(), dx.clone(), dx.clone()
+        a, ga = ot.transducer_loss_and_grad(a_buf, dt, dT, dU, 0, False, reduction=reduction)
+        b, gb = sharding.sharded_loss_and_grad(b_buf, dt, dT, dU, 0, False, reduction=reduction,
+                                               global_batch=3, exchange=ex)
+        sharding.wait_loss(b)
+        c, gc = sharding.sharded_loss_and_grad(c_buf, dt, dT, dU, 0, False, reduction=reduction,
+                                               global_batch=3)
+        assert torch.allclose(a, b, rtol=1e-6) and torch.allclose(a, c, rtol=1e-6)
+        assert torch.equal(ga, gb) and torch.equal(ga, gc)
+    ex.check()
+
+
 @pytest.mark.parametrize("reduction", ["mean", "sum"])
 def test_sharded_loss_on_one_rank_equals_plain_loss(reduction):
     from optimized_transducer_b200 import sharding
