@@ -413,18 +413,19 @@ def timeline_summary(traces):
     """From the kernels' own %globaltimer stamps, as medians over the traced steps
     (microseconds): when every stage began and ended, relative to the start of the
     step's first kernel.  A call that ran as two groups of utterances has a second
-    set of stages ("b:"); stages that did not run show -1."""
+    set of stages ("b:"; a call cut into more groups "c:", "d:" as well); stages of
+    that did not run show -1."""
     out = {}
-    rows = [t.reshape(10, 2).tolist() for t in traces]
+    rows = [t.reshape(20, 2).tolist() for t in traces]
     unused = -1  # a "first start" slot nobody wrote still holds its initial all-ones
-    for i in range(10):
-        name = ("b:" if i >= 5 else "") + STAGES[i % 5]
+    for i in range(20):
+        name = ("", "b:", "c:", "d:")[i // 5] + STAGES[i % 5]
         spans = [((r[i][0] - r[0][0]) / 1e3, (r[i][1] - r[0][0]) / 1e3) for r in rows
                  if r[i][0] != unused and r[i][1] > 0]
         out[name] = ([round(statistics.median(s[0] for s in spans), 1),
                       round(statistics.median(s[1] for s in spans), 1)] if spans else [-1.0, -1.0])
     out["step_span"] = round(statistics.median(
-        (max(r[i][1] for i in range(10)) - r[0][0]) / 1e3 for r in rows), 1)
+        (max(r[i][1] for i in range(20)) - r[0][0]) / 1e3 for r in rows), 1)
     return out
 
 
@@ -469,11 +470,22 @@ def run_ours(args, w):
     if world > 1:
         shard = sharding.shard_batch(gT, gU, gtg, w.v, world, rank, strategy=args.partition)
         T, U, tg, mine = shard.T, shard.U, shard.targets, shard.indices
+    elif args.shard_of:
+        # one GPU runs the shard that rank R of a W-rank job would hold (no exchange):
+        # what a single rank of the strong-scaling run does, without the other W-1 GPUs
+        from optimized_transducer_b200 import sharding
+        w_, r_ = (int(v) for v in args.shard_of.split(":"))
+        shard = sharding.shard_batch(gT, gU, gtg, w.v, w_, r_, strategy=args.partition)
+        T, U, tg, mine = shard.T, shard.U, shard.targets, shard.indices
     else:
         T, U, tg, mine = gT, gU, gtg, list(range(n_global))
     rows = synthetic.num_rows(T, U)
     cells_local = rows * w.v
     dT, dU, dtg = T.to(dev), U.to(dev), tg.to(dev)
+    # the lengths as the data loader has them (host tensors): the library cuts its
+    # groups of utterances at utterance boundaries with them (--no-host-lengths: it
+    # cuts at the quantiles of the rows instead)
+    host_lengths = None if args.no_host_lengths else (T, U)
     pristine = synthetic.make_utterance_logits(w, gT, gU, mine, device=dev)
     if args.dtype != "f32":  # the 16-bit extension: same values, rounded once
         pristine = pristine.to(torch.bfloat16 if args.dtype == "bf16" else torch.float16)
@@ -534,9 +546,10 @@ def run_ours(args, w):
         if world > 1:
             return sharding.sharded_loss_and_grad(
                 buf, tg_, t_, u_, 0, w.from_log_softmax, w.one_sym_per_frame, w.reduction,
-                global_batch=n_global, exchange=exchange)[0]
+                global_batch=n_global, exchange=exchange, lengths_on_host=host_lengths)[0]
         return ot.transducer_loss_and_grad(buf, tg_, t_, u_, 0, w.from_log_softmax,
-                                           w.one_sym_per_frame, w.reduction)[0]
+                                           w.one_sym_per_frame, w.reduction,
+                                           lengths_on_host=host_lengths)[0]
 
     def barrier():
         if world > 1:
@@ -763,8 +776,16 @@ def run_ours(args, w):
         # the last four + one closing kernel when the batch runs as two groups), the
         # scaling kernel of the eager schedule's backward, publish + gather of the exchange
         one_call = args.api == "call"
-        launches = ((10 if two_groups else 5) + (1 if eager and not one_call else 0)
-                    + (2 if exchange is not None else 0))
+        # below the two-group size the one-call schedule chains up to four groups (one
+        # utterance each with the lengths on the host): per group logprob, lattice,
+        # coef, gradient, plus prepare and the closing kernel
+        pipeline_on = os.environ.get("OT_B200_PIPELINE", "1") != "0"
+        chained = 0
+        if (eager and not mode_b and not two_groups and pipeline_on and T.numel() >= 2
+                and cells_local >= (64 << 20) and rows >= 64):
+            chained = min(4, int(T.numel()))
+        launches = ((10 if two_groups else (2 + 4 * chained if chained >= 2 else 5))
+                    + (1 if eager and not one_call else 0) + (2 if exchange is not None else 0))
         fwd_bytes = (0 if mode_b else es * cells_local)
         value = cells_total * args.steps / (elapsed_ms * 1e-3)
         per_cell = recorded_traffic_per_cell(args.dtype, mode_b)
@@ -802,7 +823,9 @@ def run_ours(args, w):
                                       "eager (loss and gradient in one library call, as the reference; "
                                       "backward only scales, and skips that when the upstream gradient is 1)"),
                 "stage_overlap": ("off (OT_B200_PIPELINE=0)" if os.environ.get("OT_B200_PIPELINE", "1") == "0"
-                                  else "two groups of utterances on three streams when a rank holds >= 192 Mi lattice cells (768 MB of float logits)"),
+                                  else "two groups of utterances on three streams when a rank holds >= 192 Mi lattice cells "
+                                       "(768 MB of float logits); below that up to four chained groups, each on streams of "
+                                       "its own behind its part of stage 1" + (f" (here: {chained})" if chained >= 2 else "")),
                 "host_enqueue_ms_per_step": host_ms,
             },
             "clocks": clocks.summary(),
@@ -828,8 +851,9 @@ def run_ours(args, w):
             },
             "loss": last_loss,
         }
-        if timeline is not None:
-            line["timeline_us"] = timeline
+        if timeline is not None:  # unused later sets are left out of the line
+            line["timeline_us"] = {k: v for k, v in timeline.items()
+                                   if not (k[1:2] == ":" and v == [-1.0, -1.0])}
         if per_rank is not None:
             line["per_rank"] = per_rank
         if loss_check is not None:
@@ -985,6 +1009,10 @@ def main():
                     help="the timed step: 'call' = transducer_loss_and_grad (one call, loss + in-place gradient, "
                          "no autograd graph); 'autograd' = transducer_loss(...) + loss.backward().  The other "
                          "one is measured too and reported under setup / stages")
+    ap.add_argument("--shard-of", default="", metavar="W:R",
+                    help="diagnostic, one GPU: run the shard rank R of a W-rank job would hold")
+    ap.add_argument("--no-host-lengths", action="store_true",
+                    help="do not hand the host copies of the lengths to the one-call entry")
     ap.add_argument("--partition", choices=["auto", "contiguous", "lpt", "lpt_chain"], default="lpt_chain",
                     help="how utterances are dealt to the ranks (each rank creates its own shard, so a "
                          "permuting partition costs nothing here); lpt_chain balances cells and the "

@@ -226,6 +226,35 @@ int ot_b200_loss_and_gradient(const void *d_logits, void *d_grad, const int32_t 
                               void *d_workspace, uint64_t workspace_bytes, void *d_scores,
                               void *d_loss, double loss_scale, double grad_scale, void *stream);
 
+/* ot_b200_loss_and_gradient with the caller's own cut of the batch into groups of
+ * consecutive utterances.  Batches below the two-group size are pipelined by
+ * group: stage 1 runs group after group on the caller's stream, and each group's
+ * recursion, coefficient and gradient kernels follow on streams of the library's
+ * own (two per group, created per device on first use) as soon as that group's
+ * rows are staged, so all recursions run side by side and the gradient pass of one
+ * group runs under the recursions of the others.  This is the schedule for a few
+ * utterances per GPU (a batch sharded over several GPUs), where one recursion
+ * takes longer than all streaming kernels together.
+ *   group_rows  HOST array of n_groups + 1 packed-row positions, rising strictly
+ *               from 0 to rows; 1 <= n_groups <= 4.  An utterance belongs to the
+ *               group in whose range (group_rows[g], group_rows[g+1]] it ends, so
+ *               any cut is valid; cuts AT utterance boundaries, longest utterance
+ *               first, overlap best.  NULL with n_groups = 0: min(N, 4) groups cut
+ *               at the quantiles of the rows, which is what
+ *               ot_b200_loss_and_gradient does.  n_groups = 1 forces the one-stream
+ *               schedule.  Batches below 64 Mi lattice cells run on one stream
+ *               whatever the cuts: there the step is the longest utterance's own
+ *               chain of kernels, and the schedule's cross-stream edges (6-10 us
+ *               each) and extra launches cost more than the overlap returns.
+ * Results are bitwise those of the one-stream schedule.  No reference counterpart
+ * (the reference launches its kernels one after the other, cuda.cu:402-457). */
+int ot_b200_loss_and_gradient_groups(const void *d_logits, void *d_grad, const int32_t *d_targets,
+                                     const int32_t *d_logit_lengths, const int32_t *d_target_lengths,
+                                     int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blank,
+                                     uint32_t flags, void *d_workspace, uint64_t workspace_bytes,
+                                     void *d_scores, void *d_loss, double loss_scale, double grad_scale,
+                                     const int64_t *group_rows, int32_t n_groups, void *stream);
+
 /* The forward half WITHOUT logits: the joiner's output projection is fused
  * into stage 1, so the (rows, V) tensor the reference materialises and reads
  * back (logits.logsumexp(1), cuda.cu:427; ComputeLogProbs, kernels.cu:30-60;

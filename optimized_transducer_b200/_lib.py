@@ -37,6 +37,7 @@ EXPORTS = (
     "ot_b200_forward",
     "ot_b200_backward",
     "ot_b200_loss_and_gradient",
+    "ot_b200_loss_and_gradient_groups",
     "ot_b200_scale_gradient",
     "ot_b200_forward_linear",
     "ot_b200_compute_transducer_loss",
@@ -94,6 +95,10 @@ def load():
     lib.ot_b200_loss_and_gradient.restype = ctypes.c_int
     lib.ot_b200_loss_and_gradient.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64, vp, vp,
                                               ctypes.c_double, ctypes.c_double, vp]
+    lib.ot_b200_loss_and_gradient_groups.restype = ctypes.c_int
+    lib.ot_b200_loss_and_gradient_groups.argtypes = [vp, vp, vp, vp, vp, i32, i64, i32, i32, i32, u32, vp, u64,
+                                                     vp, vp, ctypes.c_double, ctypes.c_double,
+                                                     ctypes.POINTER(i64), i32, vp]
     lib.ot_b200_forward_linear.restype = ctypes.c_int
     lib.ot_b200_forward_linear.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i32, i32, i32, i32, u32, vp, u64,
                                            vp, vp, ctypes.c_double, vp]

@@ -120,11 +120,12 @@ int fail_earlier(int code, int index, int seq) {
               seq, code, index, input_error_text(code));
 }
 
-// Resources of the two-group schedule (see run_two_groups): per device two side
-// streams and six events, created by the first call that uses the schedule and
-// kept until the process exits.  `lock` serialises the enqueue sequences of
-// concurrent host threads on one device (a sequence records and waits on the
-// shared events; it takes a few tens of microseconds and never waits for the GPU).
+// Resources of the grouped schedules (see run_two_groups, run_chained_groups): per
+// device a few side streams and events, created by the first call that uses a
+// grouped schedule and kept until the process exits.  `lock` serialises the enqueue
+// sequences of concurrent host threads on one device (a sequence records and waits
+// on the shared events; it takes a few tens of microseconds and never waits for the
+// GPU).
 struct Pipeline {
   std::mutex lock;
   bool ready = false;
@@ -132,6 +133,11 @@ struct Pipeline {
   cudaStream_t urgent = nullptr;   // both groups' recursions: highest priority, so that their few
                                    // blocks are placed ahead of the streaming kernels' thousands
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  // chained groups: per group a highest-priority stream for recursion + coefficients
+  // and an ordinary one for the gradient pass, and three events
+  cudaStream_t chain[kMaxGroups] = {nullptr, nullptr, nullptr, nullptr};
+  cudaStream_t grad[kMaxGroups] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t staged[kMaxGroups], coefd[kMaxGroups], done[kMaxGroups];
 };
 Pipeline g_pipelines[kMaxDevices];
 
@@ -148,6 +154,16 @@ cudaError_t pipeline_init(Pipeline &pl) {
     e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
     if (e != cudaSuccess) return e;
   }
+  for (int g = 0; g < kMaxGroups; ++g) {
+    e = cudaStreamCreateWithPriority(&pl.chain[g], cudaStreamNonBlocking, greatest);
+    if (e != cudaSuccess) return e;
+    e = cudaStreamCreateWithPriority(&pl.grad[g], cudaStreamNonBlocking, least);
+    if (e != cudaSuccess) return e;
+    for (cudaEvent_t *ev : {&pl.staged[g], &pl.coefd[g], &pl.done[g]}) {
+      e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming);
+      if (e != cudaSuccess) return e;
+    }
+  }
   pl.ready = true;
   return cudaSuccess;
 }
@@ -158,6 +174,12 @@ bool two_groups_allowed() {
   const char *e = getenv("OT_B200_PIPELINE");
   return !(e && strcmp(e, "0") == 0);
 }
+// OT_B200_PIPELINE=always: the chained groups for every batch they can serve,
+// whatever its size (tests compare the schedules on small batches with it).
+bool chained_groups_forced() {
+  const char *e = getenv("OT_B200_PIPELINE");
+  return e && strcmp(e, "always") == 0;
+}
 
 // Batches below this many lattice cells (rows * V) run as one group: the
 // streaming kernels of half the batch must outlast a recursion for the overlap to
@@ -165,6 +187,14 @@ bool two_groups_allowed() {
 // way; bfloat16 (whose stage 1 is bound by exp throughput, not bytes): 343 M cells
 // 0.526 -> 0.512 ms.
 constexpr uint64_t kTwoGroupsMinCells = 192ull << 20;
+// Below that, a batch of at least this many cells runs as up to four chained
+// groups (run_chained_groups).  Measured on shards of the benchmark batch, step
+// time on one stream -> chained: 16 utterances (171 M cells) 0.389 -> 0.372 ms,
+// 8 utterances (86 M cells) 0.230 -> 0.223 ms, 3-5 utterances (43 M cells)
+// 0.147 -> 0.148..0.153 ms: there the step is the longest utterance's own chain
+// (stage 1, recursion, gradient) plus 6-10 us per cross-stream edge, and the
+// schedule costs 60 us more host time per call.
+constexpr uint64_t kChainedGroupsMinCells = 64ull << 20;
 
 constexpr uint32_t kKnownFlags = OT_B200_FROM_LOG_SOFTMAX | OT_B200_ONE_SYM_PER_FRAME |
                                  OT_B200_FP64 | OT_B200_CHECK_INPUTS | OT_B200_FAST_MATH |
@@ -332,7 +362,8 @@ int run_two_groups(Problem p, void *d_grad, void *d_scores, void *d_loss, double
   cudaError_t e = pipeline_init(pl);
   if (e != cudaSuccess) return fail_cuda(e, "create the streams of the two-group schedule");
   const int64_t r1 = (p.rows / 2) & ~int64_t(15);  // a multiple of the stage-1 tile height
-  p.group_row = r1;
+  p.cuts.n = 2;
+  p.cuts.row[0] = 0; p.cuts.row[1] = r1; p.cuts.row[2] = p.rows;
   Problem a = p, b = p;
   a.group = 0; a.row_begin = 0; a.row_end = r1;
   b.group = 1; b.row_begin = r1; b.row_end = p.rows;
@@ -365,6 +396,69 @@ int run_two_groups(Problem p, void *d_grad, void *d_scores, void *d_loss, double
   OTB_TRY(launch_gradient(b, d_grad, nullptr, grad_scale, pl.side), "launch gradient");
   OTB_TRY(cudaEventRecord(pl.ev[5], pl.side), "record");
   OTB_TRY(cudaStreamWaitEvent(s, pl.ev[5], 0), "wait");
+  OTB_TRY(launch_close(p, d_scores, d_loss, loss_scale, s), "launch close");
+#undef OTB_TRY
+  return OT_B200_OK;
+}
+
+// The schedule for batches whose streaming kernels are SHORTER than a recursion
+// (a few utterances per GPU): the batch is cut into up to four groups of
+// consecutive utterances, stage 1 runs group after group on the caller's stream,
+// and every group continues on streams of its own as soon as its rows are staged:
+//
+//   s        : K0, K1(0), K1(1), ..., K1(G-1)                      ... wait all, close
+//   chain[g] :        (K1(g) done) K2(g), coef(g)                   highest priority
+//   grad[g]  :                       (coef(g) done) K3(g)
+//
+// so the recursions of all groups run side by side (two CTAs per utterance), the
+// first one starts when a G-th of stage 1 is done, and a group's gradient pass
+// runs under the recursions of the groups that are still busy.  Measured on four
+// utterances of the benchmark batch (what each of 8 GPUs holds): one stream is
+// prepare 7 + K1 36 + K2 51 + coef 4 + K3 53 us, one after the other.
+// Callers that know the lengths on the host cut at utterance boundaries, longest
+// utterance first; otherwise the cuts are the G-quantiles of the rows.
+int run_chained_groups(Problem p, void *d_grad, void *d_scores, void *d_loss, double loss_scale,
+                       double grad_scale, cudaStream_t s) {
+  const int dev = current_device_slot();
+  Pipeline &pl = g_pipelines[dev];
+  std::lock_guard<std::mutex> guard(pl.lock);
+  cudaError_t e = pipeline_init(pl);
+  if (e != cudaSuccess) return fail_cuda(e, "create the streams of the grouped schedule");
+  const int G = p.cuts.n;
+#define OTB_TRY(call, what)                          \
+  do {                                               \
+    e = (call);                                      \
+    if (e != cudaSuccess) return fail_cuda(e, what); \
+  } while (0)
+  OTB_TRY(launch_prepare(p, s), "launch prepare");
+  // stage 1 of group g: the rows from its cut (rounded up to the tile height, so
+  // that every launch starts on a tile) to the next group's; the rows of a group's
+  // first utterance that lie before the cut belong to the previous launch
+  // (a group's kernels are enqueued right behind its stage 1, not after the stage 1
+  // of every group: a host that is not ahead of the device would otherwise hold
+  // back the first recursion by the launches of all the others)
+  int64_t begin = 0;
+  for (int g = 0; g < G; ++g) {
+    int64_t end = (g + 1 == G) ? p.rows : ((p.cuts.row[g + 1] + 15) & ~int64_t(15));
+    if (end > p.rows) end = p.rows;
+    Problem q = p;
+    q.group = g;
+    if (end > begin) {
+      q.row_begin = begin; q.row_end = end;
+      OTB_TRY(launch_logprob(q, s), "launch logprob");
+      begin = end;
+    }
+    OTB_TRY(cudaEventRecord(pl.staged[g], s), "record");
+    q.row_begin = 0; q.row_end = 0;
+    OTB_TRY(cudaStreamWaitEvent(pl.chain[g], pl.staged[g], 0), "wait");
+    OTB_TRY(launch_lattice(q, d_scores, pl.chain[g]), "launch lattice");
+    OTB_TRY(launch_coef(q, d_scores, nullptr, 1.0, pl.chain[g]), "launch coef");
+    OTB_TRY(cudaEventRecord(pl.coefd[g], pl.chain[g]), "record");
+    OTB_TRY(cudaStreamWaitEvent(pl.grad[g], pl.coefd[g], 0), "wait");
+    OTB_TRY(launch_gradient(q, d_grad, nullptr, grad_scale, pl.grad[g]), "launch gradient");
+    OTB_TRY(cudaEventRecord(pl.done[g], pl.grad[g]), "record");
+  }
+  for (int g = 0; g < G; ++g) OTB_TRY(cudaStreamWaitEvent(s, pl.done[g], 0), "wait");
   OTB_TRY(launch_close(p, d_scores, d_loss, loss_scale, s), "launch close");
 #undef OTB_TRY
   return OT_B200_OK;
@@ -495,22 +589,36 @@ int ot_b200_backward(const void *d_logits, void *d_grad, int32_t N, int64_t rows
   return OT_B200_OK;
 }
 
-int ot_b200_loss_and_gradient(const void *d_logits, void *d_grad, const int32_t *d_targets,
-                              const int32_t *d_logit_lengths, const int32_t *d_target_lengths,
-                              int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blank,
-                              uint32_t flags, void *d_workspace, uint64_t workspace_bytes,
-                              void *d_scores, void *d_loss, double loss_scale, double grad_scale,
-                              void *stream) {
+int ot_b200_loss_and_gradient_groups(const void *d_logits, void *d_grad, const int32_t *d_targets,
+                                     const int32_t *d_logit_lengths, const int32_t *d_target_lengths,
+                                     int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blank,
+                                     uint32_t flags, void *d_workspace, uint64_t workspace_bytes,
+                                     void *d_scores, void *d_loss, double loss_scale, double grad_scale,
+                                     const int64_t *group_rows, int32_t n_groups, void *stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool mode_b = flags & OT_B200_FROM_LOG_SOFTMAX;
   const uint64_t es = (flags & OT_B200_FP64) ? 8 : ((flags & (OT_B200_BF16 | OT_B200_FP16)) ? 2 : 4);
-  bool two = d_grad != nullptr && !mode_b && N >= 2 && rows >= 64 && V > 0 &&
-             (uint64_t)rows * (uint64_t)V >= kTwoGroupsMinCells && two_groups_allowed();
-  if (two) {  // not while the stream is being captured: the schedule spans three streams
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) two = false;
+  GroupCuts cuts;
+  if (group_rows != nullptr || n_groups != 0) {
+    if (!group_rows || n_groups < 1 || n_groups > kMaxGroups)
+      return fail(OT_B200_ERR_ARGUMENT, "group_rows needs 1 to %d groups, got %d", kMaxGroups, n_groups);
+    bool ok = group_rows[0] == 0 && group_rows[n_groups] == rows;
+    for (int g = 0; g < n_groups; ++g) ok = ok && group_rows[g] < group_rows[g + 1];
+    if (!ok)
+      return fail(OT_B200_ERR_ARGUMENT, "group_rows must rise strictly from 0 to rows (%lld)", (long long)rows);
+    cuts.n = n_groups;
+    for (int g = 0; g <= n_groups; ++g) cuts.row[g] = group_rows[g];
   }
-  if (!two) {
+  const bool splittable = d_grad != nullptr && !mode_b && N >= 2 && rows >= 64 && V > 0 && two_groups_allowed();
+  const uint64_t cells = (uint64_t)(rows > 0 ? rows : 0) * (uint64_t)(V > 0 ? V : 0);
+  bool two = splittable && cells >= kTwoGroupsMinCells;
+  bool chained = splittable && !two && cuts.n != 1 &&
+                 (cells >= kChainedGroupsMinCells || chained_groups_forced());
+  if (two || chained) {  // not while the stream is being captured: the schedules span several streams
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) two = chained = false;
+  }
+  if (!two && !chained) {
     int rc = ot_b200_forward(d_logits, d_targets, d_logit_lengths, d_target_lengths, N, rows, V,
                              max_u, blank, flags, d_workspace, workspace_bytes, d_scores, d_loss,
                              loss_scale, stream);
@@ -533,10 +641,31 @@ int ot_b200_loss_and_gradient(const void *d_logits, void *d_grad, const int32_t 
   volatile int32_t *slot = nullptr;
   rc = attach_reports(&p, flags, s, &slot);
   if (rc) return rc;
-  rc = run_two_groups(p, d_grad, d_scores, d_loss, loss_scale, grad_scale, s);
+  if (two) {
+    rc = run_two_groups(p, d_grad, d_scores, d_loss, loss_scale, grad_scale, s);
+  } else {
+    if (cuts.n == 0) {  // the G-quantiles of the rows, on tile boundaries
+      const int G = N < kMaxGroups ? N : kMaxGroups;
+      cuts.n = G;
+      for (int g = 0; g <= G; ++g) cuts.row[g] = (g == G) ? rows : ((rows * g / G) & ~int64_t(15));
+    }
+    p.cuts = cuts;
+    rc = run_chained_groups(p, d_grad, d_scores, d_loss, loss_scale, grad_scale, s);
+  }
   if (rc) return rc;
   if (slot) return wait_for_verdict(slot, p.report_seq, s);
   return OT_B200_OK;
+}
+
+int ot_b200_loss_and_gradient(const void *d_logits, void *d_grad, const int32_t *d_targets,
+                              const int32_t *d_logit_lengths, const int32_t *d_target_lengths,
+                              int32_t N, int64_t rows, int32_t V, int32_t max_u, int32_t blank,
+                              uint32_t flags, void *d_workspace, uint64_t workspace_bytes,
+                              void *d_scores, void *d_loss, double loss_scale, double grad_scale,
+                              void *stream) {
+  return ot_b200_loss_and_gradient_groups(d_logits, d_grad, d_targets, d_logit_lengths, d_target_lengths,
+                                          N, rows, V, max_u, blank, flags, d_workspace, workspace_bytes,
+                                          d_scores, d_loss, loss_scale, grad_scale, nullptr, 0, stream);
 }
 
 int ot_b200_forward_linear(const void *d_x, const void *d_w, const float *d_bias,

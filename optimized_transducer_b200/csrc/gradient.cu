@@ -404,10 +404,10 @@ cudaError_t launch_grad_a2(const Problem &p, void *grad, const void *d_scale,
   auto kernel = gradient_kernel<X, VEC, CH, PER_UTT, kMinBlocks>;
   // 16-bit rows are half as many bytes per warp; there one resident wave that
   // strides over the buffer measured faster (277 against 289 us on bf16 cfg2).
-  // A group launch is sized for the rows the host knows the group cannot exceed
-  // by much (group 0 ends at or before group_row; group 1 starts at the utterance
-  // that straddles it): the kernel strides, so a few blocks take a second row.
-  const int64_t span = p.group == 0 ? p.group_row : (p.group == 1 ? p.rows - p.group_row : p.rows);
+  // A group launch is sized for the rows between the group's cuts, which the group
+  // cannot exceed by much (its first utterance may begin before the cut): the
+  // kernel strides, so a few blocks take a second row.
+  const int64_t span = p.group >= 0 ? p.cuts.row[p.group + 1] - p.cuts.row[p.group] : p.rows;
   const cudaError_t e = launch_pdl(kernel,
       stream_grid(kernel, &per_sm, span > 0 ? span : 1, p.flags, sizeof(X) == 2), (unsigned)kThreads, 0, s,
       static_cast<const X *>(p.logits), static_cast<X *>(grad),

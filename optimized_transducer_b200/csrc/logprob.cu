@@ -77,12 +77,13 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
                const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
                const int32_t *__restrict__ status, int N, int64_t row_begin, int64_t rows, int V,
                int max_u, int blank, typename Real<X>::type *__restrict__ den,
-               typename Real<X>::type *__restrict__ lp) {
-  // This launch covers the packed rows [row_begin, rows).
+               typename Real<X>::type *__restrict__ lp, int trace_group) {
+  // This launch covers the packed rows [row_begin, rows); `trace_group` only names
+  // the timeline slot.
   pdl_wait();
   pdl_trigger();
   if (status[kStatusCode] != 0) return;
-  if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageLogprob, row_begin > 0 ? 1 : 0));
+  if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageLogprob, trace_group));
   using T = typename Real<X>::type;
   using VT = typename VecOf<X, VEC>::type;
   constexpr int kGroups = kWarp / LPR;  // rows a warp works on at once
@@ -176,7 +177,7 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
       }
     }
   }
-  if (threadIdx.x == 0) trace_end(status, trace_slot(kStageLogprob, row_begin > 0 ? 1 : 0));
+  if (threadIdx.x == 0) trace_end(status, trace_slot(kStageLogprob, trace_group));
 }
 
 // ---------------------------------------------------------------------------
@@ -203,7 +204,7 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
                    const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
                    int32_t *__restrict__ status, int N, int64_t row_begin, int64_t rows, int V,
                    int max_u, int blank, float *__restrict__ den, float *__restrict__ lp,
-                   int tiles_per_block) {
+                   int tiles_per_block, int trace_group) {
   // This launch covers the packed rows [row_begin, rows); row_begin is a multiple
   // of the tile height, so every tile starts on a 16-byte boundary.
   extern __shared__ __align__(128) unsigned char tile_mem[];
@@ -256,7 +257,7 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
     __syncthreads();
     return;
   }
-  if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageLogprob, row_begin > 0 ? 1 : 0));
+  if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageLogprob, trace_group));
 
   // Position of this group's first row; it then advances by 16 rows per tile.
   int64_t row = row_begin + tile0 * kTmaRows + g;
@@ -330,7 +331,7 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
       }
     }
   }
-  if (threadIdx.x == 0) trace_end(status, trace_slot(kStageLogprob, row_begin > 0 ? 1 : 0));
+  if (threadIdx.x == 0) trace_end(status, trace_slot(kStageLogprob, trace_group));
 }
 
 // Log-softmax input: nothing to reduce, only the gather (thread per row).
@@ -385,7 +386,7 @@ cudaError_t launch_lse_m(const Problem &p, cudaStream_t s) {
       reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
       reinterpret_cast<const int32_t *>(p.ws + p.lay.status), p.N, p.row_begin, row_end, p.V,
       p.max_u, p.blank, reinterpret_cast<T *>(p.ws + p.lay.den),
-      reinterpret_cast<T *>(p.ws + p.lay.lp));
+      reinterpret_cast<T *>(p.ws + p.lay.lp), p.group);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
@@ -465,7 +466,7 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
           reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
           reinterpret_cast<int32_t *>(p.ws + p.lay.status), p.N, p.row_begin, row_end, p.V, p.max_u,
           p.blank, reinterpret_cast<float *>(p.ws + p.lay.den), reinterpret_cast<float *>(p.ws + p.lay.lp),
-          tiles_per_block);
+          tiles_per_block, p.group);
       return e != cudaSuccess ? e : cudaGetLastError();
     }
   }

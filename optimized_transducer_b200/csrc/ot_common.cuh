@@ -36,17 +36,29 @@ constexpr int kStatusWords = 16;
 // the workspace has kStatusBlockWords words.
 constexpr int kStatusTraceOn = 3;
 constexpr int kTraceWord = 16;
-// Word kStatusGroupSplit: when a call runs as two groups of utterances (the
-// pipelined schedule of api.cu), the first utterance of the second group; stage 0
-// derives it from the row at which the host cut the batch.
+// Words kStatusGroupSplit .. kStatusGroupSplit + kMaxGroups: when a call runs as
+// groups of utterances (the pipelined schedules of api.cu), word g holds the first
+// utterance of group g (word 0: 0; the words from the number of groups on: N);
+// stage 0 derives them from the rows at which the host cut the batch.
+constexpr int kMaxGroups = 4;
 constexpr int kStatusGroupSplit = 4;
-constexpr int kStatusBlockWords = 64;
+constexpr int kStatusBlockWords = 128;
 enum Stage { kStagePrepare = 0, kStageLogprob = 1, kStageLattice = 2, kStageCoef = 3, kStageGradient = 4, kStages_ = 5 };
-// Timeline slot of a stage: the launches of the second group of a two-group call
-// (group == 1) use slots kStages_ .. 2*kStages_-1, everything else 0 .. kStages_-1.
+// Timeline slot of a stage: the launches of group g > 0 of a grouped call use slots
+// g*kStages_ .. (g+1)*kStages_-1, everything else 0 .. kStages_-1.
 __host__ __device__ __forceinline__ int trace_slot(int stage, int group) {
-  return group == 1 ? stage + kStages_ : stage;
+  return group > 0 ? stage + group * kStages_ : stage;
 }
+constexpr int kTraceSlots = kMaxGroups * kStages_;
+static_assert(kTraceWord + 4 * kTraceSlots <= kStatusBlockWords, "the trace slots must fit into the status block");
+
+// Packed rows at which the host cuts a batch into n groups: row[0] = 0 < row[1] <
+// ... < row[n] = rows.  An utterance belongs to the group in whose range
+// (row[g], row[g+1]] it ENDS.  n == 0: the call is not grouped.
+struct GroupCuts {
+  int n = 0;
+  int64_t row[kMaxGroups + 1] = {0, 0, 0, 0, 0};
+};
 
 // Marker values of the `tgt` field of a gradient-coefficient record.
 constexpr int32_t kTgtNone = -1;     // no symbol column to patch in this row
@@ -121,13 +133,12 @@ struct Problem {
   uint32_t flags;
   char *ws;
   Layout lay;
-  // A launch covers the whole batch (group < 0) or one of two groups of
-  // utterances: group 0 = the utterances that END at or before packed row
-  // `group_row`, group 1 = the rest.  Stage 1 is cut at the row itself
-  // ([row_begin, row_end), host-known); the later stages read the utterance
-  // boundary stage 0 stored in status word kStatusGroupSplit.
+  // A launch covers the whole batch (group < 0) or one of the groups of utterances
+  // that `cuts` defines.  Stage 1 is cut at rows ([row_begin, row_end), host-known);
+  // the later stages read the utterance boundaries stage 0 stored in the status
+  // words from kStatusGroupSplit on.
   int group = -1;
-  int64_t group_row = 0;
+  GroupCuts cuts;
   int64_t row_begin = 0;
   int64_t row_end = 0;  // 0: `rows`
   // Error reports (device views of mapped host words, or NULL), written by the
@@ -271,8 +282,10 @@ __device__ __forceinline__ void tma_load_1d(void *dst, const void *src, uint32_t
 __device__ __forceinline__ void group_range(const int32_t *status, int group, int N, int &lo, int &hi) {
   lo = 0;
   hi = N;
-  if (group == 0) hi = status[kStatusGroupSplit];
-  else if (group == 1) lo = status[kStatusGroupSplit];
+  if (group >= 0) {
+    lo = status[kStatusGroupSplit + group];
+    hi = status[kStatusGroupSplit + group + 1];
+  }
 }
 
 // First statement of every kernel that reads what an earlier kernel wrote

@@ -50,10 +50,10 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
                int max_u, int modified, int64_t max_cells,
                int32_t *__restrict__ status, int64_t *__restrict__ split,
                int64_t *__restrict__ cell_split, uint4 *__restrict__ lp_fill,
-               int64_t lp_fill_count, uint4 fill_pattern, int trace, int64_t group_row) {
+               int64_t lp_fill_count, uint4 fill_pattern, int trace, GroupCuts cuts) {
   __shared__ long long scan_buf[kPrepThreads / kWarp];
   __shared__ int warp_maxu[kPrepThreads / kWarp];
-  __shared__ int group_count;
+  __shared__ int group_count[kMaxGroups + 1];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_wait();     // the previous call's kernels may still be reading this workspace
   pdl_trigger();
@@ -70,10 +70,10 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
   }
   if (tid < kStatusBlockWords) {
     // trace slots: "first start" begins at the maximum, "last end" at 0
-    const bool min_slot = tid >= kTraceWord && tid < kTraceWord + 4 * 2 * kStages_ && ((tid - kTraceWord) & 3) < 2;
+    const bool min_slot = tid >= kTraceWord && tid < kTraceWord + 4 * kTraceSlots && ((tid - kTraceWord) & 3) < 2;
     status[tid] = min_slot ? -1 : (tid == kStatusTraceOn ? trace : 0);
   }
-  if (tid == 0) group_count = 0;
+  if (tid <= kMaxGroups) group_count[tid] = 0;
   __syncthreads();
   if (tid == 0) trace_begin(status, kStagePrepare);
 
@@ -99,19 +99,23 @@ prepare_kernel(const int32_t *__restrict__ targets, const int32_t *__restrict__ 
   for (int o = 16; o > 0; o >>= 1) wmax = max(wmax, __shfl_xor_sync(kFull, wmax, o));
   if (lane == 0) warp_maxu[warp] = wmax;
   __syncthreads();
-  int ends_early = 0;  // my utterances that end at or before the group row
+  int ends_early[kMaxGroups + 1] = {0, 0, 0, 0, 0};  // [g]: my utterances that end at or before cut g
   for (int b = b0; b < b1; ++b) {
     split[b] = run_rows;
     cell_split[b] = run_cells;
     const int tc = max(Tl[b], 0), uc = min(max(Ul[b], 0), max_u);
     run_rows += (long long)tc * (uc + 1);
     run_cells += cell_block(tc, uc, modified != 0);
-    ends_early += (run_rows <= group_row) ? 1 : 0;
+#pragma unroll
+    for (int g = 1; g < kMaxGroups; ++g) ends_early[g] += (g < cuts.n && run_rows <= cuts.row[g]) ? 1 : 0;
   }
-  // Utterance ends grow with b, so the count IS the first utterance of group 1.
-  if (ends_early) atomicAdd(&group_count, ends_early);
+  // Utterance ends grow with b, so the count IS the first utterance of group g.
+#pragma unroll
+  for (int g = 1; g < kMaxGroups; ++g)
+    if (ends_early[g]) atomicAdd(&group_count[g], ends_early[g]);
   __syncthreads();
-  if (tid == 0) status[kStatusGroupSplit] = group_count;
+  if (tid <= kMaxGroups && cuts.n > 0)
+    status[kStatusGroupSplit + tid] = (tid == 0) ? 0 : (tid < cuts.n ? group_count[tid] : N);
   if (tid == 0) {
     int maxu_all = -1;
     for (int w = 0; w < kPrepThreads / kWarp; ++w) maxu_all = max(maxu_all, warp_maxu[w]);
@@ -425,7 +429,7 @@ cudaError_t launch_prepare(const Problem &p, cudaStream_t s) {
       reinterpret_cast<int64_t *>(p.ws + p.lay.split),
       reinterpret_cast<int64_t *>(p.ws + p.lay.cell_split),
       reinterpret_cast<uint4 *>(p.ws + p.lay.lp), units, pattern,
-      (p.flags & OT_B200_TRACE) ? 1 : 0, p.group_row);
+      (p.flags & OT_B200_TRACE) ? 1 : 0, p.cuts);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 

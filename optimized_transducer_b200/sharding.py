@@ -24,8 +24,8 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-from .transducer_loss import (_Call, _eager_grad, _on_device, _planned_call, _record_trace,
-                              real_dtype)
+from .transducer_loss import (_Call, _cached_cuts, _eager_grad, _on_device, _planned_call,
+                              _record_trace, real_dtype)
 
 __all__ = ["utterance_costs", "chain_lengths", "shard_time", "partition_contiguous", "partition_lpt", "imbalance",
            "Shard", "shard_batch", "all_reduce_sum", "sharded_transducer_loss", "sharded_loss_and_grad",
@@ -194,7 +194,12 @@ def shard_batch(T: torch.Tensor, U: torch.Tensor, targets: torch.Tensor, V: int,
     parts = [list(range(a, b)) for a, b in bounds]
     contiguous = True
     if strategy == "lpt_chain":
-        parts, contiguous = partition_lpt(costs, world, chain_lengths(T, U)), False
+        chains = chain_lengths(T, U)
+        parts, contiguous = partition_lpt(costs, world, chains), False
+        # Longest recursion first within a rank: the grouped schedule of the library
+        # (ot_b200_loss_and_gradient_groups) starts a group's recursion as soon as
+        # its rows are staged, and the longest one decides when the step can end.
+        parts = [sorted(p_, key=lambda b: (-chains[b], b)) for p_ in parts]
     elif strategy == "lpt" or (strategy == "auto" and imbalance(costs, parts) > max_imbalance):
         lpt = partition_lpt(costs, world)
         if strategy == "lpt" or imbalance(costs, lpt) < imbalance(costs, parts):
@@ -516,7 +521,7 @@ def sharded_transducer_loss(logits, targets, logit_lengths, target_lengths, blan
 def sharded_loss_and_grad(logits, targets, logit_lengths, target_lengths, blank,
                           from_log_softmax, one_sym_per_frame=False, reduction="mean",
                           global_batch: Optional[int] = None, group=None,
-                          exchange: Optional[PeerExchange] = None):
+                          exchange: Optional[PeerExchange] = None, lengths_on_host=None):
     """:func:`sharded_transducer_loss` without an autograd graph: one library call
     for this rank's loss and gradient (see ``transducer_loss_and_grad``) and one
     for the exchange of the scalar.  Returns ``(loss, grad)``: the loss of the
@@ -524,7 +529,8 @@ def sharded_loss_and_grad(logits, targets, logit_lengths, target_lengths, blank,
     is given) and the gradient of that loss with respect to this rank's rows
     (``logits`` itself for raw logits).  No gradient crosses ranks; the only
     coupling is the sum the reference's Python layer takes over the batch
-    (transducer_loss.py:147-152 of the reference)."""
+    (transducer_loss.py:147-152 of the reference).  ``lengths_on_host``: as for
+    ``transducer_loss_and_grad`` (``Shard.T`` / ``Shard.U`` are host tensors)."""
     assert reduction in ("mean", "sum")
     if global_batch is None:
         world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -540,7 +546,8 @@ def sharded_loss_and_grad(logits, targets, logit_lengths, target_lengths, blank,
         call = _planned_call(data, targets, logit_lengths, target_lengths, blank,
                              from_log_softmax, one_sym_per_frame)
         grad = torch.empty_like(data) if from_log_softmax else data
-        call.loss_and_gradient(grad, local, loss_scale=1.0, grad_scale=scale)
+        call.loss_and_gradient(grad, local, loss_scale=1.0, grad_scale=scale,
+                               cuts=_cached_cuts(call, lengths_on_host))
         _record_trace(call)
     else:  # a rank without utterances still joins the exchange
         local.zero_()

@@ -62,7 +62,7 @@ from . import _lib
 __all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
            "compute_transducer_loss", "stage_outputs", "transducer_loss_per_utterance",
            "PerUtteranceLossFunction", "check_inputs", "joiner_scores",
-           "transducer_loss_and_grad"]
+           "transducer_loss_and_grad", "group_cuts"]
 
 
 # Diagnostic: with OT_TRACE=1 and a list set here (collect_traces), every
@@ -316,18 +316,20 @@ class _Call:
             _lib.check(rc)
         return grad_out
 
-    def loss_and_gradient(self, grad_out=None, loss_out=None, loss_scale=1.0, grad_scale=1.0):
+    def loss_and_gradient(self, grad_out=None, loss_out=None, loss_scale=1.0, grad_scale=1.0, cuts=None):
         """Enqueues the whole step as one library call: scores, the reduced loss
         (``loss_out``, optional) and, into ``grad_out`` (optional; may be the
-        logits), ``grad_scale`` times the gradient of ``-scores.sum()``."""
+        logits), ``grad_scale`` times the gradient of ``-scores.sum()``.  ``cuts``:
+        a ctypes int64 array of packed-row positions that cut the batch into groups
+        (``ot_b200_loss_and_gradient_groups``), or None: the library decides."""
         with _on_device(self.index):
-            rc = self.lib.ot_b200_loss_and_gradient(
+            rc = self.lib.ot_b200_loss_and_gradient_groups(
                 self.logits.data_ptr(), grad_out.data_ptr() if grad_out is not None else None,
                 self.targets.data_ptr() if self.max_u else None, self.t.data_ptr(), self.u.data_ptr(),
                 self.n, self.rows, self.v, self.max_u, self.blank, self.flags,
                 self.workspace.data_ptr(), self.bytes, self.scores.data_ptr(),
                 loss_out.data_ptr() if loss_out is not None else None, loss_scale, grad_scale,
-                self._stream())
+                cuts, (len(cuts) - 1) if cuts is not None else 0, self._stream())
         if rc:
             _lib.check(rc)
         return self.scores
@@ -362,8 +364,8 @@ class _Call:
         elif name == "trace":
             # with OT_TRACE=1: per stage (prepare, logprob, lattice, coef, gradient) the
             # %globaltimer (ns) at which its first block started and its last block ended;
-            # then the same five pairs for the second group of a two-group call
-            off, count, dtype, esz = self.layout.status_off + 64, 20, torch.int64, 8
+            # then the same five pairs for the second, third and fourth group of a grouped call
+            off, count, dtype, esz = self.layout.status_off + 64, 40, torch.int64, 8
         elif name == "status":
             off, count, dtype, esz = self.layout.status_off, 16, torch.int32, 4
         else:
@@ -441,8 +443,55 @@ def _planned_call(logits, targets, logit_lengths, target_lengths, blank, from_lo
     return call
 
 
+MAX_GROUPS = 4
+
+
+def group_cuts(logit_lengths, target_lengths, max_groups=MAX_GROUPS):
+    """Packed-row positions that cut a batch into at most ``max_groups`` groups of
+    consecutive utterances, as a ctypes int64 array for
+    ``ot_b200_loss_and_gradient_groups``: one utterance per group for up to
+    ``max_groups`` utterances, else groups of about equal numbers of rows.
+    ``logit_lengths`` / ``target_lengths``: HOST tensors or sequences (T_b, U_b)."""
+    T = logit_lengths.tolist() if hasattr(logit_lengths, "tolist") else list(logit_lengths)
+    U = target_lengths.tolist() if hasattr(target_lengths, "tolist") else list(target_lengths)
+    ends, total = [], 0
+    for t, u in zip(T, U):
+        total += int(t) * (int(u) + 1)
+        ends.append(total)
+    n = len(ends)
+    g = min(max_groups, n)
+    cuts = [0]
+    if n <= max_groups:
+        cuts += ends
+    else:
+        b = 0
+        for k in range(1, g):
+            # the first utterance end at or beyond the k-th quantile, leaving one
+            # utterance at least for every later group
+            while ends[b] < total * k / g and b < n - (g - k) - 1:
+                b += 1
+            cuts.append(ends[b])
+            b += 1
+        cuts.append(total)
+    return (ctypes.c_int64 * len(cuts))(*cuts)
+
+
+def _cached_cuts(call, lengths_on_host):
+    """The cuts for ``lengths_on_host`` = (T, U) host tensors, computed once per
+    pair of tensors (and again when one of them is modified in place)."""
+    if lengths_on_host is None:
+        return None
+    t, u = lengths_on_host
+    key = (id(t), id(u), getattr(t, "_version", 0), getattr(u, "_version", 0))
+    if getattr(call, "cuts_key", None) != key:
+        call.cuts_key, call.cuts = key, group_cuts(t, u)
+        call.cuts_owner = (t, u)  # keeps the ids alive for as long as the key is
+    return call.cuts
+
+
 def transducer_loss_and_grad(logits, targets, logit_lengths, target_lengths, blank,
-                             from_log_softmax, one_sym_per_frame=False, reduction="mean"):
+                             from_log_softmax, one_sym_per_frame=False, reduction="mean",
+                             lengths_on_host=None):
     """Loss AND gradient in one library call, without an autograd graph: the
     shape of the reference's native function, which returns its scores together
     with the gradient (``_optimized_transducer.compute_transducer_loss``,
@@ -458,7 +507,14 @@ def transducer_loss_and_grad(logits, targets, logit_lengths, target_lengths, bla
     ``loss.backward()`` leaves the same values; what is saved is the autograd
     engine's and this module's per-step host work (about 130 us, against 40 us
     here), which decides the step time of a batch of a few utterances per GPU.
-    The workspace is reused from call to call (same shape, same stream)."""
+    The workspace is reused from call to call (same shape, same stream).
+
+    ``lengths_on_host``: optionally the pair (logit_lengths, target_lengths) as
+    HOST tensors (a data loader has them).  The library pipelines a batch by
+    groups of utterances (see ``ot_b200_loss_and_gradient_groups``); with the
+    lengths known on the host the groups are cut at utterance boundaries, one
+    utterance per group for up to four, which overlaps best when the longest
+    utterance comes first.  Results do not depend on it."""
     assert reduction in ("mean", "sum")
     data = logits.detach() if logits.requires_grad else logits
     call = _planned_call(data, targets, logit_lengths, target_lengths, blank,
@@ -466,7 +522,8 @@ def transducer_loss_and_grad(logits, targets, logit_lengths, target_lengths, bla
     scale = (1.0 / call.n) if reduction == "mean" else 1.0
     grad = torch.empty_like(data) if from_log_softmax else data
     loss = torch.empty((), dtype=call.real, device=call.device)
-    call.loss_and_gradient(grad, loss, loss_scale=scale, grad_scale=scale)
+    call.loss_and_gradient(grad, loss, loss_scale=scale, grad_scale=scale,
+                           cuts=_cached_cuts(call, lengths_on_host))
     _record_trace(call)
     return loss, grad
 
