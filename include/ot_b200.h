@@ -238,7 +238,7 @@ int ot_b200_loss_and_gradient(const void *d_logits, void *d_grad, const int32_t 
  *   group_rows  HOST array of n_groups + 1 packed-row positions, rising strictly
  *               from 0 to rows; 1 <= n_groups <= 4.  An utterance belongs to the
  *               group in whose range (group_rows[g], group_rows[g+1]] it ends, so
- *               any cut is valid; cuts AT utterance boundaries, longest utterance
+ *               any cut is valid; cuts AT utterance boundaries, shortest utterances
  *               first, overlap best.  NULL with n_groups = 0: min(N, 4) groups cut
  *               at the quantiles of the rows, which is what
  *               ot_b200_loss_and_gradient does.  n_groups = 1 forces the one-stream

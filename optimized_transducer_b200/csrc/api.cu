@@ -415,8 +415,9 @@ int run_two_groups(Problem p, void *d_grad, void *d_scores, void *d_loss, double
 // runs under the recursions of the groups that are still busy.  Measured on four
 // utterances of the benchmark batch (what each of 8 GPUs holds): one stream is
 // prepare 7 + K1 36 + K2 51 + coef 4 + K3 53 us, one after the other.
-// Callers that know the lengths on the host cut at utterance boundaries, longest
-// utterance first; otherwise the cuts are the G-quantiles of the rows.
+// Callers that know the lengths on the host cut at utterance boundaries, shortest
+// utterances first (their gradient pass then runs while stage 1 of the later groups
+// still streams); otherwise the cuts are the G-quantiles of the rows.
 int run_chained_groups(Problem p, void *d_grad, void *d_scores, void *d_loss, double loss_scale,
                        double grad_scale, cudaStream_t s) {
   const int dev = current_device_slot();

@@ -449,9 +449,15 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
       // 296 slots, 46 us against 36 us with every slot filled once), so such a launch
       // is cut into as few full waves as blocks of at most 24 tiles allow: equal
       // blocks, at least 4 tiles each so that the three-stage pipeline still fills.
+      // In a grouped call the recursion of the PREVIOUS group starts while this launch
+      // fills the SMs: a recursion CTA (up to ~100 KB of shared memory) fits beside one
+      // resident block but not beside two, and the blocks of a one-wave launch all live
+      // as long as the launch (measured: recursions starting 22-29 us late), so such a
+      // launch leaves one slot free on as many SMs as the batch has recursion CTAs.
       int tiles_per_block = kTmaTiles;
       {
-        const int64_t slots = 2 * (int64_t)sm_count();
+        int64_t slots = 2 * (int64_t)sm_count();
+        if (p.group >= 0) slots -= (2 * (int64_t)p.N < 64 ? 2 * (int64_t)p.N : 64);
         if (ntiles <= 3 * slots * kTmaTiles) {
           const int64_t waves = (ntiles + slots * 24 - 1) / (slots * 24);
           const int64_t even = (ntiles + slots * waves - 1) / (slots * waves);

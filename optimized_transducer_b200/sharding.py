@@ -196,10 +196,14 @@ def shard_batch(T: torch.Tensor, U: torch.Tensor, targets: torch.Tensor, V: int,
     if strategy == "lpt_chain":
         chains = chain_lengths(T, U)
         parts, contiguous = partition_lpt(costs, world, chains), False
-        # Longest recursion first within a rank: the grouped schedule of the library
-        # (ot_b200_loss_and_gradient_groups) starts a group's recursion as soon as
-        # its rows are staged, and the longest one decides when the step can end.
-        parts = [sorted(p_, key=lambda b: (-chains[b], b)) for p_ in parts]
+        # Shortest recursion first within a rank: the grouped schedule of the library
+        # (ot_b200_loss_and_gradient_groups) starts a group's recursion as soon as its
+        # rows are staged and its gradient pass as soon as the recursion ends, so the
+        # first group's gradient pass is runnable while stage 1 of the later groups is
+        # still streaming and the memory system never waits for a recursion.  Measured
+        # on shards of the benchmark batch (step time, longest first -> shortest first):
+        # 8 utterances 0.224 -> 0.212 ms, 16 utterances 0.368 -> 0.360 ms.
+        parts = [sorted(p_, key=lambda b: (chains[b], b)) for p_ in parts]
     elif strategy == "lpt" or (strategy == "auto" and imbalance(costs, parts) > max_imbalance):
         lpt = partition_lpt(costs, world)
         if strategy == "lpt" or imbalance(costs, lpt) < imbalance(costs, parts):

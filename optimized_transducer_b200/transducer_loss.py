@@ -513,8 +513,8 @@ def transducer_loss_and_grad(logits, targets, logit_lengths, target_lengths, bla
     HOST tensors (a data loader has them).  The library pipelines a batch by
     groups of utterances (see ``ot_b200_loss_and_gradient_groups``); with the
     lengths known on the host the groups are cut at utterance boundaries, one
-    utterance per group for up to four, which overlaps best when the longest
-    utterance comes first.  Results do not depend on it."""
+    utterance per group for up to four, which overlaps best when the shortest
+    utterances come first.  Results do not depend on it."""
     assert reduction in ("mean", "sum")
     data = logits.detach() if logits.requires_grad else logits
     call = _planned_call(data, targets, logit_lengths, target_lengths, blank,
