@@ -498,9 +498,9 @@ def run_ours(args, w):
     # one so that the restoring copies stay outside the timed spans.
     total_steps = args.steps + args.warmup
     free, _ = torch.cuda.mem_get_info(dev)
-    fit = int(0.5 * free // bytes_logits) - 1  # leaves room for the pristine copy, one more clone and the workspaces
+    fit = int((free - (8 << 30)) // bytes_logits) - 1  # leaves room for one more clone and the workspaces
     if fit < 2:
-        raise RuntimeError("the device cannot hold this rank's logits five times over")
+        raise RuntimeError("the device cannot hold this rank's logits four times over")
     rotating = fit < total_steps
     if rotating:
         args.no_e2e = True  # the host-buffer run needs two more device buffers and a pinned copy

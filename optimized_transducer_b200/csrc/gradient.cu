@@ -431,11 +431,13 @@ cudaError_t launch_grad16(const Problem &p, void *grad, const void *d_scale, dou
   static std::atomic<int> per_sm{0};
   auto kernel = gradient16_kernel<X, PER_UTT>;
   unsigned grid = stream_grid(kernel, &per_sm, p.rows, p.flags, true);
-  if (p.group >= 0) {
-    // In a two-group call the other group's recursion and coefficient kernels must
+  if (p.group >= 0 && p.group + 1 < p.cuts.n) {
+    // In a grouped call the next group's recursion and coefficient kernels must
     // find room UNDER this resident wave (measured with five blocks per SM: the
     // coefficient kernel of group b started 42 us late, when the first blocks of
-    // this kernel retired): leave one block slot per SM free.
+    // this kernel retired): leave one block slot per SM free.  The last group's
+    // pass has nothing to make room for and keeps the full wave (four blocks per
+    // SM cost 139 us per half of the benchmark batch against 123 us).
     const int blocks = per_sm.load(std::memory_order_relaxed);
     if (blocks > 1) {
       const unsigned smaller = (unsigned)(sm_count() * (blocks - 1));

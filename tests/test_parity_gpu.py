@@ -707,12 +707,14 @@ def test_chained_group_schedule_gives_the_same_bits(case, monkeypatch):
         assert torch.equal(got["0", 0][0], got["always", rep][0])
         assert torch.equal(got["0", 0][1], got["always", rep][1])
     assert torch.isfinite(got["always", 0][0]).item()
-    # against the oracle too (float32 cases)
+    # against the float64 oracle too (float32 cases; the bits are those of the
+    # one-stream schedule, which the other tests hold to the tighter bounds)
     if dtype == torch.float32 and rows < 5000:
         ref = O.oracle_loss(x.cpu().numpy().astype(np.float64), tg.numpy(), T.numpy(), U.numpy(), 0, False, modified)
         want = -ref["scores"].sum()
         assert abs(got["always", 0][0].item() - want) <= 1e-5 * abs(want)
-        np.testing.assert_allclose(got["always", 0][1].cpu().numpy(), ref["grad"], rtol=0, atol=3e-5)
+        np.testing.assert_allclose(got["always", 0][1].cpu().numpy(), ref["grad"], rtol=0,
+                                   atol=max(3e-5, 2 * fp32_grad_floor(ref["alpha"], ref["beta"])))
     # a bad length under the grouped schedule: NaN loss, logits untouched, reported later
     monkeypatch.setenv("OT_B200_PIPELINE", "always")
     monkeypatch.setenv("OT_CHECKS", "1")
