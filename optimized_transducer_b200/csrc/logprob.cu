@@ -196,9 +196,10 @@ constexpr int kTmaRows = 16;     // rows per tile = lane groups per block
 constexpr int kTmaStagesMax = 3;
 constexpr int kTmaTiles = 16;    // tiles per block in a launch of many waves
 
-// kTmaStages: tiles in flight per block (three are used; see the launcher).
-template <typename X, int kTmaStages>
-__global__ void __launch_bounds__(kThreads, 2)
+// kTmaStages: tiles in flight per block (three); kBlocks: resident blocks per SM the
+// registers are capped for (two; see the launcher for what else was measured).
+template <typename X, int kTmaStages, int kBlocks>
+__global__ void __launch_bounds__(kThreads, kBlocks)
 logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets,
                    const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
                    const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
@@ -434,13 +435,20 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
       // Two stages for the launches of a two-group call (so that a recursion CTA fits
       // beside the two resident blocks) were measured and are NOT used: stage 1 of
       // half the batch went from 118 to 126 us and the step from 0.669 to 0.684 ms.
-      const int stages = kTmaStagesMax;
-      const size_t smem = (size_t)stages * kTmaRows * p.V * sizeof(X);
-      static SmemGrant grant2, grant3;
+      // Two resident blocks per SM, three tiles in flight per block, for float and for
+      // 16-bit rows.  A 16-bit tile is half the bytes for the same instructions (about
+      // 180 warp instructions per row either way), so that stage is bound by
+      // instruction issue (71 % of the issue slots busy over the whole benchmark
+      // batch, 4.3 TB/s), not by bytes in flight: measured per half of the 16-bit
+      // benchmark batch, six tiles in flight per block 86 -> 104 us, three resident
+      // blocks per SM (registers capped at 80) 86 -> 89 us.
+      constexpr int kBlocksHere = 2;
+      auto tma_kernel = logprob_tma_kernel<X, kTmaStagesMax, kBlocksHere>;
+      constexpr int kStagesHere = kTmaStagesMax;
+      const size_t smem = (size_t)kStagesHere * kTmaRows * p.V * sizeof(X);
+      static SmemGrant grant;
       {
-        const cudaError_t e = stages == 2
-            ? grant2.ensure(logprob_tma_kernel<X, 2>, (size_t)2 * kTmaRows * 512 * sizeof(X))
-            : grant3.ensure(logprob_tma_kernel<X, 3>, (size_t)3 * kTmaRows * 512 * sizeof(X));
+        const cudaError_t e = grant.ensure(tma_kernel, (size_t)kStagesHere * kTmaRows * 512 * sizeof(X));
         if (e != cudaSuccess) return e;
       }
       const int64_t ntiles = (row_end - p.row_begin + kTmaRows - 1) / kTmaRows;
@@ -448,7 +456,7 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
       // 16-tile blocks ends with a mostly empty last wave (85 000 rows: 334 blocks on
       // 296 slots, 46 us against 36 us with every slot filled once), so such a launch
       // is cut into as few full waves as blocks of at most 24 tiles allow: equal
-      // blocks, at least 4 tiles each so that the three-stage pipeline still fills.
+      // blocks, at least one tile more than the pipeline holds.
       // In a grouped call the recursion of the PREVIOUS group starts while this launch
       // fills the SMs: a recursion CTA (up to ~100 KB of shared memory) fits beside one
       // resident block but not beside two, and the blocks of a one-wave launch all live
@@ -456,16 +464,16 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
       // launch leaves one slot free on as many SMs as the batch has recursion CTAs.
       int tiles_per_block = kTmaTiles;
       {
-        int64_t slots = 2 * (int64_t)sm_count();
+        int64_t slots = kBlocksHere * (int64_t)sm_count();
         if (p.group >= 0) slots -= (2 * (int64_t)p.N < 64 ? 2 * (int64_t)p.N : 64);
         if (ntiles <= 3 * slots * kTmaTiles) {
           const int64_t waves = (ntiles + slots * 24 - 1) / (slots * 24);
           const int64_t even = (ntiles + slots * waves - 1) / (slots * waves);
-          tiles_per_block = (int)(even < 4 ? 4 : even);
+          tiles_per_block = (int)(even < kStagesHere + 1 ? kStagesHere + 1 : even);
         }
       }
       const unsigned grid = (unsigned)((ntiles + tiles_per_block - 1) / tiles_per_block);
-      const cudaError_t e = launch_pdl(stages == 2 ? logprob_tma_kernel<X, 2> : logprob_tma_kernel<X, 3>,
+      const cudaError_t e = launch_pdl(tma_kernel,
           grid, (unsigned)kThreads, smem, s,
           static_cast<const X *>(p.logits), p.targets, p.T, p.U,
           reinterpret_cast<const int64_t *>(p.ws + p.lay.split),
