@@ -93,6 +93,40 @@ def test_shards_tile_the_batch(strategy):
     assert sorted(owners) == list(range(w.n)) and bool((seen == 1).all())
 
 
+def test_chain_aware_shards_put_the_shortest_recursion_first():
+    """lpt_chain orders a rank's utterances by the length of their recursion
+    (T + U), shortest first: the order in which the library's grouped schedule
+    overlaps best."""
+    w = synthetic.CONFIGS["cfg2"]
+    T, U, tg = synthetic.make_lengths(w)
+    for world in (2, 4, 8):
+        for rank in range(world):
+            s = sharding.shard_batch(T, U, tg, w.v, world, rank, "lpt_chain")
+            chains = (s.T + s.U).tolist()
+            assert chains == sorted(chains)
+
+
+def test_group_cuts_follow_utterance_boundaries():
+    """The row positions handed to ot_b200_loss_and_gradient_groups: strictly
+    rising from 0 to the number of rows, every cut at the end of an utterance, at
+    most four groups, one utterance per group for up to four utterances."""
+    from optimized_transducer_b200.transducer_loss import MAX_GROUPS, group_cuts
+    rng = np.random.default_rng(5)
+    for n in (1, 2, 3, 4, 5, 9, 32):
+        T = torch.from_numpy(rng.integers(1, 60, n).astype(np.int32))
+        U = torch.from_numpy(rng.integers(0, 12, n).astype(np.int32))
+        ends = np.cumsum(T.numpy().astype(np.int64) * (U.numpy() + 1)).tolist()
+        cuts = list(group_cuts(T, U))
+        assert cuts[0] == 0 and cuts[-1] == ends[-1]
+        assert all(a < b for a, b in zip(cuts, cuts[1:]))
+        assert set(cuts[1:]) <= set(ends)
+        assert len(cuts) - 1 == min(n, MAX_GROUPS)
+    # lists work as well as tensors; a first utterance that holds most rows still leaves
+    # every later group an utterance
+    cuts = list(group_cuts([100, 1, 1, 1, 1, 1], [0] * 6))
+    assert cuts == [0, 100, 101, 102, 105]
+
+
 def test_more_ranks_than_utterances():
     T = torch.tensor([5, 7], dtype=torch.int32)
     U = torch.tensor([2, 3], dtype=torch.int32)
