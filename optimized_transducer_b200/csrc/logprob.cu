@@ -181,6 +181,22 @@ logprob_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets
 }
 
 // ---------------------------------------------------------------------------
+// Maximum of two packed pairs of 16-bit values (exact; NaN handling of fmaxf).
+template <typename X> __device__ __forceinline__ uint32_t pmax16(uint32_t a, uint32_t b);
+template <> __device__ __forceinline__ uint32_t pmax16<__nv_bfloat16>(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&a),
+                                   *reinterpret_cast<const __nv_bfloat162 *>(&b));
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+template <> __device__ __forceinline__ uint32_t pmax16<__half>(uint32_t a, uint32_t b) {
+  const __half2 r = __hmax2(*reinterpret_cast<const __half2 *>(&a), *reinterpret_cast<const __half2 *>(&b));
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+template <> __device__ __forceinline__ uint32_t pmax16<float>(uint32_t a, uint32_t) { return a; }  // unused
+template <typename X> __device__ __forceinline__ uint32_t packed_neg_inf() { return 0u; }
+template <> __device__ __forceinline__ uint32_t packed_neg_inf<__nv_bfloat16>() { return 0xff80ff80u; }
+template <> __device__ __forceinline__ uint32_t packed_neg_inf<__half>() { return 0xfc00fc00u; }
+
 // The same stage with the rows staged through shared memory by bulk copies, for
 // the common shape: float rows of 64 < V/4 <= 128 vectors (V = 260..512,
 // V % 4 == 0), standard transducer.  A block walks over `tiles_per_block`
@@ -198,7 +214,9 @@ constexpr int kTmaTiles = 16;    // tiles per block in a launch of many waves
 
 // kTmaStages: tiles in flight per block (three); kBlocks: resident blocks per SM the
 // registers are capped for (two; see the launcher for what else was measured).
-template <typename X, int kTmaStages, int kBlocks>
+// kFull: the first kFull of a lane's eight vectors exist in every row the launcher
+// sends here (4 for V/4 > 64, 7 for V/4 > 112), so only the others are range-checked.
+template <typename X, int kTmaStages, int kBlocks, int kFull>
 __global__ void __launch_bounds__(kThreads, kBlocks)
 logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ targets,
                    const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
@@ -287,13 +305,16 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
     if (row < rows) {
       const X *p = reinterpret_cast<const X *>(tile_mem + (size_t)(k % kTmaStages) * tile_bytes) + (size_t)g * V;
       float x[CH * 4];
+      // 16-bit rows: the maximum is taken on the packed pairs (half the instructions)
+      [[maybe_unused]] uint32_t pm = packed_neg_inf<X>();
 #pragma unroll
       for (int j = 0; j < CH; ++j) {
         const int vi = j * LPR + gl;
-        if (vi < nvec) {
+        if (j < kFull || vi < nvec) {
           const VT v = *reinterpret_cast<const VT *>(p + vi * 4);
           if constexpr (sizeof(X) == 2) {  // two words of two elements each
             const uint32_t *w = reinterpret_cast<const uint32_t *>(&v);
+            pm = pmax16<X>(pm, pmax16<X>(w[0], w[1]));
             const float2 a = Pair16<X>::widen(w[0]), b = Pair16<X>::widen(w[1]);
             x[j * 4 + 0] = a.x; x[j * 4 + 1] = a.y; x[j * 4 + 2] = b.x; x[j * 4 + 3] = b.y;
           } else {
@@ -305,9 +326,15 @@ logprob_tma_kernel(const X *__restrict__ logits, const int32_t *__restrict__ tar
           x[j * 4 + 0] = ninf; x[j * 4 + 1] = ninf; x[j * 4 + 2] = ninf; x[j * 4 + 3] = ninf;
         }
       }
-      float m = x[0];
+      float m;
+      if constexpr (sizeof(X) == 2) {
+        const float2 mm = Pair16<X>::widen(pm);
+        m = fmaxf(mm.x, mm.y);
+      } else {
+        m = x[0];
 #pragma unroll
-      for (int i = 1; i < CH * 4; ++i) m = fmaxf(m, x[i]);
+        for (int i = 1; i < CH * 4; ++i) m = fmaxf(m, x[i]);
+      }
       m = group_max<float, LPR>(m, gmask);
       float s = 0;
       if (m - m == 0.0f) s = add_exps(x, m, s);  // an infinite maximum needs no sum
@@ -443,12 +470,15 @@ cudaError_t launch_logprob_t(const Problem &p, cudaStream_t s) {
       // benchmark batch, six tiles in flight per block 86 -> 104 us, three resident
       // blocks per SM (registers capped at 80) 86 -> 89 us.
       constexpr int kBlocksHere = 2;
-      auto tma_kernel = logprob_tma_kernel<X, kTmaStagesMax, kBlocksHere>;
+      const bool wide = nv > 112;  // V/4 in (112, 128]: seven of a lane's eight vectors always exist
+      auto tma_kernel = wide ? logprob_tma_kernel<X, kTmaStagesMax, kBlocksHere, 7>
+                             : logprob_tma_kernel<X, kTmaStagesMax, kBlocksHere, 4>;
       constexpr int kStagesHere = kTmaStagesMax;
       const size_t smem = (size_t)kStagesHere * kTmaRows * p.V * sizeof(X);
-      static SmemGrant grant;
+      static SmemGrant grant_wide, grant_narrow;
       {
-        const cudaError_t e = grant.ensure(tma_kernel, (size_t)kStagesHere * kTmaRows * 512 * sizeof(X));
+        const cudaError_t e = (wide ? grant_wide : grant_narrow)
+                                  .ensure(tma_kernel, (size_t)kStagesHere * kTmaRows * 512 * sizeof(X));
         if (e != cudaSuccess) return e;
       }
       const int64_t ntiles = (row_end - p.row_begin + kTmaRows - 1) / kTmaRows;
