@@ -727,6 +727,62 @@ def test_chained_group_schedule_gives_the_same_bits(case, monkeypatch):
         ot.check_inputs(DEV)
 
 
+def test_two_host_threads_share_the_grouped_schedule(monkeypatch):
+    """Two host threads, each on a CUDA stream of its own, call the one-call entry
+    at the same time; both calls run as chained groups, i.e. they share the
+    library's per-device streams and events (their enqueue sequences are
+    serialised by a mutex, nothing else is).  Every result must carry the bits of
+    the same input evaluated alone on one stream."""
+    import threading
+    shapes = [([23, 41, 17, 30], [7, 3, 9, 5]), ([19, 28, 35], [6, 4, 8])]
+    v, reps = 64, 12
+    data, want = [], []
+    monkeypatch.setenv("OT_B200_PIPELINE", "0")
+    for i, (T, U) in enumerate(shapes):
+        T = torch.tensor(T, dtype=torch.int32)
+        U = torch.tensor(U, dtype=torch.int32)
+        gen = torch.Generator().manual_seed(100 + i)
+        tg = torch.randint(1, v, (T.numel(), int(U.max())), dtype=torch.int32, generator=gen)
+        xs = [(torch.randn(synthetic.num_rows(T, U), v, generator=gen) * 2).to(DEV) for _ in range(reps)]
+        data.append((xs, tg.to(DEV), T.to(DEV), U.to(DEV), (T, U)))
+        want.append([tuple(t.clone() for t in ot.transducer_loss_and_grad(x.clone(), tg.to(DEV), T.to(DEV), U.to(DEV),
+                                                                         0, False, False, "sum")) for x in xs])
+    torch.cuda.synchronize()
+    monkeypatch.setenv("OT_B200_PIPELINE", "always")
+    streams = [torch.cuda.Stream(device=DEV) for _ in shapes]
+    got = [[] for _ in shapes]
+    errors = []
+    start = threading.Barrier(len(shapes))
+
+    def worker(i):
+        try:
+            xs, tg, T, U, host = data[i]
+            torch.cuda.set_device(DEV)
+            start.wait()
+            with torch.cuda.stream(streams[i]):
+                for x in xs:
+                    buf = x.clone()
+                    loss, grad = ot.transducer_loss_and_grad(buf, tg, T, U, 0, False, False, "sum",
+                                                             lengths_on_host=host)
+                    got[i].append((loss.clone(), grad.clone()))
+            streams[i].synchronize()
+        except Exception as e:  # reported by the main thread
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(len(shapes))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    torch.cuda.synchronize()
+    assert not errors, errors
+    ot.check_inputs(DEV)
+    for i in range(len(shapes)):
+        assert len(got[i]) == reps
+        for (l0, g0), (l1, g1) in zip(want[i], got[i]):
+            assert torch.equal(l0, l1) and torch.equal(g0, g1)
+
+
 def test_group_cuts_are_validated():
     x, tg, T, U = random_batch(58, 3, (9, 14), (3, 6), 40)
     dx, dt, dT, dU = to_dev(x, tg, T, U)
