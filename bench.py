@@ -965,6 +965,26 @@ def run_fused(args, w):
     torch.cuda.synchronize()
     ms = statistics.median(ev[it][0].elapsed_time(ev[it][1]) for it in range(args.warmup, n_it))
     k_us = statistics.median((int(t[3]) - int(t[2])) / 1e3 for t in (s.cpu() for s in spans[args.warmup:]))
+    # forward + backward without logits (joiner_loss): the library recomputes the logits
+    # tile in backward and writes the bfloat16 gradient with respect to the logits; the
+    # three contractions with it are PyTorch matmuls
+    from optimized_transducer_b200.transducer_loss import collect_traces
+    xa, wa, ba = (t.clone().requires_grad_(True) for t in (x, wt, bias))
+    ev3 = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_it)]
+    bspans = []
+    collect_traces(bspans)
+    for it in range(n_it):
+        xa.grad = wa.grad = ba.grad = None
+        ev3[it][0].record()
+        jl = ot.joiner_loss(xa, wa, ba, dtg, dT, dU, 0, reduction="sum")
+        ev3[it][1].record()
+        jl.backward()
+        ev3[it][2].record()
+    torch.cuda.synchronize()
+    collect_traces(None)
+    jf_ms = statistics.median(ev3[it][0].elapsed_time(ev3[it][1]) for it in range(args.warmup, n_it))
+    jb_ms = statistics.median(ev3[it][1].elapsed_time(ev3[it][2]) for it in range(args.warmup, n_it))
+    g_us = statistics.median((int(t[9]) - int(t[8])) / 1e3 for t in (s_.cpu() for s_ in bspans[args.warmup:]))
     flops = 2.0 * rows * d * w.v
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -982,6 +1002,16 @@ def run_fused(args, w):
                      "peak_source": f"{kind} dense bf16 GEMM", "traffic": None,
                      "us_per_launch": k_us, "timing": "the kernel's own %globaltimer span (first block start to last block end)"},
         "bytes_never_written": rows * w.v * 4,
+        "joiner_loss": {
+            "what": "forward + backward from the joiner's operands, no float logits: forward as above; backward = "
+                    "linear_gradient_kernel (logits tile recomputed on the tensor cores, bfloat16 gradient "
+                    "with respect to the logits written) + three PyTorch contractions with that tile",
+            "forward_ms": jf_ms, "backward_ms": jb_ms,
+            "linear_gradient_kernel_us": g_us,
+            "linear_gradient_kernel_tflops": flops / (g_us * 1e-6) / 1e12,
+            "linear_gradient_kernel_frac_of_peak": flops / (g_us * 1e-6) / 1e12 / peak,
+            "gradient_bytes_written": rows * w.v * 2,
+        },
         "gpu_launches": 4 * args.steps,
         "loss": float(out.item()),
     }

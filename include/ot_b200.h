@@ -278,6 +278,25 @@ int ot_b200_forward_linear(const void *d_x, const void *d_w, const float *d_bias
                            void *d_workspace, uint64_t workspace_bytes, void *d_scores, void *d_loss,
                            double loss_scale, void *stream);
 
+/* The backward half of ot_b200_forward_linear as far as the logits go:
+ *   d_grad_logits[r, v] = scale * d(-sum_b scores[b]) / d logits[r, v]     bfloat16, (rows, V)
+ * with logits = x * w^T + bias RECOMPUTED tile by tile on the tensor cores (the same
+ * copies and MMAs as the forward kernel) and the gradient formula of ot_b200_backward
+ * (kernels.cu:522-779 of the reference) applied in the epilogue, from the per-row
+ * records the forward call left in the workspace.  The (rows, V) logits exist in
+ * neither half; the caller contracts the gradient tile with its operands
+ * (dX = G * w, dW = G^T * x, dbias = column sums of G), e.g. with library GEMMs.
+ *   d_workspace  the workspace of the ot_b200_forward_linear call, same N, rows, V, max_u
+ *   scale = scale_host * (d_scale ? *d_scale : 1); d_scale a device float or NULL
+ * V a multiple of 4, d_grad_logits 8-byte aligned, D a multiple of 8, x and w 16-byte
+ * aligned.  When the forward call's verdict was not OK the gradient is all zeros.
+ * flags may hold OT_B200_REPORT_ERRORS, OT_B200_FAST_MATH, OT_B200_TRACE.  No
+ * counterpart in the reference (it needs the logits, cuda.cu:427-453). */
+int ot_b200_backward_linear(const void *d_x, const void *d_w, const float *d_bias, int32_t N,
+                            int64_t rows, int32_t D, int32_t V, int32_t max_u, int32_t blank,
+                            uint32_t flags, const void *d_workspace, uint64_t workspace_bytes,
+                            void *d_grad_logits, const float *d_scale, double scale_host, void *stream);
+
 /* d_grad[i] *= *d_scale for i < count, unless *d_scale == 1 (then the buffer is
  * not touched: the kernel's blocks return after one load).  The counterpart of
  * `ctx.grad.mul_(loss_grad)` (transducer_loss.py:162) for a gradient that

@@ -40,6 +40,7 @@ EXPORTS = (
     "ot_b200_loss_and_gradient_groups",
     "ot_b200_scale_gradient",
     "ot_b200_forward_linear",
+    "ot_b200_backward_linear",
     "ot_b200_compute_transducer_loss",
     "ot_b200_poll_errors",
     "ot_b200_read_input_status",
@@ -102,6 +103,9 @@ def load():
     lib.ot_b200_forward_linear.restype = ctypes.c_int
     lib.ot_b200_forward_linear.argtypes = [vp, vp, vp, vp, vp, vp, i32, i64, i32, i32, i32, i32, u32, vp, u64,
                                            vp, vp, ctypes.c_double, vp]
+    lib.ot_b200_backward_linear.restype = ctypes.c_int
+    lib.ot_b200_backward_linear.argtypes = [vp, vp, vp, i32, i64, i32, i32, i32, i32, u32, vp, u64, vp, vp,
+                                            ctypes.c_double, vp]
     lib.ot_b200_scale_gradient.restype = ctypes.c_int
     lib.ot_b200_scale_gradient.argtypes = [vp, i64, vp, u32, vp]
     lib.ot_b200_compute_transducer_loss.restype = ctypes.c_int

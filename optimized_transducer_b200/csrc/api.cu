@@ -485,6 +485,13 @@ int wait_for_verdict(volatile int32_t *slot, int32_t want, cudaStream_t s) {
 
 }  // namespace otb
 
+namespace otb {
+// fused_linear.cu
+cudaError_t launch_linear_gradient(const Problem &p, const void *x, const void *w, const float *bias,
+                                   int D, void *grad, const float *d_scale, float scale_host,
+                                   cudaStream_t s);
+}  // namespace otb
+
 using namespace otb;
 
 extern "C" {
@@ -706,6 +713,42 @@ int ot_b200_forward_linear(const void *d_x, const void *d_w, const float *d_bias
   e = launch_coef(p, d_scores, d_loss, loss_scale, s);
   if (e != cudaSuccess) return fail_cuda(e, "launch coef");
   if (slot) return wait_for_verdict(slot, p.report_seq, s);
+  return OT_B200_OK;
+}
+
+int ot_b200_backward_linear(const void *d_x, const void *d_w, const float *d_bias, int32_t N,
+                            int64_t rows, int32_t D, int32_t V, int32_t max_u, int32_t blank,
+                            uint32_t flags, const void *d_workspace, uint64_t workspace_bytes,
+                            void *d_grad_logits, const float *d_scale, double scale_host, void *stream) {
+  if (flags & (OT_B200_FROM_LOG_SOFTMAX | OT_B200_ONE_SYM_PER_FRAME | OT_B200_FP64 | OT_B200_BF16 | OT_B200_FP16 |
+               OT_B200_SCALE_PER_UTTERANCE | OT_B200_CHECK_INPUTS))
+    return fail(OT_B200_ERR_ARGUMENT, "ot_b200_backward_linear: standard transducer, bfloat16 operands; flags may "
+                                      "hold OT_B200_REPORT_ERRORS, OT_B200_FAST_MATH, OT_B200_TRACE");
+  Problem p;
+  int rc = check_common(N, rows, V, max_u, blank, flags, d_workspace, workspace_bytes, &p.lay);
+  if (rc) return rc;
+  if (!d_x || !d_w || !d_grad_logits) return fail(OT_B200_ERR_ARGUMENT, "a required device pointer is NULL");
+  if (D <= 0 || D % 8 != 0)
+    return fail(OT_B200_ERR_ARGUMENT, "ot_b200_backward_linear: D must be a positive multiple of 8, got %d", D);
+  if (V % 4 != 0)
+    return fail(OT_B200_ERR_ARGUMENT, "ot_b200_backward_linear: V must be a multiple of 4 (8-byte groups of the bfloat16 gradient), got %d", V);
+  if (reinterpret_cast<uintptr_t>(d_x) % 16 != 0 || reinterpret_cast<uintptr_t>(d_w) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(d_grad_logits) % 8 != 0)
+    return fail(OT_B200_ERR_ARGUMENT, "ot_b200_backward_linear: x and w must be 16-byte, the gradient 8-byte aligned");
+  p.logits = nullptr; p.targets = nullptr; p.T = nullptr; p.U = nullptr;
+  p.N = N; p.rows = rows; p.V = V; p.max_u = max_u; p.blank = blank; p.flags = flags;
+  p.ws = static_cast<char *>(const_cast<void *>(d_workspace));
+  {  // a pending record of a failed call (the forward half of this very loss, perhaps) is raised here
+    int32_t *sticky = nullptr;
+    int32_t seq = 0;
+    rc = begin_reported_call(flags, &sticky, &seq);
+    if (rc) return rc;
+  }
+  const cudaError_t e = launch_linear_gradient(p, d_x, d_w, d_bias, D, d_grad_logits, d_scale, (float)scale_host,
+                                               static_cast<cudaStream_t>(stream));
+  if (e == cudaErrorNotSupported)
+    return fail(OT_B200_ERR_CUDA, "ot_b200_backward_linear: the driver's tensor-map encoder is not available or refused the operands");
+  if (e != cudaSuccess) return fail_cuda(e, "launch linear gradient");
   return OT_B200_OK;
 }
 

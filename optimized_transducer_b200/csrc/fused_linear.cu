@@ -46,9 +46,12 @@ constexpr int kTileM = 128;     // rows per tile = TMEM lanes
 constexpr int kTileN = 256;     // columns per MMA = half of TMEM
 constexpr int kBlockK = 64;     // bfloat16 elements per K block = one 128-byte swizzle row
 constexpr int kMmaK = 16;       // K of one tcgen05.mma for 16-bit operands
-constexpr int kRing = 4;        // shared-memory stages
+constexpr int kRing = 4;        // shared-memory stages of the forward kernel
+constexpr int kRingGrad = 3;    // ... of the gradient kernel, whose epilogue needs a staging buffer too
+constexpr int kOutPitch = 17;   // words per row of a warp's 32 x 16-word output staging tile (conflict-free)
 constexpr int kEpilogueWarps = 8;
 constexpr int kFusedThreads = 64 + 32 * kEpilogueWarps;
+constexpr uint32_t kOutBytes = kEpilogueWarps * 32 * kOutPitch * 4;
 constexpr int kMaxBiasColumns = 7680;  // bias staged in shared memory behind the ring: vocabularies up to this size
 constexpr uint32_t kBytesA = kTileM * kBlockK * 2;   // 16 KB
 constexpr uint32_t kBytesB = kTileN * kBlockK * 2;   // 32 KB
@@ -152,30 +155,43 @@ __device__ __forceinline__ float pick32(const float (&x)[32], int idx) {
   return (idx & 1) ? d[1] : d[0];
 }
 
-__global__ void __launch_bounds__(kFusedThreads, 1)
-linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                      const float *__restrict__ bias, const int32_t *__restrict__ targets,
-                      const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
-                      const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
-                      int32_t *__restrict__ status, int N, int64_t rows, int D, int V, int max_u,
-                      int blank, float *__restrict__ den, float *__restrict__ lp) {
+// What the gradient variant needs besides the operands (see linear_gradient_kernel).
+struct GradArgs {
+  const CoefA<float> *coef;   // per-row coefficient records of the forward half
+  __nv_bfloat16 *grad;        // (rows, V) out
+  const float *d_scale;       // device scalar or NULL
+  float scale_host;
+};
+
+// Body of both kernels.  kGrad == false: stage 1 (den, lp).  kGrad == true: the
+// gradient with respect to the logits, from the RECOMPUTED logits tile.
+template <bool kGrad>
+__device__ __forceinline__ void
+linear_body(const CUtensorMap &map_x, const CUtensorMap &map_w,
+            const float *__restrict__ bias, const int32_t *__restrict__ targets,
+            const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
+            const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
+            int32_t *__restrict__ status, int N, int64_t rows, int D, int V, int max_u,
+            int blank, float *__restrict__ den, float *__restrict__ lp, const GradArgs ga) {
+  constexpr int R = kGrad ? kRingGrad : kRing;  // stages of the operand ring
   extern __shared__ __align__(1024) unsigned char ring_mem[];
   __shared__ FusedShared sh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned char *ring = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(ring_mem) + 1023) & ~uintptr_t(1023));  // swizzle atoms are 1024-byte aligned
   // behind the ring: the bias of every column, padded with zeros to whole column tiles
-  float *bias_s = reinterpret_cast<float *>(ring + (size_t)kRing * kStageBytes);
-  {
-    const int padded = ((V + kTileN - 1) / kTileN) * kTileN;
-    for (int i = threadIdx.x; i < padded; i += kFusedThreads)
-      bias_s[i] = (bias != nullptr && i < V) ? __ldg(bias + i) : 0.f;
-  }
+  float *bias_s = reinterpret_cast<float *>(ring + (size_t)R * kStageBytes);
+  const int padded_v = ((V + kTileN - 1) / kTileN) * kTileN;
+  for (int i = threadIdx.x; i < padded_v; i += kFusedThreads)
+    bias_s[i] = (bias != nullptr && i < V) ? __ldg(bias + i) : 0.f;
+  // gradient kernel: behind the bias, per epilogue warp a 32 x 16-word tile through
+  // which a chunk of the gradient is turned from "thread = row" into row-contiguous stores
+  [[maybe_unused]] uint32_t *out_s = reinterpret_cast<uint32_t *>(bias_s + padded_v);
 
   pdl_wait();     // stage 0 (splits, status, the -inf fill of lp) is complete
   pdl_trigger();
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kRing; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
+    for (int i = 0; i < R; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&sh.acc_full[i], 1); mbar_init(&sh.acc_empty[i], 32 * kEpilogueWarps); }
     sh.abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -191,7 +207,7 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = sh.tmem_base;
   const bool run = status[kStatusCode] == 0;  // bad inputs: nothing is computed
-  if (run && threadIdx.x == 0) trace_begin(status, kStageLogprob);
+  if (run && threadIdx.x == 0) trace_begin(status, kGrad ? kStageGradient : kStageLogprob);
 
   const int64_t row_tiles = (rows + kTileM - 1) / kTileM;
   const int col_tiles = (V + kTileN - 1) / kTileN;
@@ -203,8 +219,8 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     for (int64_t tile = blockIdx.x; tile < row_tiles && !sh.abort; tile += gridDim.x) {
       for (int ct = 0; ct < col_tiles && !sh.abort; ++ct) {
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kRing;
-          if (it >= kRing && !mbar_wait(&sh.empty[s], ((it / kRing) - 1) & 1, &sh.abort)) { sh.abort = 1; break; }
+          const int s = it % R;
+          if (it >= R && !mbar_wait(&sh.empty[s], ((it / R) - 1) & 1, &sh.abort)) { sh.abort = 1; break; }
           unsigned char *a = ring + (size_t)s * kStageBytes;
           mbar_expect_tx(&sh.full[s], kStageBytes);
           // rows / columns past the ends of x and w are filled with zeros by the copy
@@ -217,7 +233,7 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       __shared__ int never;  // the drain must not stop because of the abort flag itself
       never = 0;
       const volatile int *nullptr_abort = &never;
-      for (uint32_t j = (it > kRing ? it - kRing : 0); j < it; ++j) mbar_wait(&sh.full[j % kRing], (j / kRing) & 1, nullptr_abort);
+      for (uint32_t j = (it > R ? it - R : 0); j < it; ++j) mbar_wait(&sh.full[j % R], (j / R) & 1, nullptr_abort);
       atomicCAS(status + kStatusCopyTimeout, 0, 1);
     }
   } else if (run && warp == 1 && lane == 0) {
@@ -230,8 +246,8 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d = tmem + (uint32_t)(buf * kTileN);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % kRing;
-          if (!mbar_wait(&sh.full[s], (it / kRing) & 1, &sh.abort)) { sh.abort = 1; break; }
+          const int s = it % R;
+          if (!mbar_wait(&sh.full[s], (it / R) & 1, &sh.abort)) { sh.abort = 1; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a = smem_u32(ring + (size_t)s * kStageBytes);
           const uint64_t da = smem_desc(a), db = smem_desc(a + kBytesA);
@@ -246,6 +262,98 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     }
     if (sh.abort) atomicCAS(status + kStatusCopyTimeout, 0, 1);
   } else if (run && warp >= 2) {
+   if constexpr (kGrad) {
+    // --------------------------- epilogue, gradient ---------------------------
+    // Thread = row, as below.  Per row the record of the coefficient kernel gives
+    //   k2 = (c + beta) * log2(e) + log2(scale),   y[v] = 2^(logit[v] * log2(e) + k2)
+    // (the formula of gradient16_kernel, gradient.cu), the two columns that carry a
+    // second term are multiplied by 1 - exp(sub - beta), and the row's part of the
+    // chunk is rounded to bfloat16 and stored; the two warps of a quarter take the
+    // even / the odd chunks and never meet.
+    const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;
+    const int r_in_tile = quarter * 32 + lane;
+    const float scale_all = ga.d_scale ? ga.scale_host * __ldg(ga.d_scale) : ga.scale_host;
+    const bool fold = scale_all > 0.f && scale_all < 3.0e38f;
+    const float mul = fold ? 1.f : scale_all;
+    const float k_scale = fold ? __log2f(scale_all) : 0.f;
+    uint32_t acc_it = 0;
+    for (int64_t tile = blockIdx.x; tile < row_tiles && !sh.abort; tile += gridDim.x) {
+      const int64_t row = tile * kTileM + r_in_tile;
+      const bool live = row < rows;
+      bool zero_row = true;
+      float k2 = 0.f, f_b = 1.f, f_t = 1.f;
+      int tgt = -1;
+      if (live) {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(ga.coef + row));
+        const int2 ids = __ldg(reinterpret_cast<const int2 *>(ga.coef + row) + 2);
+        zero_row = ids.x == kTgtZeroRow;
+        k2 = (a.x + a.y) * kLog2e + k_scale;
+        const bool reachable = a.y > neg_inf<float>();  // else every term of the row is 0
+        f_b = reachable ? 1.f - ex2_approx((a.z - a.y) * kLog2e) : 1.f;
+        f_t = reachable ? 1.f - ex2_approx((a.w - a.y) * kLog2e) : 1.f;
+        tgt = ids.x >= 0 ? ids.x : -1;
+      }
+      uint32_t *mine = out_s + (warp - 2) * 32 * kOutPitch;
+      for (int ct = 0; ct < col_tiles && !sh.abort; ++ct, ++acc_it) {
+        const int buf = acc_it & 1;
+        if (!mbar_wait(&sh.acc_full[buf], (acc_it >> 1) & 1, &sh.abort)) { sh.abort = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kTileN);
+#pragma unroll 1
+        for (int c = part; c < kTileN / 32; c += 2) {
+          const int col0 = ct * kTileN + c * 32;
+          if (col0 >= V) break;  // only padding columns from here on (warp-uniform)
+          float x[32];
+          tmem_load_32(taddr + (uint32_t)(c * 32), x);
+          if (live) {  // the collective load above is executed by every lane; the rest is per row
+            const float4 *bs = reinterpret_cast<const float4 *>(bias_s + col0);  // broadcast loads
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 bv = bs[i];
+              x[4 * i + 0] += bv.x; x[4 * i + 1] += bv.y; x[4 * i + 2] += bv.z; x[4 * i + 3] += bv.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = zero_row ? 0.f : mul * ex2_approx(fmaf(x[i], kLog2e, k2));
+            if ((unsigned)(blank - col0) < 32u) {  // warp-uniform
+              const int bi = blank - col0;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) x[i] = (i == bi) ? x[i] * f_b : x[i];
+            }
+            if ((unsigned)(tgt - col0) < 32u) {  // per row: one chunk in sixteen
+              const int ti = tgt - col0;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) x[i] = (i == ti) ? x[i] * f_t : x[i];
+            }
+            // round to bfloat16 pairs and leave the row's 16 words in the warp's staging tile
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              mine[lane * kOutPitch + j] = Pair16<__nv_bfloat16>::round(x[2 * j], x[2 * j + 1]);
+          }
+          __syncwarp();
+          // Row-contiguous stores: a store instruction covers the 64 bytes of this chunk
+          // in two rows (lanes 0-15 / 16-31), i.e. 4-6 sectors, where a thread-per-row
+          // store touches 32 (measured with 8-byte stores per row: 0.30 of the tensor peak).
+          // V is even (the launcher checks V % 4 == 0): a word is inside the row or outside.
+          {
+            const int word = lane & 15;
+            const bool col_ok = col0 + 2 * word < V;
+#pragma unroll 4
+            for (int r2 = 0; r2 < 16; ++r2) {
+              const int rr = 2 * r2 + (lane >> 4);
+              const int64_t orow = tile * kTileM + quarter * 32 + rr;
+              if (col_ok && orow < rows)
+                reinterpret_cast<uint32_t *>(ga.grad + orow * (int64_t)V + col0)[word] = mine[rr * kOutPitch + word];
+            }
+          }
+          __syncwarp();  // the tile is rewritten by the next chunk
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(&sh.acc_empty[buf]);
+      }
+    }
+    if (sh.abort && lane == 0) atomicCAS(status + kStatusCopyTimeout, 0, 1);
+   } else {
     // -------------------------------- epilogue --------------------------------
     // TMEM lanes 32*(warp % 4) .. +31 are the ones a warp may read; the two warps of
     // a quarter take the even / the odd 32-column chunks.
@@ -336,14 +444,51 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       asm volatile("bar.sync 2, %0;" ::"r"(32 * kEpilogueWarps) : "memory");  // half[] may be overwritten again
     }
     if (sh.abort && lane == 0) atomicCAS(status + kStatusCopyTimeout, 0, 1);
+   }
   }
   // Everybody meets here, whatever happened; then tensor memory goes back.
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  if (run && threadIdx.x == 0) trace_end(status, kStageLogprob);
+  if (run && threadIdx.x == 0) trace_end(status, kGrad ? kStageGradient : kStageLogprob);
   if (warp == 1)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemColumns) : "memory");
+  if (kGrad && !run) {
+    // the forward half refused its inputs: the gradient is all zeros (the loss is NaN
+    // and the failure is reported by the forward call's verdict)
+    uint32_t *g = reinterpret_cast<uint32_t *>(ga.grad);
+    const int64_t words = rows * (int64_t)V / 2;
+    for (int64_t i = (int64_t)blockIdx.x * kFusedThreads + threadIdx.x; i < words; i += (int64_t)gridDim.x * kFusedThreads)
+      g[i] = 0u;
+  }
+}
+
+__global__ void __launch_bounds__(kFusedThreads, 1)
+linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                      const float *__restrict__ bias, const int32_t *__restrict__ targets,
+                      const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
+                      const int64_t *__restrict__ split, const int64_t *__restrict__ cell_split,
+                      int32_t *__restrict__ status, int N, int64_t rows, int D, int V, int max_u,
+                      int blank, float *__restrict__ den, float *__restrict__ lp) {
+  linear_body<false>(map_x, map_w, bias, targets, Tl, Ul, split, cell_split, status, N, rows, D, V, max_u,
+                     blank, den, lp, GradArgs{nullptr, nullptr, nullptr, 1.f});
+}
+
+// The gradient of -sum(scores) with respect to the logits, times `scale`, in
+// bfloat16, from the joiner's operands: the 128-row logits tile is recomputed on
+// the tensor cores exactly as in linear_logprob_kernel (same copies, same MMAs,
+// same accumulators) and the epilogue applies the formula of the streaming
+// gradient pass (exp(logit + c + beta) minus the special terms on at most two
+// columns, optimized_transducer/csrc/kernels.cu:522-779 of the reference) with the
+// per-row records the coefficient kernel left in the workspace.  The logits are
+// never stored, in the forward half or here; what is stored is the gradient tile.
+__global__ void __launch_bounds__(kFusedThreads, 1)
+linear_gradient_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                       const float *__restrict__ bias, int32_t *__restrict__ status, int64_t rows, int D,
+                       int V, int blank, const CoefA<float> *__restrict__ coef,
+                       __nv_bfloat16 *__restrict__ grad, const float *__restrict__ d_scale, float scale_host) {
+  linear_body<true>(map_x, map_w, bias, nullptr, nullptr, nullptr, nullptr, nullptr, status, 0, rows, D, V, 0,
+                    blank, nullptr, nullptr, GradArgs{coef, grad, d_scale, scale_host});
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -407,6 +552,31 @@ cudaError_t launch_linear_logprob(const Problem &p, const void *x, const void *w
                  reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
                  reinterpret_cast<int32_t *>(p.ws + p.lay.status), p.N, p.rows, D, p.V, p.max_u, p.blank,
                  reinterpret_cast<float *>(p.ws + p.lay.den), reinterpret_cast<float *>(p.ws + p.lay.lp));
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+// The gradient with respect to the logits from the joiner's operands (see
+// linear_gradient_kernel).  V must be a multiple of 4 and grad 8-byte aligned.
+cudaError_t launch_linear_gradient(const Problem &p, const void *x, const void *w, const float *bias,
+                                   int D, void *grad, const float *d_scale, float scale_host,
+                                   cudaStream_t s) {
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, x, (uint64_t)p.rows, (uint64_t)D, kTileM) ||
+      !make_map(&map_w, w, (uint64_t)p.V, (uint64_t)D, kTileN))
+    return cudaErrorNotSupported;
+  if (p.V > kMaxBiasColumns || p.V % 4 != 0) return cudaErrorNotSupported;
+  const int padded = ((p.V + kTileN - 1) / kTileN) * kTileN;
+  const size_t smem = (size_t)kRingGrad * kStageBytes + 1024 + (size_t)padded * sizeof(float) + kOutBytes;
+  static SmemGrant grant;
+  cudaError_t e = grant.ensure(linear_gradient_kernel, smem);
+  if (e != cudaSuccess) return e;
+  const int64_t row_tiles = (p.rows + kTileM - 1) / kTileM;
+  const int sms = sm_count();
+  const unsigned grid = (unsigned)(row_tiles < sms ? row_tiles : sms);
+  e = launch_pdl(linear_gradient_kernel, grid, (unsigned)kFusedThreads, smem, s, map_x, map_w, bias,
+                 reinterpret_cast<int32_t *>(p.ws + p.lay.status), p.rows, D, p.V, p.blank,
+                 reinterpret_cast<const CoefA<float> *>(p.ws + p.lay.coef),
+                 static_cast<__nv_bfloat16 *>(grad), d_scale, scale_host);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 

@@ -62,7 +62,7 @@ from . import _lib
 __all__ = ["transducer_loss", "TransducerLoss", "TransducerLossFunction",
            "compute_transducer_loss", "stage_outputs", "transducer_loss_per_utterance",
            "PerUtteranceLossFunction", "check_inputs", "joiner_scores",
-           "transducer_loss_and_grad", "group_cuts"]
+           "transducer_loss_and_grad", "group_cuts", "joiner_loss", "JoinerLossFunction"]
 
 
 # Diagnostic: with OT_TRACE=1 and a list set here (collect_traces), every
@@ -616,6 +616,112 @@ def joiner_scores(joiner_in, weight, bias, targets, logit_lengths, target_length
     cell = view.cell_index()
     return {"scores": scores, "den": view.stage("den").clone(), "lp": view.stage("lp").view(-1, 2)[cell],
             "alpha": view.stage("alpha")[cell], "beta": view.stage("beta")[cell]}
+
+
+class JoinerLossFunction(torch.autograd.Function):
+    """Transducer loss straight from the joiner's last projection, forward AND
+    backward, without the (rows, V) logits: see :func:`joiner_loss`."""
+
+    @staticmethod
+    def forward(ctx, joiner_in, weight, bias, targets, logit_lengths, target_lengths, blank, reduction):
+        assert reduction in ("mean", "sum")
+        x, w = joiner_in.detach(), weight.detach()
+        b = bias.detach() if bias is not None else None
+        rows, d = x.shape
+        v = w.size(0)
+        n, max_u = int(logit_lengths.size(0)), int(targets.size(1))
+        lib = _lib.load()
+        flags = (_CHECK_FLAG[_check_mode()] | (_lib.FAST_MATH if _fast_math(False) else 0)
+                 | (_lib.LINEAR_DOMAIN if _linear_domain() else 0))
+        if os.environ.get("OT_TRACE", "0") == "1":
+            flags |= _lib.TRACE
+        lay = _layout(n, rows, max_u, 0)
+        dev = x.device
+        ws = torch.empty(int(lay.total_bytes), dtype=torch.uint8, device=dev)
+        scores = torch.empty(n, dtype=torch.float32, device=dev)
+        loss = torch.empty((), dtype=torch.float32, device=dev)
+        scale = (1.0 / n) if reduction == "mean" else 1.0
+        with _on_device(dev.index):
+            rc = lib.ot_b200_forward_linear(
+                x.data_ptr(), w.data_ptr(), b.data_ptr() if b is not None else None,
+                targets.data_ptr() if max_u else None, logit_lengths.data_ptr(), target_lengths.data_ptr(),
+                n, rows, d, v, max_u, int(blank), flags, ws.data_ptr(), int(lay.total_bytes),
+                scores.data_ptr(), loss.data_ptr(), scale, torch.cuda.current_stream(dev.index).cuda_stream)
+        if rc:
+            _lib.check(rc)
+        ctx.save_for_backward(x, w, b if b is not None else torch.empty(0, device=dev))
+        ctx.meta = (n, rows, d, v, max_u, int(blank), flags & ~_lib.CHECK_INPUTS, ws, int(lay.total_bytes), scale,
+                    b is not None, int(lay.status_off))
+        return loss
+
+    @staticmethod
+    def backward(ctx, loss_grad):
+        x, w, b = ctx.saved_tensors
+        n, rows, d, v, max_u, blank, flags, ws, ws_bytes, scale, has_bias, status_off = ctx.meta
+        lib = _lib.load()
+        dev = x.device
+        g = torch.empty((rows, v), dtype=torch.bfloat16, device=dev)  # the gradient tile the contractions read
+        up = loss_grad.detach().to(device=dev, dtype=torch.float32).contiguous()
+        with _on_device(dev.index):
+            rc = lib.ot_b200_backward_linear(
+                x.data_ptr(), w.data_ptr(), b.data_ptr() if has_bias else None, n, rows, d, v, max_u, blank,
+                flags, ws.data_ptr(), ws_bytes, g.data_ptr(), up.data_ptr(), scale,
+                torch.cuda.current_stream(dev.index).cuda_stream)
+        if rc:
+            _lib.check(rc)
+        if trace_log is not None:  # diagnostic (OT_TRACE=1): the stage timeline of this loss
+            trace_log.append(ws[status_off + 64:status_off + 64 + 320].view(torch.int64).clone())
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = g @ w                      # (rows, V) x (V, D)
+        if ctx.needs_input_grad[1]:
+            gw = g.t() @ x                  # (V, rows) x (rows, D)
+        if has_bias and ctx.needs_input_grad[2]:
+            gb = g.sum(0, dtype=torch.float32)
+        return gx, gw, gb, None, None, None, None, None
+
+
+def joiner_loss(joiner_in, weight, bias, targets, logit_lengths, target_lengths, blank,
+                reduction="mean"):
+    """The transducer loss of ``logits = joiner_in @ weight.T + bias`` with
+    gradients for ``joiner_in``, ``weight`` and ``bias``, WITHOUT the (rows, V)
+    logits in either direction.  Forward: :func:`joiner_scores` (projection,
+    logsumexp and gather in one tensor-core kernel).  Backward: the library
+    recomputes the logits tile by tile on the tensor cores and writes the gradient
+    with respect to the logits in bfloat16 (``ot_b200_backward_linear``); the three
+    contractions with it (``G @ weight``, ``G.T @ joiner_in``, column sums) are
+    PyTorch matmuls.  What is saved against the reference's path: the float
+    logits (4 V bytes per row, written by the projection, read by the loss,
+    overwritten by its gradient) never exist; the only (rows, V) tensor is the
+    bfloat16 gradient, alive during ``backward`` only.
+
+    ``joiner_in`` (rows, D) and ``weight`` (V, D) bfloat16, ``bias`` (V,) float32 or
+    None; D a multiple of 8, V a multiple of 4; standard transducer; ``reduction``
+    "mean" or "sum".  The gradient with respect to the logits is rounded to
+    bfloat16 (2^-9 relative), like the activations around it."""
+    who = "joiner_loss"
+    if joiner_in.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise RuntimeError(f"{who}: joiner_in and weight must be bfloat16")
+    if joiner_in.dim() != 2 or weight.dim() != 2 or joiner_in.size(1) != weight.size(1):
+        raise RuntimeError(f"{who}: expected joiner_in (rows, D) and weight (V, D)")
+    if not (joiner_in.is_cuda and joiner_in.is_contiguous() and weight.is_contiguous()
+            and weight.device == joiner_in.device):
+        raise RuntimeError(f"{who}: contiguous CUDA tensors on one device are required (sm_100a kernels, no CPU path)")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != weight.size(0)
+                             or bias.device != joiner_in.device or not bias.is_contiguous()):
+        raise RuntimeError(f"{who}: bias must be a contiguous float32 tensor of V entries")
+    if joiner_in.size(1) % 8 != 0 or weight.size(0) % 4 != 0:
+        raise RuntimeError(f"{who}: D must be a multiple of 8 and V a multiple of 4, got D={joiner_in.size(1)}, "
+                           f"V={weight.size(0)}")
+    for name, t in (("targets", targets), ("logit_lengths", logit_lengths), ("target_lengths", target_lengths)):
+        if t.dtype != torch.int32 or not t.is_contiguous() or t.device != joiner_in.device:
+            raise RuntimeError(f"{who}: expected {name} to be a contiguous int32 tensor on {joiner_in.device}")
+    if targets.dim() != 2 or logit_lengths.dim() != 1 or logit_lengths.shape != target_lengths.shape \
+            or targets.size(0) != logit_lengths.size(0) or not (0 <= blank < weight.size(0)) \
+            or joiner_in.size(0) == 0:
+        raise RuntimeError(f"{who}: inconsistent argument shapes, or blank outside [0, V)")
+    return JoinerLossFunction.apply(joiner_in, weight, bias, targets, logit_lengths, target_lengths, blank,
+                                    reduction)
 
 
 class TransducerLossFunction(torch.autograd.Function):

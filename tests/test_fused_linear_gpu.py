@@ -72,3 +72,84 @@ def test_bad_lengths_are_reported_not_followed():
         ot.joiner_scores(x.to(DEV), w.to(DEV), None, torch.from_numpy(tg).to(DEV),
                          torch.from_numpy(Tb).to(DEV), torch.from_numpy(U).to(DEV), 0)
     torch.cuda.synchronize()
+
+
+# ---------------------------------------------------------------------------
+# forward + backward without logits: joiner_loss
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", [
+    # seed, N, T range, U range, D, V, bias, reduction, upstream factor
+    (11, 3, (5, 12), (2, 6), 64, 40, False, "sum", 1.0),     # one column tile, a partial row tile
+    (12, 4, (20, 40), (5, 12), 512, 500, True, "mean", 3.0), # the benchmark's shape of operands
+    (13, 2, (30, 50), (3, 9), 200, 1028, True, "sum", 0.5),  # five column tiles, the last one ragged
+])
+def test_joiner_loss_gradients_against_the_materialised_path(shape):
+    """d loss / d (joiner_in, weight, bias) of joiner_loss against autograd through
+    float32 logits = x @ W^T + b and transducer_loss on them.  The library writes
+    the gradient with respect to the logits in bfloat16, so the three contractions
+    see it rounded to 2^-9 relative: each result is held to 1 % of its largest
+    entry (measured: a few 1e-3), the loss itself to 2e-5."""
+    seed, n, tr, ur, d, v, bias, reduction, factor = shape
+    x, w, b, tg, T, U, _ = _case(seed, n, tr, ur, d, v, bias)
+    dt, dT, dU = (torch.from_numpy(a).to(DEV) for a in (tg, T, U))
+    xa = x.to(DEV).requires_grad_(True)
+    wa = w.to(DEV).requires_grad_(True)
+    ba = b.to(DEV).requires_grad_(True) if b is not None else None
+    loss = ot.joiner_loss(xa, wa, ba, dt, dT, dU, 0, reduction=reduction)
+    (loss * factor).backward()
+    xr = x.to(DEV).float().requires_grad_(True)
+    wr = w.to(DEV).float().requires_grad_(True)
+    br = b.to(DEV).clone().requires_grad_(True) if b is not None else None
+    logits = xr @ wr.T + (br if br is not None else 0)
+    want = ot.transducer_loss(logits.contiguous(), dt, dT, dU, 0, False, reduction=reduction)
+    (want * factor).backward()
+    torch.cuda.synchronize()
+    ot.check_inputs(DEV)
+    assert abs(loss.item() - want.item()) <= 2e-5 * abs(want.item())
+    pairs = [("joiner_in", xa.grad, xr.grad), ("weight", wa.grad, wr.grad)]
+    if b is not None:
+        pairs.append(("bias", ba.grad, br.grad))
+    for name, got, ref in pairs:
+        assert got.shape == ref.shape, name
+        err = (got.float() - ref).abs().max().item()
+        top = ref.abs().max().item()
+        assert err <= 1e-2 * top, (name, err, top)
+
+
+def test_gradient_with_respect_to_the_logits_entry_by_entry():
+    """With W = identity (D = V) the logits ARE the rows of joiner_in and
+    d loss / d joiner_in is the library's bfloat16 gradient tile itself: every entry
+    against the float64 oracle gradient on those logits, to the rounding of the
+    storage type (2^-8 relative) plus 2e-5."""
+    rng = np.random.default_rng(21)
+    n, v = 3, 64
+    T = rng.integers(6, 14, n).astype(np.int32)
+    U = rng.integers(2, 6, n).astype(np.int32)
+    rows = int(splits(T, U)[-1])
+    x = torch.from_numpy((rng.standard_normal((rows, v)) * 2).astype(np.float32)).to(torch.bfloat16)
+    w = torch.eye(v, dtype=torch.bfloat16)
+    tg = rng.integers(1, v, (n, int(U.max()))).astype(np.int32)
+    ref = O.oracle_loss(x.double().numpy(), tg, T, U, 0)
+    dt, dT, dU = (torch.from_numpy(a).to(DEV) for a in (tg, T, U))
+    xa = x.to(DEV).requires_grad_(True)
+    loss = ot.joiner_loss(xa, w.to(DEV), None, dt, dT, dU, 0, reduction="sum")
+    loss.backward()
+    torch.cuda.synchronize()
+    want = -ref["scores"].sum()
+    assert abs(loss.item() - want) <= 1e-5 * abs(want)
+    g = xa.grad.double().cpu().numpy()
+    assert np.all(np.abs(g - ref["grad"]) <= 2.0 ** -8 * np.abs(ref["grad"]) + 2e-5)
+
+
+def test_joiner_loss_with_bad_lengths_gives_zero_gradients(monkeypatch):
+    monkeypatch.setenv("OT_CHECKS", "1")
+    x, w, b, tg, T, U, _ = _case(15, 3, (5, 9), (2, 4), 64, 20, False)
+    Tb = T.copy(); Tb[1] += 1
+    xa = x.to(DEV).requires_grad_(True)
+    wa = w.to(DEV).requires_grad_(True)
+    loss = ot.joiner_loss(xa, wa, None, torch.from_numpy(tg).to(DEV), torch.from_numpy(Tb).to(DEV),
+                          torch.from_numpy(U).to(DEV), 0)
+    assert torch.isnan(loss).item()
+    with pytest.raises(RuntimeError, match="an earlier call on this device"):
+        loss.backward()
+    torch.cuda.synchronize()
