@@ -48,7 +48,7 @@ constexpr int kBlockK = 64;     // bfloat16 elements per K block = one 128-byte 
 constexpr int kMmaK = 16;       // K of one tcgen05.mma for 16-bit operands
 constexpr int kRing = 4;        // shared-memory stages of the forward kernel
 constexpr int kRingGrad = 3;    // ... of the gradient kernel, whose epilogue needs a staging buffer too
-constexpr int kOutPitch = 17;   // words per row of a warp's 32 x 16-word output staging tile (conflict-free)
+constexpr int kOutPitch = 18;   // words per row of a warp's 32 x 16-word output staging tile (8-byte aligned rows)
 constexpr int kEpilogueWarps = 8;
 constexpr int kFusedThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t kOutBytes = kEpilogueWarps * 32 * kOutPitch * 4;
@@ -129,6 +129,31 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, float (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// The same load without the wait, and the wait as a statement that "produces" the
+// registers, so that nothing that reads them can be scheduled above it.
+__device__ __forceinline__ void tmem_load_32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_load_32_wait(uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+        "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+        "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+        "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :
+      : "memory");
 }
 
 struct FusedShared {
@@ -300,56 +325,83 @@ linear_body(const CUtensorMap &map_x, const CUtensorMap &map_w,
         if (!mbar_wait(&sh.acc_full[buf], (acc_it >> 1) & 1, &sh.abort)) { sh.abort = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kTileN);
-#pragma unroll 1
-        for (int c = part; c < kTileN / 32; c += 2) {
+        // The warp's chunks of this accumulator (c = part, part + 2, ...), the load of the
+        // next one in flight while the current one is worked on; the accumulator goes
+        // back to the MMA warp as soon as the last load has landed, before the stores.
+        uint32_t rr[2][32];
+        bool arrived = false;
+        if (ct * kTileN + part * 32 < V) tmem_load_32_issue(taddr + (uint32_t)(part * 32), rr[0]);
+#pragma unroll
+        for (int k = 0; k < kTileN / 64; ++k) {
+          const int c = part + 2 * k;
           const int col0 = ct * kTileN + c * 32;
-          if (col0 >= V) break;  // only padding columns from here on (warp-uniform)
-          float x[32];
-          tmem_load_32(taddr + (uint32_t)(c * 32), x);
-          if (live) {  // the collective load above is executed by every lane; the rest is per row
-            const float4 *bs = reinterpret_cast<const float4 *>(bias_s + col0);  // broadcast loads
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float4 bv = bs[i];
-              x[4 * i + 0] += bv.x; x[4 * i + 1] += bv.y; x[4 * i + 2] += bv.z; x[4 * i + 3] += bv.w;
+          if (col0 < V) {  // warp-uniform
+            uint32_t (&cur)[32] = rr[k & 1];
+            tmem_load_32_wait(cur);
+            if (k + 1 < kTileN / 64 && col0 + 64 < V) {
+              tmem_load_32_issue(taddr + (uint32_t)((c + 2) * 32), rr[(k + 1) & 1]);
+            } else {
+              asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+              mbar_arrive(&sh.acc_empty[buf]);
+              arrived = true;
             }
+            if (live) {  // the collective loads are executed by every lane; the rest is per row
+              float x[32];
+              const float4 *bs = reinterpret_cast<const float4 *>(bias_s + col0);  // broadcast loads
 #pragma unroll
-            for (int i = 0; i < 32; ++i) x[i] = zero_row ? 0.f : mul * ex2_approx(fmaf(x[i], kLog2e, k2));
-            if ((unsigned)(blank - col0) < 32u) {  // warp-uniform
-              const int bi = blank - col0;
+              for (int i = 0; i < 8; ++i) {
+                const float4 bv = bs[i];
+                x[4 * i + 0] = __uint_as_float(cur[4 * i + 0]) + bv.x; x[4 * i + 1] = __uint_as_float(cur[4 * i + 1]) + bv.y;
+                x[4 * i + 2] = __uint_as_float(cur[4 * i + 2]) + bv.z; x[4 * i + 3] = __uint_as_float(cur[4 * i + 3]) + bv.w;
+              }
 #pragma unroll
-              for (int i = 0; i < 32; ++i) x[i] = (i == bi) ? x[i] * f_b : x[i];
+              for (int i = 0; i < 32; ++i) x[i] = zero_row ? 0.f : ex2_approx(fmaf(x[i], kLog2e, k2));
+              if (!fold) {  // uniform, rare: a scale that cannot move into the exponent
+#pragma unroll
+                for (int i = 0; i < 32; ++i) x[i] *= mul;
+              }
+              if ((unsigned)(blank - col0) < 32u) {  // warp-uniform
+                const int bi = blank - col0;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) x[i] = (i == bi) ? x[i] * f_b : x[i];
+              }
+              if ((unsigned)(tgt - col0) < 32u) {  // per row: one chunk in sixteen
+                const int ti = tgt - col0;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) x[i] = (i == ti) ? x[i] * f_t : x[i];
+              }
+              // round to bfloat16 pairs and leave the row's 16 words in the warp's staging tile
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint2 *>(mine + lane * kOutPitch + 2 * j) =
+                    make_uint2(Pair16<__nv_bfloat16>::round(x[4 * j], x[4 * j + 1]),
+                               Pair16<__nv_bfloat16>::round(x[4 * j + 2], x[4 * j + 3]));
             }
-            if ((unsigned)(tgt - col0) < 32u) {  // per row: one chunk in sixteen
-              const int ti = tgt - col0;
+            __syncwarp();
+            // Row-contiguous stores: a store instruction covers the 64 bytes of this chunk
+            // in four rows (eight lanes of 8 bytes each), i.e. 8-12 sectors, where a
+            // thread-per-row store touches 32 (measured with 8-byte stores per row: 0.30
+            // of the tensor peak).  V % 4 == 0 (the launcher checks): a group of four
+            // columns is inside the row or outside, and every row starts on 8 bytes.
+            {
+              const int pair = lane & 7;
+              const bool col_ok = col0 + 4 * pair < V;
 #pragma unroll
-              for (int i = 0; i < 32; ++i) x[i] = (i == ti) ? x[i] * f_t : x[i];
+              for (int r4 = 0; r4 < 8; ++r4) {
+                const int rw = 4 * r4 + (lane >> 3);
+                const int64_t orow = tile * kTileM + quarter * 32 + rw;
+                if (col_ok && orow < rows)
+                  reinterpret_cast<uint2 *>(ga.grad + orow * (int64_t)V + col0)[pair] =
+                      *reinterpret_cast<const uint2 *>(mine + rw * kOutPitch + 2 * pair);
+              }
             }
-            // round to bfloat16 pairs and leave the row's 16 words in the warp's staging tile
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              mine[lane * kOutPitch + j] = Pair16<__nv_bfloat16>::round(x[2 * j], x[2 * j + 1]);
+            __syncwarp();  // the tile is rewritten by the next chunk
           }
-          __syncwarp();
-          // Row-contiguous stores: a store instruction covers the 64 bytes of this chunk
-          // in two rows (lanes 0-15 / 16-31), i.e. 4-6 sectors, where a thread-per-row
-          // store touches 32 (measured with 8-byte stores per row: 0.30 of the tensor peak).
-          // V is even (the launcher checks V % 4 == 0): a word is inside the row or outside.
-          {
-            const int word = lane & 15;
-            const bool col_ok = col0 + 2 * word < V;
-#pragma unroll 4
-            for (int r2 = 0; r2 < 16; ++r2) {
-              const int rr = 2 * r2 + (lane >> 4);
-              const int64_t orow = tile * kTileM + quarter * 32 + rr;
-              if (col_ok && orow < rows)
-                reinterpret_cast<uint32_t *>(ga.grad + orow * (int64_t)V + col0)[word] = mine[rr * kOutPitch + word];
-            }
-          }
-          __syncwarp();  // the tile is rewritten by the next chunk
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(&sh.acc_empty[buf]);
+        if (!arrived) {  // this warp has no chunk in this column tile
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(&sh.acc_empty[buf]);
+        }
       }
     }
     if (sh.abort && lane == 0) atomicCAS(status + kStatusCopyTimeout, 0, 1);
