@@ -51,7 +51,9 @@ constexpr int kRingGrad = 3;    // ... of the gradient kernel, whose epilogue ne
 constexpr int kOutPitch = 18;   // words per row of a warp's 32 x 16-word output staging tile (8-byte aligned rows)
 constexpr int kEpilogueWarps = 8;
 constexpr int kFusedThreads = 64 + 32 * kEpilogueWarps;
-constexpr uint32_t kOutBytes = kEpilogueWarps * 32 * kOutPitch * 4;
+constexpr int kGradEpilogueWarps = 16;  // the gradient kernel: four warps per TMEM lane quarter
+constexpr int kGradThreads = 64 + 32 * kGradEpilogueWarps;
+constexpr uint32_t kOutBytes = kGradEpilogueWarps * 32 * kOutPitch * 4;
 constexpr int kMaxBiasColumns = 7680;  // bias staged in shared memory behind the ring: vocabularies up to this size
 constexpr uint32_t kBytesA = kTileM * kBlockK * 2;   // 16 KB
 constexpr uint32_t kBytesB = kTileN * kBlockK * 2;   // 32 KB
@@ -199,6 +201,8 @@ linear_body(const CUtensorMap &map_x, const CUtensorMap &map_w,
             int32_t *__restrict__ status, int N, int64_t rows, int D, int V, int max_u,
             int blank, float *__restrict__ den, float *__restrict__ lp, const GradArgs ga) {
   constexpr int R = kGrad ? kRingGrad : kRing;  // stages of the operand ring
+  constexpr int kEW = kGrad ? kGradEpilogueWarps : kEpilogueWarps;  // epilogue warps
+  constexpr int kThreadsHere = 64 + 32 * kEW;
   extern __shared__ __align__(1024) unsigned char ring_mem[];
   __shared__ FusedShared sh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -207,7 +211,7 @@ linear_body(const CUtensorMap &map_x, const CUtensorMap &map_w,
   // behind the ring: the bias of every column, padded with zeros to whole column tiles
   float *bias_s = reinterpret_cast<float *>(ring + (size_t)R * kStageBytes);
   const int padded_v = ((V + kTileN - 1) / kTileN) * kTileN;
-  for (int i = threadIdx.x; i < padded_v; i += kFusedThreads)
+  for (int i = threadIdx.x; i < padded_v; i += kThreadsHere)
     bias_s[i] = (bias != nullptr && i < V) ? __ldg(bias + i) : 0.f;
   // gradient kernel: behind the bias, per epilogue warp a 32 x 16-word tile through
   // which a chunk of the gradient is turned from "thread = row" into row-contiguous stores
@@ -217,7 +221,7 @@ linear_body(const CUtensorMap &map_x, const CUtensorMap &map_w,
   pdl_trigger();
   if (threadIdx.x == 0) {
     for (int i = 0; i < R; ++i) { mbar_init(&sh.full[i], 1); mbar_init(&sh.empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&sh.acc_full[i], 1); mbar_init(&sh.acc_empty[i], 32 * kEpilogueWarps); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&sh.acc_full[i], 1); mbar_init(&sh.acc_empty[i], 32 * kEW); }
     sh.abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -293,8 +297,8 @@ linear_body(const CUtensorMap &map_x, const CUtensorMap &map_w,
     //   k2 = (c + beta) * log2(e) + log2(scale),   y[v] = 2^(logit[v] * log2(e) + k2)
     // (the formula of gradient16_kernel, gradient.cu), the two columns that carry a
     // second term are multiplied by 1 - exp(sub - beta), and the row's part of the
-    // chunk is rounded to bfloat16 and stored; the two warps of a quarter take the
-    // even / the odd chunks and never meet.
+    // chunk is rounded to bfloat16 and stored; the four warps of a TMEM lane quarter
+    // take every fourth chunk each and never meet.
     const int quarter = warp & 3;
     const int part = (warp - 2) >> 2;
     const int r_in_tile = quarter * 32 + lane;
@@ -325,22 +329,20 @@ linear_body(const CUtensorMap &map_x, const CUtensorMap &map_w,
         if (!mbar_wait(&sh.acc_full[buf], (acc_it >> 1) & 1, &sh.abort)) { sh.abort = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kTileN);
-        // The warp's chunks of this accumulator (c = part, part + 2, ...), the load of the
-        // next one in flight while the current one is worked on; the accumulator goes
-        // back to the MMA warp as soon as the last load has landed, before the stores.
-        uint32_t rr[2][32];
+        // The warp's chunks of this accumulator (c = part, part + kParts, ...); the
+        // accumulator goes back to the MMA warp as soon as the warp's last load has
+        // landed, before that chunk is worked on and stored.
+        constexpr int kParts = kEW / 4;
+        uint32_t cur[32];
         bool arrived = false;
-        if (ct * kTileN + part * 32 < V) tmem_load_32_issue(taddr + (uint32_t)(part * 32), rr[0]);
 #pragma unroll
-        for (int k = 0; k < kTileN / 64; ++k) {
-          const int c = part + 2 * k;
+        for (int k = 0; k < kTileN / 32 / kParts; ++k) {
+          const int c = part + kParts * k;
           const int col0 = ct * kTileN + c * 32;
           if (col0 < V) {  // warp-uniform
-            uint32_t (&cur)[32] = rr[k & 1];
+            tmem_load_32_issue(taddr + (uint32_t)(c * 32), cur);
             tmem_load_32_wait(cur);
-            if (k + 1 < kTileN / 64 && col0 + 64 < V) {
-              tmem_load_32_issue(taddr + (uint32_t)((c + 2) * 32), rr[(k + 1) & 1]);
-            } else {
+            if (!(k + 1 < kTileN / 32 / kParts && col0 + 32 * kParts < V)) {
               asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
               mbar_arrive(&sh.acc_empty[buf]);
               arrived = true;
@@ -510,7 +512,7 @@ linear_body(const CUtensorMap &map_x, const CUtensorMap &map_w,
     // and the failure is reported by the forward call's verdict)
     uint32_t *g = reinterpret_cast<uint32_t *>(ga.grad);
     const int64_t words = rows * (int64_t)V / 2;
-    for (int64_t i = (int64_t)blockIdx.x * kFusedThreads + threadIdx.x; i < words; i += (int64_t)gridDim.x * kFusedThreads)
+    for (int64_t i = (int64_t)blockIdx.x * kThreadsHere + threadIdx.x; i < words; i += (int64_t)gridDim.x * kThreadsHere)
       g[i] = 0u;
   }
 }
@@ -534,7 +536,7 @@ linear_logprob_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 // columns, optimized_transducer/csrc/kernels.cu:522-779 of the reference) with the
 // per-row records the coefficient kernel left in the workspace.  The logits are
 // never stored, in the forward half or here; what is stored is the gradient tile.
-__global__ void __launch_bounds__(kFusedThreads, 1)
+__global__ void __launch_bounds__(kGradThreads, 1)
 linear_gradient_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                        const float *__restrict__ bias, int32_t *__restrict__ status, int64_t rows, int D,
                        int V, int blank, const CoefA<float> *__restrict__ coef,
@@ -625,7 +627,7 @@ cudaError_t launch_linear_gradient(const Problem &p, const void *x, const void *
   const int64_t row_tiles = (p.rows + kTileM - 1) / kTileM;
   const int sms = sm_count();
   const unsigned grid = (unsigned)(row_tiles < sms ? row_tiles : sms);
-  e = launch_pdl(linear_gradient_kernel, grid, (unsigned)kFusedThreads, smem, s, map_x, map_w, bias,
+  e = launch_pdl(linear_gradient_kernel, grid, (unsigned)kGradThreads, smem, s, map_x, map_w, bias,
                  reinterpret_cast<int32_t *>(p.ws + p.lay.status), p.rows, D, p.V, p.blank,
                  reinterpret_cast<const CoefA<float> *>(p.ws + p.lay.coef),
                  static_cast<__nv_bfloat16 *>(grad), d_scale, scale_host);
