@@ -1022,6 +1022,43 @@ def run_fused(args, w):
     jf_ms = statistics.median(ev3[it][0].elapsed_time(ev3[it][1]) for it in range(args.warmup, n_it))
     jb_ms = statistics.median(ev3[it][1].elapsed_time(ev3[it][2]) for it in range(args.warmup, n_it))
     g_us = statistics.median((int(t[9]) - int(t[8])) / 1e3 for t in (s_.cpu() for s_ in bspans[args.warmup:]))
+    # the same loss with the logits materialised in bfloat16 (projection by the library
+    # GEMM, the 16-bit transducer loss of this package, autograd through both): what
+    # joiner_loss is an alternative to
+    from optimized_transducer_b200.transducer_loss import _padded_columns
+
+    def materialised(wt_, bias_):
+        xm, wm, bm = (t.clone().requires_grad_(True) for t in (x, wt_, bias_))
+        evm = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_it)]
+        for it in range(n_it):
+            xm.grad = wm.grad = bm.grad = None
+            evm[it][0].record()
+            ml = ot.transducer_loss(torch.nn.functional.linear(xm, wm, bm.to(torch.bfloat16)), dtg, dT, dU, 0,
+                                    False, reduction="sum")
+            evm[it][1].record()
+            ml.backward()
+            evm[it][2].record()
+        torch.cuda.synchronize()
+        return {"forward_ms": statistics.median(evm[it][0].elapsed_time(evm[it][1]) for it in range(args.warmup, n_it)),
+                "backward_ms": statistics.median(evm[it][1].elapsed_time(evm[it][2]) for it in range(args.warmup, n_it)),
+                "loss": float(ml.item())}
+
+    mat = materialised(wt, bias)
+    mat["what"] = ("the same loss and gradients through torch.nn.functional.linear -> (rows, V) bfloat16 logits "
+                   "-> transducer_loss -> autograd (library GEMMs on both sides)")
+    vp = _padded_columns(w.v)
+    mat_padded = None
+    if vp != w.v:
+        # a model whose vocabulary is padded so that rows of logits are a multiple of 16
+        # bytes (zero weight rows, a bias of -1e30: the same loss): the library GEMMs of
+        # the materialised path stay on their tensor-core kernels
+        wp = torch.zeros((vp, d), dtype=wt.dtype, device=dev)
+        wp[:w.v] = wt
+        bp = torch.full((vp,), -1e30, dtype=torch.float32, device=dev)
+        bp[:w.v] = bias
+        mat_padded = materialised(wp, bp)
+        mat_padded["what"] = f"the same with the vocabulary padded from {w.v} to {vp} entries by the caller"
+    from optimized_transducer_b200.transducer_loss import _padded_columns
     flops = 2.0 * rows * d * w.v
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -1047,7 +1084,9 @@ def run_fused(args, w):
             "linear_gradient_kernel_us": g_us,
             "linear_gradient_kernel_tflops": flops / (g_us * 1e-6) / 1e12,
             "linear_gradient_kernel_frac_of_peak": flops / (g_us * 1e-6) / 1e12 / peak,
-            "gradient_bytes_written": rows * w.v * 2,
+            "gradient_bytes_written": rows * _padded_columns(w.v) * 2,
+            "materialised_bf16_logits": mat,
+            "materialised_bf16_logits_padded_vocabulary": mat_padded,
         },
         "gpu_launches": 4 * args.steps,
         "loss": float(out.item()),

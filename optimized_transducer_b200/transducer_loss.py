@@ -618,6 +618,33 @@ def joiner_scores(joiner_in, weight, bias, targets, logit_lengths, target_length
             "alpha": view.stage("alpha")[cell], "beta": view.stage("beta")[cell]}
 
 
+def _padded_columns(v):
+    """The number of columns the backward pass of :func:`joiner_loss` gives its
+    bfloat16 gradient tile: ``v`` when rows of ``v`` entries already are a multiple
+    of 16 bytes; else the next multiple of 64 when that adds at most 1/32, else
+    the next multiple of 8."""
+    if v % 8 == 0:
+        return v
+    v64 = -(-v // 64) * 64
+    return v64 if (v64 - v) * 32 <= v else -(-v // 8) * 8
+
+
+# The column sums of the gradient tile (the bias gradient) as a tensor-core
+# contraction with eight rows of ones, float32 out: measured 0.11 ms against
+# 0.21 ms for ``sum(0)`` on 686 128 x 512; for wide rows ``sum(0)`` is used.
+_COLUMN_SUMS_BY_MATMUL_MAX_V = 1024
+_ONES = {}
+
+
+def _ones_rows(rows, device):
+    key = (rows, device)
+    t = _ONES.get(key)
+    if t is None:
+        _ONES.clear()  # one batch shape at a time: 16 bytes per row
+        t = _ONES[key] = torch.ones((8, rows), dtype=torch.bfloat16, device=device)
+    return t
+
+
 class JoinerLossFunction(torch.autograd.Function):
     """Transducer loss straight from the joiner's last projection, forward AND
     backward, without the (rows, V) logits: see :func:`joiner_loss`."""
@@ -660,12 +687,29 @@ class JoinerLossFunction(torch.autograd.Function):
         n, rows, d, v, max_u, blank, flags, ws, ws_bytes, scale, has_bias, status_off = ctx.meta
         lib = _lib.load()
         dev = x.device
-        g = torch.empty((rows, v), dtype=torch.bfloat16, device=dev)  # the gradient tile the contractions read
+        # The gradient tile the contractions read has rows of 2 * V bytes.  When that is
+        # not a multiple of 16 (V = 500: 1000 bytes) the matmuls that read it fall off
+        # the library's tensor-core kernels (measured, rows = 686 128, D = 512:
+        # G @ W 1.40 ms and G.T @ X 1.15 ms with V = 500 against 0.33 ms each with the
+        # rows padded to 512 columns).  So the projection is widened for this pass:
+        # zero weight rows and a bias of -1e30 make the kernel write exact zeros into
+        # the padding columns, which then drop out of all three contractions.
+        vp = _padded_columns(v)
+        wk, bk = w, (b if has_bias else None)
+        if vp != v:
+            wk = torch.zeros((vp, d), dtype=w.dtype, device=dev)
+            wk[:v] = w
+            bk = torch.full((vp,), -1e30, dtype=torch.float32, device=dev)
+            if has_bias:
+                bk[:v] = b
+            else:
+                bk[:v] = 0
+        g = torch.empty((rows, vp), dtype=torch.bfloat16, device=dev)
         up = loss_grad.detach().to(device=dev, dtype=torch.float32).contiguous()
         with _on_device(dev.index):
             rc = lib.ot_b200_backward_linear(
-                x.data_ptr(), w.data_ptr(), b.data_ptr() if has_bias else None, n, rows, d, v, max_u, blank,
-                flags, ws.data_ptr(), ws_bytes, g.data_ptr(), up.data_ptr(), scale,
+                x.data_ptr(), wk.data_ptr(), bk.data_ptr() if bk is not None else None, n, rows, d, vp, max_u,
+                blank, flags, ws.data_ptr(), ws_bytes, g.data_ptr(), up.data_ptr(), scale,
                 torch.cuda.current_stream(dev.index).cuda_stream)
         if rc:
             _lib.check(rc)
@@ -673,11 +717,17 @@ class JoinerLossFunction(torch.autograd.Function):
             trace_log.append(ws[status_off + 64:status_off + 64 + 320].view(torch.int64).clone())
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
-            gx = g @ w                      # (rows, V) x (V, D)
+            gx = g @ wk                     # (rows, V') x (V', D)
         if ctx.needs_input_grad[1]:
-            gw = g.t() @ x                  # (V, rows) x (rows, D)
+            # float32 out of the library's reduction over the rows, rounded once (a
+            # bfloat16 output of this contraction measured 8e-3 of its largest entry
+            # off the float64 result, the float32 one 1e-4, at the same speed)
+            gw = torch.mm(g.t(), x, out_dtype=torch.float32)[:v].to(w.dtype)
         if has_bias and ctx.needs_input_grad[2]:
-            gb = g.sum(0, dtype=torch.float32)
+            if vp <= _COLUMN_SUMS_BY_MATMUL_MAX_V:
+                gb = torch.mm(_ones_rows(rows, dev), g, out_dtype=torch.float32)[0, :v].contiguous()
+            else:
+                gb = g.sum(0, dtype=torch.float32)[:v].contiguous()
         return gx, gw, gb, None, None, None, None, None
 
 
@@ -690,7 +740,9 @@ def joiner_loss(joiner_in, weight, bias, targets, logit_lengths, target_lengths,
     recomputes the logits tile by tile on the tensor cores and writes the gradient
     with respect to the logits in bfloat16 (``ot_b200_backward_linear``); the three
     contractions with it (``G @ weight``, ``G.T @ joiner_in``, column sums) are
-    PyTorch matmuls.  What is saved against the reference's path: the float
+    PyTorch matmuls; for a V whose rows of bfloat16 are not a multiple of 16 bytes
+    the tile is given padding columns of exact zeros (see ``_padded_columns``),
+    because those matmuls are three to four times slower on unaligned rows.  What is saved against the reference's path: the float
     logits (4 V bytes per row, written by the projection, read by the loss,
     overwritten by its gradient) never exist; the only (rows, V) tensor is the
     bfloat16 gradient, alive during ``backward`` only.

@@ -82,6 +82,7 @@ def test_bad_lengths_are_reported_not_followed():
     (11, 3, (5, 12), (2, 6), 64, 40, False, "sum", 1.0),     # one column tile, a partial row tile
     (12, 4, (20, 40), (5, 12), 512, 500, True, "mean", 3.0), # the benchmark's shape of operands
     (13, 2, (30, 50), (3, 9), 200, 1028, True, "sum", 0.5),  # five column tiles, the last one ragged
+    (14, 3, (6, 12), (2, 5), 64, 36, False, "mean", 1.0),    # rows of 72 bytes, no bias: the padded gradient tile
 ])
 def test_joiner_loss_gradients_against_the_materialised_path(shape):
     """d loss / d (joiner_in, weight, bias) of joiner_loss against autograd through

@@ -104,3 +104,14 @@ def test_check_modes(monkeypatch):
     monkeypatch.delenv("OT_CHECKS")
     assert _check_mode() == "deferred"
     assert _CHECK_FLAG["deferred"] == _lib.REPORT_ERRORS and _CHECK_FLAG["strict"] == _lib.CHECK_INPUTS
+
+
+def test_gradient_tile_of_the_logits_free_backward_has_16_byte_rows():
+    """joiner_loss pads the bfloat16 gradient tile so that its rows are a multiple
+    of 16 bytes (the library contractions that read it need that to stay on the
+    tensor cores), to a multiple of 64 columns when that is nearly free."""
+    from optimized_transducer_b200.transducer_loss import _padded_columns
+    assert [_padded_columns(v) for v in (64, 500, 504, 5000, 20, 36, 1028)] == [64, 512, 504, 5000, 24, 40, 1032]
+    for v in range(4, 7681, 4):
+        vp = _padded_columns(v)
+        assert v <= vp <= 7680 and vp % 8 == 0 and vp - v < 64
