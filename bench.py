@@ -917,7 +917,7 @@ def run_ours(args, w):
 def run_pack(args, w):
     """Measurement of the packing helpers (callers' side of the packed layout) on
     the workload's shapes with D = 512 features: forward = one pass that writes
-    rows*D*4 bytes, backward = two summation passes that read them."""
+    rows*D*4 bytes, backward = both sums from one read of them (two reads for small batches)."""
     import torch
     from optimized_transducer_b200 import packing, synthetic
 
@@ -951,6 +951,9 @@ def run_pack(args, w):
     peak, peak_kind = measured_hbm_peak()
     f_ms, b_ms = statistics.median(fwd), statistics.median(bwd)
     bytes_out = rows * d * 4
+    # the library's own choice (pack.cu): one read needs U + 1 <= 128 and two device-fills of CTAs
+    two_reads = (os.environ.get("OT_B200_PACK_SUM") == "two" or int(U.max()) + 1 > 128
+                 or n_utt * ((d // 4 + 7) // 8) < 2 * torch.cuda.get_device_properties(dev).multi_processor_count)
     line = {
         "metric": "packed joiner-input elements (rows*D)/s, forward", "value": rows * d / (f_ms * 1e-3),
         "unit": "elements/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
@@ -960,9 +963,12 @@ def run_pack(args, w):
         "roofline": {"kernel": "pack_add_frames_kernel", "bound": "hbm", "achieved": bytes_out / (f_ms * 1e-3) / 1e9,
                      "peak": peak, "unit": "GB/s", "frac": bytes_out / (f_ms * 1e-3) / 1e9 / peak,
                      "peak_source": f"{peak_kind} copy bandwidth", "traffic": None},
-        "backward": {"ms": b_ms, "kernels": "pack_sum_kernel x2 (+ autograd's gradient copy)",
-                     "achieved_gbs": 2 * bytes_out / (b_ms * 1e-3) / 1e9},
-        "gpu_launches": 5 * args.steps,  # forward: prepare + add; backward: prepare + two sums
+        "backward": {"ms": b_ms,
+                     "kernels": "prepare + pack_sum_kernel x2, two reads of the gradient (OT_B200_PACK_SUM=two)"
+                     if two_reads else "prepare + pack_sum_slab_kernel: both sums from one read of the gradient",
+                     "achieved_gbs": (2 if two_reads else 1) * bytes_out / (b_ms * 1e-3) / 1e9,
+                     "frac_of_peak_one_read": bytes_out / (b_ms * 1e-3) / 1e9 / peak},
+        "gpu_launches": (5 if two_reads else 4) * args.steps,  # forward: prepare + add; backward: prepare + sums
     }
     print(json.dumps(line), flush=True)
 

@@ -13,6 +13,8 @@
 //   unpack_copy   padded[b,t,u]    = in[row(b,t,u)], 0 elsewhere    (packed -> padded)
 //   sum_over_u    genc[b,t] = sum_u g[row(b,t,u)],  0 for t >= T_b  (backward of pack_add)
 //   sum_over_t    gdec[b,u] = sum_t g[row(b,t,u)],  0 for u >  U_b
+//                 (both from one read of g where the batch is large enough:
+//                 pack_sum_slab_kernel)
 // The copies give one warp a packed row (16-byte loads when D % 4 == 0 and the
 // bases are aligned); a warp takes runs of 8 rows and walks (b, t, u)
 // incrementally.  pack_add writes by frames and the sums read rows a fixed stride
@@ -347,6 +349,149 @@ pack_sum_kernel(const T *__restrict__ g, T *__restrict__ out, const int32_t *__r
   }
 }
 
+// Both sums of the backward pass from ONE read of the gradient.  A CTA takes one
+// utterance and one piece of LANES vectors (128 bytes) of every packed row of it, all
+// frames: thread = (row lane rl, vector dv), RL = THREADS / LANES packed rows side by
+// side.  Consecutive rows of a frame are consecutive u, so thread (rl, dv) meets
+// u = rl, rl + RL, ... (at most KU of them: U + 1 <= RL * KU) in every frame:
+//   sum over t: one accumulator per u of the thread, in registers, stored at the end;
+//               nobody else has that (u, vector);
+//   sum over u: the thread's KU values of a frame, then the row lanes of its warp by
+//               shuffles, then one entry per warp and frame in shared memory; the
+//               warps meet once per round of FR frames (two buffers, one barrier per
+//               round), in a fixed order.
+// All loads of a round (FR * KU vectors per thread) are issued before the first add.
+// Results do not depend on timing.  The outputs' padding (t >= T_b, u > U_b) is zeroed
+// by the CTA for its piece.
+// The CTAs of an utterance all take as long as the utterance has rows, and a CTA alone
+// streams only a few tens of GB/s, so the order matters at the end of the launch:
+// blockIdx.y is the utterance's RANK by rows, largest first (found by the CTA itself
+// from the lengths, for batches of up to THREADS utterances).
+constexpr int kSlabMaxU1 = 128;
+
+template <typename T, int VEC, int LANES, int THREADS, int KU, int FR, int BLOCKS>
+__global__ void __launch_bounds__(THREADS, BLOCKS)
+pack_sum_slab_kernel(const T *__restrict__ g, T *__restrict__ genc, T *__restrict__ gdec,
+                     const int32_t *__restrict__ Tl, const int32_t *__restrict__ Ul,
+                     const int64_t *__restrict__ split, const int32_t *__restrict__ status, int N,
+                     int D, int max_t, int max_u1) {
+  using VT = typename VecOf<T, VEC>::type;
+  using A = Acc<T, VEC>;
+  using Rt = typename Real<T>::type;
+  constexpr int RL = THREADS / LANES;
+  constexpr int kWarps = THREADS / kWarp;
+  static_assert(LANES <= kWarp && FR * LANES <= THREADS && RL * KU >= kSlabMaxU1, "layout");
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rl = tid / LANES, dv = tid % LANES;
+  int b = blockIdx.y;
+  if (status[0] == 0 && N <= THREADS) {
+    __shared__ int ranked;
+    if (tid < N) {
+      const int64_t mine = (int64_t)Tl[tid] * (Ul[tid] + 1);
+      int before = 0;
+      for (int j = 0; j < N; ++j) {
+        const int64_t other = (int64_t)Tl[j] * (Ul[j] + 1);
+        before += (other > mine || (other == mine && j < tid)) ? 1 : 0;
+      }
+      if (before == (int)blockIdx.y) ranked = tid;
+    }
+    __syncthreads();
+    b = ranked;
+  }
+  const int nvec = D / VEC;
+  const int vi = blockIdx.x * LANES + dv;  // this thread's vector of a row
+  const bool col = vi < nvec;
+  VT *oe = reinterpret_cast<VT *>(genc + (int64_t)b * max_t * D);
+  VT *od = reinterpret_cast<VT *>(gdec + (int64_t)b * max_u1 * D);
+  const auto pack = [](const A &a) {
+    VT z;
+    T *ze = reinterpret_cast<T *>(&z);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) ze[e] = from_real<T>(a.v[e]);
+    return z;
+  };
+  A zero;
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) zero.v[e] = (Rt)0;
+  if (status[0] != 0) {  // this CTA's piece of both outputs
+    A n;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) n.v[e] = (Rt)__int_as_float(0x7fc00000);
+    const VT nan = pack(n);
+    if (col) {
+      for (int t = rl; t < max_t; t += RL) oe[(int64_t)t * nvec + vi] = nan;
+      for (int u = rl; u < max_u1; u += RL) od[(int64_t)u * nvec + vi] = nan;
+    }
+    return;
+  }
+  __shared__ A red[2][kWarps][FR][LANES];
+  const int Tn = Tl[b], U1 = Ul[b] + 1;
+  const VT *base = reinterpret_cast<const VT *>(g) + (split[b] + rl) * nvec + vi;
+  const VT vzero = pack(zero);
+  A dec[KU];
+#pragma unroll
+  for (int k = 0; k < KU; ++k) dec[k] = zero;
+  int round = 0;
+  for (int f0 = 0; f0 < Tn; f0 += FR, ++round) {  // Tn is the CTA's: so are the barriers
+    VT v[FR][KU];
+#pragma unroll
+    for (int j = 0; j < FR; ++j)
+#pragma unroll
+      for (int k = 0; k < KU; ++k)
+        v[j][k] = (col && f0 + j < Tn && rl + k * RL < U1)
+                      ? __ldcs(base + ((int64_t)(f0 + j) * U1 + k * RL) * nvec) : vzero;
+    A(*mine)[FR][LANES] = red[round & 1];
+#pragma unroll
+    for (int j = 0; j < FR; ++j) {
+      A e = zero;
+#pragma unroll
+      for (int k = 0; k < KU; ++k) {
+        acc_add<T, VEC>(e, v[j][k]);
+        acc_add<T, VEC>(dec[k], v[j][k]);
+      }
+      // the row lanes of this warp that hold the same vector: lanes dv, dv + LANES, ...
+#pragma unroll
+      for (int o = LANES; o < kWarp; o <<= 1)
+#pragma unroll
+        for (int x = 0; x < VEC; ++x) e.v[x] += __shfl_xor_sync(kFull, e.v[x], o);
+      if (lane < LANES) mine[warp][j][lane] = e;
+    }
+    __syncthreads();
+    // A buffer is rewritten two rounds later, i.e. after the next barrier, which every
+    // reader of this round has passed by then.
+    if (tid < FR * LANES) {
+      const int j = tid / LANES, d = tid % LANES;
+      const int vo = blockIdx.x * LANES + d;
+      if (f0 + j < Tn && vo < nvec) {
+        A sum = mine[0][j][d];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) {
+          const A &o = mine[w][j][d];
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) sum.v[x] += o.v[x];
+        }
+        oe[(int64_t)(f0 + j) * nvec + vo] = pack(sum);
+      }
+    }
+  }
+  if (col) {
+#pragma unroll
+    for (int k = 0; k < KU; ++k) {
+      const int u = rl + k * RL;
+      if (u < U1) od[(int64_t)u * nvec + vi] = pack(dec[k]);
+    }
+    for (int t = Tn + rl; t < max_t; t += RL) oe[(int64_t)t * nvec + vi] = vzero;
+    for (int u = U1 + rl; u < max_u1; u += RL) od[(int64_t)u * nvec + vi] = vzero;
+  }
+}
+
+// OT_B200_PACK_SUM=two: the backward pass as two kernels that each read the gradient
+// (pack_sum_kernel) even where the one-read kernel applies; read at every call.
+bool two_pass_sums_forced() {
+  const char *v = getenv("OT_B200_PACK_SUM");
+  return v != nullptr && strcmp(v, "two") == 0;
+}
+
 int fail(int code, const char *msg) {
   set_last_error(msg);
   return code;
@@ -483,6 +628,33 @@ int ot_b200_pack_joiner_input_backward(const void *d_grad_out, const int32_t *d_
   const dim3 ge((unsigned)max_t, (unsigned)N), gd((unsigned)max_u1, (unsigned)N);
   const auto aligned = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool al = aligned(d_grad_out) && aligned(d_grad_encoder) && aligned(d_grad_decoder);
+  // The one-read kernel needs whole vectors, U + 1 <= 128 and enough CTAs (utterances
+  // x row pieces) to fill the device twice: a CTA alone streams only a few tens of
+  // GB/s, so a handful of long utterances is better served by the two kernels below,
+  // whose grids follow the frames and the columns.
+  const int sum_vec = (flags & OT_B200_FP64) ? 2 : 4;
+  const int sum_lanes = (flags & (OT_B200_BF16 | OT_B200_FP16)) ? 16 : 8;  // 128 bytes of a row
+  if (al && D % sum_vec == 0 && max_u1 <= kSlabMaxU1 && !two_pass_sums_forced()) {
+    const int pieces = (D / sum_vec + sum_lanes - 1) / sum_lanes;
+    if ((int64_t)N * pieces >= 2 * (int64_t)sm_count() && N <= 65535) {
+      const dim3 gs((unsigned)pieces, (unsigned)N);
+      // 256 threads: 32 rows side by side (512 threads, 64 rows and half the accumulators
+      // per thread, measured 0.43 against 0.32 ms on the benchmark's lengths with D = 512)
+#define OTB_PACK_SLAB(T, VEC, LANES, FR)                                                            \
+  pack_sum_slab_kernel<T, VEC, LANES, kThreads, kSlabMaxU1 * LANES / kThreads, FR, 2>               \
+      <<<gs, kThreads, 0, s>>>(static_cast<const T *>(d_grad_out), static_cast<T *>(d_grad_encoder), \
+                               static_cast<T *>(d_grad_decoder), d_logit_lengths, d_target_lengths, \
+                               split, status, N, D, max_t, max_u1)
+      if (flags & OT_B200_FP64) OTB_PACK_SLAB(double, 2, 8, 4);
+      else if (flags & OT_B200_BF16) OTB_PACK_SLAB(__nv_bfloat16, 4, 16, 2);
+      else if (flags & OT_B200_FP16) OTB_PACK_SLAB(__half, 4, 16, 2);
+      else OTB_PACK_SLAB(float, 4, 8, 4);
+#undef OTB_PACK_SLAB
+      const cudaError_t es = cudaGetLastError();
+      if (es != cudaSuccess) return fail(OT_B200_ERR_CUDA, cudaGetErrorString(es));
+      return OT_B200_OK;
+    }
+  }
 #define OTB_PACK_SUM(T, VEC)                                                                        \
   do {                                                                                              \
     pack_sum_kernel<T, VEC, true><<<ge, kThreads, 0, s>>>(                                          \

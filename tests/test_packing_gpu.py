@@ -159,6 +159,75 @@ def test_sixteen_bit_packing(d, dtype):
     assert torch.equal(packing.pack_padded(back, dT, dU), packed)
 
 
+@pytest.mark.parametrize("case", [
+    # dtype, D, N, T range, U range, extra padding of (max_t, max_u1)
+    ("float32", 512, 24, (1, 40), (0, 30), (2, 1)),     # 16 pieces of 128 bytes per row
+    ("float32", 520, 20, (3, 21), (0, 127), (0, 0)),    # a ragged 17th piece; U + 1 up to the kernel's 128
+    ("float64", 256, 20, (2, 35), (0, 40), (1, 3)),
+    ("bfloat16", 1024, 20, (2, 30), (0, 33), (3, 0)),   # pieces of 16 vectors of 4
+    ("float16", 1000, 20, (1, 30), (0, 20), (0, 2)),
+])
+def test_backward_of_the_joiner_packing_from_one_read(case, monkeypatch):
+    """Batches with enough (utterance, row piece) pairs to fill the device take both
+    sums of the backward pass from ONE read of the gradient (pack_sum_slab_kernel);
+    OT_B200_PACK_SUM=two keeps the two kernels that each read it.  Both against the
+    float64 oracle of the reference's recipe; padding (t >= T_b, u > U_b) is zero."""
+    dtype, d, n, tr, ur, (pad_t, pad_u) = case
+    tdt = getattr(torch, dtype)
+    rng, T, U = _lengths(31, n, tr, ur)
+    T[0], U[0] = tr[0], ur[0]
+    T[1], U[1] = tr[1], ur[1]
+    max_t, max_u1 = int(T.max()) + pad_t, int(U.max()) + 1 + pad_u
+    rows = int(splits(T, U)[-1])
+    g = torch.from_numpy(rng.standard_normal((rows, d)).astype(np.float32)).to(tdt)
+    genc, gdec = O.pack_joiner_backward_oracle(g.double().numpy(), T, U, max_t, max_u1)
+    dT, dU = torch.from_numpy(T).to(DEV), torch.from_numpy(U).to(DEV)
+    rel = {"float32": 2.0 ** -22, "float64": 2.0 ** -50, "bfloat16": 2.0 ** -8, "float16": 2.0 ** -11}[dtype]
+    floor = {"float32": 5e-5, "float64": 1e-12, "bfloat16": 1e-4, "float16": 1e-4}[dtype]
+    for mode in (None, "two"):
+        if mode is None:
+            monkeypatch.delenv("OT_B200_PACK_SUM", raising=False)
+        else:
+            monkeypatch.setenv("OT_B200_PACK_SUM", mode)
+        e = torch.zeros(n, max_t, d, dtype=tdt, device=DEV, requires_grad=True)
+        q = torch.zeros(n, max_u1, d, dtype=tdt, device=DEV, requires_grad=True)
+        packing.pack_joiner_input(e, q, dT, dU).backward(g.to(DEV))
+        torch.cuda.synchronize()
+        for name, got, ref in (("encoder", e.grad, genc), ("decoder", q.grad, gdec)):
+            got = got.double().cpu().numpy()
+            err = np.abs(got - ref)
+            assert np.all(err <= rel * np.abs(ref) + floor), (mode, name, float(err.max()))
+            assert np.all(got[ref == 0] == 0), (mode, name)  # the padding is exactly zero
+    ot.check_inputs(DEV)
+
+
+def test_one_read_backward_fills_nan_when_the_lengths_do_not_fit(monkeypatch):
+    """The same kernel with an utterance longer than the padded tensors: it must not
+    follow the lengths; every element of both gradients is NaN and the failure is
+    found by the next check."""
+    monkeypatch.setenv("OT_CHECKS", "1")
+    monkeypatch.delenv("OT_B200_PACK_SUM", raising=False)
+    rng, T, U = _lengths(32, 24, (4, 9), (1, 4))
+    max_t, max_u1, d = int(T.max()), int(U.max()) + 1, 512
+    lib = packing._lib.load()
+    Tbad = T.copy(); Tbad[5] = max_t + 1
+    rows = int(splits(Tbad, U)[-1])
+    g = torch.ones(rows, d, device=DEV)
+    genc = torch.zeros(24, max_t, d, device=DEV)
+    gdec = torch.zeros(24, max_u1, d, device=DEV)
+    dT, dU = torch.from_numpy(Tbad).to(DEV), torch.from_numpy(U).to(DEV)
+    ws = packing._workspace(24, g.device)
+    rc = lib.ot_b200_pack_joiner_input_backward(
+        g.data_ptr(), dT.data_ptr(), dU.data_ptr(), 24, rows, d, max_t, max_u1, packing._flags(g),
+        ws.data_ptr(), genc.data_ptr(), gdec.data_ptr(), packing._stream(g))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert bool(torch.isnan(genc).all()) and bool(torch.isnan(gdec).all())
+    with pytest.raises(RuntimeError, match="do not fit"):
+        ot.check_inputs(DEV, wait=False)
+    ot.check_inputs(DEV)
+
+
 @pytest.mark.parametrize("mode", ["1", "2"])
 def test_lengths_that_do_not_fit_are_reported_and_the_output_is_nan(mode, monkeypatch):
     """An utterance longer than the padded tensor: the kernels must not follow the
