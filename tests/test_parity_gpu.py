@@ -148,6 +148,75 @@ def test_float32_error_is_not_worse_than_the_references():
     assert np.max(np.abs(out["grad"] - ref32["grad"])) <= fp32_grad_floor(ref32["alpha"], ref32["beta"])
 
 
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_seeded_sweep_of_shapes_flags_and_entry_points(seed):
+    """Forty random configurations per seed: 1-10 utterances, T up to 1/3/20/80/300,
+    U up to 0/1/5/40/130, twelve vocabulary sizes on both sides of the kernels' shape
+    limits, any blank, targets that may equal the blank, raw or log-softmax input,
+    both recursions, float32 and float64, through each entry point (the reference's
+    native function, its autograd surface, the one-call entry with and without host
+    lengths).  Loss: 1e-5 relative (float64: 1e-10).  Gradient against the float64
+    oracle: 1e-5 where float32 can hold it, else 1.5 times the larger of the float32
+    floor (helpers.fp32_grad_floor) and the error that the reference's own algorithm
+    makes in float32 on the same input (in most long cases the two errors agree to
+    three digits: the difference from float64 is the arithmetic's, not the kernel's)."""
+    rng = np.random.default_rng(seed)
+    for case in range(40):
+        n = int(rng.integers(1, 11))
+        tmax = int(rng.choice([1, 3, 20, 80, 300]))
+        umax = int(rng.choice([0, 1, 5, 40, 130]))
+        v = int(rng.choice([2, 3, 7, 37, 64, 260, 300, 500, 512, 513, 1024, 1030]))
+        from_ls, modified = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+        blank = int(rng.choice([0, v - 1, int(rng.integers(0, v))]))
+        dtype = np.float64 if rng.integers(0, 4) == 0 else np.float32
+        api = str(rng.choice(["native", "autograd", "one call", "one call, host lengths"]))
+        scale = float(rng.choice([0.5, 2.0, 8.0]))
+        T = rng.integers(1, tmax + 1, n).astype(np.int32)
+        U = rng.integers(0, umax + 1, n).astype(np.int32)
+        if modified:
+            U = np.minimum(U, T - 1).astype(np.int32)
+        rows = int(splits(T, U)[-1])
+        if rows * v > 20e6:
+            continue
+        x = (rng.standard_normal((rows, v)) * scale).astype(dtype)
+        if from_ls:
+            m = x.max(1, keepdims=True)
+            x = (x - (m + np.log(np.exp(x - m).sum(1, keepdims=True)))).astype(dtype)
+        tg = rng.integers(0, v, (n, max(int(U.max()), 0))).astype(np.int32)
+        what = dict(seed=seed, case=case, T=T.tolist(), U=U.tolist(), v=v, from_ls=from_ls, modified=modified,
+                    blank=blank, dtype=np.dtype(dtype).name, api=api)
+        truth = O.oracle_loss(x.astype(np.float64), tg, T, U, blank, from_ls, modified)
+        dx, dt, dT, dU = to_dev(x, tg, T, U)
+        if api == "native":
+            dx.requires_grad_(True)
+            scores, grad = ot.compute_transducer_loss(dx, dt, dT, dU, blank, from_ls, modified)
+            loss = -scores.double().sum().item()
+        elif api == "autograd":
+            dx.requires_grad_(True)
+            out = ot.transducer_loss(dx, dt, dT, dU, blank, from_ls, modified, reduction="sum")
+            out.backward()
+            loss, grad = out.item(), dx.grad
+        else:
+            host = (torch.from_numpy(T), torch.from_numpy(U)) if api.endswith("host lengths") else None
+            out, grad = ot.transducer_loss_and_grad(dx, dt, dT, dU, blank, from_ls, modified, reduction="sum",
+                                                    lengths_on_host=host)
+            loss = out.item()
+        torch.cuda.synchronize()
+        ot.check_inputs(DEV)
+        want = -truth["scores"].sum()
+        err = float(np.max(np.abs(grad.double().cpu().numpy() - truth["grad"]))) if rows else 0.0
+        if dtype == np.float64:
+            assert abs(loss - want) <= 1e-10 * max(1.0, abs(want)), what
+            assert err <= 1e-10, (what, err)
+            continue
+        assert abs(loss - want) <= 1e-5 * max(1.0, abs(want)), what
+        bound = max(1e-5, 1.5 * fp32_grad_floor(truth["alpha"], truth["beta"]))
+        if err > bound:
+            ref32 = O.oracle_loss(x, tg, T, U, blank, from_ls, modified)
+            bound = max(bound, 1.5 * float(np.max(np.abs(ref32["grad"] - truth["grad"]))))
+        assert err <= bound, (what, err, bound)
+
+
 # ---------------------------------------------------------------------------
 # 3. the Python surface (the reference's tests, re-expressed)
 # ---------------------------------------------------------------------------
