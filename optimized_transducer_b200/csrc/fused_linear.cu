@@ -575,9 +575,21 @@ bool make_map(CUtensorMap *map, const void *base, uint64_t outer, uint64_t inner
   const cuuint64_t strides[1] = {inner * 2};
   const cuuint32_t box[2] = {(cuuint32_t)kBlockK, box_outer};
   const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const auto encode = [&]() {
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // The encoder is a driver call and wants the device's context current on this
+    // thread.  A thread that has only been handed cached memory so far (an autograd
+    // worker whose first job is a small batch) has made no runtime call that binds
+    // it: bind it the way the runtime does for its own calls, and ask again.
+    (void)cudaFree(nullptr);
+    r = encode();
+  }
+  return r == CUDA_SUCCESS;
 }
 
 }  // namespace

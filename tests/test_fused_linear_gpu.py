@@ -8,6 +8,8 @@ Tolerances: den and the log-probs to 1e-5 relative to max(1, |value|) plus the
 float32 accumulation error of a D-term dot product (2e-5 absolute); scores to
 1e-5 relative.
 """
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -154,3 +156,30 @@ def test_joiner_loss_with_bad_lengths_gives_zero_gradients(monkeypatch):
     with pytest.raises(RuntimeError, match="an earlier call on this device"):
         loss.backward()
     torch.cuda.synchronize()
+
+
+def test_first_backward_of_a_process_may_be_a_small_batch():
+    """The tensor maps are made by a driver call that needs the device's context
+    current on the calling thread.  backward() runs on an autograd worker thread,
+    and when the process has only handled small tensors so far that thread has made
+    no runtime call that binds the context (its memory comes from the caching
+    allocator): the library binds it and asks again.  Needs a fresh process."""
+    import subprocess
+    import sys
+    code = (
+        "import torch, optimized_transducer_b200 as ot\n"
+        "dev = 'cuda:0'\n"
+        "T = torch.tensor([2, 4, 5], dtype=torch.int32, device=dev)\n"
+        "U = torch.tensor([0, 1, 0], dtype=torch.int32, device=dev)\n"
+        "rows = int((T * (U + 1)).sum())\n"
+        "x = torch.randn(rows, 64, device=dev).to(torch.bfloat16).requires_grad_(True)\n"
+        "w = torch.randn(256, 64, device=dev).to(torch.bfloat16).requires_grad_(True)\n"
+        "tg = torch.ones(3, 1, dtype=torch.int32, device=dev)\n"
+        "loss = ot.joiner_loss(x, w, None, tg, T, U, 0, reduction='sum')\n"
+        "loss.backward()\n"
+        "torch.cuda.synchronize()\n"
+        "assert torch.isfinite(x.grad.float()).all() and torch.isfinite(w.grad.float()).all()\n"
+        "print('ok', float(loss))\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.startswith("ok"), (r.stdout[-300:], r.stderr[-600:])
