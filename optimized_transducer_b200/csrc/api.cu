@@ -181,6 +181,13 @@ bool chained_groups_forced() {
   return e && strcmp(e, "always") == 0;
 }
 
+// OT_B200_PIPELINE=chain: the chained groups also for batches of the two-group size
+// (to measure one schedule against the other on the same batch).
+bool chain_preferred() {
+  const char *e = getenv("OT_B200_PIPELINE");
+  return e && strcmp(e, "chain") == 0;
+}
+
 // Batches below this many lattice cells (rows * V) run as one group: the
 // streaming kernels of half the batch must outlast a recursion for the overlap to
 // pay.  Measured, float: 343 M cells 0.725 -> 0.669 ms, 171 M cells 0.39 ms either
@@ -619,9 +626,9 @@ int ot_b200_loss_and_gradient_groups(const void *d_logits, void *d_grad, const i
   }
   const bool splittable = d_grad != nullptr && !mode_b && N >= 2 && rows >= 64 && V > 0 && two_groups_allowed();
   const uint64_t cells = (uint64_t)(rows > 0 ? rows : 0) * (uint64_t)(V > 0 ? V : 0);
-  bool two = splittable && cells >= kTwoGroupsMinCells;
+  bool two = splittable && cells >= kTwoGroupsMinCells && !chain_preferred();
   bool chained = splittable && !two && cuts.n != 1 &&
-                 (cells >= kChainedGroupsMinCells || chained_groups_forced());
+                 (cells >= kChainedGroupsMinCells || chained_groups_forced() || chain_preferred());
   if (two || chained) {  // not while the stream is being captured: the schedules span several streams
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) two = chained = false;
