@@ -404,8 +404,16 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   if (threadIdx.x == 0) trace_begin(status, trace_slot(kStageLattice, group));
   const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
   const int nwarps = (U1 + kWarp - 1) / kWarp;
-  if (warp >= nwarps) return;
-  const int nact = nwarps * kWarp;
+  // The warp behind the last column warp (the launcher adds one when the block has
+  // room) does nothing but request the log-prob chunks: two dozen instructions per
+  // block of steps that the first column warp, which heads the dependency chain,
+  // no longer issues.  Without it thread 0 requests them.
+  const bool has_loader = (int)blockDim.x > nwarps * kWarp;
+  if (warp > nwarps || (warp == nwarps && !has_loader)) return;
+  const bool loader = warp == nwarps;
+  const bool requests = has_loader ? (loader && lane == 0) : (u == 0);
+  const int nact = (nwarps + (has_loader ? 1 : 0)) * kWarp;
+  const bool solo = nact == kWarp;  // one warp in all: a warp barrier will do
   const P *lp2 = reinterpret_cast<const P *>(lp) + off;
   P *stage = reinterpret_cast<P *>(stage_mem) + 2;  // slack: column 0 reads the pair before its row
   const bool col = u < U1;
@@ -423,7 +431,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   const int nchunks = (nrows + K - 1) / K;
   const int nphases = nchunks > 0 ? nchunks + nwarps - 1 : 0;
   const int delay = backward ? nwarps - 1 - warp : warp;
-  if (u == 0) {
+  if (requests) {
     for (int i = 0; i < nstages; ++i) mbar_init(&full_bar[i], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -434,22 +442,41 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     row0 = m * K;
     n = min(K, nrows - row0);
   };
-  auto issue = [&](int j) {  // thread 0 only
+  // Chunk j lives in ring stage j % nstages and completes phase (j / nstages) & 1 of
+  // that stage's barrier.  Both are carried along instead of computed: a division by
+  // the run-time ring size costs some 25 dependent instructions, at the head of every
+  // block of steps, on a warp that has nothing else to issue.
+  auto issue = [&](int j, int slot) {  // thread 0 only; slot = j % nstages
     int row0, n;
     chunk_rows(j, row0, n);
     const uint32_t bytes = (uint32_t)((((int64_t)n * U1 * sizeof(P)) + 15) & ~int64_t(15));
-    uint64_t *bar = &full_bar[j % nstages];
+    uint64_t *bar = &full_bar[slot];
     mbar_expect_tx(bar, bytes);
-    tma_load_1d(stage + (int64_t)(j % nstages) * stage_pairs, lp2 + (int64_t)row0 * U1, bytes, bar);
+    tma_load_1d(stage + (int64_t)slot * stage_pairs, lp2 + (int64_t)row0 * U1, bytes, bar);
   };
-  auto wait_chunk = [&](int j) {
-    uint64_t *bar = &full_bar[j % nstages];
-    const uint32_t parity = (uint32_t)((j / nstages) & 1);
+  auto wait_chunk = [&](int slot, uint32_t parity) {
+    uint64_t *bar = &full_bar[slot];
     for (int spin = 0; spin < (1 << 22); ++spin)
       if (mbar_try_wait(bar, parity)) return;
     atomicCAS(status + kStatusCopyTimeout, 0, 1 + b);  // bounded: report and carry on
   };
+  int issue_slot = 2;           // of chunk p + 2 (nstages >= 4)
+  int slot = 0;                 // of the chunk this warp works on next
+  uint32_t slot_parity = 0;
+  auto advance = [&]() {
+    if (++slot == nstages) { slot = 0; slot_parity ^= 1u; }
+  };
 
+  if (loader) {
+    if (lane == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j, j);
+    bar_active(nact);
+    for (int p = 0; p < nphases; ++p) {
+      if (lane == 0 && p + 2 < nchunks) issue(p + 2, issue_slot);
+      if (++issue_slot == nstages) issue_slot = 0;
+      bar_active(nact);
+    }
+    return;
+  }
   if (!backward) {
     // ------------------------------ alpha ------------------------------
     const bool produce = (lane == kWarp - 1) && (warp + 1 < nwarps);
@@ -462,19 +489,21 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     T *al = alpha + off;
     N own = (u == 0) ? N::from_log((T)0) : N::zero();
     if (u == 0) al[0] = 0;
-    if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);  // by the thread that initialised the barriers
+    if (requests) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j, j);  // by the thread that initialised the barriers
     // blank log-prob of the final cell, for the score (fetched long before it is needed)
     const T fin_blank = (u == U) ? lp2[cell_pos<MODIFIED>(Tn - 1, U, U1)].x : (T)0;
-    if (nwarps > 1) bar_active(nact); else __syncwarp();
+    if (!solo) bar_active(nact); else __syncwarp();
     const bool first_col = (u == 0);  // has no symbol predecessor
     for (int p = 0; p < nphases; ++p) {
-      if (u == 0 && p + 2 < nchunks) issue(p + 2);
+      if (requests && p + 2 < nchunks) issue(p + 2, issue_slot);
+      if (++issue_slot == nstages) issue_slot = 0;
       const int q = p - delay;
       if (q >= 0 && q < nchunks) {
         int row0, n;
         chunk_rows(q, row0, n);
-        wait_chunk(q);
-        const P *rowp = stage + (int64_t)(q % nstages) * stage_pairs + uc;
+        wait_chunk(slot, slot_parity);
+        const P *rowp = stage + (int64_t)slot * stage_pairs + uc;
+        advance();
         T *st = al + (int64_t)(row0 + 1) * U1 + uc;  // entry of the block's first step
         // No range checks anywhere in a step.  Log-probs: entries that are no
         // lattice cell hold -inf (stage 0 fills, stage 1 overwrites the real
@@ -522,7 +551,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         }
         own.renorm();  // K <= 16 steps since the last one
       }
-      if (nwarps > 1) bar_active(nact); else __syncwarp();
+      if (!solo) bar_active(nact); else __syncwarp();
     }
     if (u == U) scores[b] = own.log() + fin_blank;  // column U's last step is the last step
     if (u == 0) trace_end(status, trace_slot(kStageLattice, group));
@@ -541,8 +570,8 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     }
     // "after step top": the boundary column of this warp before any step
     if (lane == 0) out_edge[top & kMask] = own;  // column U: the final cell; every other column: nothing yet
-    if (u == 0) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j);
-    if (nwarps > 1) bar_active(nact); else __syncwarp();
+    if (requests) for (int j = 0; j < 2 && j < nchunks; ++j) issue(j, j);
+    if (!solo) bar_active(nact); else __syncwarp();
     // Column U starts with the final cell and computes from the first step on,
     // unless it has no other cell (standard: T == 1; one symbol per frame:
     // U == T-1): then it must keep the final cell for column U-1 to read.
@@ -550,13 +579,15 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
     const bool keep = (u == U) && hi < s_lo;
     const bool wr = col && !keep;
     for (int p = 0; p < nphases; ++p) {
-      if (u == 0 && p + 2 < nchunks) issue(p + 2);
+      if (requests && p + 2 < nchunks) issue(p + 2, issue_slot);
+      if (++issue_slot == nstages) issue_slot = 0;
       const int q = p - delay;
       if (q >= 0 && q < nchunks) {
         int row0, n;
         chunk_rows(q, row0, n);
-        wait_chunk(q);
-        const P *rowp = stage + (int64_t)(q % nstages) * stage_pairs + (int64_t)(n - 1) * U1 + uc;
+        wait_chunk(slot, slot_parity);
+        const P *rowp = stage + (int64_t)slot * stage_pairs + (int64_t)(n - 1) * U1 + uc;
+        advance();
         T *st = be + (int64_t)(row0 + n - 1) * U1 + uc;  // entry of the block's first step
         N lb, ls;
         {
@@ -597,7 +628,7 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
         }
         own.renorm();
       }
-      if (nwarps > 1) bar_active(nact); else __syncwarp();
+      if (!solo) bar_active(nact); else __syncwarp();
     }
     if (u == 0) scores_beta[b] = own.log();  // column 0's last step is the last step
     if (u == 0) trace_end(status, trace_slot(kStageLattice, group));
@@ -705,6 +736,13 @@ bool lockstep_forced() {
 }
 
 // Returns cudaErrorNotSupported when the lattice is too wide for the skewed kernel.
+// OT_B200_LATTICE_LOADER=0: the log-prob chunks are requested by the first column
+// warp, as before the loader warp was added (to measure one against the other).
+bool loader_warp_wanted() {
+  const char *e = getenv("OT_B200_LATTICE_LOADER");
+  return !(e && strcmp(e, "0") == 0);
+}
+
 template <typename T, int ARITH, bool MODIFIED>
 cudaError_t launch_skewed(const Problem &p, void *scores, cudaStream_t s) {
   using P = typename Pair<T>::type;
@@ -726,7 +764,8 @@ cudaError_t launch_skewed(const Problem &p, void *scores, cudaStream_t s) {
     const cudaError_t e = grant.ensure(kernel, smem);
     if (e != cudaSuccess) return e;
   }
-  const cudaError_t le = launch_pdl(kernel, 2u * (unsigned)p.N, (unsigned)(nwarps * kWarp), smem, s,
+  const int loader_warps = (nwarps < kMaxWarps && loader_warp_wanted()) ? 1 : 0;  // see the kernel
+  const cudaError_t le = launch_pdl(kernel, 2u * (unsigned)p.N, (unsigned)((nwarps + loader_warps) * kWarp), smem, s,
       reinterpret_cast<const T *>(p.ws + p.lay.lp), p.T, p.U,
       reinterpret_cast<const int64_t *>(p.ws + p.lay.cell_split),
       reinterpret_cast<int32_t *>(p.ws + p.lay.status),
