@@ -463,8 +463,14 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
   int issue_slot = 2;           // of chunk p + 2 (nstages >= 4)
   int slot = 0;                 // of the chunk this warp works on next
   uint32_t slot_parity = 0;
-  auto advance = [&]() {
+  // The completion of the NEXT chunk is looked at once, without waiting, at the head
+  // of a block of steps; the answer is needed a block later, so the barrier's latency
+  // (about 90 cycles, which used to open every block) runs beside the steps.  A chunk
+  // that has not landed by then is waited for at the head of its own block as before.
+  bool landed = false;
+  auto advance = [&](bool more) {
     if (++slot == nstages) { slot = 0; slot_parity ^= 1u; }
+    landed = more && mbar_try_wait(&full_bar[slot], slot_parity);
   };
 
   if (loader) {
@@ -501,9 +507,9 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       if (q >= 0 && q < nchunks) {
         int row0, n;
         chunk_rows(q, row0, n);
-        wait_chunk(slot, slot_parity);
+        if (!landed) wait_chunk(slot, slot_parity);
         const P *rowp = stage + (int64_t)slot * stage_pairs + uc;
-        advance();
+        advance(q + 1 < nchunks);
         T *st = al + (int64_t)(row0 + 1) * U1 + uc;  // entry of the block's first step
         // No range checks anywhere in a step.  Log-probs: entries that are no
         // lattice cell hold -inf (stage 0 fills, stage 1 overwrites the real
@@ -585,9 +591,9 @@ lattice_skew_kernel(const T *__restrict__ lp, const int32_t *__restrict__ Tl,
       if (q >= 0 && q < nchunks) {
         int row0, n;
         chunk_rows(q, row0, n);
-        wait_chunk(slot, slot_parity);
+        if (!landed) wait_chunk(slot, slot_parity);
         const P *rowp = stage + (int64_t)slot * stage_pairs + (int64_t)(n - 1) * U1 + uc;
-        advance();
+        advance(q + 1 < nchunks);
         T *st = be + (int64_t)(row0 + n - 1) * U1 + uc;  // entry of the block's first step
         N lb, ls;
         {
